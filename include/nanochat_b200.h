@@ -1,0 +1,130 @@
+/*
+ * C ABI of the B200 (sm_100a) decode hot path: the fp8 (e4m3) KV-cache append/quantise step and single-token
+ * attention over that cache. Every entry point takes plain device pointers, sizes and a cudaStream_t passed as
+ * void*, launches on that stream, never synchronises or allocates (unless its comment says otherwise), and
+ * returns an NCB_* status instead of aborting. The caller owns every buffer and keeps it alive until the stream
+ * has run the launch.
+ *
+ * The reference binds its kernels the same way: nvcc-built shared objects loaded with ctypes.CDLL and called
+ * with pointer(tensor), ints and stream() (native.py:43-65; model/ops/qk_prologue.py:18-20;
+ * inference/decoder.py:131-148). The entry points below replace, on the decode path,
+ *   k_prologue  (model/kernels/decode.cu:551-565, row math model/kernels/qk_row.cuh:26-51)  -> kv_append_fp8
+ *   k_attn      (model/kernels/decode.cu:567-675)                                           -> decode_attn_fp8*
+ *   the (m, l, acc) merge inside k_attn (model/kernels/decode.cu:548,661-674)               -> decode_attn_merge
+ * and are split over two libraries, kv_append and decode_attn, one per kernel file as in the reference.
+ *
+ * Cache layout ("pages"). One cache buffer per layer: uint8 [n_slots][Hkv][pages_per_slot][NCB_PAGE_BYTES].
+ * A page holds NCB_PAGE_TOKENS = 64 consecutive positions of one (slot, kv head):
+ *   [0, 8192)       K rows: position j at j*128; the row's 16-byte chunk c is stored at chunk c ^ ((j >> 2) & 7)
+ *   [8192, 16384)   V transposed: 32-position group gi, half h (positions 16h..16h+15 of the group), dim d:
+ *                   16 bytes at 8192 + gi*4096 + h*2048 + d*16, byte (j & 15)
+ *   [16384, 16640)  K scales, fp32[64]
+ *   [16640, 16896)  V scales, fp32[64]
+ * so that a (slot, kv head, split) thread block streams one contiguous region with one bulk copy per page and
+ * feeds the tensor cores from shared memory without conflicts or transposes. A stored byte b with scale s stands
+ * for the value e4m3(b) * s; s = amax / 448 over the row's 128 bf16 values.
+ */
+#ifndef NANOCHAT_B200_H
+#define NANOCHAT_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NCB_HEAD_DIM 128
+#define NCB_PAGE_TOKENS 64
+#define NCB_PAGE_BYTES 16896
+#define NCB_PART_FLOATS 132 /* one partial attention state: m, l, 2 pad, o[128]; fp32 */
+
+enum {
+    NCB_OK = 0,
+    NCB_ERR_ARG = 1,         /* a size, ratio or pointer argument is out of range or NULL */
+    NCB_ERR_ALIGN = 2,       /* a pointer or stride misses its required alignment */
+    NCB_ERR_WORKSPACE = 3,   /* the workspace is smaller than decode_attn_workspace_bytes() */
+    NCB_ERR_LAUNCH = 4,      /* the CUDA runtime refused the launch; see cudaGetLastError */
+    NCB_ERR_UNSUPPORTED = 5  /* Hq / Hkv above 8 */
+};
+
+/* Bits a kernel ORs into the caller's optional device status word (int32, may be NULL). */
+enum {
+    NCB_DEV_BAD_POSITION = 1, /* kv_append_fp8: a row's position or slot is outside the cache; the row was skipped */
+    NCB_DEV_WAIT_TIMEOUT = 2, /* decode_attn_fp8: a bounded wait on a copy barrier ran out; outputs are invalid */
+    NCB_DEV_BAD_LENGTH = 4    /* decode_attn_fp8: a length or slot is outside the cache; the sequence was skipped */
+};
+
+const char *ncb_status_string(int status);
+
+/* ---- library kv_append -------------------------------------------------------------------------------------- */
+
+/* Bytes of one layer's cache for n_slots sequences of at most max_len positions (rounded up to whole pages). */
+long long kv_cache_bytes(int n_slots, int kv_heads, int max_len);
+/* Pages per (slot, kv head) for max_len positions. */
+int kv_cache_pages(int max_len);
+
+/*
+ * Fused rotary + QK-RMSNorm + quantise + append for `rows` new tokens (replaces k_prologue, decode.cu:551-565).
+ *   qkv       bf16 [rows][qkv_row_stride]: per row Hq q heads, then Hkv k heads, then Hkv v heads of 128
+ *   q_gain, k_gain   fp32 [128], shared by the heads (decode.cu:464)
+ *   cos, sin  fp32 [table_len][64], indexed by absolute position (decode.cu:498)
+ *   pos       int32 [rows]: each row's position; the row's k, v are written at that position
+ *   slot_map  int32 [rows] or NULL (row r writes slot r) (decode.cu:556)
+ *   q_out     bf16 [rows][Hq][128]: normed, rotated q
+ *   kv_cache  the layer's pages (layout above)
+ *   status    int32 device word or NULL
+ * Arithmetic: every fp32 operation individually rounded in the order fixed by oracle/kv_append_oracle.c, so q
+ * bits, cache bytes and scales are exact functions of the inputs. Rows whose position >= pages_per_slot * 64 or
+ * >= table_len, or whose slot >= n_slots, are skipped and flagged in *status.
+ */
+int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                  const void *pos, const void *slot_map, void *q_out, void *kv_cache, long long rows, int Hq,
+                  int Hkv, long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot, void *status,
+                  void *stream);
+
+/* ---- library decode_attn ------------------------------------------------------------------------------------ */
+
+/* Pages one thread block covers when chunk_pages == 0 is passed below; depends only on these three values. */
+int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len);
+/* Workspace bytes for the split partials; chunk_pages == 0 selects decode_attn_chunk_pages(). */
+long long decode_attn_workspace_bytes(int B, int Hq, int max_kv_len, int Hkv, int chunk_pages);
+
+/*
+ * out[b, h, :] = softmax_j(q[b, h] . K[j] * softmax_scale) V[j] over the cached positions
+ * j in [max(0, lens[b] - window), lens[b]) of slot slot_map[b] (replaces k_attn, decode.cu:567-675; the current
+ * token is read from the cache, where kv_append_fp8 put it, instead of from registers).
+ *   q         bf16 [B][Hq][128]
+ *   lens      int32 [B]: cached positions per sequence (0 gives a zero output row)
+ *   slot_map  int32 [B] or NULL
+ *   workspace >= decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages), 16-byte aligned; contents are
+ *             scratch, calls sharing it must be stream-ordered
+ *   out       bf16 [B][Hq][128]
+ *   max_kv_len   an upper bound of every lens[b]; sizes the grid (lens stay on the device)
+ *   window    0 for none, else the number of most recent positions attended (decode.cu:575)
+ *   chunk_pages  0 for the built-in choice
+ * Two launches: the split-KV kernel (one block per sequence, kv head and chunk of pages; all Hq/Hkv query heads
+ * of the kv head share each K/V byte) and the merge kernel.
+ */
+int decode_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
+                    long long workspace_bytes, void *out, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,
+                    int max_kv_len, int window, int chunk_pages, float softmax_scale, void *status, void *stream);
+
+/*
+ * As decode_attn_fp8, but leaves the un-normalised state of each (b, h) in part_out, fp32
+ * [B][Hq][NCB_PART_FLOATS] = (m in log2 units, l, 0, 0, o[128]) with out = o / l, for merging across GPUs that
+ * each hold a slice of the positions (the merge rule of decode.cu:548,661-670 is associative).
+ */
+int decode_attn_fp8_partial(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
+                            void *workspace, long long workspace_bytes, void *part_out, int B, int Hq, int Hkv,
+                            int n_slots, int pages_per_slot, int max_kv_len, int window, int chunk_pages,
+                            float softmax_scale, void *status, void *stream);
+
+/*
+ * Merge n_parts states per row: parts fp32 [n_parts][rows][NCB_PART_FLOATS] (e.g. the all-gathered part_out of
+ * every rank, rows = B * Hq) into out bf16 [rows][128]. A state with m = -inf counts as empty; a row whose states
+ * are all empty gives zeros.
+ */
+int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,108 @@
+"""Host-side operators of the decode hot path, thin ctypes calls into the sm_100a kernels.
+
+They keep the call style of the reference's op wrappers (model/ops/qk_prologue.py:13-21: tensors in, tensors out,
+pointers + sizes + stream() passed to an extern "C" entry) and stand where inference/decoder.py's step graph
+calls k_prologue and k_attn (model/kernels/decode.cu:859-863). Every function launches on the current stream and
+returns without synchronising; a non-zero native status raises NativeError. There is no CPU or PyTorch fallback."""
+
+import torch
+from torch import Tensor
+
+from .kv_cache import HEAD_DIM, Fp8KVCache
+from .native import check, cuda_library, pointer, stream
+
+PART_FLOATS = 132
+
+
+def rotary_table(positions: int, theta: float, device: "torch.device | str" = "cpu") -> tuple[Tensor, Tensor]:
+    """cos, sin fp32 (positions, 64) of the angles t theta^(-2i/128), computed in fp64 and rounded once
+    (reference model/modeling.py:169-176)."""
+    exponent = torch.arange(0, HEAD_DIM, 2, dtype=torch.float64) / HEAD_DIM
+    freqs = torch.arange(positions, dtype=torch.float64)[:, None] * theta ** -exponent
+    return freqs.cos().float().to(device), freqs.sin().float().to(device)
+
+
+def kv_append(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tensor, sin: Tensor, pos: Tensor,
+              cache: Fp8KVCache, Hq: int, slot_map: Tensor | None = None, q_out: Tensor | None = None,
+              status: Tensor | None = None) -> Tensor:
+    """Norm + rotate q and k, quantise k and v to e4m3 with per-(token, head) scales and append them at `pos`.
+    qkv (rows, (Hq + 2 Hkv) * 128) bf16, row stride free; gains fp32 (128,); cos/sin fp32 (T, 64); pos int32
+    (rows,); slot_map int32 (rows,) or None. Returns q_out (rows, Hq, 128) bf16."""
+    rows, Hkv = qkv.shape[0], cache.kv_heads
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(-1) == 1 and qkv.shape[1] == (Hq + 2 * Hkv) * HEAD_DIM
+    assert pos.dtype == torch.int32 and pos.shape == (rows,) and pos.is_contiguous()
+    assert cos.shape == sin.shape and cos.shape[1] == HEAD_DIM // 2 and cos.is_contiguous() and sin.is_contiguous()
+    assert q_gain.dtype == k_gain.dtype == cos.dtype == sin.dtype == torch.float32
+    assert slot_map is None or (slot_map.dtype == torch.int32 and slot_map.shape == (rows,))
+    if q_out is None:
+        q_out = torch.empty((rows, Hq, HEAD_DIM), dtype=torch.bfloat16, device=qkv.device)
+    rc = cuda_library("kv_append").kv_append_fp8(
+        pointer(qkv), pointer(q_gain), pointer(k_gain), pointer(cos), pointer(sin), pointer(pos), pointer(slot_map),
+        pointer(q_out), pointer(cache.pages), rows, Hq, Hkv, qkv.stride(0), cos.shape[0], cache.n_slots,
+        cache.pages_per_slot, pointer(status), stream())
+    check(rc, "kv_append_fp8")
+    return q_out
+
+
+def chunk_pages_for(B: int, Hkv: int, max_kv_len: int) -> int:
+    return cuda_library("decode_attn").decode_attn_chunk_pages(B, Hkv, max_kv_len)
+
+
+def workspace_bytes(B: int, Hq: int, Hkv: int, max_kv_len: int, chunk_pages: int = 0) -> int:
+    return cuda_library("decode_attn").decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages)
+
+
+def _attend(entry: str, q: Tensor, cache: Fp8KVCache, lens: Tensor, result: Tensor, max_kv_len: int,
+            slot_map: Tensor | None, window: int, chunk_pages: int, softmax_scale: float | None,
+            workspace: Tensor | None, status: Tensor | None) -> None:
+    B, Hq = q.shape[0], q.shape[1]
+    assert q.dtype == torch.bfloat16 and q.is_contiguous() and q.shape[2] == HEAD_DIM
+    assert lens.dtype == torch.int32 and lens.shape == (B,) and lens.is_contiguous()
+    assert slot_map is None or (slot_map.dtype == torch.int32 and slot_map.shape == (B,))
+    need = workspace_bytes(B, Hq, cache.kv_heads, min(max_kv_len, cache.capacity), chunk_pages)
+    if workspace is None:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
+    rc = getattr(cuda_library("decode_attn"), entry)(
+        pointer(q), pointer(cache.pages), pointer(lens), pointer(slot_map), pointer(workspace), workspace.numel(),
+        pointer(result), B, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, max_kv_len, window, chunk_pages,
+        scale, pointer(status), stream())
+    check(rc, entry)
+
+
+def decode_attention(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int, slot_map: Tensor | None = None,
+                     window: int = 0, chunk_pages: int = 0, softmax_scale: float | None = None,
+                     workspace: Tensor | None = None, out: Tensor | None = None,
+                     status: Tensor | None = None) -> Tensor:
+    """out[b, h] = softmax(q[b, h] . K * scale) V over the cached positions [max(0, lens[b] - window), lens[b]) of
+    slot slot_map[b]. q (B, Hq, 128) bf16; lens int32 (B,) on the device; max_kv_len an upper bound of lens known
+    to the host. Returns (B, Hq, 128) bf16."""
+    if out is None:
+        out = torch.empty_like(q)
+    _attend("decode_attn_fp8", q, cache, lens, out, max_kv_len, slot_map, window, chunk_pages, softmax_scale,
+            workspace, status)
+    return out
+
+
+def decode_attention_partial(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int,
+                             slot_map: Tensor | None = None, window: int = 0, chunk_pages: int = 0,
+                             softmax_scale: float | None = None, workspace: Tensor | None = None,
+                             part: Tensor | None = None, status: Tensor | None = None) -> Tensor:
+    """As decode_attention but returns the un-normalised state fp32 (B, Hq, 132) = (m, l, 0, 0, o[128]) for merging
+    with the states of other position slices (merge_partials)."""
+    if part is None:
+        part = torch.empty((q.shape[0], q.shape[1], PART_FLOATS), dtype=torch.float32, device=q.device)
+    _attend("decode_attn_fp8_partial", q, cache, lens, part, max_kv_len, slot_map, window, chunk_pages,
+            softmax_scale, workspace, status)
+    return part
+
+
+def merge_partials(parts: Tensor, out: Tensor | None = None) -> Tensor:
+    """parts fp32 (n_parts, B, Hq, 132) -> normalised bf16 (B, Hq, 128)."""
+    assert parts.dtype == torch.float32 and parts.is_contiguous() and parts.shape[-1] == PART_FLOATS
+    n_parts, B, Hq = parts.shape[:3]
+    if out is None:
+        out = torch.empty((B, Hq, HEAD_DIM), dtype=torch.bfloat16, device=parts.device)
+    rc = cuda_library("decode_attn").decode_attn_merge(pointer(parts), n_parts, B * Hq, pointer(out), stream())
+    check(rc, "decode_attn_merge")
+    return out

@@ -1,0 +1,620 @@
+/*
+ * decode_attn_fp8: single-token attention over the paged e4m3 KV cache, split over the KV length, plus the
+ * (m, l, o) merge kernel. Replaces the reference's k_attn (model/kernels/decode.cu:567-675) and its in-kernel
+ * merge (decode.cu:548,661-674) for an fp8 cache, grouped-query heads and split KV.
+ *
+ * Roofline: HBM. Each (kv head, position) costs 264 bytes (128 K + 128 V + two fp32 scales) and is read exactly
+ * once for all G = Hq / Hkv query heads that share it. Everything else is shaped to keep that stream busy:
+ *
+ *   - one thread block per (sequence, kv head, chunk of pages); a page (include/nanochat_b200.h) is one contiguous
+ *     16,896-byte record, fetched by ONE cp.async.bulk into a STAGES-deep shared-memory ring and signalled on an
+ *     mbarrier (full/empty pair per stage); a producer warp issues the copies, four consumer warps each take
+ *     every fourth page and never synchronise with each other until the end;
+ *   - no fp8 -> float conversion of K or V at all: both contractions run on the tensor cores as
+ *     mma.sync.m16n8k32 e4m3 x e4m3 -> fp32 with the CACHE as the A operand (16 positions, or 16 dims, per tile)
+ *     and the N = 8 columns holding the group's query heads. bf16 queries and fp32 probabilities do not fit e4m3's
+ *     3 mantissa bits, so each is split into two e4m3 terms, x ~ hi + lo / 16, which keeps bf16-level precision
+ *     (relative error 2^-8); the two terms of a head are adjacent columns (2 head, 2 head + 1), so G <= 4 fills
+ *     one 8-column tile and G <= 8 two (template parameter NT);
+ *   - the per-position K scale multiplies the fp32 score, the per-position V scale is folded into the
+ *     probability before it is split, and the running maximum tracks score + log2(v scale) so the folded
+ *     probabilities stay in (0, 1]; statistics and accumulators are fp32, exponentials are exp2 with log2(e)
+ *     folded into the score scale;
+ *   - the page layout (swizzled K rows, V stored transposed in 16-position blocks) makes every ldmatrix
+ *     conflict-free and lets the score accumulators turn into the PV operand with four shuffles.
+ *
+ * Positions outside [begin, len) inside the first and last page are masked with selects; their V bytes are zeroed
+ * in shared memory first because an e4m3 NaN byte times a zero probability would still be NaN.
+ *
+ * Every wait is bounded: when a barrier does not flip within about a second the block records
+ * NCB_DEV_WAIT_TIMEOUT in the caller's status word, stops consuming, drains its own copies (bounded again) and
+ * returns.
+ */
+#include "ncb_common.cuh"
+
+constexpr int CONSUMER_WARPS = 4;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int PRODUCER_TID = CONSUMER_WARPS * 32;
+/* ring depth: two blocks per SM must fit 227 KB of shared memory together with the merge area */
+constexpr __host__ __device__ int stages_of(int NT) { return NT == 1 ? 6 : 5; }
+constexpr int PART = NCB_PART_FLOATS;
+constexpr uint32_t WAIT_TRIES = 1u << 19; /* x <= 2 us suspend hint each: about one second */
+constexpr float P_SCALE = 256.f;          /* folded probabilities in (0, 1] -> e4m3 range, exact power of two */
+constexpr float LO_SCALE = 16.f;          /* second term's gain: the first term's rounding error is <= 2^-4 ulp-wise */
+constexpr float MIN_LOG2_VSCALE = -64.f;
+
+struct AttnArgs {
+    const bf16 *q;
+    const uint8_t *cache;
+    const int32_t *lens, *slot_map;
+    float *parts; /* [B][Hq][max_chunks][PART] */
+    int B, Hq, Hkv, n_slots, pages_per_slot, window, chunk_pages, max_chunks;
+    float scale_log2; /* softmax scale * log2(e) */
+    int *status;
+};
+
+/* ---- PTX wrappers ------------------------------------------------------------------------------------------- */
+
+static __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+static __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+static __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+static __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+/* True once the barrier's phase of the given parity has completed; gives up after WAIT_TRIES bounded tries. */
+static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t tries = 0; tries < WAIT_TRIES; tries++) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done)
+                     : "r"(bar), "r"(parity), "r"(2000u)
+                     : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+static __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+static __device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3,
+                                                   uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+/* d += A B, A 16x32 e4m3 (row), B 32x8 e4m3 (col), fp32 accumulators. */
+static __device__ __forceinline__ void mma_e4m3(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+/* e4m3 bytes of (hi, lo), hi in bits 8..15. */
+static __device__ __forceinline__ uint32_t cvt_e4m3x2(float hi, float lo) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+/* The two e4m3 bytes of x (low 16 bits) as floats: .x from the low byte. */
+static __device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t x) {
+    uint32_t h;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"((uint16_t)x));
+    return __half22float2(*reinterpret_cast<const __half2 *>(&h));
+}
+/* x[0..3] -> word of first terms e4m3(x) and word of second terms e4m3((x - first) * 16); byte i from x[i]. */
+static __device__ __forceinline__ void split4(const float *x, uint32_t &hi, uint32_t &lo) {
+    const uint32_t h01 = cvt_e4m3x2(x[1], x[0]), h23 = cvt_e4m3x2(x[3], x[2]);
+    const float2 f01 = e4m3x2_to_float2(h01), f23 = e4m3x2_to_float2(h23);
+    const uint32_t l01 = cvt_e4m3x2((x[1] - f01.y) * LO_SCALE, (x[0] - f01.x) * LO_SCALE);
+    const uint32_t l23 = cvt_e4m3x2((x[3] - f23.y) * LO_SCALE, (x[2] - f23.x) * LO_SCALE);
+    hi = h01 | (h23 << 16);
+    lo = l01 | (l23 << 16);
+}
+static __device__ __forceinline__ float ex2(float x) { /* exp2, -inf -> 0 */
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+static __device__ __forceinline__ float lg2(float x) { /* log2, 0 -> -inf */
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+/* max over the 8 lanes that share lane % 4 (one query head's positions) */
+static __device__ __forceinline__ float head_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+}
+static __device__ __forceinline__ float head_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    return v + __shfl_xor_sync(0xffffffffu, v, 16);
+}
+
+/* Where a sequence's attended positions and pages lie; shared by the split and merge kernels. */
+struct Span {
+    int begin, len, first_page, last_page; /* positions [begin, len), pages [first_page, last_page) */
+};
+static __device__ __forceinline__ Span span_of(int len, int window) {
+    Span s;
+    s.len = len;
+    s.begin = (window > 0 && len > window) ? len - window : 0;
+    s.first_page = s.begin / PAGE_TOKENS;
+    s.last_page = (len + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    return s;
+}
+
+/* ---- split-KV kernel ---------------------------------------------------------------------------------------- */
+
+constexpr int merge_floats(int NT) { return CONSUMER_WARPS * 4 * NT * PART; }
+constexpr size_t attn_smem(int NT) { return (size_t)stages_of(NT) * PAGE_BYTES + merge_floats(NT) * sizeof(float); }
+
+template <int NT>
+__global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
+    constexpr int STAGES = stages_of(NT);
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES]; /* full[STAGES], empty[STAGES] */
+    __shared__ float q_scale[4 * NT];
+    __shared__ int abort_flag;
+    float *merge = reinterpret_cast<float *>(smem + (size_t)STAGES * PAGE_BYTES);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int G = a.Hq / a.Hkv;
+
+    int len = a.lens[b];
+    const int slot = a.slot_map ? a.slot_map[b] : b;
+    if (len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots) {
+        if (tid == 0 && chunk == 0 && kvh == 0) flag(a.status, NCB_DEV_BAD_LENGTH);
+        return; /* the merge kernel makes the same test and writes zeros */
+    }
+    const Span sp = span_of(len, a.window);
+    const int pg0 = sp.first_page + chunk * a.chunk_pages;
+    const int n = min(a.chunk_pages, sp.last_page - pg0);
+    if (n <= 0) return;
+
+    const uint8_t *pages = a.cache + (((size_t)slot * a.Hkv + kvh) * a.pages_per_slot + pg0) * PAGE_BYTES;
+    const uint32_t ring = smem_u32(smem), full = smem_u32(bars), empty = full + STAGES * 8;
+
+    if (tid == PRODUCER_TID) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full + 8 * s, 1);
+            mbar_init(empty + 8 * s, 1);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int i = 0; i < min(n, STAGES); i++) { /* fill the ring before anything else happens */
+            mbar_expect_tx(full + 8 * i, PAGE_BYTES);
+            bulk_load(ring + i * PAGE_BYTES, pages + (size_t)i * PAGE_BYTES, PAGE_BYTES, full + 8 * i);
+        }
+    }
+    /* the group's queries as fp32, staged in the (not yet used) merge area */
+    const bf16 *q = a.q + ((size_t)b * a.Hq + (size_t)kvh * G) * HEAD_DIM;
+    for (int i = tid; i < G * HEAD_DIM; i += THREADS) merge[i] = __bfloat162float(q[i]);
+    __syncthreads();
+    if (warp < CONSUMER_WARPS) { /* per-head amax -> scale; each consumer warp takes heads warp, warp + 4 */
+        for (int h = warp; h < G; h += CONSUMER_WARPS) {
+            float m = 0.f;
+            for (int i = lane; i < HEAD_DIM; i += 32) m = fmaxf(m, fabsf(merge[h * HEAD_DIM + i]));
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0) q_scale[h] = m / 448.f;
+        }
+    }
+    __syncthreads();
+
+    /* each consumer warp's running state: per tile, head t's maximum (log2 units), this lane's share of the sum,
+     * and O^T fragments (dims 16 dt + g, + 8; columns = head t's two terms) */
+    float m[NT], l[NT], oacc[NT][8][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        m[nt] = -INFINITY;
+        l[nt] = 0.f;
+#pragma unroll
+        for (int dt = 0; dt < 8; dt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) oacc[nt][dt][i] = 0.f;
+    }
+
+    if (warp == CONSUMER_WARPS) { /* ---- producer: refill stages as consumers release them ---- */
+        if (lane == 0) {
+            int issued = min(n, STAGES);
+            for (int i = STAGES; i < n; i++) {
+                const int s = i % STAGES;
+                if (!mbar_wait(empty + 8 * s, ((i / STAGES) & 1) ^ 1)) {
+                    flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+                    atomicExch(&abort_flag, 1);
+                    break;
+                }
+                if (*(volatile int *)&abort_flag) break;
+                mbar_expect_tx(full + 8 * s, PAGE_BYTES);
+                bulk_load(ring + s * PAGE_BYTES, pages + (size_t)i * PAGE_BYTES, PAGE_BYTES, full + 8 * s);
+                issued = i + 1;
+            }
+            if (*(volatile int *)&abort_flag) /* drain: the block must not exit under copies still in flight */
+                for (int i = max(0, issued - STAGES); i < issued; i++) mbar_wait(full + 8 * (i % STAGES), (i / STAGES) & 1);
+        }
+    } else { /* ---- consumers ---- */
+        /* B fragments of q: column g = (head g / 2 of the tile, term g % 2); b0 = dims 32 ks + 4 t .. + 3,
+         * b1 = dims 32 ks + 16 + 4 t .. + 3 */
+        uint32_t qf[NT][4][2];
+        float qfac[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int hc = 4 * nt + (g >> 1), hs = 4 * nt + t; /* the head of this lane's B column / C columns */
+            const float sc = hc < G ? q_scale[hc] : 0.f, inv = sc > 0.f ? 1.f / sc : 0.f;
+            qfac[nt] = (hs < G ? q_scale[hs] : 0.f) * a.scale_log2;
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++)
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    float x[4];
+                    uint32_t hi, lo;
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        x[i] = hc < G ? merge[hc * HEAD_DIM + 32 * ks + 16 * half + 4 * t + i] * inv : 0.f;
+                    split4(x, hi, lo);
+                    qf[nt][ks][half] = (g & 1) ? lo : hi;
+                }
+        }
+        /* everyone has read the staged q before any warp reuses the merge area at the end: the final
+         * __syncthreads orders that; nothing else writes it until then */
+
+        for (int i = warp; i < n; i += CONSUMER_WARPS) {
+            const int s = i % STAGES;
+            if (*(volatile int *)&abort_flag) break;
+            if (!mbar_wait(full + 8 * s, (i / STAGES) & 1)) {
+                if (lane == 0) {
+                    flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+                    atomicExch(&abort_flag, 1);
+                }
+                break;
+            }
+            uint8_t *page = smem + (size_t)s * PAGE_BYTES;
+            const uint32_t page_u = ring + s * PAGE_BYTES;
+            const int key0 = (pg0 + i) * PAGE_TOKENS; /* the page's first position */
+            const bool partial = key0 < sp.begin || key0 + PAGE_TOKENS > sp.len;
+            if (partial) { /* zero the V bytes of positions outside [begin, len) */
+#pragma unroll
+                for (int blk = 0; blk < 4; blk++) { /* 16-position blocks: (group, half) */
+                    const int first = key0 + 16 * blk;
+                    uint32_t keep[4];
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        keep[w] = 0;
+#pragma unroll
+                        for (int bb = 0; bb < 4; bb++) {
+                            const int pos = first + 4 * w + bb;
+                            if (pos >= sp.begin && pos < sp.len) keep[w] |= 0xffu << (8 * bb);
+                        }
+                    }
+                    if ((keep[0] & keep[1] & keep[2] & keep[3]) == 0xffffffffu) continue;
+                    for (int d = lane; d < HEAD_DIM; d += 32) {
+                        uint4 *row = reinterpret_cast<uint4 *>(page + PAGE_V + blk * 2048 + d * 16);
+                        uint4 v = *row;
+                        v.x &= keep[0], v.y &= keep[1], v.z &= keep[2], v.w &= keep[3];
+                        *row = v;
+                    }
+                }
+                __syncwarp();
+            }
+#pragma unroll
+            for (int gi = 0; gi < 2; gi++) { /* 32 positions at a time */
+                const int first = key0 + 32 * gi;
+                if (partial && (first >= sp.len || first + 32 <= sp.begin)) continue;
+                /* ---- scores: A = K rows (position 4 r + 2 mt [+ 1 for rows 8..15]), B = q ---- */
+                float sc[NT][2][4];
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                        for (int c = 0; c < 4; c++) sc[nt][mt][c] = 0.f;
+#pragma unroll
+                for (int mt = 0; mt < 2; mt++) {
+                    const int row = 32 * gi + 4 * (lane & 7) + 2 * mt + ((lane >> 3) & 1);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        uint32_t a0, a1, a2, a3;
+                        const int c = 2 * ks + (lane >> 4);
+                        ldmatrix_x4(a0, a1, a2, a3, page_u + PAGE_K + row * HEAD_DIM + ((c ^ (lane & 7)) << 4));
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) mma_e4m3(sc[nt][mt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+                    }
+                }
+                /* this lane: head t of each tile, positions first + 4 g + {0, 1, 2, 3} */
+                const float4 ks4 = *reinterpret_cast<const float4 *>(page + PAGE_KS + (32 * gi + 4 * g) * 4);
+                const float4 vs4 = *reinterpret_cast<const float4 *>(page + PAGE_VS + (32 * gi + 4 * g) * 4);
+                const float ksc[4] = {ks4.x, ks4.y, ks4.z, ks4.w}, vsc[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
+                bool valid[4];
+                float lv[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int pos = first + 4 * g + j;
+                    valid[j] = !partial || (pos >= sp.begin && pos < sp.len);
+                    lv[j] = fmaxf(lg2(vsc[j]), MIN_LOG2_VSCALE);
+                }
+                uint32_t pb[NT][2];
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    float x[4], top = -INFINITY;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float raw = sc[nt][j >> 1][2 * (j & 1)] + sc[nt][j >> 1][2 * (j & 1) + 1] * (1.f / LO_SCALE);
+                        x[j] = raw * (ksc[j] * qfac[nt]);
+                        top = fmaxf(top, valid[j] ? x[j] + lv[j] : -INFINITY);
+                    }
+                    top = fmaxf(head_max(top), m[nt]);
+                    if (__any_sync(0xffffffffu, top > m[nt])) { /* some head's maximum moved: rescale */
+                        const float c = m[nt] == -INFINITY ? 0.f : ex2(m[nt] - top);
+                        l[nt] *= c;
+#pragma unroll
+                        for (int dt = 0; dt < 8; dt++)
+#pragma unroll
+                            for (int e = 0; e < 4; e++) oacc[nt][dt][e] *= c;
+                        m[nt] = top;
+                    }
+                    float p[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float e = (valid[j] && top != -INFINITY) ? ex2(x[j] - top) : 0.f;
+                        l[nt] += e;
+                        p[j] = (valid[j] && top != -INFINITY) ? e * (vsc[j] * P_SCALE) : 0.f;
+                    }
+                    uint32_t whi, wlo;
+                    split4(p, whi, wlo);
+                    /* C layout -> B layout: column g of positions 4 t .. 4 t + 3 (and + 16) lives in lane
+                     * 4 t + g / 2 (and + 16), first term if g is even */
+                    const int src = 4 * t + (g >> 1);
+                    const uint32_t h0 = __shfl_sync(0xffffffffu, whi, src), l0 = __shfl_sync(0xffffffffu, wlo, src);
+                    const uint32_t h1 = __shfl_sync(0xffffffffu, whi, src + 16), l1 = __shfl_sync(0xffffffffu, wlo, src + 16);
+                    pb[nt][0] = (g & 1) ? l0 : h0;
+                    pb[nt][1] = (g & 1) ? l1 : h1;
+                }
+                /* ---- values: A = V^T rows (dim 16 dt + r), B = folded probabilities ---- */
+                const uint32_t vbase = page_u + PAGE_V + gi * 4096 + (lane >> 4) * 2048 + (8 * ((lane >> 3) & 1) + (lane & 7)) * 16;
+#pragma unroll
+                for (int dt = 0; dt < 8; dt++) {
+                    uint32_t a0, a1, a2, a3;
+                    ldmatrix_x4(a0, a1, a2, a3, vbase + dt * 256);
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) mma_e4m3(oacc[nt][dt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + 8 * s);
+        }
+        __syncwarp();
+    }
+    __syncthreads(); /* all staged-q reads are done; the merge area is free */
+
+    if (warp < CONSUMER_WARPS) {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int h = 4 * nt + t;
+            float *mine = merge + (warp * 4 * NT + h) * PART;
+            const float lsum = head_sum(l[nt]);
+            if (g == 0) mine[0] = m[nt], mine[1] = lsum;
+#pragma unroll
+            for (int dt = 0; dt < 8; dt++) {
+                mine[4 + 16 * dt + g] = (oacc[nt][dt][0] + oacc[nt][dt][1] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
+                mine[4 + 16 * dt + g + 8] = (oacc[nt][dt][2] + oacc[nt][dt][3] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < HEAD_DIM) { /* merge the four warps' states per head; thread = dim */
+        for (int h = 0; h < G; h++) {
+            float top = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; w++) top = fmaxf(top, merge[(w * 4 * NT + h) * PART]);
+            float lsum = 0.f, o = 0.f;
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; w++) {
+                const float *st = merge + (w * 4 * NT + h) * PART;
+                const float c = st[0] == -INFINITY ? 0.f : ex2(st[0] - top);
+                lsum += c * st[1];
+                o += c * st[4 + tid];
+            }
+            float *out = a.parts + (((size_t)b * a.Hq + (size_t)kvh * G + h) * a.max_chunks + chunk) * PART;
+            if (tid == 0) out[0] = top, out[1] = lsum;
+            out[4 + tid] = o;
+        }
+    }
+}
+
+/* ---- merge kernel ------------------------------------------------------------------------------------------- */
+
+struct MergeArgs {
+    const float *parts;
+    long long rows, part_stride, row_stride; /* state (row, p) at parts + row * row_stride + p * part_stride */
+    int n_parts;                             /* > 0: fixed; 0: from lens (the split kernel's chunks) */
+    const int32_t *lens, *slot_map;
+    int Hq, window, chunk_pages, n_slots, pages_per_slot, max_chunks;
+    bf16 *out;       /* [rows][128] normalised, or NULL */
+    float *part_out; /* [rows][PART] merged state, or NULL */
+};
+
+constexpr int MERGE_WARPS = 4;
+
+__global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
+    const long long row = (long long)blockIdx.x * MERGE_WARPS + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= a.rows) return;
+    int n = a.n_parts;
+    if (n == 0) {
+        const int b = (int)(row / a.Hq), len = a.lens[b], slot = a.slot_map ? a.slot_map[b] : b;
+        if (!(len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots)) {
+            const Span sp = span_of(len, a.window);
+            n = min((sp.last_page - sp.first_page + a.chunk_pages - 1) / a.chunk_pages, a.max_chunks);
+        }
+    }
+    const float *st = a.parts + row * a.row_stride;
+    float top = -INFINITY;
+    for (int p = lane; p < n; p += 32) top = fmaxf(top, st[p * a.part_stride]);
+    for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    float lsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < n; p++) {
+        const float *s = st + p * a.part_stride;
+        const float mp = s[0];
+        const float c = mp == -INFINITY ? 0.f : ex2(mp - top);
+        const float4 o = *reinterpret_cast<const float4 *>(s + 4 + 4 * lane);
+        lsum += c * s[1];
+        acc.x += c * o.x, acc.y += c * o.y, acc.z += c * o.z, acc.w += c * o.w;
+    }
+    if (a.part_out) {
+        float *o = a.part_out + row * PART;
+        if (lane == 0) *reinterpret_cast<float4 *>(o) = make_float4(top, lsum, 0.f, 0.f);
+        *reinterpret_cast<float4 *>(o + 4 + 4 * lane) = acc;
+    }
+    if (a.out) {
+        const bool any = lsum > 0.f;
+        const float x = any ? __fdiv_rn(acc.x, lsum) : 0.f, y = any ? __fdiv_rn(acc.y, lsum) : 0.f;
+        const float z = any ? __fdiv_rn(acc.z, lsum) : 0.f, w = any ? __fdiv_rn(acc.w, lsum) : 0.f;
+        uint2 u;
+        *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(x, y);
+        *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(z, w);
+        *reinterpret_cast<uint2 *>(a.out + row * HEAD_DIM + 4 * lane) = u;
+    }
+}
+
+/* ---- host side ---------------------------------------------------------------------------------------------- */
+
+static int sm_count() {
+    static const int count = [] {
+        int device = 0, c = 0;
+        if (cudaGetDevice(&device) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || c <= 0) return 148;
+        return c;
+    }();
+    return count;
+}
+
+static int pages_of(int len) { return (len + PAGE_TOKENS - 1) / PAGE_TOKENS; }
+
+template <int NT> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
+    static bool done[64] = {};
+    int device = 0;
+    cudaError_t rc = cudaGetDevice(&device);
+    if (rc != cudaSuccess) return rc;
+    if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
+    rc = cudaFuncSetAttribute(k_decode_attn<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem(NT));
+    if (rc == cudaSuccess && device >= 0 && device < 64) done[device] = true;
+    return rc;
+}
+
+static int launch_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
+                        long long workspace_bytes, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,
+                        int max_kv_len, int window, int &chunk_pages, float softmax_scale, void *status,
+                        cudaStream_t stream) {
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || n_slots <= 0 || pages_per_slot <= 0 || max_kv_len < 0 ||
+        window < 0 || chunk_pages < 0 || !(softmax_scale > 0.f))
+        return NCB_ERR_ARG;
+    if (Hq / Hkv > 8) return NCB_ERR_UNSUPPORTED;
+    if (B > 65535 || Hkv > 65535) return NCB_ERR_ARG;
+    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
+    if (chunk_pages == 0) chunk_pages = decode_attn_chunk_pages(B, Hkv, max_kv_len);
+    if (B == 0) return NCB_OK;
+    if (!q || !kv_cache || !lens || !workspace) return NCB_ERR_ARG;
+    if (((uintptr_t)q | (uintptr_t)kv_cache | (uintptr_t)workspace) % 16 != 0) return NCB_ERR_ALIGN;
+    if (workspace_bytes < decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages)) return NCB_ERR_WORKSPACE;
+    const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
+    AttnArgs a = {(const bf16 *)q, (const uint8_t *)kv_cache, (const int32_t *)lens, (const int32_t *)slot_map,
+                  (float *)workspace, B, Hq, Hkv, n_slots, pages_per_slot, window, chunk_pages, max_chunks,
+                  softmax_scale * 1.4426950408889634f, (int *)status};
+    const dim3 grid(max_chunks, Hkv, B);
+    if (Hq / Hkv <= 4) {
+        if (prepare<1>() != cudaSuccess) return NCB_ERR_LAUNCH;
+        k_decode_attn<1><<<grid, THREADS, attn_smem(1), stream>>>(a);
+    } else {
+        if (prepare<2>() != cudaSuccess) return NCB_ERR_LAUNCH;
+        k_decode_attn<2><<<grid, THREADS, attn_smem(2), stream>>>(a);
+    }
+    return cudaGetLastError() == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+}
+
+static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
+    if (a.rows == 0) return NCB_OK;
+    const long long blocks = (a.rows + MERGE_WARPS - 1) / MERGE_WARPS;
+    if (blocks > 0x7fffffffLL) return NCB_ERR_ARG;
+    k_merge<<<(unsigned)blocks, MERGE_WARPS * 32, 0, stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+}
+
+static int attend(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
+                  long long workspace_bytes, void *out, void *part_out, int B, int Hq, int Hkv, int n_slots,
+                  int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale, void *status,
+                  void *stream) {
+    if (!out && !part_out) return NCB_ERR_ARG;
+    if (((uintptr_t)out | (uintptr_t)part_out) % 16 != 0) return NCB_ERR_ALIGN;
+    const int rc = launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots,
+                                pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status,
+                                (cudaStream_t)stream);
+    if (rc != NCB_OK || B == 0) return rc;
+    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
+    const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
+    MergeArgs m = {(const float *)workspace, (long long)B * Hq, PART, (long long)max_chunks * PART, 0,
+                   (const int32_t *)lens, (const int32_t *)slot_map, Hq, window, chunk_pages, n_slots, pages_per_slot,
+                   max_chunks, (bf16 *)out, (float *)part_out};
+    return launch_merge(m, (cudaStream_t)stream);
+}
+
+extern "C" {
+
+int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len) {
+    if (B <= 0 || Hkv <= 0 || max_kv_len <= 0) return 1;
+    /* aim at about eight blocks per resident slot (2 per SM) when every sequence is max_kv_len long */
+    const long long total = (long long)B * Hkv * pages_of(max_kv_len), slots = 2LL * sm_count();
+    long long c = total / (8 * slots);
+    if (c < 1) c = 1;
+    if (c > 64) c = 64;
+    return (int)c;
+}
+
+long long decode_attn_workspace_bytes(int B, int Hq, int max_kv_len, int Hkv, int chunk_pages) {
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || max_kv_len < 0 || chunk_pages < 0) return -1;
+    if (chunk_pages == 0) chunk_pages = decode_attn_chunk_pages(B, Hkv, max_kv_len);
+    const long long max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
+    return (long long)B * Hq * max_chunks * PART * (long long)sizeof(float);
+}
+
+int decode_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
+                    long long workspace_bytes, void *out, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,
+                    int max_kv_len, int window, int chunk_pages, float softmax_scale, void *status, void *stream) {
+    if (!out && B > 0) return NCB_ERR_ARG;
+    return attend(q, kv_cache, lens, slot_map, workspace, workspace_bytes, out, nullptr, B, Hq, Hkv, n_slots,
+                  pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream);
+}
+
+int decode_attn_fp8_partial(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
+                            void *workspace, long long workspace_bytes, void *part_out, int B, int Hq, int Hkv,
+                            int n_slots, int pages_per_slot, int max_kv_len, int window, int chunk_pages,
+                            float softmax_scale, void *status, void *stream) {
+    if (!part_out && B > 0) return NCB_ERR_ARG;
+    return attend(q, kv_cache, lens, slot_map, workspace, workspace_bytes, nullptr, part_out, B, Hq, Hkv, n_slots,
+                  pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream);
+}
+
+int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out, void *stream) {
+    if (n_parts <= 0 || rows < 0) return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    if (!parts || !out) return NCB_ERR_ARG;
+    if (((uintptr_t)parts | (uintptr_t)out) % 16 != 0) return NCB_ERR_ALIGN;
+    MergeArgs m = {(const float *)parts, rows, rows * PART, PART, n_parts, nullptr, nullptr, 1, 0, 1, 1, 1, n_parts,
+                   (bf16 *)out, nullptr};
+    return launch_merge(m, (cudaStream_t)stream);
+}
+
+} /* extern "C" */

@@ -1,0 +1,210 @@
+/*
+ * kv_append_fp8: fused rotary + QK-RMSNorm + per-(token, head) scale + e4m3 pack + append into the paged cache.
+ * Replaces the reference's k_prologue (model/kernels/decode.cu:551-565; row math model/kernels/qk_row.cuh:26-51)
+ * for an fp8 cache and Hq != Hkv.
+ *
+ * Work item = one head row of 128 values (a q, k or v head of one token), handled by 8 lanes; lane t owns dims
+ * 8t..8t+7 and their rotation partners 64+8t..64+8t+7, the ownership of qk_row.cuh:11-12,44-50. A 128-thread block
+ * holds 16 items. The kernel is bound by launch latency and a few KB of traffic per token, so it is written for
+ * exactness: every fp32 operation is an explicit round-to-nearest intrinsic in the order of
+ * oracle/kv_append_oracle.c (no FMA contraction, sqrt + divide instead of rsqrtf), which makes q bits, cache
+ * bytes and scales exact functions of the inputs.
+ */
+#include "ncb_common.cuh"
+
+constexpr int LANES = 8;
+constexpr int VEC = 8;
+constexpr int BLOCK = 128;
+constexpr int ITEMS_PER_BLOCK = BLOCK / LANES;
+
+static __device__ __forceinline__ void load_bf16x8(const bf16 *p, float *v) {
+    const uint4 u = *reinterpret_cast<const uint4 *>(p);
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&u);
+#pragma unroll
+    for (int i = 0; i < VEC / 2; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+static __device__ __forceinline__ void load_f32x8(const float *p, float *v) {
+    *reinterpret_cast<float4 *>(v) = *reinterpret_cast<const float4 *>(p);
+    *reinterpret_cast<float4 *>(v + 4) = *reinterpret_cast<const float4 *>(p + 4);
+}
+
+/* The 8-lane group's shuffle mask and butterfly reductions (offsets 4, 2, 1). */
+static __device__ __forceinline__ unsigned group_mask() {
+    return 0xffu << ((threadIdx.x & 31) & ~(LANES - 1));
+}
+static __device__ __forceinline__ float group_sum(float v) {
+    const unsigned mask = group_mask();
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(mask, v, o));
+    return v;
+}
+static __device__ __forceinline__ float group_max(float v) {
+    const unsigned mask = group_mask();
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(mask, v, o));
+    return v;
+}
+
+/* x1, x2 (this lane's 8 + 8 values) -> normed, gained, rotated values rounded to bf16 and widened again. */
+static __device__ __forceinline__ void norm_rotate(float *x1, float *x2, const float *gain, const float *cs,
+                                                   const float *sn, int o) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; i++)
+        ss = __fadd_rn(ss, __fadd_rn(__fmul_rn(x1[i], x1[i]), __fmul_rn(x2[i], x2[i])));
+    ss = group_sum(ss);
+    const float mean = __fdiv_rn(ss, (float)HEAD_DIM);
+    const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(mean, FLT_EPSILON)));
+    float g1[VEC], g2[VEC], c[VEC], s[VEC];
+    load_f32x8(gain + o, g1);
+    load_f32x8(gain + HALF + o, g2);
+    load_f32x8(cs + o, c);
+    load_f32x8(sn + o, s);
+#pragma unroll
+    for (int i = 0; i < VEC; i++) {
+        const float n1 = __fmul_rn(__fmul_rn(x1[i], r), g1[i]), n2 = __fmul_rn(__fmul_rn(x2[i], r), g2[i]);
+        const float y1 = __fadd_rn(__fmul_rn(n1, c[i]), __fmul_rn(n2, s[i]));
+        const float y2 = __fsub_rn(__fmul_rn(n2, c[i]), __fmul_rn(n1, s[i]));
+        x1[i] = __bfloat162float(__float2bfloat16_rn(y1));
+        x2[i] = __bfloat162float(__float2bfloat16_rn(y2));
+    }
+}
+
+static __device__ __forceinline__ uint4 pack_bf16x8(const float *v) {
+    uint4 u;
+    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&u);
+#pragma unroll
+    for (int i = 0; i < VEC / 2; i++) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    return u;
+}
+
+/* scale = amax / 448 over the group's 128 values; bytes = e4m3(x / scale); a zero row gives scale 0, bytes 0. */
+static __device__ __forceinline__ float quantise(const float *x1, const float *x2, uint8_t *b1, uint8_t *b2) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; i++) amax = fmaxf(amax, fmaxf(fabsf(x1[i]), fabsf(x2[i])));
+    amax = group_max(amax);
+    if (!(amax > 0.f)) {
+#pragma unroll
+        for (int i = 0; i < VEC; i++) b1[i] = b2[i] = 0;
+        return 0.f;
+    }
+    const float scale = __fdiv_rn(amax, 448.f);
+#pragma unroll
+    for (int i = 0; i < VEC; i++) {
+        b1[i] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(x1[i], scale), __NV_SATFINITE, __NV_E4M3);
+        b2[i] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(x2[i], scale), __NV_SATFINITE, __NV_E4M3);
+    }
+    return scale;
+}
+
+struct AppendArgs {
+    const bf16 *qkv;
+    const float *q_gain, *k_gain, *cs, *sn;
+    const int32_t *pos, *slot_map;
+    bf16 *q_out;
+    uint8_t *cache;
+    long long rows, qkv_row_stride;
+    int Hq, Hkv, table_len, n_slots, pages_per_slot;
+    int *status;
+};
+
+__global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
+    const int items = a.Hq + 2 * a.Hkv;
+    const long long item = (long long)blockIdx.x * ITEMS_PER_BLOCK + threadIdx.x / LANES;
+    if (item >= a.rows * items) return; /* whole 8-lane groups leave together */
+    const long long row = item / items;
+    const int which = (int)(item % items), t = threadIdx.x % LANES, o = t * VEC;
+    const int p = a.pos[row];
+    const int slot = a.slot_map ? a.slot_map[row] : (int)row;
+    if (p < 0 || p >= a.table_len || p >= a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots) {
+        if (t == 0) flag(a.status, NCB_DEV_BAD_POSITION);
+        return;
+    }
+    const bf16 *x = a.qkv + row * a.qkv_row_stride + (size_t)which * HEAD_DIM;
+    float x1[VEC], x2[VEC];
+    load_bf16x8(x + o, x1);
+    load_bf16x8(x + HALF + o, x2);
+    const size_t tab = (size_t)p * HALF;
+    if (which < a.Hq) {
+        norm_rotate(x1, x2, a.q_gain, a.cs + tab, a.sn + tab, o);
+        bf16 *q = a.q_out + ((size_t)row * a.Hq + which) * HEAD_DIM;
+        *reinterpret_cast<uint4 *>(q + o) = pack_bf16x8(x1);
+        *reinterpret_cast<uint4 *>(q + HALF + o) = pack_bf16x8(x2);
+        return;
+    }
+    const bool is_k = which < a.Hq + a.Hkv;
+    const int head = is_k ? which - a.Hq : which - a.Hq - a.Hkv;
+    if (is_k) norm_rotate(x1, x2, a.k_gain, a.cs + tab, a.sn + tab, o);
+    uint8_t b1[VEC], b2[VEC];
+    const float scale = quantise(x1, x2, b1, b2);
+    const int j = p % PAGE_TOKENS;
+    uint8_t *page = a.cache + (((size_t)slot * a.Hkv + head) * a.pages_per_slot + p / PAGE_TOKENS) * PAGE_BYTES;
+    if (is_k) {
+        /* dims 8t..8t+7 sit in chunk t/2 at byte (t&1)*8; the partners in chunk 4 + t/2 */
+        uint2 lo, hi;
+        memcpy(&lo, b1, 8);
+        memcpy(&hi, b2, 8);
+        *reinterpret_cast<uint2 *>(page + page_k_chunk(j, t >> 1) + (t & 1) * 8) = lo;
+        *reinterpret_cast<uint2 *>(page + page_k_chunk(j, 4 + (t >> 1)) + (t & 1) * 8) = hi;
+        if (t == 0) reinterpret_cast<float *>(page + PAGE_KS)[j] = scale;
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; i++) {
+            page[page_v_byte(j, o + i)] = b1[i];
+            page[page_v_byte(j, HALF + o + i)] = b2[i];
+        }
+        if (t == 0) reinterpret_cast<float *>(page + PAGE_VS)[j] = scale;
+    }
+}
+
+extern "C" {
+
+const char *ncb_status_string(int status) {
+    switch (status) {
+    case NCB_OK: return "ok";
+    case NCB_ERR_ARG: return "invalid argument";
+    case NCB_ERR_ALIGN: return "misaligned pointer or stride";
+    case NCB_ERR_WORKSPACE: return "workspace too small";
+    case NCB_ERR_LAUNCH: return "kernel launch failed";
+    case NCB_ERR_UNSUPPORTED: return "unsupported head ratio";
+    default: return "unknown status";
+    }
+}
+
+int kv_cache_pages(int max_len) { return max_len <= 0 ? 0 : (max_len + PAGE_TOKENS - 1) / PAGE_TOKENS; }
+
+long long kv_cache_bytes(int n_slots, int kv_heads, int max_len) {
+    if (n_slots < 0 || kv_heads < 0 || max_len < 0) return -1;
+    return (long long)n_slots * kv_heads * kv_cache_pages(max_len) * PAGE_BYTES;
+}
+
+int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                  const void *pos, const void *slot_map, void *q_out, void *kv_cache, long long rows, int Hq,
+                  int Hkv, long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot, void *status,
+                  void *stream) {
+    if (rows < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || table_len <= 0 || n_slots <= 0 || pages_per_slot <= 0)
+        return NCB_ERR_ARG;
+    if (qkv_row_stride < (long long)(Hq + 2 * Hkv) * HEAD_DIM) return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    if (!qkv || !q_gain || !k_gain || !cos || !sin || !pos || !q_out || !kv_cache) return NCB_ERR_ARG;
+    const uintptr_t all = (uintptr_t)qkv | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)cos | (uintptr_t)sin |
+                          (uintptr_t)q_out | (uintptr_t)kv_cache;
+    if (all % 16 != 0 || qkv_row_stride % 8 != 0) return NCB_ERR_ALIGN;
+    const long long items = rows * (Hq + 2 * Hkv);
+    const long long blocks = (items + ITEMS_PER_BLOCK - 1) / ITEMS_PER_BLOCK;
+    if (blocks > 0x7fffffffLL) return NCB_ERR_ARG;
+    AppendArgs a = {(const bf16 *)qkv, (const float *)q_gain, (const float *)k_gain, (const float *)cos,
+                    (const float *)sin, (const int32_t *)pos, (const int32_t *)slot_map, (bf16 *)q_out,
+                    (uint8_t *)kv_cache, rows, qkv_row_stride, Hq, Hkv, table_len, n_slots, pages_per_slot,
+                    (int *)status};
+    k_kv_append<<<(unsigned)blocks, BLOCK, 0, (cudaStream_t)stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+}
+
+} /* extern "C" */

@@ -1,0 +1,42 @@
+"""Seeded synthetic inputs shared by the tests: the shapes and distributions of the benchmark configurations
+(q ~ N(0,1) in bf16; K, V ~ N(0,1) quantised per (token, head) with scale = amax / 448)."""
+
+import numpy as np
+import torch
+
+from oracle import kv_append as okv
+
+HEAD_DIM = 128
+
+
+def bf16_bits(t: torch.Tensor) -> np.ndarray:
+    """bf16 tensor -> uint16 bit patterns (numpy)."""
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def bits_bf16(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def randn_bf16(gen: torch.Generator, *shape: int) -> np.ndarray:
+    return bf16_bits(torch.randn(*shape, generator=gen).bfloat16())
+
+
+def attention_case(seed: int, Hq: int, Hkv: int, lens: list[int]) -> dict:
+    """q bits (B, Hq, 128) and per sequence quantised K, V: lists of (Hkv, n, 128) u8 and (Hkv, n) fp32."""
+    gen = torch.Generator().manual_seed(seed)
+    B = len(lens)
+    case = {"q": randn_bf16(gen, B, Hq, HEAD_DIM), "k_bytes": [], "k_scale": [], "v_bytes": [], "v_scale": [],
+            "lens": list(lens), "Hq": Hq, "Hkv": Hkv}
+    for n in lens:
+        for name in ("k", "v"):
+            b, s = okv.quant_rows(randn_bf16(gen, Hkv, n, HEAD_DIM))
+            case[f"{name}_bytes"].append(b)
+            case[f"{name}_scale"].append(s)
+    return case
+
+
+def error_stats(got_bits: np.ndarray, want_bits: np.ndarray) -> tuple[float, float]:
+    """(max-abs, mean-abs) difference of two bf16 bit arrays."""
+    d = np.abs(okv.bf16_to_f32(got_bits).astype(np.float64) - okv.bf16_to_f32(want_bits).astype(np.float64))
+    return float(d.max()) if d.size else 0.0, float(d.mean()) if d.size else 0.0

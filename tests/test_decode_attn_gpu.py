@@ -1,0 +1,197 @@
+"""decode_attn_fp8 on the GPU, through the C ABI, against the float64 checker (oracle/attention.py) and the
+committed outputs of the reference's own attention function. Tolerance on bf16 outputs: max-abs 2e-2, mean-abs
+2e-3 (the path's stated bound); the kernel is also held to a tighter internal bound against the float64 checker."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import nanochat_b200 as ncb
+from oracle import attention as oat
+from oracle import kv_append as okv
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+GOLDEN = np.load(Path(__file__).resolve().parent / "golden" / "reference_vectors.npz")
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3       # the path's tolerance
+TIGHT_MAX, TIGHT_MEAN = 6e-3, 4e-4   # what the two-term e4m3 split should hold against the float64 checker
+SCALE = 128 ** -0.5
+
+
+def load_cache(case, max_len, slots=None, n_slots=None):
+    B = len(case["lens"])
+    slots = list(range(B)) if slots is None else slots
+    cache = ncb.Fp8KVCache(n_slots or (max(slots) + 1), case["Hkv"], max_len)
+    for b, slot in enumerate(slots):
+        if case["lens"][b]:
+            cache.write(slot, *(torch.from_numpy(case[k][b]) for k in ("k_bytes", "k_scale", "v_bytes", "v_scale")))
+    return cache
+
+
+def run(case, max_len=None, window=0, chunk_pages=0, slots=None, n_slots=None, poison=False):
+    lens = case["lens"]
+    max_len = max_len or max(max(lens), 1)
+    cache = load_cache(case, max_len, slots, n_slots)
+    if poison:  # bytes and scales past each sequence's end become NaN patterns: they must never reach the output
+        for b, n in enumerate(lens):
+            slot = b if slots is None else slots[b]
+            tail = cache.capacity - n
+            if tail:
+                nan_b = torch.full((case["Hkv"], tail, 128), 0x7f, dtype=torch.uint8)
+                nan_s = torch.full((case["Hkv"], tail), float("nan"))
+                cache.write(slot, nan_b, nan_s, nan_b, nan_s, start=n)
+    q = helpers.bits_bf16(case["q"]).cuda()
+    lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    slot_map = None if slots is None else torch.tensor(slots, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ncb.decode_attention(q, cache, lens_t, max_kv_len=max(lens), slot_map=slot_map, window=window,
+                               chunk_pages=chunk_pages, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    return helpers.bf16_bits(out.cpu())
+
+
+def check(case, got, window=0, tight=True):
+    want = oat.decode_attention(case["q"], case["k_bytes"], case["k_scale"], case["v_bytes"], case["v_scale"], SCALE,
+                                window=window)
+    max_abs, mean_abs = helpers.error_stats(got, want)
+    assert np.isfinite(max_abs), "non-finite output"
+    assert max_abs <= MAX_ABS and mean_abs <= MEAN_ABS, (max_abs, mean_abs)
+    if tight:
+        ref = max(1.0, float(np.abs(okv.bf16_to_f32(want)).max()))  # outputs above 1 scale the bound
+        assert max_abs <= TIGHT_MAX * ref and mean_abs <= TIGHT_MEAN * ref, (max_abs, mean_abs)
+    return max_abs, mean_abs
+
+
+def test_config0_against_checker_and_reference_output():
+    """Batch 1, 10 heads, 1024 positions, seed 0: the reference-runnable configuration."""
+    case = helpers.attention_case(0, 10, 10, [1024])
+    got = run(case)
+    check(case, got)
+    max_abs, mean_abs = helpers.error_stats(got, GOLDEN["attn_cfg0_out"])
+    assert max_abs <= MAX_ABS and mean_abs <= MEAN_ABS, (max_abs, mean_abs)
+
+
+def test_gqa_against_reference_output():
+    case = helpers.attention_case(2, 8, 2, [300, 77])
+    got = run(case)
+    check(case, got)
+    max_abs, mean_abs = helpers.error_stats(got, GOLDEN["attn_gqa_out"])
+    assert max_abs <= MAX_ABS and mean_abs <= MEAN_ABS, (max_abs, mean_abs)
+
+
+@pytest.mark.parametrize("n", [1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 383, 384, 385, 1000])
+def test_length_edges(n):
+    case = helpers.attention_case(100 + n, 8, 2, [n])
+    check(case, run(case, poison=True))
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(1, 1), (2, 2), (2, 1), (4, 1), (8, 1), (6, 2), (12, 4), (32, 8), (16, 4), (10, 10)])
+def test_head_ratios(Hq, Hkv):
+    case = helpers.attention_case(200 + Hq * 10 + Hkv, Hq, Hkv, [150, 64, 1, 500])
+    check(case, run(case, poison=True))
+
+
+@pytest.mark.parametrize("chunk_pages", [1, 2, 3, 7, 64])
+def test_split_sizes_agree(chunk_pages):
+    case = helpers.attention_case(300, 8, 2, [900, 64, 129, 5])
+    check(case, run(case, chunk_pages=chunk_pages, poison=True))
+
+
+@pytest.mark.parametrize("window", [1, 5, 63, 64, 65, 200, 10000])
+def test_window_edges(window):
+    case = helpers.attention_case(400 + window, 8, 2, [300, 64, 3, 129])
+    check(case, run(case, window=window, chunk_pages=2, poison=True), window=window)
+
+
+def test_ragged_batch_with_slot_map_and_empty_sequence():
+    lens = [0, 17, 640, 64, 1, 333]
+    case = helpers.attention_case(500, 16, 4, lens)
+    got = run(case, max_len=700, slots=[5, 0, 3, 1, 4, 2], n_slots=6, poison=True)
+    check(case, got)
+    assert not got[0].any(), "an empty sequence gives a zero row"
+
+
+def test_scale_extremes():
+    """A zero V row, a zero K row, one dominant V scale and one tiny one."""
+    case = helpers.attention_case(600, 4, 1, [200])
+    case["v_bytes"][0][0, 10] = 0
+    case["v_scale"][0][0, 10] = 0
+    case["k_bytes"][0][0, 11] = 0
+    case["k_scale"][0][0, 11] = 0
+    case["v_scale"][0][0, 12] *= 1000
+    case["v_scale"][0][0, 13] *= 1e-6
+    case["k_scale"][0][0, 14] *= 8
+    check(case, run(case), tight=False)
+
+
+def test_peaked_attention():
+    """One key aligned with the query dominates the softmax."""
+    case = helpers.attention_case(700, 4, 1, [300])
+    q = okv.bf16_to_f32(case["q"][0, 0])
+    b, s = okv.quant_rows(okv.f32_to_bf16(q * 3)[None])
+    case["k_bytes"][0][0, 123], case["k_scale"][0][0, 123] = b[0], s[0]
+    check(case, run(case))
+
+
+def test_out_of_range_length_is_flagged_and_zeroed():
+    case = helpers.attention_case(800, 4, 2, [64, 64])
+    cache = load_cache(case, 64)
+    q = helpers.bits_bf16(case["q"]).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lens = torch.tensor([64, 65], dtype=torch.int32, device="cuda")  # 65 > capacity 64
+    out = ncb.decode_attention(q, cache, lens, max_kv_len=64, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 4
+    assert not helpers.bf16_bits(out.cpu())[1].any()
+    check({**case, "lens": [64], "q": case["q"][:1], "k_bytes": case["k_bytes"][:1], "k_scale": case["k_scale"][:1],
+           "v_bytes": case["v_bytes"][:1], "v_scale": case["v_scale"][:1]}, helpers.bf16_bits(out.cpu())[:1])
+
+
+def test_partial_states_merge_to_the_whole():
+    """A sequence cut into slices held by different caches (as ranks would hold them): per-slice states merged by
+    decode_attn_merge equal attention over the whole."""
+    n, cuts = 1500, [0, 400, 400, 1100, 1500]  # includes an empty slice
+    case = helpers.attention_case(900, 8, 2, [n, 700])
+    q = helpers.bits_bf16(case["q"]).cuda()
+    parts = []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        sl = {**case, "lens": [max(0, min(b, L) - min(a, L)) for L in case["lens"]]}
+        for key in ("k_bytes", "k_scale", "v_bytes", "v_scale"):
+            sl[key] = [x[:, a:b] for x in case[key]]
+        cache = load_cache(sl, max(max(sl["lens"]), 1))
+        lens = torch.tensor(sl["lens"], dtype=torch.int32, device="cuda")
+        parts.append(ncb.decode_attention_partial(q, cache, lens, max_kv_len=max(max(sl["lens"]), 1)))
+    out = ncb.merge_partials(torch.stack(parts))
+    torch.cuda.synchronize()
+    check(case, helpers.bf16_bits(out.cpu()))
+
+
+def test_append_then_attend():
+    """The step as the decoder runs it: kv_append_fp8 writes the new token, decode_attn_fp8 reads it back. Checked
+    against the oracles chained the same way."""
+    gen = torch.Generator().manual_seed(1000)
+    Hq, Hkv, B, T = 8, 2, 3, 70
+    cos, sin = ncb.rotary_table(128, 1e4)
+    ones = torch.ones(128)
+    cache = ncb.Fp8KVCache(B, Hkv, 128)
+    logical = {k: [[] for _ in range(B)] for k in ("k_bytes", "k_scale", "v_bytes", "v_scale")}
+    for t in range(T):
+        qkv = torch.randn(B, (Hq + 2 * Hkv) * 128, generator=gen).bfloat16()
+        pos = torch.full((B,), t, dtype=torch.int32)
+        q = ncb.kv_append(qkv.cuda(), ones.cuda(), ones.cuda(), cos.cuda(), sin.cuda(), pos.cuda(), cache, Hq)
+        want = okv.kv_append(helpers.bf16_bits(qkv), ones.numpy(), ones.numpy(), cos.numpy(), sin.numpy(),
+                             pos.numpy(), Hq, Hkv)
+        for b in range(B):
+            for key in logical:
+                logical[key][b].append(want[key][b])
+    lens = torch.full((B,), T, dtype=torch.int32, device="cuda")
+    out = ncb.decode_attention(q, cache, lens, max_kv_len=T)
+    torch.cuda.synchronize()
+    assert np.array_equal(helpers.bf16_bits(q.cpu()), want["q"])
+    case = {"q": want["q"], "lens": [T] * B, "Hq": Hq, "Hkv": Hkv}
+    for key in logical:
+        case[key] = [np.stack(logical[key][b], axis=1) for b in range(B)]
+    check(case, helpers.bf16_bits(out.cpu()))
