@@ -1,0 +1,358 @@
+"""Benchmark of the decode hot path: single-token attention over the paged fp8 (e4m3) KV cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload target8k|ragged]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+One JSON line on rank 0. A step is one decode-attention pass (split-KV kernel + merge kernel) over one batch.
+
+  workload  target8k: batch 64 per GPU, 32 query heads, 8 KV heads, head dim 128, every sequence 8,192 positions
+            (the shapes of the GQA sweep at the length the bandwidth target is stated on); ragged: the sweep
+            itself, lengths uniform in [512, 16384]. With N GPUs the global batch is 64 N sequences, assigned to
+            ranks by summed length (weak scaling, no collective on the data path).
+  value     whole-job algorithmic GB/s with the cache, q and lens resident in HBM:
+            bytes = sum_b len_b * Hkv * 264 + B * Hq * 512 per step (K + V bytes, two fp32 scales, q in, out).
+  e2e       the same metric through the public operators with HOST buffers: each step copies the new token's fused
+            qkv row and positions from pinned memory, runs kv_append_fp8 + decode_attn_fp8 and copies the output
+            back to pinned memory, synchronising every step. The KV cache is decoder state that lives in HBM
+            between steps (as in the reference's decoder), so it is not a per-step input.
+  roofline  the split-KV kernel alone (CUDA events around a loop of decode_attn_fp8_split launches on the same
+            inputs) against the measured HBM copy bandwidth in MEASURED_PEAKS.json.
+  cpu_baseline  the reference's CPU attention (a torch restatement of inference/modeling_nanochat.py:48-56, see
+            oracle/attention.py) on a bounded sample of the same workload, all host threads.
+
+--impl reference times that CPU restatement alone, on the same config and metric.
+Data is synthetic: q ~ N(0,1) bf16; K, V ~ N(0,1) quantised per (token, head) with scale = amax / 448."""
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HQ, HKV, D, BATCH = 32, 8, 128, 64
+METRIC, UNIT = "decode_attention_hbm_gbs", "GB/s"
+
+
+def algorithmic_bytes(lens, Hq=HQ, Hkv=HKV) -> int:
+    return sum(int(n) for n in lens) * Hkv * 264 + len(lens) * Hq * 512
+
+
+def workload_lens(workload: str, n_seqs: int, seed: int = 0) -> list[int]:
+    if workload == "target8k":
+        return [8192] * n_seqs
+    gen = torch.Generator().manual_seed(seed)
+    return torch.randint(512, 16385, (n_seqs,), generator=gen).tolist()
+
+
+def peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, an earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """SM clock and throttle reasons of one GPU, polled through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period: float = 0.01):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period, self.stop_flag, self.thread = period, threading.Event(), None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nvml = None
+
+    NAMES = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+             "hw_power_brake_slowdown": 0x80, "sync_boost": 0x10}
+
+    def poll(self):
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
+                reasons = getattr(self.nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                    self.nvml.nvmlDeviceGetCurrentClocksThrottleReasons
+                bits = reasons(self.handle)
+                self.reasons.update(name for name, bit in self.NAMES.items() if bits & bit)
+            except Exception:
+                pass
+            self.stop_flag.wait(self.period)
+
+    def __enter__(self):
+        if self.nvml:
+            self.thread = threading.Thread(target=self.poll, daemon=True)
+            self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop_flag.set()
+        if self.thread:
+            self.thread.join()
+
+    def summary(self) -> dict:
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_sample(lens, seed: int):
+    """Logical bf16 K/V (kv heads expanded to query heads, as the reference needs) and q for a few sequences."""
+    gen = torch.Generator().manual_seed(seed)
+    out = []
+    for n in lens:
+        q = torch.randn(1, HQ, 1, D, generator=gen).bfloat16()
+        kv = []
+        for _ in range(2):
+            x = torch.randn(HKV, n, D, generator=gen)
+            scale = x.abs().amax(-1, keepdim=True) / 448.0
+            deq = (x / scale).to(torch.float8_e4m3fn).float() * scale
+            kv.append(deq.bfloat16().repeat_interleave(HQ // HKV, dim=0)[None])
+        out.append((q, kv[0], kv[1]))
+    return out
+
+
+def time_cpu_reference(lens, budget_s: float, seed: int = 1234) -> dict:
+    """The reference's CPU attention on `lens`, repeated for about budget_s seconds; median pass time."""
+    from oracle.attention import eager_attention_port
+
+    threads = len(os.sched_getaffinity(0))
+    torch.set_num_threads(threads)
+    sample = cpu_sample(lens, seed)
+    times = []
+    deadline = time.perf_counter() + budget_s
+    for rep in range(1000):
+        t0 = time.perf_counter()
+        for q, k, v in sample:
+            eager_attention_port(q, k, v, D ** -0.5)
+        times.append(time.perf_counter() - t0)
+        if rep >= 3 and time.perf_counter() > deadline:
+            break
+    warm = times[1:] if len(times) > 1 else times
+    t = statistics.median(warm)
+    return {"value": algorithmic_bytes(lens) / t / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{len(lens)} sequences of the workload ({sum(lens)} positions), bf16 K/V dequantised outside "
+                      f"the timed region, {len(warm)} timed passes, median", "seconds_per_pass": t}
+
+
+def synthetic_cache(lens, max_len: int, seed: int, device):
+    """A cache filled with quantised N(0,1) keys and values, generated on the device."""
+    import nanochat_b200 as ncb
+
+    gen = torch.Generator(device=device).manual_seed(seed)
+    cache = ncb.Fp8KVCache(len(lens), HKV, max_len, device=device)
+    for slot, n in enumerate(lens):
+        packed = []
+        for _ in range(2):
+            x = torch.randn(HKV, n, D, generator=gen, device=device)
+            scale = x.abs().amax(-1) / 448.0
+            packed += [(x / scale[..., None]).to(torch.float8_e4m3fn).view(torch.uint8), scale]
+        cache.write(slot, *packed)
+    return cache
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    lens_all = workload_lens(args.workload, BATCH * world)
+    sample = lens_all[:args.cpu_sample]
+    from oracle.attention import eager_attention_port
+
+    threads = len(os.sched_getaffinity(0))
+    torch.set_num_threads(threads)
+    data = cpu_sample(sample, 1234)
+    step = lambda: [eager_attention_port(q, k, v, D ** -0.5) for q, k, v in data]
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = algorithmic_bytes(sample) * args.steps / dt / 1e9
+    note = f"each step = {len(sample)} sequences of the workload ({sum(sample)} positions) on the host cores"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_of(args, world, extra={"reference_step": note}),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": note},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def config_of(args, world: int, extra: dict | None = None) -> dict:
+    cfg = {"workload": {"target8k": "GQA sweep shapes at the bandwidth-target length: batch 64 per GPU, Hq 32, Hkv 8, "
+                                    "head_dim 128, every sequence 8192 positions, e4m3 KV with per-(token, head) fp32 "
+                                    "scales",
+                        "ragged": "GQA sweep: batch 64 per GPU, Hq 32, Hkv 8, head_dim 128, lengths uniform in "
+                                  "[512, 16384], e4m3 KV with per-(token, head) fp32 scales"}[args.workload],
+           "global_batch": BATCH * world, "parallelism": f"batch-sharded x{world}", "seed": 0,
+           "l2": "inputs (>= 0.5 GB of KV per GPU) exceed the 126 MB L2; no flush needed"}
+    cfg.update(extra or {})
+    return cfg
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="target8k", choices=["target8k", "ragged"])
+    ap.add_argument("--cpu-sample", type=int, default=4, help="sequences in the CPU baseline's sample")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--chunk-pages", type=int, default=0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch.distributed as dist
+
+    import nanochat_b200 as ncb
+    from nanochat_b200 import attention as ops
+    from nanochat_b200.sharding import shard_batch
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    lens_all = workload_lens(args.workload, BATCH * world)
+    mine = shard_batch(lens_all, world)[rank]
+    lens = [lens_all[i] for i in mine]
+    B = len(lens)
+    e2e_steps = min(args.steps, 200)
+    headroom = args.warmup + e2e_steps + 8
+    max_len = max(lens) + headroom
+    cache = synthetic_cache(lens, max_len, seed=1000 + rank, device=device)
+    gen = torch.Generator(device=device).manual_seed(2000 + rank)
+    q = torch.randn(B, HQ, D, generator=gen, device=device).bfloat16()
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=device)
+    max_kv = max(lens)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    chunk = args.chunk_pages or ops.chunk_pages_for(B, HKV, max_kv)
+    workspace = torch.empty(ncb.workspace_bytes(B, HQ, HKV, max_kv + headroom, chunk), dtype=torch.uint8, device=device)
+    out = torch.empty_like(q)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps: int, warmup: int) -> float:
+        """Milliseconds for `steps` calls after `warmup`: CUDA events on the launching stream, barrier and
+        synchronize on both sides, max over ranks."""
+        for _ in range(warmup):
+            fn()
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(end)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    step = lambda: ncb.decode_attention(q, cache, lens_t, max_kv, chunk_pages=chunk, workspace=workspace, out=out,
+                                        status=status)
+    split = lambda: ops.decode_attention_split(q, cache, lens_t, max_kv, workspace, chunk_pages=chunk, status=status)
+
+    with ClockSampler(local) as clocks:
+        ms_total = timed(step, args.steps, args.warmup)
+    ms_split = timed(split, args.steps, 3)
+
+    # ---- end to end through the public operators with host buffers
+    cos, sin = ncb.rotary_table(max_len, 1e4, device=device)
+    ones = torch.ones(D, device=device)
+    host_gen = torch.Generator().manual_seed(3000 + rank)
+    qkv_host = torch.randn(B, (HQ + 2 * HKV) * D, generator=host_gen).bfloat16().pin_memory()
+    pos_host = torch.tensor(lens, dtype=torch.int32).pin_memory()
+    out_host = torch.empty(B, HQ, D, dtype=torch.bfloat16).pin_memory()
+    qkv_dev, pos_dev, len_dev = torch.empty_like(qkv_host, device=device), torch.empty_like(pos_host, device=device), \
+        torch.empty_like(pos_host, device=device)
+    q_dev = torch.empty(B, HQ, D, dtype=torch.bfloat16, device=device)
+    e2e_bytes = 0
+
+    def e2e_step():
+        nonlocal e2e_bytes
+        qkv_dev.copy_(qkv_host, non_blocking=True)
+        pos_dev.copy_(pos_host, non_blocking=True)
+        ncb.kv_append(qkv_dev, ones, ones, cos, sin, pos_dev, cache, HQ, q_out=q_dev, status=status)
+        torch.add(pos_dev, 1, out=len_dev)
+        top = int(pos_host.max()) + 1
+        ncb.decode_attention(q_dev, cache, len_dev, top, chunk_pages=chunk, workspace=workspace, out=out, status=status)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        e2e_bytes += algorithmic_bytes((pos_host + 1).tolist())
+        pos_host.add_(1)  # the next step's token goes one position further
+
+    for _ in range(args.warmup):
+        e2e_step()
+    barrier()
+    e2e_bytes = 0
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], device=device)
+    total_e2e_bytes = torch.tensor([float(e2e_bytes)], device=device)
+    total_bytes = torch.tensor([float(algorithmic_bytes(lens))], device=device)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+        dist.all_reduce(total_e2e_bytes)
+        dist.all_reduce(total_bytes)
+    assert status.item() == 0, f"device status {status.item()}"
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        step_bytes = float(total_bytes.item())
+        value = step_bytes * args.steps / (ms_total * 1e-3) / 1e9
+        split_gbs = algorithmic_bytes(lens) * args.steps / (ms_split * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "e4m3 operands, fp32 accumulate and softmax", "data": "synthetic",
+            "config": config_of(args, world, extra={"chunk_pages": chunk, "pct_of_8TBs_per_gpu": value / world / 80.0}),
+            "clocks": clocks.summary(),
+            "e2e": {"value": float(total_e2e_bytes.item()) / float(e2e_s.item()) / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": qkv_host.numel() * 2 + pos_host.numel() * 4,
+                    "d2h_bytes_per_step": out_host.numel() * 2, "steps": e2e_steps,
+                    "ms_per_step": float(e2e_s.item()) / e2e_steps * 1e3,
+                    "what": "pinned-host qkv row + positions in, kv_append_fp8 + decode_attn_fp8, output to pinned host, "
+                            "synchronised every step; the KV cache is resident decoder state"},
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "k_decode_attn<1> (split-KV)", "achieved": split_gbs, "peak": peak,
+                         "unit": UNIT, "frac": split_gbs / peak, "peak_kind": peak_kind, "traffic": None,
+                         "us_per_launch": ms_split / args.steps * 1e3,
+                         "algorithmic_bytes_per_launch": algorithmic_bytes(lens)},
+        }
+        if world == 1:
+            line["cpu_baseline"] = time_cpu_reference(lens[:args.cpu_sample], args.cpu_seconds)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -118,6 +118,16 @@ int decode_attn_fp8_partial(const void *q, const void *kv_cache, const void *len
                             float softmax_scale, void *status, void *stream);
 
 /*
+ * The first of decode_attn_fp8's two launches alone: the split-KV kernel, leaving one state per (b, h, chunk) in
+ * the workspace. For timing that kernel by itself and for callers that merge elsewhere; same arguments and
+ * checks as decode_attn_fp8 without `out`.
+ */
+int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
+                          void *workspace, long long workspace_bytes, int B, int Hq, int Hkv, int n_slots,
+                          int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale,
+                          void *status, void *stream);
+
+/*
  * Merge n_parts states per row: parts fp32 [n_parts][rows][NCB_PART_FLOATS] (e.g. the all-gathered part_out of
  * every rank, rows = B * Hq) into out bf16 [rows][128]. A state with m = -inf counts as empty; a row whose states
  * are all empty gives zeros.

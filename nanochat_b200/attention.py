@@ -52,7 +52,7 @@ def workspace_bytes(B: int, Hq: int, Hkv: int, max_kv_len: int, chunk_pages: int
     return cuda_library("decode_attn").decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages)
 
 
-def _attend(entry: str, q: Tensor, cache: Fp8KVCache, lens: Tensor, result: Tensor, max_kv_len: int,
+def _attend(entry: str, q: Tensor, cache: Fp8KVCache, lens: Tensor, result: Tensor | None, max_kv_len: int,
             slot_map: Tensor | None, window: int, chunk_pages: int, softmax_scale: float | None,
             workspace: Tensor | None, status: Tensor | None) -> None:
     B, Hq = q.shape[0], q.shape[1]
@@ -63,10 +63,12 @@ def _attend(entry: str, q: Tensor, cache: Fp8KVCache, lens: Tensor, result: Tens
     if workspace is None:
         workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
     scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
+    head = [pointer(q), pointer(cache.pages), pointer(lens), pointer(slot_map), pointer(workspace), workspace.numel()]
+    if result is not None:
+        head.append(pointer(result))
     rc = getattr(cuda_library("decode_attn"), entry)(
-        pointer(q), pointer(cache.pages), pointer(lens), pointer(slot_map), pointer(workspace), workspace.numel(),
-        pointer(result), B, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, max_kv_len, window, chunk_pages,
-        scale, pointer(status), stream())
+        *head, B, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, max_kv_len, window, chunk_pages, scale,
+        pointer(status), stream())
     check(rc, entry)
 
 
@@ -95,6 +97,14 @@ def decode_attention_partial(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_
     _attend("decode_attn_fp8_partial", q, cache, lens, part, max_kv_len, slot_map, window, chunk_pages,
             softmax_scale, workspace, status)
     return part
+
+
+def decode_attention_split(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int, workspace: Tensor,
+                           slot_map: Tensor | None = None, window: int = 0, chunk_pages: int = 0,
+                           softmax_scale: float | None = None, status: Tensor | None = None) -> None:
+    """Only the split-KV launch of decode_attention; per-chunk states stay in `workspace`."""
+    _attend("decode_attn_fp8_split", q, cache, lens, None, max_kv_len, slot_map, window, chunk_pages, softmax_scale,
+            workspace, status)
 
 
 def merge_partials(parts: Tensor, out: Tensor | None = None) -> Tensor:

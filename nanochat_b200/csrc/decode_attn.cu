@@ -607,6 +607,14 @@ int decode_attn_fp8_partial(const void *q, const void *kv_cache, const void *len
                   pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream);
 }
 
+int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
+                          void *workspace, long long workspace_bytes, int B, int Hq, int Hkv, int n_slots,
+                          int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale,
+                          void *status, void *stream) {
+    return launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots, pages_per_slot,
+                        max_kv_len, window, chunk_pages, softmax_scale, status, (cudaStream_t)stream);
+}
+
 int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out, void *stream) {
     if (n_parts <= 0 || rows < 0) return NCB_ERR_ARG;
     if (rows == 0) return NCB_OK;

@@ -37,6 +37,7 @@ SIGNATURES = {
         "decode_attn_workspace_bytes": ([c_int, c_int, c_int, c_int, c_int], c_ll),
         "decode_attn_fp8": ([c_ptr] * 5 + [c_ll, c_ptr] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_fp8_partial": ([c_ptr] * 5 + [c_ll, c_ptr] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
+        "decode_attn_fp8_split": ([c_ptr] * 5 + [c_ll] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_merge": ([c_ptr, c_int, c_ll, c_ptr, c_ptr], c_int),
     },
 }
