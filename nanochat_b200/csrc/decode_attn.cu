@@ -7,9 +7,11 @@
  * once for all G = Hq / Hkv query heads that share it. Everything else is shaped to keep that stream busy:
  *
  *   - one thread block per (sequence, kv head, chunk of pages); a page (include/nanochat_b200.h) is one contiguous
- *     16,896-byte record, fetched by ONE cp.async.bulk into a STAGES-deep shared-memory ring and signalled on an
- *     mbarrier (full/empty pair per stage); a producer warp issues the copies, four consumer warps each take
- *     every fourth page and never synchronise with each other until the end;
+ *     16,896-byte record fetched by ONE cp.async.bulk that signals an mbarrier. Each of the block's WARPS warps
+ *     owns one shared-memory stage and one barrier: it takes every WARPS-th page of the chunk, waits for it,
+ *     consumes it and immediately issues its next page into the same stage. Warps never synchronise with each
+ *     other until the end, a barrier is only ever waited on by the warp that armed it (so its phases are observed
+ *     strictly in order), and two blocks per SM keep twelve pages (about 200 KB) in flight or in use per SM;
  *   - no fp8 -> float conversion of K or V at all: both contractions run on the tensor cores as
  *     mma.sync.m16n8k32 e4m3 x e4m3 -> fp32 with the CACHE as the A operand (16 positions, or 16 dims, per tile)
  *     and the N = 8 columns holding the group's query heads. bf16 queries and fp32 probabilities do not fit e4m3's
@@ -26,22 +28,21 @@
  * Positions outside [begin, len) inside the first and last page are masked with selects; their V bytes are zeroed
  * in shared memory first because an e4m3 NaN byte times a zero probability would still be NaN.
  *
- * Every wait is bounded: when a barrier does not flip within about a second the block records
- * NCB_DEV_WAIT_TIMEOUT in the caller's status word, stops consuming, drains its own copies (bounded again) and
- * returns.
+ * Every wait is bounded: when a barrier does not flip within about a second the warp records
+ * NCB_DEV_WAIT_TIMEOUT in the caller's status word, waits once more (bounded again) for its copy in flight, stops
+ * consuming and falls through to the block's final barriers.
  */
 #include "ncb_common.cuh"
 
-constexpr int CONSUMER_WARPS = 4;
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int PRODUCER_TID = CONSUMER_WARPS * 32;
-/* ring depth: two blocks per SM must fit 227 KB of shared memory together with the merge area */
-constexpr __host__ __device__ int stages_of(int NT) { return NT == 1 ? 6 : 5; }
+constexpr int WARPS = 6; /* = stages per block; 6 x 16,896 B x 2 blocks fit one SM's shared memory */
+constexpr int THREADS = WARPS * 32;
 constexpr int PART = NCB_PART_FLOATS;
 constexpr uint32_t WAIT_TRIES = 1u << 19; /* x <= 2 us suspend hint each: about one second */
 constexpr float P_SCALE = 256.f;          /* folded probabilities in (0, 1] -> e4m3 range, exact power of two */
 constexpr float LO_SCALE = 16.f;          /* second term's gain: the first term's rounding error is <= 2^-4 ulp-wise */
 constexpr float MIN_LOG2_VSCALE = -64.f;
+constexpr size_t ATTN_SMEM = (size_t)WARPS * PAGE_BYTES;
+static_assert(WARPS * 4 * 2 * PART * sizeof(float) <= ATTN_SMEM, "the merge area reuses the ring");
 
 struct AttnArgs {
     const bf16 *q;
@@ -63,9 +64,6 @@ static __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 static __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-static __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 /* True once the barrier's phase of the given parity has completed; gives up after WAIT_TRIES bounded tries. */
 static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t tries = 0; tries < WAIT_TRIES; tries++) {
@@ -80,9 +78,11 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) 
     }
     return false;
 }
-static __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+/* One page from global to shared memory; the barrier receives the byte count when the copy has landed. */
+static __device__ __forceinline__ void page_load(uint32_t dst, const void *src, uint32_t bar) {
+    mbar_expect_tx(bar, PAGE_BYTES);
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
+                 "l"(src), "r"((uint32_t)PAGE_BYTES), "r"(bar)
                  : "memory");
 }
 static __device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3,
@@ -157,23 +157,18 @@ static __device__ __forceinline__ Span span_of(int len, int window) {
 
 /* ---- split-KV kernel ---------------------------------------------------------------------------------------- */
 
-constexpr int merge_floats(int NT) { return CONSUMER_WARPS * 4 * NT * PART; }
-constexpr size_t attn_smem(int NT) { return (size_t)stages_of(NT) * PAGE_BYTES + merge_floats(NT) * sizeof(float); }
-
 template <int NT>
 __global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
-    constexpr int STAGES = stages_of(NT);
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t bars[2 * STAGES]; /* full[STAGES], empty[STAGES] */
-    __shared__ float q_scale[4 * NT];
-    __shared__ int abort_flag;
-    float *merge = reinterpret_cast<float *>(smem + (size_t)STAGES * PAGE_BYTES);
+    extern __shared__ __align__(128) uint8_t smem[];       /* WARPS stages of one page; later the merge area */
+    __shared__ __align__(8) uint64_t bars[WARPS];          /* one "page landed" barrier per warp */
+    __shared__ float q_stage[4 * NT * HEAD_DIM], q_scale[4 * NT];
+    float *merge = reinterpret_cast<float *>(smem);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int G = a.Hq / a.Hkv;
 
-    int len = a.lens[b];
+    const int len = a.lens[b];
     const int slot = a.slot_map ? a.slot_map[b] : b;
     if (len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots) {
         if (tid == 0 && chunk == 0 && kvh == 0) flag(a.status, NCB_DEV_BAD_LENGTH);
@@ -185,37 +180,52 @@ __global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
     if (n <= 0) return;
 
     const uint8_t *pages = a.cache + (((size_t)slot * a.Hkv + kvh) * a.pages_per_slot + pg0) * PAGE_BYTES;
-    const uint32_t ring = smem_u32(smem), full = smem_u32(bars), empty = full + STAGES * 8;
+    uint8_t *page = smem + (size_t)warp * PAGE_BYTES; /* this warp's stage */
+    const uint32_t page_u = smem_u32(page), bar = smem_u32(bars + warp);
 
-    if (tid == PRODUCER_TID) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(full + 8 * s, 1);
-            mbar_init(empty + 8 * s, 1);
-        }
-        abort_flag = 0;
+    if (lane == 0) { /* arm this warp's barrier and start its first page before anything else happens */
+        mbar_init(bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        for (int i = 0; i < min(n, STAGES); i++) { /* fill the ring before anything else happens */
-            mbar_expect_tx(full + 8 * i, PAGE_BYTES);
-            bulk_load(ring + i * PAGE_BYTES, pages + (size_t)i * PAGE_BYTES, PAGE_BYTES, full + 8 * i);
-        }
+        if (warp < n) page_load(page_u, pages + (size_t)warp * PAGE_BYTES, bar);
     }
-    /* the group's queries as fp32, staged in the (not yet used) merge area */
+    /* the group's queries as fp32 and each head's scale amax / 448 */
     const bf16 *q = a.q + ((size_t)b * a.Hq + (size_t)kvh * G) * HEAD_DIM;
-    for (int i = tid; i < G * HEAD_DIM; i += THREADS) merge[i] = __bfloat162float(q[i]);
+    for (int i = tid; i < G * HEAD_DIM; i += THREADS) q_stage[i] = __bfloat162float(q[i]);
     __syncthreads();
-    if (warp < CONSUMER_WARPS) { /* per-head amax -> scale; each consumer warp takes heads warp, warp + 4 */
-        for (int h = warp; h < G; h += CONSUMER_WARPS) {
-            float m = 0.f;
-            for (int i = lane; i < HEAD_DIM; i += 32) m = fmaxf(m, fabsf(merge[h * HEAD_DIM + i]));
-            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            if (lane == 0) q_scale[h] = m / 448.f;
-        }
+    for (int h = warp; h < G; h += WARPS) {
+        float m = 0.f;
+        for (int i = lane; i < HEAD_DIM; i += 32) m = fmaxf(m, fabsf(q_stage[h * HEAD_DIM + i]));
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) q_scale[h] = m / 448.f;
     }
     __syncthreads();
 
-    /* each consumer warp's running state: per tile, head t's maximum (log2 units), this lane's share of the sum,
-     * and O^T fragments (dims 16 dt + g, + 8; columns = head t's two terms) */
+    /* B fragments of q: column g = (head g / 2 of the tile, term g % 2); b0 = dims 32 ks + 4 t .. + 3,
+     * b1 = dims 32 ks + 16 + 4 t .. + 3 */
+    uint32_t qf[NT][4][2];
+    float qfac[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int hc = 4 * nt + (g >> 1), hs = 4 * nt + t; /* the head of this lane's B column / C columns */
+        const float sc = hc < G ? q_scale[hc] : 0.f, inv = sc > 0.f ? 1.f / sc : 0.f;
+        qfac[nt] = (hs < G ? q_scale[hs] : 0.f) * a.scale_log2;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++)
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float x[4];
+                uint32_t hi, lo;
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    x[i] = hc < G ? q_stage[hc * HEAD_DIM + 32 * ks + 16 * half + 4 * t + i] * inv : 0.f;
+                split4(x, hi, lo);
+                qf[nt][ks][half] = (g & 1) ? lo : hi;
+            }
+    }
+
+    /* the warp's running state: per tile, head t's maximum (log2 units), this lane's share of the sum, and O^T
+     * fragments (dims 16 dt + g, + 8; columns = head t's two terms) */
     float m[NT], l[NT], oacc[NT][8][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
@@ -227,201 +237,153 @@ __global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
             for (int i = 0; i < 4; i++) oacc[nt][dt][i] = 0.f;
     }
 
-    if (warp == CONSUMER_WARPS) { /* ---- producer: refill stages as consumers release them ---- */
-        if (lane == 0) {
-            int issued = min(n, STAGES);
-            for (int i = STAGES; i < n; i++) {
-                const int s = i % STAGES;
-                if (!mbar_wait(empty + 8 * s, ((i / STAGES) & 1) ^ 1)) {
-                    flag(a.status, NCB_DEV_WAIT_TIMEOUT);
-                    atomicExch(&abort_flag, 1);
-                    break;
-                }
-                if (*(volatile int *)&abort_flag) break;
-                mbar_expect_tx(full + 8 * s, PAGE_BYTES);
-                bulk_load(ring + s * PAGE_BYTES, pages + (size_t)i * PAGE_BYTES, PAGE_BYTES, full + 8 * s);
-                issued = i + 1;
-            }
-            if (*(volatile int *)&abort_flag) /* drain: the block must not exit under copies still in flight */
-                for (int i = max(0, issued - STAGES); i < issued; i++) mbar_wait(full + 8 * (i % STAGES), (i / STAGES) & 1);
+    uint32_t phase = 0;
+    for (int i = warp; i < n; i += WARPS, phase ^= 1) {
+        if (!mbar_wait(bar, phase)) {
+            if (lane == 0) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+            mbar_wait(bar, phase); /* the block must not exit under a copy still in flight */
+            break;
         }
-    } else { /* ---- consumers ---- */
-        /* B fragments of q: column g = (head g / 2 of the tile, term g % 2); b0 = dims 32 ks + 4 t .. + 3,
-         * b1 = dims 32 ks + 16 + 4 t .. + 3 */
-        uint32_t qf[NT][4][2];
-        float qfac[NT];
+        const int key0 = (pg0 + i) * PAGE_TOKENS; /* the page's first position */
+        const bool partial = key0 < sp.begin || key0 + PAGE_TOKENS > sp.len;
+        if (partial) { /* zero the V bytes of positions outside [begin, len) */
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            const int hc = 4 * nt + (g >> 1), hs = 4 * nt + t; /* the head of this lane's B column / C columns */
-            const float sc = hc < G ? q_scale[hc] : 0.f, inv = sc > 0.f ? 1.f / sc : 0.f;
-            qfac[nt] = (hs < G ? q_scale[hs] : 0.f) * a.scale_log2;
+            for (int blk = 0; blk < 4; blk++) { /* 16-position blocks: (group, half) */
+                const int first = key0 + 16 * blk;
+                uint32_t keep[4];
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++)
+                for (int w = 0; w < 4; w++) {
+                    keep[w] = 0;
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    float x[4];
-                    uint32_t hi, lo;
-#pragma unroll
-                    for (int i = 0; i < 4; i++)
-                        x[i] = hc < G ? merge[hc * HEAD_DIM + 32 * ks + 16 * half + 4 * t + i] * inv : 0.f;
-                    split4(x, hi, lo);
-                    qf[nt][ks][half] = (g & 1) ? lo : hi;
-                }
-        }
-        /* everyone has read the staged q before any warp reuses the merge area at the end: the final
-         * __syncthreads orders that; nothing else writes it until then */
-
-        for (int i = warp; i < n; i += CONSUMER_WARPS) {
-            const int s = i % STAGES;
-            if (*(volatile int *)&abort_flag) break;
-            if (!mbar_wait(full + 8 * s, (i / STAGES) & 1)) {
-                if (lane == 0) {
-                    flag(a.status, NCB_DEV_WAIT_TIMEOUT);
-                    atomicExch(&abort_flag, 1);
-                }
-                break;
-            }
-            uint8_t *page = smem + (size_t)s * PAGE_BYTES;
-            const uint32_t page_u = ring + s * PAGE_BYTES;
-            const int key0 = (pg0 + i) * PAGE_TOKENS; /* the page's first position */
-            const bool partial = key0 < sp.begin || key0 + PAGE_TOKENS > sp.len;
-            if (partial) { /* zero the V bytes of positions outside [begin, len) */
-#pragma unroll
-                for (int blk = 0; blk < 4; blk++) { /* 16-position blocks: (group, half) */
-                    const int first = key0 + 16 * blk;
-                    uint32_t keep[4];
-#pragma unroll
-                    for (int w = 0; w < 4; w++) {
-                        keep[w] = 0;
-#pragma unroll
-                        for (int bb = 0; bb < 4; bb++) {
-                            const int pos = first + 4 * w + bb;
-                            if (pos >= sp.begin && pos < sp.len) keep[w] |= 0xffu << (8 * bb);
-                        }
-                    }
-                    if ((keep[0] & keep[1] & keep[2] & keep[3]) == 0xffffffffu) continue;
-                    for (int d = lane; d < HEAD_DIM; d += 32) {
-                        uint4 *row = reinterpret_cast<uint4 *>(page + PAGE_V + blk * 2048 + d * 16);
-                        uint4 v = *row;
-                        v.x &= keep[0], v.y &= keep[1], v.z &= keep[2], v.w &= keep[3];
-                        *row = v;
+                    for (int bb = 0; bb < 4; bb++) {
+                        const int pos = first + 4 * w + bb;
+                        if (pos >= sp.begin && pos < sp.len) keep[w] |= 0xffu << (8 * bb);
                     }
                 }
-                __syncwarp();
-            }
-#pragma unroll
-            for (int gi = 0; gi < 2; gi++) { /* 32 positions at a time */
-                const int first = key0 + 32 * gi;
-                if (partial && (first >= sp.len || first + 32 <= sp.begin)) continue;
-                /* ---- scores: A = K rows (position 4 r + 2 mt [+ 1 for rows 8..15]), B = q ---- */
-                float sc[NT][2][4];
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                    for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-                        for (int c = 0; c < 4; c++) sc[nt][mt][c] = 0.f;
-#pragma unroll
-                for (int mt = 0; mt < 2; mt++) {
-                    const int row = 32 * gi + 4 * (lane & 7) + 2 * mt + ((lane >> 3) & 1);
-#pragma unroll
-                    for (int ks = 0; ks < 4; ks++) {
-                        uint32_t a0, a1, a2, a3;
-                        const int c = 2 * ks + (lane >> 4);
-                        ldmatrix_x4(a0, a1, a2, a3, page_u + PAGE_K + row * HEAD_DIM + ((c ^ (lane & 7)) << 4));
-#pragma unroll
-                        for (int nt = 0; nt < NT; nt++) mma_e4m3(sc[nt][mt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
-                    }
-                }
-                /* this lane: head t of each tile, positions first + 4 g + {0, 1, 2, 3} */
-                const float4 ks4 = *reinterpret_cast<const float4 *>(page + PAGE_KS + (32 * gi + 4 * g) * 4);
-                const float4 vs4 = *reinterpret_cast<const float4 *>(page + PAGE_VS + (32 * gi + 4 * g) * 4);
-                const float ksc[4] = {ks4.x, ks4.y, ks4.z, ks4.w}, vsc[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
-                bool valid[4];
-                float lv[4];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const int pos = first + 4 * g + j;
-                    valid[j] = !partial || (pos >= sp.begin && pos < sp.len);
-                    lv[j] = fmaxf(lg2(vsc[j]), MIN_LOG2_VSCALE);
-                }
-                uint32_t pb[NT][2];
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    float x[4], top = -INFINITY;
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const float raw = sc[nt][j >> 1][2 * (j & 1)] + sc[nt][j >> 1][2 * (j & 1) + 1] * (1.f / LO_SCALE);
-                        x[j] = raw * (ksc[j] * qfac[nt]);
-                        top = fmaxf(top, valid[j] ? x[j] + lv[j] : -INFINITY);
-                    }
-                    top = fmaxf(head_max(top), m[nt]);
-                    if (__any_sync(0xffffffffu, top > m[nt])) { /* some head's maximum moved: rescale */
-                        const float c = m[nt] == -INFINITY ? 0.f : ex2(m[nt] - top);
-                        l[nt] *= c;
-#pragma unroll
-                        for (int dt = 0; dt < 8; dt++)
-#pragma unroll
-                            for (int e = 0; e < 4; e++) oacc[nt][dt][e] *= c;
-                        m[nt] = top;
-                    }
-                    float p[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const float e = (valid[j] && top != -INFINITY) ? ex2(x[j] - top) : 0.f;
-                        l[nt] += e;
-                        p[j] = (valid[j] && top != -INFINITY) ? e * (vsc[j] * P_SCALE) : 0.f;
-                    }
-                    uint32_t whi, wlo;
-                    split4(p, whi, wlo);
-                    /* C layout -> B layout: column g of positions 4 t .. 4 t + 3 (and + 16) lives in lane
-                     * 4 t + g / 2 (and + 16), first term if g is even */
-                    const int src = 4 * t + (g >> 1);
-                    const uint32_t h0 = __shfl_sync(0xffffffffu, whi, src), l0 = __shfl_sync(0xffffffffu, wlo, src);
-                    const uint32_t h1 = __shfl_sync(0xffffffffu, whi, src + 16), l1 = __shfl_sync(0xffffffffu, wlo, src + 16);
-                    pb[nt][0] = (g & 1) ? l0 : h0;
-                    pb[nt][1] = (g & 1) ? l1 : h1;
-                }
-                /* ---- values: A = V^T rows (dim 16 dt + r), B = folded probabilities ---- */
-                const uint32_t vbase = page_u + PAGE_V + gi * 4096 + (lane >> 4) * 2048 + (8 * ((lane >> 3) & 1) + (lane & 7)) * 16;
-#pragma unroll
-                for (int dt = 0; dt < 8; dt++) {
-                    uint32_t a0, a1, a2, a3;
-                    ldmatrix_x4(a0, a1, a2, a3, vbase + dt * 256);
-#pragma unroll
-                    for (int nt = 0; nt < NT; nt++) mma_e4m3(oacc[nt][dt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+                if ((keep[0] & keep[1] & keep[2] & keep[3]) == 0xffffffffu) continue;
+                for (int d = lane; d < HEAD_DIM; d += 32) {
+                    uint4 *row = reinterpret_cast<uint4 *>(page + PAGE_V + blk * 2048 + d * 16);
+                    uint4 v = *row;
+                    v.x &= keep[0], v.y &= keep[1], v.z &= keep[2], v.w &= keep[3];
+                    *row = v;
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(empty + 8 * s);
         }
-        __syncwarp();
-    }
-    __syncthreads(); /* all staged-q reads are done; the merge area is free */
-
-    if (warp < CONSUMER_WARPS) {
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            const int h = 4 * nt + t;
-            float *mine = merge + (warp * 4 * NT + h) * PART;
-            const float lsum = head_sum(l[nt]);
-            if (g == 0) mine[0] = m[nt], mine[1] = lsum;
+        for (int gi = 0; gi < 2; gi++) { /* 32 positions at a time */
+            const int first = key0 + 32 * gi;
+            if (partial && (first >= sp.len || first + 32 <= sp.begin)) continue;
+            /* ---- scores: A = K rows (position 4 r + 2 mt [+ 1 for rows 8..15]), B = q ---- */
+            float sc[NT][2][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) sc[nt][mt][c] = 0.f;
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                const int row = 32 * gi + 4 * (lane & 7) + 2 * mt + ((lane >> 3) & 1);
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) {
+                    uint32_t a0, a1, a2, a3;
+                    const int c = 2 * ks + (lane >> 4);
+                    ldmatrix_x4(a0, a1, a2, a3, page_u + PAGE_K + row * HEAD_DIM + ((c ^ (lane & 7)) << 4));
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) mma_e4m3(sc[nt][mt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+                }
+            }
+            /* this lane: head t of each tile, positions first + 4 g + {0, 1, 2, 3} */
+            const float4 ks4 = *reinterpret_cast<const float4 *>(page + PAGE_KS + (32 * gi + 4 * g) * 4);
+            const float4 vs4 = *reinterpret_cast<const float4 *>(page + PAGE_VS + (32 * gi + 4 * g) * 4);
+            const float ksc[4] = {ks4.x, ks4.y, ks4.z, ks4.w}, vsc[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
+            bool valid[4];
+            float lv[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int pos = first + 4 * g + j;
+                valid[j] = !partial || (pos >= sp.begin && pos < sp.len);
+                lv[j] = fmaxf(lg2(vsc[j]), MIN_LOG2_VSCALE);
+            }
+            uint32_t pb[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                float x[4], top = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float raw = sc[nt][j >> 1][2 * (j & 1)] + sc[nt][j >> 1][2 * (j & 1) + 1] * (1.f / LO_SCALE);
+                    x[j] = raw * (ksc[j] * qfac[nt]);
+                    top = fmaxf(top, valid[j] ? x[j] + lv[j] : -INFINITY);
+                }
+                top = fmaxf(head_max(top), m[nt]);
+                if (__any_sync(0xffffffffu, top > m[nt])) { /* some head's maximum moved: rescale */
+                    const float c = m[nt] == -INFINITY ? 0.f : ex2(m[nt] - top);
+                    l[nt] *= c;
+#pragma unroll
+                    for (int dt = 0; dt < 8; dt++)
+#pragma unroll
+                        for (int e = 0; e < 4; e++) oacc[nt][dt][e] *= c;
+                    m[nt] = top;
+                }
+                float p[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const bool on = valid[j] && top != -INFINITY;
+                    const float e = on ? ex2(x[j] - top) : 0.f;
+                    l[nt] += e;
+                    p[j] = on ? e * (vsc[j] * P_SCALE) : 0.f;
+                }
+                uint32_t whi, wlo;
+                split4(p, whi, wlo);
+                /* C layout -> B layout: column g of positions 4 t .. 4 t + 3 (and + 16) lives in lane
+                 * 4 t + g / 2 (and + 16), first term if g is even */
+                const int src = 4 * t + (g >> 1);
+                const uint32_t h0 = __shfl_sync(0xffffffffu, whi, src), l0 = __shfl_sync(0xffffffffu, wlo, src);
+                const uint32_t h1 = __shfl_sync(0xffffffffu, whi, src + 16), l1 = __shfl_sync(0xffffffffu, wlo, src + 16);
+                pb[nt][0] = (g & 1) ? l0 : h0;
+                pb[nt][1] = (g & 1) ? l1 : h1;
+            }
+            /* ---- values: A = V^T rows (dim 16 dt + r), B = folded probabilities ---- */
+            const uint32_t vbase = page_u + PAGE_V + gi * 4096 + (lane >> 4) * 2048 + (8 * ((lane >> 3) & 1) + (lane & 7)) * 16;
 #pragma unroll
             for (int dt = 0; dt < 8; dt++) {
-                mine[4 + 16 * dt + g] = (oacc[nt][dt][0] + oacc[nt][dt][1] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
-                mine[4 + 16 * dt + g + 8] = (oacc[nt][dt][2] + oacc[nt][dt][3] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
+                uint32_t a0, a1, a2, a3;
+                ldmatrix_x4(a0, a1, a2, a3, vbase + dt * 256);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) mma_e4m3(oacc[nt][dt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
             }
+        }
+        __syncwarp(); /* every lane has read the stage */
+        if (lane == 0 && i + WARPS < n) {
+            /* order this warp's reads (and the masking writes) of the stage before the copy engine's writes */
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            page_load(page_u, pages + (size_t)(i + WARPS) * PAGE_BYTES, bar);
+        }
+    }
+    __syncthreads(); /* every warp is done with its stage and has no copy in flight: the ring becomes the merge area */
+
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int h = 4 * nt + t;
+        float *mine = merge + (warp * 4 * NT + h) * PART;
+        const float lsum = head_sum(l[nt]);
+        if (g == 0) mine[0] = m[nt], mine[1] = lsum;
+#pragma unroll
+        for (int dt = 0; dt < 8; dt++) {
+            mine[4 + 16 * dt + g] = (oacc[nt][dt][0] + oacc[nt][dt][1] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
+            mine[4 + 16 * dt + g + 8] = (oacc[nt][dt][2] + oacc[nt][dt][3] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
         }
     }
     __syncthreads();
-    if (tid < HEAD_DIM) { /* merge the four warps' states per head; thread = dim */
+    if (tid < HEAD_DIM) { /* merge the warps' states per head; thread = dim */
         for (int h = 0; h < G; h++) {
             float top = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; w++) top = fmaxf(top, merge[(w * 4 * NT + h) * PART]);
+            for (int w = 0; w < WARPS; w++) top = fmaxf(top, merge[(w * 4 * NT + h) * PART]);
             float lsum = 0.f, o = 0.f;
 #pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; w++) {
+            for (int w = 0; w < WARPS; w++) {
                 const float *st = merge + (w * 4 * NT + h) * PART;
                 const float c = st[0] == -INFINITY ? 0.f : ex2(st[0] - top);
                 lsum += c * st[1];
@@ -510,7 +472,7 @@ template <int NT> static cudaError_t prepare() { /* opt in to the large dynamic 
     cudaError_t rc = cudaGetDevice(&device);
     if (rc != cudaSuccess) return rc;
     if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
-    rc = cudaFuncSetAttribute(k_decode_attn<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem(NT));
+    rc = cudaFuncSetAttribute(k_decode_attn<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM);
     if (rc == cudaSuccess && device >= 0 && device < 64) done[device] = true;
     return rc;
 }
@@ -537,10 +499,10 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     const dim3 grid(max_chunks, Hkv, B);
     if (Hq / Hkv <= 4) {
         if (prepare<1>() != cudaSuccess) return NCB_ERR_LAUNCH;
-        k_decode_attn<1><<<grid, THREADS, attn_smem(1), stream>>>(a);
+        k_decode_attn<1><<<grid, THREADS, ATTN_SMEM, stream>>>(a);
     } else {
         if (prepare<2>() != cudaSuccess) return NCB_ERR_LAUNCH;
-        k_decode_attn<2><<<grid, THREADS, attn_smem(2), stream>>>(a);
+        k_decode_attn<2><<<grid, THREADS, ATTN_SMEM, stream>>>(a);
     }
     return cudaGetLastError() == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }

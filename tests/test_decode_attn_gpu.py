@@ -54,14 +54,16 @@ def run(case, max_len=None, window=0, chunk_pages=0, slots=None, n_slots=None, p
 
 
 def check(case, got, window=0, tight=True):
+    """The path's tolerance holds for outputs of magnitude <= 1 (every benchmark configuration); larger outputs
+    scale both bounds, since one bf16 rounding step at magnitude 16 already exceeds 2e-2."""
     want = oat.decode_attention(case["q"], case["k_bytes"], case["k_scale"], case["v_bytes"], case["v_scale"], SCALE,
                                 window=window)
     max_abs, mean_abs = helpers.error_stats(got, want)
     assert np.isfinite(max_abs), "non-finite output"
-    assert max_abs <= MAX_ABS and mean_abs <= MEAN_ABS, (max_abs, mean_abs)
+    ref = max(1.0, float(np.abs(okv.bf16_to_f32(want)).max()))
+    assert max_abs <= MAX_ABS * ref and mean_abs <= MEAN_ABS * ref, (max_abs, mean_abs, ref)
     if tight:
-        ref = max(1.0, float(np.abs(okv.bf16_to_f32(want)).max()))  # outputs above 1 scale the bound
-        assert max_abs <= TIGHT_MAX * ref and mean_abs <= TIGHT_MEAN * ref, (max_abs, mean_abs)
+        assert max_abs <= TIGHT_MAX * ref and mean_abs <= TIGHT_MEAN * ref, (max_abs, mean_abs, ref)
     return max_abs, mean_abs
 
 
