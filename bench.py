@@ -133,13 +133,11 @@ def time_cpu_reference(lens, budget_s: float, seed: int = 1234) -> dict:
     sample = cpu_sample(lens, seed)
     times = []
     deadline = time.perf_counter() + budget_s
-    for rep in range(1000):
+    while len(times) < 4 or time.perf_counter() < deadline:
         t0 = time.perf_counter()
         for q, k, v in sample:
             eager_attention_port(q, k, v, D ** -0.5)
         times.append(time.perf_counter() - t0)
-        if rep >= 3 and time.perf_counter() > deadline:
-            break
     warm = times[1:] if len(times) > 1 else times
     t = statistics.median(warm)
     return {"value": algorithmic_bytes(lens) / t / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
