@@ -35,6 +35,7 @@ extern "C" {
 #define NCB_PAGE_TOKENS 64
 #define NCB_PAGE_BYTES 16896
 #define NCB_PART_FLOATS 132 /* one partial attention state: m, l, 2 pad, o[128]; fp32 */
+#define NCB_STATIC_SCRATCH_BYTES (8u << 20) /* the built-in scratch of decode_attn_fp8_static */
 
 enum {
     NCB_OK = 0,
@@ -42,7 +43,8 @@ enum {
     NCB_ERR_ALIGN = 2,       /* a pointer or stride misses its required alignment */
     NCB_ERR_WORKSPACE = 3,   /* the workspace is smaller than decode_attn_workspace_bytes() */
     NCB_ERR_LAUNCH = 4,      /* the CUDA runtime refused the launch; see cudaGetLastError */
-    NCB_ERR_UNSUPPORTED = 5  /* Hq / Hkv above 8 */
+    NCB_ERR_UNSUPPORTED = 5, /* Hq / Hkv above 8 */
+    NCB_ERR_STATIC_LIMIT = 6 /* decode_attn_fp8_static: the call needs more than NCB_STATIC_SCRATCH_BYTES */
 };
 
 /* Bits a kernel ORs into the caller's optional device status word (int32, may be NULL). */
@@ -126,6 +128,27 @@ int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens,
                           void *workspace, long long workspace_bytes, int B, int Hq, int Hkv, int n_slots,
                           int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale,
                           void *status, void *stream);
+
+/*
+ * decode_attn_fp8 for callers that cannot hand over a workspace because they cannot allocate device memory at
+ * all: code running inside someone else's memory plan (a serving engine that gives a plug-in only its input and
+ * output tensors), hosts that forbid cudaMalloc after start-up, or a thin FFI shim with no allocator behind it.
+ * No counterpart in the reference, whose decoder allocates all of its own buffers up front in dec_create.
+ *
+ * Same arguments and results as decode_attn_fp8 minus the workspace: the per-chunk states go to an array built
+ * into the library, NCB_STATIC_SCRATCH_BYTES (8 MiB) of device memory that every GPU loading decode_attn holds
+ * until the process exits. A call whose states need more (decode_attn_workspace_bytes() for the same B, Hq,
+ * max_kv_len, Hkv, chunk_pages) is refused with NCB_ERR_STATIC_LIMIT; pass a larger chunk_pages to shrink the need.
+ * The entry point itself calls no cudaMalloc, cudaFree or any other allocating routine.
+ *
+ * The first call on each device looks up the array's device address (with that device current) and remembers it;
+ * make that first call outside any stream capture. Every call on a device shares the one array: calls must be
+ * stream-ordered with respect to each other, since two that overlap on the GPU would overwrite each other's
+ * states. Nothing in the array has to start at zero; each call writes every state it later reads.
+ */
+int decode_attn_fp8_static(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *out,
+                           int B, int Hq, int Hkv, int n_slots, int pages_per_slot, int max_kv_len, int window,
+                           int chunk_pages, float softmax_scale, void *status, void *stream);
 
 /*
  * Merge n_parts states per row: parts fp32 [n_parts][rows][NCB_PART_FLOATS] (e.g. the all-gathered part_out of

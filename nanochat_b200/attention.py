@@ -86,6 +86,28 @@ def decode_attention(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int
     return out
 
 
+def decode_attention_static(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int,
+                            slot_map: Tensor | None = None, window: int = 0, chunk_pages: int = 0,
+                            softmax_scale: float | None = None, out: Tensor | None = None,
+                            status: Tensor | None = None) -> Tensor:
+    """decode_attention for callers that may not allocate device memory: the per-chunk states live in 8 MiB built
+    into the library instead of a workspace tensor (pass `out`, and nothing here allocates). Raises NativeError
+    (status 6) when the call would need more. Calls on one device share that memory, so keep them stream-ordered;
+    make the first call on a device outside CUDA-graph capture."""
+    B, Hq = q.shape[0], q.shape[1]
+    assert q.dtype == torch.bfloat16 and q.is_contiguous() and q.shape[2] == HEAD_DIM
+    assert lens.dtype == torch.int32 and lens.shape == (B,) and lens.is_contiguous()
+    assert slot_map is None or (slot_map.dtype == torch.int32 and slot_map.shape == (B,))
+    if out is None:
+        out = torch.empty_like(q)
+    scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
+    rc = cuda_library("decode_attn").decode_attn_fp8_static(
+        pointer(q), pointer(cache.pages), pointer(lens), pointer(slot_map), pointer(out), B, Hq, cache.kv_heads,
+        cache.n_slots, cache.pages_per_slot, max_kv_len, window, chunk_pages, scale, pointer(status), stream())
+    check(rc, "decode_attn_fp8_static")
+    return out
+
+
 def decode_attention_partial(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int,
                              slot_map: Tensor | None = None, window: int = 0, chunk_pages: int = 0,
                              softmax_scale: float | None = None, workspace: Tensor | None = None,

@@ -32,6 +32,8 @@
  * NCB_DEV_WAIT_TIMEOUT in the caller's status word, waits once more (bounded again) for its copy in flight, stops
  * consuming and falls through to the block's final barriers.
  */
+#include <mutex>
+
 #include "ncb_common.cuh"
 
 constexpr int WARPS = 6; /* = stages per block; 6 x 16,896 B x 2 blocks fit one SM's shared memory */
@@ -533,6 +535,28 @@ static int attend(const void *q, const void *kv_cache, const void *lens, const v
     return launch_merge(m, (cudaStream_t)stream);
 }
 
+/* ---- built-in scratch for callers that cannot allocate ------------------------------------------------------- */
+
+/* The per-chunk states of decode_attn_fp8_static. In host code this name is only a handle for
+ * cudaGetSymbolAddress; the kernels get the device address that call returns. */
+static __device__ __align__(256) unsigned char g_static_scratch[NCB_STATIC_SCRATCH_BYTES];
+
+/* The array's address on the current device, looked up once per device. */
+static int static_scratch(void **ptr) {
+    static std::mutex lock;
+    static void *address[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return NCB_ERR_LAUNCH;
+    std::lock_guard<std::mutex> guard(lock);
+    if (!address[device]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return NCB_ERR_LAUNCH;
+        address[device] = p;
+    }
+    *ptr = address[device];
+    return NCB_OK;
+}
+
 extern "C" {
 
 int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len) {
@@ -566,6 +590,22 @@ int decode_attn_fp8_partial(const void *q, const void *kv_cache, const void *len
                             float softmax_scale, void *status, void *stream) {
     if (!part_out && B > 0) return NCB_ERR_ARG;
     return attend(q, kv_cache, lens, slot_map, workspace, workspace_bytes, nullptr, part_out, B, Hq, Hkv, n_slots,
+                  pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream);
+}
+
+int decode_attn_fp8_static(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *out,
+                           int B, int Hq, int Hkv, int n_slots, int pages_per_slot, int max_kv_len, int window,
+                           int chunk_pages, float softmax_scale, void *status, void *stream) {
+    if (!out && B > 0) return NCB_ERR_ARG;
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || pages_per_slot <= 0 || max_kv_len < 0 || chunk_pages < 0) return NCB_ERR_ARG;
+    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
+    if (chunk_pages == 0) chunk_pages = decode_attn_chunk_pages(B, Hkv, max_kv_len);
+    const long long need = decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages);
+    if (need > (long long)NCB_STATIC_SCRATCH_BYTES) return NCB_ERR_STATIC_LIMIT;
+    void *scratch = nullptr;
+    const int rc = static_scratch(&scratch);
+    if (rc != NCB_OK) return rc;
+    return attend(q, kv_cache, lens, slot_map, scratch, NCB_STATIC_SCRATCH_BYTES, out, nullptr, B, Hq, Hkv, n_slots,
                   pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream);
 }
 

@@ -37,12 +37,13 @@ SIGNATURES = {
         "decode_attn_workspace_bytes": ([c_int, c_int, c_int, c_int, c_int], c_ll),
         "decode_attn_fp8": ([c_ptr] * 5 + [c_ll, c_ptr] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_fp8_partial": ([c_ptr] * 5 + [c_ll, c_ptr] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
+        "decode_attn_fp8_static": ([c_ptr] * 5 + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_fp8_split": ([c_ptr] * 5 + [c_ll] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_merge": ([c_ptr, c_int, c_ll, c_ptr, c_ptr], c_int),
     },
 }
 STATUS = {0: "ok", 1: "invalid argument", 2: "misaligned pointer or stride", 3: "workspace too small",
-          4: "kernel launch failed", 5: "unsupported head ratio"}
+          4: "kernel launch failed", 5: "unsupported head ratio", 6: "needs more than the built-in scratch"}
 
 
 class NativeError(RuntimeError):
