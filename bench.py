@@ -212,6 +212,7 @@ def main() -> None:
     ap.add_argument("--cpu-sample", type=int, default=4, help="sequences in the CPU baseline's sample")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--chunk-pages", type=int, default=0)
+    ap.add_argument("--e2e-steps", type=int, default=200, help="steps of the end-to-end loop (profiling runs shrink it)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -237,7 +238,7 @@ def main() -> None:
     mine = shard_batch(lens_all, world)[rank]
     lens = [lens_all[i] for i in mine]
     B = len(lens)
-    e2e_steps = min(args.steps, 200)
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
     headroom = args.warmup + e2e_steps + 8
     max_len = max(lens) + headroom
     cache = synthetic_cache(lens, max_len, seed=1000 + rank, device=device)
@@ -345,7 +346,7 @@ def main() -> None:
                          "us_per_launch": ms_split / args.steps * 1e3,
                          "algorithmic_bytes_per_launch": algorithmic_bytes(lens)},
         }
-        if world == 1:
+        if world == 1 and args.cpu_seconds > 0:
             line["cpu_baseline"] = time_cpu_reference(lens[:args.cpu_sample], args.cpu_seconds)
         print(json.dumps(line))
     if world > 1:
