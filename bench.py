@@ -285,35 +285,23 @@ def main() -> None:
         ms_total = timed(step, args.steps, args.warmup)
     ms_split = timed(split, args.steps, 3)
 
-    # ---- end to end through the public operators with host buffers
+    # ---- end to end through the public step object with host buffers
     cos, sin = ncb.rotary_table(max_len, 1e4, device=device)
     ones = torch.ones(D, device=device)
     host_gen = torch.Generator().manual_seed(3000 + rank)
-    qkv_host = torch.randn(B, (HQ + 2 * HKV) * D, generator=host_gen).bfloat16().pin_memory()
-    pos_host = torch.tensor(lens, dtype=torch.int32).pin_memory()
-    out_host = torch.empty(B, HQ, D, dtype=torch.bfloat16).pin_memory()
-    qkv_dev, pos_dev, len_dev = torch.empty_like(qkv_host, device=device), torch.empty_like(pos_host, device=device), \
-        torch.empty_like(pos_host, device=device)
-    q_dev = torch.empty(B, HQ, D, dtype=torch.bfloat16, device=device)
-    e2e_bytes = 0
+    decode = ncb.DecodeStep(cache, HQ, cos, sin, ones, ones, B, chunk_pages=chunk)
+    decode.qkv_host.copy_(torch.randn(decode.qkv_host.shape, generator=host_gen).bfloat16())
+    decode.pos_host.copy_(torch.tensor(lens, dtype=torch.int32))
 
     def e2e_step():
-        nonlocal e2e_bytes
-        qkv_dev.copy_(qkv_host, non_blocking=True)
-        pos_dev.copy_(pos_host, non_blocking=True)
-        ncb.kv_append(qkv_dev, ones, ones, cos, sin, pos_dev, cache, HQ, q_out=q_dev, status=status)
-        torch.add(pos_dev, 1, out=len_dev)
-        top = int(pos_host.max()) + 1
-        ncb.decode_attention(q_dev, cache, len_dev, top, chunk_pages=chunk, workspace=workspace, out=out, status=status)
-        out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        e2e_bytes += algorithmic_bytes((pos_host + 1).tolist())
-        pos_host.add_(1)  # the next step's token goes one position further
+        decode.run()  # pinned host in, graph replay (copies, kv_append_fp8, decode_attn_fp8), pinned host out, sync
+        decode.pos_host.add_(1)  # the next step's token goes one position further
 
     for _ in range(args.warmup):
         e2e_step()
     barrier()
-    e2e_bytes = 0
+    # every timed step attends one position more than the one before
+    e2e_bytes = sum(algorithmic_bytes([n + args.warmup + k + 1 for n in lens]) for k in range(e2e_steps))
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         e2e_step()
@@ -327,6 +315,7 @@ def main() -> None:
         dist.all_reduce(total_e2e_bytes)
         dist.all_reduce(total_bytes)
     assert status.item() == 0, f"device status {status.item()}"
+    decode.check()
 
     if rank == 0:
         peak, peak_kind = peaks()
@@ -340,11 +329,12 @@ def main() -> None:
             "config": config_of(args, world, extra={"chunk_pages": chunk, "pct_of_8TBs_per_gpu": value / world / 80.0}),
             "clocks": clocks.summary(),
             "e2e": {"value": float(total_e2e_bytes.item()) / float(e2e_s.item()) / 1e9, "unit": UNIT,
-                    "h2d_bytes_per_step": qkv_host.numel() * 2 + pos_host.numel() * 4,
-                    "d2h_bytes_per_step": out_host.numel() * 2, "steps": e2e_steps,
+                    "h2d_bytes_per_step": decode.h2d_bytes,
+                    "d2h_bytes_per_step": decode.d2h_bytes, "steps": e2e_steps,
                     "ms_per_step": float(e2e_s.item()) / e2e_steps * 1e3,
-                    "what": "pinned-host qkv row + positions in, kv_append_fp8 + decode_attn_fp8, output to pinned host, "
-                            "synchronised every step; the KV cache is resident decoder state"},
+                    "what": "DecodeStep.run(): pinned-host qkv rows + positions in, kv_append_fp8 + decode_attn_fp8 "
+                            "(one CUDA graph), output to pinned host, synchronised every step; the KV cache is "
+                            "resident decoder state"},
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "k_decode_attn<1> (split-KV)", "achieved": split_gbs, "peak": peak,
                          "unit": UNIT, "frac": split_gbs / peak, "peak_kind": peak_kind, "traffic": None,

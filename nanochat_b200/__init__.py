@@ -5,6 +5,7 @@ from .attention import (decode_attention, decode_attention_partial, kv_append, m
                         workspace_bytes)
 from .kv_cache import Fp8KVCache
 from .native import NativeError, build_library, cuda_library
+from .step import DecodeStep
 
-__all__ = ["Fp8KVCache", "NativeError", "build_library", "cuda_library", "decode_attention",
+__all__ = ["DecodeStep", "Fp8KVCache", "NativeError", "build_library", "cuda_library", "decode_attention",
            "decode_attention_partial", "kv_append", "merge_partials", "rotary_table", "workspace_bytes"]

@@ -363,6 +363,8 @@ __global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
             page_load(page_u, pages + (size_t)(i + WARPS) * PAGE_BYTES, bar);
         }
     }
+    /* the merge kernel may start occupying free SM resources now; it still waits for this grid to finish */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __syncthreads(); /* every warp is done with its stage and has no copy in flight: the ring becomes the merge area */
 
 #pragma unroll
@@ -415,6 +417,9 @@ constexpr int MERGE_WARPS = 4;
 __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
     const long long row = (long long)blockIdx.x * MERGE_WARPS + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    /* launched with programmatic stream serialisation: wait here until the grid before it (the split kernel, whose
+     * states this reads) has completed and its writes are visible; a no-op after an ordinary launch */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (row >= a.rows) return;
     int n = a.n_parts;
     if (n == 0) {
@@ -513,8 +518,16 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
     if (a.rows == 0) return NCB_OK;
     const long long blocks = (a.rows + MERGE_WARPS - 1) / MERGE_WARPS;
     if (blocks > 0x7fffffffLL) return NCB_ERR_ARG;
-    k_merge<<<(unsigned)blocks, MERGE_WARPS * 32, 0, stream>>>(a);
-    return cudaGetLastError() == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)blocks);
+    config.blockDim = dim3(MERGE_WARPS * 32);
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1; /* overlap its launch with the split kernel's tail */
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, k_merge, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 static int attend(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,

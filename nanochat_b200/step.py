@@ -1,0 +1,88 @@
+"""One decode step of the attention path for a fixed set of slots, captured once as a CUDA graph and replayed.
+
+The reference runs its whole step as captured graphs launched from Python through one ctypes call
+(model/kernels/decode.cu:848-902,1000-1016,1107-1110; inference/decoder.py:285) because at decode sizes the step is
+bound by launch latency, not by kernels. This is the same idea for the part of the step this package owns:
+
+    pinned host qkv rows + positions --copy--> device --kv_append_fp8--> cache, q --decode_attn_fp8--> out
+    --copy--> pinned host
+
+The caller writes `qkv_host` and `pos_host`, calls run(), and reads `out_host`. Sequence lengths are pos + 1 (the
+new token is attended through the cache). The graph is sized for the cache's capacity, so it stays valid as the
+sequences grow."""
+
+import torch
+from torch import Tensor
+
+from . import attention as ops
+from .kv_cache import HEAD_DIM, Fp8KVCache
+
+
+class DecodeStep:
+    def __init__(self, cache: Fp8KVCache, Hq: int, cos: Tensor, sin: Tensor, q_gain: Tensor, k_gain: Tensor,
+                 batch: int, slot_map: Tensor | None = None, window: int = 0, chunk_pages: int = 0,
+                 softmax_scale: float | None = None, max_kv_len: int | None = None):
+        dev, Hkv = cache.device, cache.kv_heads
+        self.cache, self.Hq, self.batch = cache, Hq, batch
+        self.cos, self.sin, self.q_gain, self.k_gain = cos, sin, q_gain, k_gain
+        self.slot_map, self.window, self.softmax_scale = slot_map, window, softmax_scale
+        self.max_kv_len = min(max_kv_len or cache.capacity, cache.capacity)
+        self.chunk_pages = chunk_pages or ops.chunk_pages_for(batch, Hkv, self.max_kv_len)
+        width = (Hq + 2 * Hkv) * HEAD_DIM
+        self.qkv_host = torch.zeros((batch, width), dtype=torch.bfloat16).pin_memory()
+        self.pos_host = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        self.out_host = torch.zeros((batch, Hq, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
+        self.qkv = torch.empty((batch, width), dtype=torch.bfloat16, device=dev)
+        self.pos = torch.empty(batch, dtype=torch.int32, device=dev)
+        self.lens = torch.empty(batch, dtype=torch.int32, device=dev)
+        self.q = torch.empty((batch, Hq, HEAD_DIM), dtype=torch.bfloat16, device=dev)
+        self.out = torch.empty((batch, Hq, HEAD_DIM), dtype=torch.bfloat16, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        need = ops.workspace_bytes(batch, Hq, Hkv, self.max_kv_len, self.chunk_pages)
+        self.workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        self.stream = torch.cuda.Stream(dev)
+        self.graph: torch.cuda.CUDAGraph | None = None
+
+    @property
+    def h2d_bytes(self) -> int:
+        return self.qkv_host.numel() * 2 + self.pos_host.numel() * 4
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self.out_host.numel() * 2
+
+    def _enqueue(self) -> None:
+        self.qkv.copy_(self.qkv_host, non_blocking=True)
+        self.pos.copy_(self.pos_host, non_blocking=True)
+        ops.kv_append(self.qkv, self.q_gain, self.k_gain, self.cos, self.sin, self.pos, self.cache, self.Hq,
+                      slot_map=self.slot_map, q_out=self.q, status=self.status)
+        torch.add(self.pos, 1, out=self.lens)
+        ops.decode_attention(self.q, self.cache, self.lens, self.max_kv_len, slot_map=self.slot_map,
+                             window=self.window, chunk_pages=self.chunk_pages, softmax_scale=self.softmax_scale,
+                             workspace=self.workspace, out=self.out, status=self.status)
+        self.out_host.copy_(self.out, non_blocking=True)
+
+    def capture(self) -> None:
+        """Run the step once eagerly (first-use set-up must happen outside capture; the token it appends is
+        overwritten by the next run at the same position) and capture it."""
+        self.stream.wait_stream(torch.cuda.current_stream(self.cache.device))
+        with torch.cuda.stream(self.stream):
+            self._enqueue()
+            self.stream.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.stream):
+                self._enqueue()
+
+    def run(self) -> None:
+        """Append the tokens in qkv_host at pos_host and attend; out_host holds the result on return."""
+        if self.graph is None:
+            self.capture()
+        with torch.cuda.stream(self.stream):
+            self.graph.replay()
+        self.stream.synchronize()
+
+    def check(self) -> None:
+        """Raise if a kernel flagged a bad position / length or a wait that ran out (reads the device word)."""
+        code = int(self.status.item())
+        if code:
+            raise RuntimeError(f"device status {code:#x} (NCB_DEV_* bits)")

@@ -197,3 +197,29 @@ def test_append_then_attend():
     for key in logical:
         case[key] = [np.stack(logical[key][b], axis=1) for b in range(B)]
     check(case, helpers.bf16_bits(out.cpu()))
+
+
+def test_decode_step_graph_matches_eager_operators():
+    """DecodeStep (copies + append + attention as one CUDA graph, pinned host buffers) against the same operators
+    called one by one, over several steps of a growing ragged batch."""
+    gen = torch.Generator().manual_seed(1200)
+    Hq, Hkv, lens = 8, 2, [130, 5, 64]
+    B = len(lens)
+    case = helpers.attention_case(1201, Hq, Hkv, lens)
+    cos, sin = ncb.rotary_table(256, 1e4, device="cuda")
+    gain = (1 + 0.1 * torch.randn(128, generator=gen)).cuda()
+    caches = [load_cache(case, 256) for _ in range(2)]
+    step = ncb.DecodeStep(caches[0], Hq, cos, sin, gain, gain, B)
+    pos = torch.tensor(lens, dtype=torch.int32)
+    for _ in range(4):
+        qkv = torch.randn(B, (Hq + 2 * Hkv) * 128, generator=gen).bfloat16()
+        step.qkv_host.copy_(qkv)
+        step.pos_host.copy_(pos)
+        step.run()
+        q = ncb.kv_append(qkv.cuda(), gain, gain, cos, sin, pos.cuda(), caches[1], Hq)
+        want = ncb.decode_attention(q, caches[1], (pos + 1).cuda(), max_kv_len=int(pos.max()) + 1)
+        torch.cuda.synchronize()
+        assert torch.equal(step.out_host, want.cpu())
+        pos += 1
+    step.check()
+    assert torch.equal(caches[0].pages, caches[1].pages)
