@@ -161,6 +161,39 @@ def synthetic_cache(lens, max_len: int, seed: int, device):
     return cache
 
 
+def bench_longctx(rank: int, world: int, device, steps: int, warmup: int, timed) -> dict:
+    """Long-context decode attention: batch 4, Hq 32, Hkv 8, 131,072 positions per sequence. With N > 1 ranks every
+    sequence's positions are cut into N page-aligned slices; each rank attends over its slice, the un-normalised
+    (m, l, o) states are all-gathered over NCCL and merged locally. Total work is fixed (strong scaling)."""
+    import nanochat_b200 as ncb
+    from nanochat_b200 import sharding
+
+    B, N = 4, 131072
+    begin, end = sharding.kv_slices(N, world)[rank]
+    n_local = end - begin
+    cache = synthetic_cache([n_local] * B, max(n_local, 1), seed=5000 + rank, device=device)
+    gen = torch.Generator(device=device).manual_seed(6000)  # q is replicated: same seed on every rank
+    q = torch.randn(B, HQ, D, generator=gen, device=device).bfloat16()
+    lens_t = torch.full((B,), n_local, dtype=torch.int32, device=device)
+    chunk = ncb.attention.chunk_pages_for(B, HKV, max(n_local, 1))
+    workspace = torch.empty(max(16, ncb.workspace_bytes(B, HQ, HKV, max(n_local, 1), chunk)), dtype=torch.uint8,
+                            device=device)
+    if world == 1:
+        out = torch.empty_like(q)
+        step = lambda: ncb.decode_attention(q, cache, lens_t, n_local, chunk_pages=chunk, workspace=workspace, out=out)
+    else:
+        part = torch.empty((B, HQ, 132), dtype=torch.float32, device=device)
+        step = lambda: sharding.attend_kv_sharded(q, cache, lens_t, max(n_local, 1), chunk_pages=chunk,
+                                                  workspace=workspace, part=part)
+    ms = timed(step, steps, warmup)
+    total = algorithmic_bytes([N] * B)
+    return {"workload": "batch 4, Hq 32, Hkv 8, head_dim 128, 131072 positions per sequence, KV split by length over "
+                        f"{world} GPU(s)", "value": total * steps / (ms * 1e-3) / 1e9, "unit": UNIT,
+            "ms_per_step": ms / steps, "steps": steps, "scaling": "strong", "chunk_pages": chunk,
+            "collective": None if world == 1 else "all_gather_into_tensor of fp32 [4][32][132] per rank (NCCL), "
+                                                  "then decode_attn_merge on every rank"}
+
+
 def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
@@ -212,6 +245,7 @@ def main() -> None:
     ap.add_argument("--cpu-sample", type=int, default=4, help="sequences in the CPU baseline's sample")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--chunk-pages", type=int, default=0)
+    ap.add_argument("--longctx", type=int, default=1, help="also time the KV-length-sharded long-context case (0: skip)")
     ap.add_argument("--e2e-steps", type=int, default=200, help="steps of the end-to-end loop (profiling runs shrink it)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -316,6 +350,8 @@ def main() -> None:
         dist.all_reduce(total_bytes)
     assert status.item() == 0, f"device status {status.item()}"
     decode.check()
+    del cache, decode, workspace
+    longctx = bench_longctx(rank, world, device, min(args.steps, 100), 5, timed) if args.longctx else None
 
     if rank == 0:
         peak, peak_kind = peaks()
@@ -341,6 +377,8 @@ def main() -> None:
                          "us_per_launch": ms_split / args.steps * 1e3,
                          "algorithmic_bytes_per_launch": algorithmic_bytes(lens)},
         }
+        if longctx:
+            line["longctx"] = longctx
         if world == 1 and args.cpu_seconds > 0:
             line["cpu_baseline"] = time_cpu_reference(lens[:args.cpu_sample], args.cpu_seconds)
         print(json.dumps(line))

@@ -574,10 +574,11 @@ extern "C" {
 
 int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len) {
     if (B <= 0 || Hkv <= 0 || max_kv_len <= 0) return 1;
-    /* aim at about eight blocks per resident slot (2 per SM) when every sequence is max_kv_len long */
+    /* aim at about eight blocks per resident slot (2 per SM) when every sequence is max_kv_len long; small problems
+     * get one page per warp (WARPS pages per block) or, below one block per slot, as many blocks as there are pages */
     const long long total = (long long)B * Hkv * pages_of(max_kv_len), slots = 2LL * sm_count();
     long long c = total / (8 * slots);
-    if (c < 1) c = 1;
+    if (c < WARPS) c = min((long long)WARPS, max(1LL, total / slots));
     if (c > 64) c = 64;
     return (int)c;
 }

@@ -60,9 +60,9 @@ def append_owner(position: int, slices: Sequence[tuple[int, int]]) -> int:
 def gather_states(part: Tensor, group: "dist.ProcessGroup | None" = None) -> Tensor:
     """part fp32 (B, Hq, 132) of this rank -> (world, B, Hq, 132) of every rank, in rank order. One collective."""
     world = dist.get_world_size(group)
-    out = torch.empty((world, *part.shape), dtype=part.dtype, device=part.device)
-    dist.all_gather_into_tensor(out, part.contiguous(), group=group)
-    return out
+    out = torch.empty((world * part.shape[0], *part.shape[1:]), dtype=part.dtype, device=part.device)
+    dist.all_gather_into_tensor(out, part.contiguous(), group=group)  # concatenated along dim 0 in rank order
+    return out.view(world, *part.shape)
 
 
 def attend_kv_sharded(q: Tensor, cache, local_lens: Tensor, max_local_len: int,

@@ -1,0 +1,105 @@
+"""Host-side partitioning logic and the N > 1 gather path on CPU ranks (gloo, world size 2)."""
+
+import math
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from nanochat_b200 import sharding
+from oracle import attention as oat
+from oracle import kv_append as okv
+from tests import helpers
+
+
+def test_shard_batch_partitions_and_balances():
+    gen = torch.Generator().manual_seed(0)
+    lens = torch.randint(512, 16385, (64,), generator=gen).tolist()
+    for world in (1, 2, 4, 8):
+        shards = sharding.shard_batch(lens, world)
+        assert sorted(i for s in shards for i in s) == list(range(64))
+        loads = [sum(lens[i] for i in s) for s in shards]
+        assert max(loads) - min(loads) <= max(lens)  # the LPT bound
+        assert max(loads) <= 1.05 * sum(lens) / world
+    assert sharding.shard_batch([], 3) == [[], [], []]
+    assert sharding.shard_batch([5, 5, 5], 2) == [[0, 2], [1]]
+
+
+def test_kv_slices_cover_contiguously_on_page_boundaries():
+    for n in (0, 1, 63, 64, 65, 1000, 131072, 131073):
+        for world in (1, 2, 3, 8):
+            slices = sharding.kv_slices(n, world)
+            assert len(slices) == world and slices[0][0] == 0 and slices[-1][1] == n
+            for (a, b), (c, d) in zip(slices[:-1], slices[1:]):
+                assert b == c and a <= b
+                assert b % 64 == 0 or b == n
+            pages = [math.ceil((b - a) / 64) for a, b in slices]
+            assert max(pages) - min(pages) <= 1
+
+
+def test_append_owner():
+    slices = sharding.kv_slices(1000, 4)  # 16 pages: 4 each -> [0,256) [256,512) [512,768) [768,1000)
+    assert sharding.append_owner(1000, slices) == 3   # the tail grows in the last rank's slice
+    assert sharding.append_owner(300, slices) == 1
+    assert sharding.append_owner(0, sharding.kv_slices(0, 4)) == 0
+
+
+def state_tensor(state) -> torch.Tensor:
+    """(m natural-log, l, o) -> fp32 (Hq, 132) in the kernels' layout: m in log2 units, l, 0, 0, o[128]."""
+    m, l, o = state
+    out = np.zeros((m.shape[0], 132), dtype=np.float32)
+    out[:, 0] = m / math.log(2.0)
+    out[:, 1] = l
+    out[:, 4:] = o
+    return torch.from_numpy(out)
+
+
+def merge_tensor(parts: torch.Tensor) -> np.ndarray:
+    """CPU restatement of decode_attn_merge over (n_parts, rows, 132) -> (rows, 128) float64."""
+    p = parts.double().numpy()
+    m, l, o = p[..., 0], p[..., 1], p[..., 4:]
+    top = m.max(0)
+    w = np.where(np.isfinite(m), np.exp2(m - np.where(np.isfinite(top), top, 0.0)), 0.0)
+    den = (w * l).sum(0)
+    return np.where(den[:, None] > 0, (w[..., None] * o).sum(0) / np.where(den > 0, den, 1.0)[:, None], 0.0)
+
+
+def worker(rank: int, world: int, port: int, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        Hq, Hkv, lens = 8, 2, [700, 64, 129]
+        case = helpers.attention_case(77, Hq, Hkv, lens)  # same seed on every rank: q is replicated
+        rows = []
+        for b, n in enumerate(lens):
+            a, e = sharding.kv_slices(n, world)[rank]
+            k = oat.dequant(case["k_bytes"][b][:, a:e], case["k_scale"][b][:, a:e])
+            v = oat.dequant(case["v_bytes"][b][:, a:e], case["v_scale"][b][:, a:e])
+            q = okv.bf16_to_f32(case["q"][b]).astype(np.float64)
+            rows.append(state_tensor(oat.attention_state(q, k, v, 128 ** -0.5)))
+        part = torch.stack(rows)  # (B, Hq, 132), this rank's slice only
+        gathered = sharding.gather_states(part)
+        assert gathered.shape == (world, len(lens), Hq, 132)
+        assert torch.equal(gathered[rank], part)
+        merged = merge_tensor(gathered.reshape(world, -1, 132)).reshape(len(lens), Hq, 128)
+        want = okv.bf16_to_f32(oat.decode_attention(case["q"], case["k_bytes"], case["k_scale"], case["v_bytes"],
+                                                    case["v_scale"], 128 ** -0.5))
+        err = float(np.abs(merged - want).max())
+        if rank == 0:
+            result.put(err)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_and_merge_over_two_gloo_ranks():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    mp.spawn(worker, args=(2, port, result), nprocs=2, join=True)
+    assert result.get(timeout=10) < 4e-3  # only the bf16 rounding of the reference output remains
