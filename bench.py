@@ -350,6 +350,7 @@ def main() -> None:
         dist.all_reduce(total_bytes)
     assert status.item() == 0, f"device status {status.item()}"
     decode.check()
+    h2d_bytes, d2h_bytes = decode.h2d_bytes, decode.d2h_bytes
     del cache, decode, workspace
     longctx = bench_longctx(rank, world, device, min(args.steps, 100), 5, timed) if args.longctx else None
 
@@ -365,8 +366,8 @@ def main() -> None:
             "config": config_of(args, world, extra={"chunk_pages": chunk, "pct_of_8TBs_per_gpu": value / world / 80.0}),
             "clocks": clocks.summary(),
             "e2e": {"value": float(total_e2e_bytes.item()) / float(e2e_s.item()) / 1e9, "unit": UNIT,
-                    "h2d_bytes_per_step": decode.h2d_bytes,
-                    "d2h_bytes_per_step": decode.d2h_bytes, "steps": e2e_steps,
+                    "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps,
                     "ms_per_step": float(e2e_s.item()) / e2e_steps * 1e3,
                     "what": "DecodeStep.run(): pinned-host qkv rows + positions in, kv_append_fp8 + decode_attn_fp8 "
                             "(one CUDA graph), output to pinned host, synchronised every step; the KV cache is "
