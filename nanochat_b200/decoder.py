@@ -1,0 +1,212 @@
+"""The decode step around the fp8 attention path: a greedy decoder for nanochat-shaped models.
+
+Stands where the reference's NativeDecoder / decode.cu step graph stands (inference/decoder.py:123-324;
+model/kernels/decode.cu:848-891): per layer
+    norm -> qkv GEMM -> [kv_append_fp8 -> decode_attn_fp8] -> o GEMM + residual -> norm -> up GEMM, relu^2 ->
+    down GEMM + residual
+then the final norm, the lm_head GEMM and an argmax. The bracketed part is this package's kernels; the GEMMs are
+plain library GEMMs (torch.matmul -> cuBLAS) and the norms/activations are torch operators in this first cut —
+the reference's own GEMM kernel is Hopper-only wgmma (decode.cu:232-359) and has to be replaced either way. The
+whole step is captured in one CUDA graph per batch size, the reference's remedy for launch-bound decode steps.
+
+Model semantics follow the reference's exported model (inference/modeling_nanochat.py:113-195): parameter-free RMS
+norm with eps FLT_EPSILON, h = x0 = norm(embed), per layer h = resid_lambda h + x0_lambda x0 (fp32, rounded once),
+QK-norm with per-dimension gains + the "-theta, split halves" rotary, relu^2 MLP, fp32 logits from the bf16 head.
+Value embeddings, sliding windows and the logit cap are not part of the benchmark configurations; windows are
+supported per layer, the cap (monotone) does not change a greedy choice (decode.cu:195).
+
+Prefill runs prompt tokens as rows through the same kernels, every row attending to the positions up to its own
+(decode.cu:859-863,1041-1051; inference/decoder.py:211-222); the prompt's last token is the first decode step's
+input (decoder.py:196,207,215)."""
+
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from . import attention as ops
+from .kv_cache import HEAD_DIM, Fp8KVCache
+
+EPS = 1.1920928955078125e-07  # FLT_EPSILON (reference model/ops/linear.py:20)
+
+
+@dataclass
+class DecoderConfig:
+    n_layers: int
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    intermediate: int
+    vocab: int
+    rope_theta: float = 10000.0
+    max_len: int = 1024
+    windows: list[int] = field(default_factory=list)  # per layer, 0 = full attention
+
+    @property
+    def qkv_width(self) -> int:
+        return (self.n_heads + 2 * self.n_kv_heads) * HEAD_DIM
+
+
+@dataclass
+class LayerWeights:
+    wqkv: Tensor   # bf16 [(Hq + 2 Hkv) 128, C]: q heads, k heads, v heads
+    wo: Tensor     # bf16 [C, Hq 128]
+    wup: Tensor    # bf16 [F, C]
+    wdown: Tensor  # bf16 [C, F]
+    q_gain: Tensor  # fp32 [128]
+    k_gain: Tensor  # fp32 [128]
+    resid_lambda: float = 1.0
+    x0_lambda: float = 0.0
+
+
+@dataclass
+class DecoderWeights:
+    embed: Tensor    # bf16 [V, C]
+    lm_head: Tensor  # bf16 [V, C]
+    layers: list[LayerWeights]
+
+    @staticmethod
+    def random_init(cfg: DecoderConfig, seed: int, device: "torch.device | str", std: float = 0.02) -> "DecoderWeights":
+        """bf16 weights drawn from N(0, std) on the CPU generator (identical on every machine), gains = 1."""
+        gen = torch.Generator().manual_seed(seed)
+        C, Fdim = cfg.hidden, cfg.intermediate
+
+        def w(*shape):
+            return (torch.randn(*shape, generator=gen) * std).bfloat16().to(device)
+
+        layers = [LayerWeights(w(cfg.qkv_width, C), w(C, cfg.n_heads * HEAD_DIM), w(Fdim, C), w(C, Fdim),
+                               torch.ones(HEAD_DIM, device=device), torch.ones(HEAD_DIM, device=device))
+                  for _ in range(cfg.n_layers)]
+        return DecoderWeights(w(cfg.vocab, C), w(cfg.vocab, C), layers)
+
+
+def rms_norm(x: Tensor) -> Tensor:
+    return F.rms_norm(x, (x.size(-1),), eps=EPS)
+
+
+class Decoder:
+    """Greedy decoding of up to n_slots sequences with an fp8 KV cache per layer."""
+
+    def __init__(self, cfg: DecoderConfig, weights: DecoderWeights, n_slots: int, device: "torch.device | str" = "cuda"):
+        self.cfg, self.w, self.n_slots, self.device = cfg, weights, n_slots, torch.device(device)
+        self.caches = [Fp8KVCache(n_slots, cfg.n_kv_heads, cfg.max_len, device=device) for _ in range(cfg.n_layers)]
+        self.capacity = self.caches[0].capacity
+        self.cos, self.sin = ops.rotary_table(self.capacity, cfg.rope_theta, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.windows = cfg.windows or [0] * cfg.n_layers
+        self._graphs: dict[int, tuple] = {}
+        self._workspaces: dict[tuple[int, int], Tensor] = {}
+
+    # ---- one pass over `rows` tokens -------------------------------------------------------------------------
+
+    def _workspace(self, rows: int, max_kv_len: int) -> Tensor:
+        key = (rows, max_kv_len)
+        if key not in self._workspaces:
+            need = ops.workspace_bytes(rows, self.cfg.n_heads, self.cfg.n_kv_heads, max_kv_len)
+            self._workspaces[key] = torch.empty(max(need, 16), dtype=torch.uint8, device=self.device)
+        return self._workspaces[key]
+
+    def hidden_rows(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int,
+                    attend_last_layer: bool = True) -> Tensor:
+        """Final-normed hidden states (rows, C) bf16 of `tokens` at positions `pos` of slots `slot_map`; appends
+        every row's k, v to the caches. max_kv_len bounds pos + 1."""
+        cfg = self.cfg
+        rows = tokens.shape[0]
+        lens = pos + 1
+        workspace = self._workspace(rows, max_kv_len)
+        h = x0 = rms_norm(self.w.embed[tokens])
+        for i, layer in enumerate(self.w.layers):
+            if layer.resid_lambda != 1.0 or layer.x0_lambda != 0.0:
+                h = (layer.resid_lambda * h.float() + layer.x0_lambda * x0.float()).to(h.dtype)
+            qkv = rms_norm(h) @ layer.wqkv.T
+            q = ops.kv_append(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i], cfg.n_heads,
+                              slot_map=slot_map, status=self.status)
+            if i == cfg.n_layers - 1 and not attend_last_layer:
+                return h  # prefill: the last layer only has to fill its cache (decode.cu:862)
+            att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map, window=self.windows[i],
+                                       workspace=workspace, status=self.status)
+            h = h + att.view(rows, -1) @ layer.wo.T
+            h = h + F.relu(rms_norm(h) @ layer.wup.T).square() @ layer.wdown.T
+        return rms_norm(h)
+
+    def logits_rows(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int) -> Tensor:
+        """fp32 logits (rows, V): the bf16 head's GEMM accumulated and kept in fp32."""
+        return self.head(self.hidden_rows(tokens, pos, slot_map, max_kv_len))
+
+    def head(self, hidden: Tensor) -> Tensor:
+        """The bf16 head GEMM with its fp32 accumulator kept as the output (modeling_nanochat.py:190-192)."""
+        return torch.mm(hidden, self.w.lm_head.T, out_dtype=torch.float32)
+
+    # ---- prefill ----------------------------------------------------------------------------------------------
+
+    @torch.no_grad()
+    def prefill(self, prompts: list[list[int]], slots: list[int], rows_per_pass: int = 1024) -> None:
+        """Cache positions 0 .. len - 2 of every prompt (its last token is the first decode input). Sequences are
+        processed in passes of at most rows_per_pass rows; a pass holds whole position ranges in order, so every row
+        finds the earlier positions of its sequence either in the cache or earlier in its own pass."""
+        todo = [(slot, t, tok) for slot, p in zip(slots, prompts) for t, tok in enumerate(p[:-1])]
+        for at in range(0, len(todo), rows_per_pass):
+            part = todo[at:at + rows_per_pass]
+            slot_map = torch.tensor([s for s, _, _ in part], dtype=torch.int32, device=self.device)
+            pos = torch.tensor([t for _, t, _ in part], dtype=torch.int32, device=self.device)
+            tokens = torch.tensor([k for _, _, k in part], dtype=torch.long, device=self.device)
+            self.hidden_rows(tokens, pos, slot_map, max(t for _, t, _ in part) + 1, attend_last_layer=False)
+
+    # ---- decode -----------------------------------------------------------------------------------------------
+
+    def _step_graph(self, batch: int):
+        """The captured step for `batch` slots 0 .. batch - 1: tokens, pos (device) -> argmax tokens; pos += 1."""
+        if batch in self._graphs:
+            return self._graphs[batch]
+        dev = self.device
+        tokens = torch.zeros(batch, dtype=torch.long, device=dev)
+        pos = torch.zeros(batch, dtype=torch.int32, device=dev)
+        slot_map = torch.arange(batch, dtype=torch.int32, device=dev)
+        logits = torch.empty((batch, self.cfg.vocab), dtype=torch.float32, device=dev)
+
+        def body():
+            logits.copy_(self.head(self.hidden_rows(tokens, pos, slot_map, self.capacity)))
+            tokens.copy_(logits.argmax(-1))  # ties to the lowest id, as decode.cu:90-96
+            pos.add_(1)
+
+        stream = torch.cuda.Stream(dev)
+        stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(stream):
+            body()  # eager warm-up: first-use set-up outside capture; it writes position 0, rewritten on replay
+            pos.zero_()
+            tokens.zero_()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                body()
+        self._graphs[batch] = (graph, stream, tokens, pos, logits)
+        return self._graphs[batch]
+
+    @torch.no_grad()
+    def generate(self, prompts: list[list[int]], max_new_tokens: int) -> tuple[list[list[int]], dict]:
+        """Greedy continuation of every prompt (slot b = prompt b). Returns the new tokens and timings: prefill
+        seconds, decode seconds (the max_new_tokens steps), tokens per second of the decode phase."""
+        B = len(prompts)
+        assert B <= self.n_slots and all(len(p) >= 1 for p in prompts)
+        assert max(len(p) for p in prompts) - 1 + max_new_tokens <= self.capacity
+        graph, stream, tokens, pos, logits = self._step_graph(B)
+        start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        with torch.cuda.stream(stream):
+            start.record()
+            self.prefill(prompts, list(range(B)))
+            tokens.copy_(torch.tensor([p[-1] for p in prompts], dtype=torch.long), non_blocking=False)
+            pos.copy_(torch.tensor([len(p) - 1 for p in prompts], dtype=torch.int32))
+            out = torch.empty((max_new_tokens, B), dtype=torch.long, device=self.device)
+            mid.record()
+            for t in range(max_new_tokens):
+                graph.replay()
+                out[t].copy_(tokens)
+            end.record()
+        stream.synchronize()
+        code = int(self.status.item())
+        if code:
+            raise RuntimeError(f"device status {code:#x} (NCB_DEV_* bits)")
+        decode_s = mid.elapsed_time(end) * 1e-3
+        return out.T.tolist(), {"prefill_s": start.elapsed_time(mid) * 1e-3, "decode_s": decode_s,
+                                "tokens_per_s": B * max_new_tokens / decode_s}

@@ -40,3 +40,20 @@ def error_stats(got_bits: np.ndarray, want_bits: np.ndarray) -> tuple[float, flo
     """(max-abs, mean-abs) difference of two bf16 bit arrays."""
     d = np.abs(okv.bf16_to_f32(got_bits).astype(np.float64) - okv.bf16_to_f32(want_bits).astype(np.float64))
     return float(d.max()) if d.size else 0.0, float(d.mean()) if d.size else 0.0
+
+
+def tiny_decoder_weights(seed: int = 21) -> tuple[dict, dict]:
+    """A 2-layer, 2-head (hidden 256), vocab 512 random-init model on the CPU: bf16 weights ~ N(0, 0.02)
+    (the benchmark's initialisation) and fp32 QK gains 1 + 0.1 N(0, 1). Returns (config dict, weight dict)."""
+    cfg = {"n_layers": 2, "hidden": 256, "n_heads": 2, "n_kv_heads": 2, "intermediate": 1024, "vocab": 512,
+           "rope_theta": 10000.0, "max_len": 256}
+    gen = torch.Generator().manual_seed(seed)
+    C, H, Fd, V = cfg["hidden"], cfg["n_heads"], cfg["intermediate"], cfg["vocab"]
+
+    def w(*shape):
+        return (torch.randn(*shape, generator=gen) * 0.02).bfloat16()
+
+    layers = [{"wqkv": w(3 * H * HEAD_DIM, C), "wo": w(C, H * HEAD_DIM), "wup": w(Fd, C), "wdown": w(C, Fd),
+               "q_gain": (1 + 0.1 * torch.randn(HEAD_DIM, generator=gen)).float(),
+               "k_gain": (1 + 0.1 * torch.randn(HEAD_DIM, generator=gen)).float()} for _ in range(cfg["n_layers"])]
+    return cfg, {"embed": w(V, C), "lm_head": w(V, C), "layers": layers}
