@@ -40,6 +40,9 @@ sys.path.insert(0, str(ROOT))
 
 HQ, HKV, D, BATCH = 32, 8, 128, 64
 METRIC, UNIT = "decode_attention_hbm_gbs", "GB/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_decode_attn<1> launch on the target8k workload, from the
+# ncu capture summarised in profiles/decode_attn_split_target8k.md (1.1082 GB read + 8.3 MB written)
+TARGET8K_TRAFFIC_BYTES = 1_108_153_000 + 8_263_000
 
 
 def algorithmic_bytes(lens, Hq=HQ, Hkv=HKV) -> int:
@@ -194,6 +197,30 @@ def bench_longctx(rank: int, world: int, device, steps: int, warmup: int, timed)
                                                   "then decode_attn_merge on every rank"}
 
 
+def bench_decoder(rank: int, world: int, device, new_tokens: int) -> dict:
+    """End-to-end greedy decode of the random-init d20 model (20 layers, d_model 1280, 10 heads, vocab 65536, bf16
+    weights ~ N(0, 0.02)): batch 8 per GPU, 512-token prompts, `new_tokens` generated tokens; every rank runs its own
+    batch (replicated weights, no collective), tokens/s is the sum over ranks of the decode phase."""
+    import torch.distributed as dist
+
+    from nanochat_b200.decoder import Decoder, DecoderConfig, DecoderWeights
+
+    cfg = DecoderConfig(n_layers=20, hidden=1280, n_heads=10, n_kv_heads=10, intermediate=5120, vocab=65536,
+                        rope_theta=10000.0, max_len=512 + new_tokens)
+    decoder = Decoder(cfg, DecoderWeights.random_init(cfg, 0, device), 8, device)
+    gen = torch.Generator().manual_seed(100 + rank)
+    prompts = torch.randint(0, 65536, (8, 512), generator=gen).tolist()
+    decoder.generate(prompts, 8)  # warm-up: graph capture, cuBLAS heuristics
+    _, t = decoder.generate(prompts, new_tokens)
+    stats = torch.tensor([t["decode_s"], t["prefill_s"]], device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    decode_s, prefill_s = stats.tolist()
+    return {"workload": "random-init d20, batch 8 per GPU, prompt 512, greedy, fp8 KV cache", "new_tokens": new_tokens,
+            "tokens_per_s": 8 * world * new_tokens / decode_s, "ms_per_step": decode_s / new_tokens * 1e3,
+            "prefill_s": prefill_s, "scaling": "weak (replicas)"}
+
+
 def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
@@ -245,6 +272,7 @@ def main() -> None:
     ap.add_argument("--cpu-sample", type=int, default=4, help="sequences in the CPU baseline's sample")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--chunk-pages", type=int, default=0)
+    ap.add_argument("--decoder", type=int, default=1, help="also time end-to-end greedy decoding of d20 (0: skip)")
     ap.add_argument("--longctx", type=int, default=1, help="also time the KV-length-sharded long-context case (0: skip)")
     ap.add_argument("--e2e-steps", type=int, default=200, help="steps of the end-to-end loop (profiling runs shrink it)")
     args = ap.parse_args()
@@ -353,6 +381,7 @@ def main() -> None:
     h2d_bytes, d2h_bytes = decode.h2d_bytes, decode.d2h_bytes
     del cache, decode, workspace
     longctx = bench_longctx(rank, world, device, min(args.steps, 100), 5, timed) if args.longctx else None
+    decoder = bench_decoder(rank, world, device, 256) if args.decoder else None
 
     if rank == 0:
         peak, peak_kind = peaks()
@@ -374,12 +403,15 @@ def main() -> None:
                             "resident decoder state"},
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "k_decode_attn<1> (split-KV)", "achieved": split_gbs, "peak": peak,
-                         "unit": UNIT, "frac": split_gbs / peak, "peak_kind": peak_kind, "traffic": None,
+                         "unit": UNIT, "frac": split_gbs / peak, "peak_kind": peak_kind,
+                         "traffic": TARGET8K_TRAFFIC_BYTES if args.workload == "target8k" and not args.chunk_pages else None,
                          "us_per_launch": ms_split / args.steps * 1e3,
                          "algorithmic_bytes_per_launch": algorithmic_bytes(lens)},
         }
         if longctx:
             line["longctx"] = longctx
+        if decoder:
+            line["decoder"] = decoder
         if world == 1 and args.cpu_seconds > 0:
             line["cpu_baseline"] = time_cpu_reference(lens[:args.cpu_sample], args.cpu_seconds)
         print(json.dumps(line))

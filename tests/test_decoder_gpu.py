@@ -52,14 +52,16 @@ def test_generate_prefill_and_graph_decode_reproduce_reference_tokens():
     tokens, timing = dec.generate(prompts, 6)
     ref = uncapped(GOLDEN["logits"], float(GOLDEN["softcap"]))[:, :6]
     top2 = np.sort(ref, -1)[..., -2:]
-    clear = (top2[..., 1] - top2[..., 0]) > 4e-2
+    clear = (top2[..., 1] - top2[..., 0]) > 1.5e-2
     # a greedy stream is only comparable up to its first near-tie
+    compared = 0
     for b in range(2):
         for t in range(6):
             if not clear[b, t]:
                 break
             assert tokens[b][t] == int(GOLDEN["tokens"][b, t]), (b, t)
-    assert clear[:, 0].all() and timing["tokens_per_s"] > 0
+            compared += 1
+    assert compared >= 6 and timing["tokens_per_s"] > 0
     # a second call reuses the captured graph and gives the same stream
     again, _ = dec.generate(prompts, 6)
     assert again == tokens
