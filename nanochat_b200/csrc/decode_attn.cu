@@ -8,8 +8,8 @@
  *
  *   - one thread block per (sequence, kv head, chunk of pages); a page (include/nanochat_b200.h) is one contiguous
  *     16,896-byte record fetched by ONE cp.async.bulk that signals an mbarrier. Each of the block's WARPS warps
- *     owns one shared-memory stage and one barrier: it takes every WARPS-th page of the chunk, waits for it,
- *     consumes it and immediately issues its next page into the same stage. Warps never synchronise with each
+ *     owns one shared-memory stage and one barrier: it waits for its page, consumes it, draws the chunk's next
+ *     unassigned page from a shared counter and immediately issues it into the same stage. Warps never synchronise with each
  *     other until the end, a barrier is only ever waited on by the warp that armed it (so its phases are observed
  *     strictly in order), and two blocks per SM keep twelve pages (about 200 KB) in flight or in use per SM;
  *   - no fp8 -> float conversion of K or V at all: both contractions run on the tensor cores as
@@ -147,13 +147,19 @@ static __device__ __forceinline__ float head_sum(float v) {
 /* Where a sequence's attended positions and pages lie; shared by the split and merge kernels. */
 struct Span {
     int begin, len, first_page, last_page; /* positions [begin, len), pages [first_page, last_page) */
+    int n_chunks, chunk;                   /* the pages cut into n_chunks runs of `chunk` pages (the last may be shorter) */
 };
-static __device__ __forceinline__ Span span_of(int len, int window) {
+/* chunk_pages is an upper bound: a sequence takes the fewest chunks that respect it and then evens them out, so no
+ * block is left with a stub (129 pages at 27 per chunk are 5 chunks of 26, 26, 26, 26, 25). */
+static __device__ __forceinline__ Span span_of(int len, int window, int chunk_pages) {
     Span s;
     s.len = len;
     s.begin = (window > 0 && len > window) ? len - window : 0;
     s.first_page = s.begin / PAGE_TOKENS;
     s.last_page = (len + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    const int pages = s.last_page - s.first_page;
+    s.n_chunks = (pages + chunk_pages - 1) / chunk_pages;
+    s.chunk = s.n_chunks > 0 ? (pages + s.n_chunks - 1) / s.n_chunks : 0;
     return s;
 }
 
@@ -164,6 +170,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];       /* WARPS stages of one page; later the merge area */
     __shared__ __align__(8) uint64_t bars[WARPS];          /* one "page landed" barrier per warp */
     __shared__ float q_stage[4 * NT * HEAD_DIM], q_scale[4 * NT];
+    __shared__ int next_page; /* the chunk's next unassigned page: warps draw from it as they finish one */
     float *merge = reinterpret_cast<float *>(smem);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -176,15 +183,17 @@ __global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
         if (tid == 0 && chunk == 0 && kvh == 0) flag(a.status, NCB_DEV_BAD_LENGTH);
         return; /* the merge kernel makes the same test and writes zeros */
     }
-    const Span sp = span_of(len, a.window);
-    const int pg0 = sp.first_page + chunk * a.chunk_pages;
-    const int n = min(a.chunk_pages, sp.last_page - pg0);
+    const Span sp = span_of(len, a.window, a.chunk_pages);
+    if (chunk >= sp.n_chunks) return;
+    const int pg0 = sp.first_page + chunk * sp.chunk;
+    const int n = min(sp.chunk, sp.last_page - pg0);
     if (n <= 0) return;
 
     const uint8_t *pages = a.cache + (((size_t)slot * a.Hkv + kvh) * a.pages_per_slot + pg0) * PAGE_BYTES;
     uint8_t *page = smem + (size_t)warp * PAGE_BYTES; /* this warp's stage */
     const uint32_t page_u = smem_u32(page), bar = smem_u32(bars + warp);
 
+    if (tid == 0) next_page = WARPS; /* pages 0 .. WARPS - 1 start with warps 0 .. WARPS - 1 */
     if (lane == 0) { /* arm this warp's barrier and start its first page before anything else happens */
         mbar_init(bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -240,7 +249,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
     }
 
     uint32_t phase = 0;
-    for (int i = warp; i < n; i += WARPS, phase ^= 1) {
+    for (int i = warp; i < n; phase ^= 1) {
         if (!mbar_wait(bar, phase)) {
             if (lane == 0) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
             mbar_wait(bar, phase); /* the block must not exit under a copy still in flight */
@@ -357,11 +366,16 @@ __global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
             }
         }
         __syncwarp(); /* every lane has read the stage */
-        if (lane == 0 && i + WARPS < n) {
-            /* order this warp's reads (and the masking writes) of the stage before the copy engine's writes */
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            page_load(page_u, pages + (size_t)(i + WARPS) * PAGE_BYTES, bar);
+        int next = n;
+        if (lane == 0) {
+            next = atomicAdd(&next_page, 1);
+            if (next < n) {
+                /* order this warp's reads (and the masking writes) of the stage before the copy engine's writes */
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                page_load(page_u, pages + (size_t)next * PAGE_BYTES, bar);
+            }
         }
+        i = __shfl_sync(0xffffffffu, next, 0);
     }
     /* the merge kernel may start occupying free SM resources now; it still waits for this grid to finish */
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -414,33 +428,50 @@ struct MergeArgs {
 
 constexpr int MERGE_WARPS = 4;
 
+/* One block per row; warp w folds states w, w + 4, ... into a running state (its loads are independent of the fold,
+ * so they overlap), then the four running states are merged through shared memory. Lane = four output dims. */
 __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
-    const long long row = (long long)blockIdx.x * MERGE_WARPS + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
+    __shared__ float sm[MERGE_WARPS], sl[MERGE_WARPS];
+    __shared__ float4 so[MERGE_WARPS][32];
+    const long long row = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     /* launched with programmatic stream serialisation: wait here until the grid before it (the split kernel, whose
      * states this reads) has completed and its writes are visible; a no-op after an ordinary launch */
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (row >= a.rows) return;
     int n = a.n_parts;
     if (n == 0) {
         const int b = (int)(row / a.Hq), len = a.lens[b], slot = a.slot_map ? a.slot_map[b] : b;
         if (!(len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots)) {
-            const Span sp = span_of(len, a.window);
-            n = min((sp.last_page - sp.first_page + a.chunk_pages - 1) / a.chunk_pages, a.max_chunks);
+            n = min(span_of(len, a.window, a.chunk_pages).n_chunks, a.max_chunks);
         }
     }
     const float *st = a.parts + row * a.row_stride;
-    float top = -INFINITY;
-    for (int p = lane; p < n; p += 32) top = fmaxf(top, st[p * a.part_stride]);
-    for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
-    float lsum = 0.f;
+    float top = -INFINITY, lsum = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < n; p++) {
+#pragma unroll 2
+    for (int p = warp; p < n; p += MERGE_WARPS) {
         const float *s = st + p * a.part_stride;
-        const float mp = s[0];
-        const float c = mp == -INFINITY ? 0.f : ex2(mp - top);
+        const float mp = s[0], lp = s[1];
         const float4 o = *reinterpret_cast<const float4 *>(s + 4 + 4 * lane);
-        lsum += c * s[1];
+        const float next = fmaxf(top, mp);
+        const float c0 = top == -INFINITY ? 0.f : ex2(top - next), c1 = mp == -INFINITY ? 0.f : ex2(mp - next);
+        lsum = lsum * c0 + lp * c1;
+        acc.x = acc.x * c0 + o.x * c1, acc.y = acc.y * c0 + o.y * c1;
+        acc.z = acc.z * c0 + o.z * c1, acc.w = acc.w * c0 + o.w * c1;
+        top = next;
+    }
+    if (lane == 0) sm[warp] = top, sl[warp] = lsum;
+    so[warp][lane] = acc;
+    __syncthreads();
+    if (warp != 0) return;
+    top = fmaxf(fmaxf(sm[0], sm[1]), fmaxf(sm[2], sm[3]));
+    lsum = 0.f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < MERGE_WARPS; w++) {
+        const float c = sm[w] == -INFINITY ? 0.f : ex2(sm[w] - top);
+        const float4 o = so[w][lane];
+        lsum += c * sl[w];
         acc.x += c * o.x, acc.y += c * o.y, acc.z += c * o.z, acc.w += c * o.w;
     }
     if (a.part_out) {
@@ -516,7 +547,7 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
 
 static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
     if (a.rows == 0) return NCB_OK;
-    const long long blocks = (a.rows + MERGE_WARPS - 1) / MERGE_WARPS;
+    const long long blocks = a.rows; /* one block per row */
     if (blocks > 0x7fffffffLL) return NCB_ERR_ARG;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)blocks);
