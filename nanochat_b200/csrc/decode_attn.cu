@@ -11,7 +11,8 @@
  *     owns one shared-memory stage and one barrier: it waits for its page, consumes it, draws the chunk's next
  *     unassigned page from a shared counter and immediately issues it into the same stage. Warps never synchronise with each
  *     other until the end, a barrier is only ever waited on by the warp that armed it (so its phases are observed
- *     strictly in order), and two blocks per SM keep twelve pages (about 200 KB) in flight or in use per SM;
+ *     strictly in order), and three blocks of four warps per SM keep twelve pages (about 200 KB) in flight or in
+ *     use per SM while staggering the blocks' start-up and drain phases;
  *   - no fp8 -> float conversion of K or V at all: both contractions run on the tensor cores as
  *     mma.sync.m16n8k32 e4m3 x e4m3 -> fp32 with the CACHE as the A operand (16 positions, or 16 dims, per tile)
  *     and the N = 8 columns holding the group's query heads. bf16 queries and fp32 probabilities do not fit e4m3's
@@ -36,7 +37,11 @@
 
 #include "ncb_common.cuh"
 
-constexpr int WARPS = 6; /* = stages per block; 6 x 16,896 B x 2 blocks fit one SM's shared memory */
+#ifndef NCB_WARPS
+#define NCB_WARPS 4
+#endif
+constexpr int WARPS = NCB_WARPS; /* = stages per block; 12 stages of 16,896 B fit one SM's shared memory */
+constexpr int BLOCKS_PER_SM = 12 / WARPS;
 constexpr int THREADS = WARPS * 32;
 constexpr int PART = NCB_PART_FLOATS;
 constexpr uint32_t WAIT_TRIES = 1u << 19; /* x <= 2 us suspend hint each: about one second */
@@ -45,6 +50,7 @@ constexpr float LO_SCALE = 16.f;          /* second term's gain: the first term'
 constexpr float MIN_LOG2_VSCALE = -64.f;
 constexpr size_t ATTN_SMEM = (size_t)WARPS * PAGE_BYTES;
 static_assert(WARPS * 4 * 2 * PART * sizeof(float) <= ATTN_SMEM, "the merge area reuses the ring");
+static_assert(THREADS >= HEAD_DIM && 12 % WARPS == 0, "the final merge maps one thread to one output dim");
 
 struct AttnArgs {
     const bf16 *q;
@@ -166,7 +172,7 @@ static __device__ __forceinline__ Span span_of(int len, int window, int chunk_pa
 /* ---- split-KV kernel ---------------------------------------------------------------------------------------- */
 
 template <int NT>
-__global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
+__global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];       /* WARPS stages of one page; later the merge area */
     __shared__ __align__(8) uint64_t bars[WARPS];          /* one "page landed" barrier per warp */
     __shared__ float q_stage[4 * NT * HEAD_DIM], q_scale[4 * NT];
@@ -368,7 +374,11 @@ __global__ void __launch_bounds__(THREADS, 2) k_decode_attn(AttnArgs a) {
         __syncwarp(); /* every lane has read the stage */
         int next = n;
         if (lane == 0) {
+#ifdef NCB_STATIC_PAGES
+            next = i + WARPS;
+#else
             next = atomicAdd(&next_page, 1);
+#endif
             if (next < n) {
                 /* order this warp's reads (and the masking writes) of the stage before the copy engine's writes */
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -605,12 +615,13 @@ extern "C" {
 
 int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len) {
     if (B <= 0 || Hkv <= 0 || max_kv_len <= 0) return 1;
-    /* aim at about eight blocks per resident slot (2 per SM) when every sequence is max_kv_len long; small problems
-     * get one page per warp (WARPS pages per block) or, below one block per slot, as many blocks as there are pages */
-    const long long total = (long long)B * Hkv * pages_of(max_kv_len), slots = 2LL * sm_count();
-    long long c = total / (8 * slots);
+    /* aim at about four blocks per resident slot (BLOCKS_PER_SM per SM) when every sequence is max_kv_len long,
+     * at most 32 pages each (measured: longer chunks gain nothing and unbalance ragged batches); small problems get
+     * one page per warp (WARPS pages per block) or, below one block per slot, as many blocks as there are pages */
+    const long long total = (long long)B * Hkv * pages_of(max_kv_len), slots = (long long)BLOCKS_PER_SM * sm_count();
+    long long c = total / (4 * slots);
     if (c < WARPS) c = min((long long)WARPS, max(1LL, total / slots));
-    if (c > 64) c = 64;
+    if (c > 32) c = 32;
     return (int)c;
 }
 

@@ -9,6 +9,7 @@ failed build raises, and so does a non-zero status from any entry point (check()
 import ctypes
 import functools
 import hashlib
+import os
 import subprocess
 import tempfile
 from pathlib import Path
@@ -51,7 +52,10 @@ class NativeError(RuntimeError):
 
 
 def command() -> list[str]:
-    return ["nvcc", "-gencode=arch=compute_100a,code=sm_100a", "-O3", "-lineinfo",
+    """The nvcc command; NCB_NVCC_FLAGS (space-separated, e.g. "-DWARPS=4") adds flags for experiments and, being
+    part of the command, selects its own cached library."""
+    extra = os.environ.get("NCB_NVCC_FLAGS", "").split()
+    return ["nvcc", "-gencode=arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", *extra,
             "-Xcompiler", "-fPIC", "-shared", "-o"]
 
 
@@ -69,8 +73,9 @@ def build_library(name: str) -> Path:
     path = library_path(name)
     if not path.exists():
         NATIVE.mkdir(exist_ok=True)
-        for stale in NATIVE.glob(f"{name}-*.so"):
-            stale.unlink(missing_ok=True)
+        if not os.environ.get("NCB_NVCC_FLAGS"):
+            for stale in NATIVE.glob(f"{name}-*.so"):
+                stale.unlink(missing_ok=True)
         with tempfile.TemporaryDirectory(dir=NATIVE) as tmp:
             built = Path(tmp) / path.name
             subprocess.run([*command(), str(built), str(KERNELS / f"{name}.cu")], check=True)
