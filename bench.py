@@ -186,15 +186,23 @@ def bench_longctx(rank: int, world: int, device, steps: int, warmup: int, timed)
         step = lambda: ncb.decode_attention(q, cache, lens_t, n_local, chunk_pages=chunk, workspace=workspace, out=out)
     else:
         part = torch.empty((B, HQ, 132), dtype=torch.float32, device=device)
-        step = lambda: sharding.attend_kv_sharded(q, cache, lens_t, max(n_local, 1), chunk_pages=chunk,
-                                                  workspace=workspace, part=part)
+        nccl_step = lambda: sharding.attend_kv_sharded(q, cache, lens_t, max(n_local, 1), chunk_pages=chunk,
+                                                       workspace=workspace, part=part)
+        ms_nccl = timed(nccl_step, steps, warmup)
+        peers = sharding.PeerStates(B, HQ)
+        out = torch.empty_like(q)
+        step = lambda: sharding.attend_kv_sharded_fused(q, cache, lens_t, max(n_local, 1), peers, out=out,
+                                                        chunk_pages=chunk, workspace=workspace)
     ms = timed(step, steps, warmup)
+    if world > 1:
+        assert int(peers.status.item()) == 0, "a peer wait ran out"
     total = algorithmic_bytes([N] * B)
     return {"workload": "batch 4, Hq 32, Hkv 8, head_dim 128, 131072 positions per sequence, KV split by length over "
                         f"{world} GPU(s)", "value": total * steps / (ms * 1e-3) / 1e9, "unit": UNIT,
             "ms_per_step": ms / steps, "steps": steps, "scaling": "strong", "chunk_pages": chunk,
-            "collective": None if world == 1 else "all_gather_into_tensor of fp32 [4][32][132] per rank (NCCL), "
-                                                  "then decode_attn_merge on every rank"}
+            "collective": None if world == 1 else "none: decode_attn_merge_peers loads every rank's fp32 [4][32][132] "
+                                                  "states over NVLink after a bounded flag wait",
+            "nccl_variant_ms_per_step": None if world == 1 else ms_nccl / steps}
 
 
 def bench_decoder(rank: int, world: int, device, new_tokens: int) -> dict:

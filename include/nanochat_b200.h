@@ -157,6 +157,24 @@ int decode_attn_fp8_static(const void *q, const void *kv_cache, const void *lens
  */
 int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out, void *stream);
 
+/*
+ * decode_attn_merge across GPUs without a collective library: the exchange and the merge in ONE kernel over peer
+ * memory (NVLink). Each rank r has left its rows' states in a buffer that every peer can address
+ * (parts[r], fp32 [rows][NCB_PART_FLOATS], e.g. written by decode_attn_fp8_partial), and owns an array of
+ * `world` uint32 flags that every peer can address (flags[r]). The kernel, on rank `rank`:
+ *   1. publishes: stores `epoch` into flags[q][rank] of every rank q (its states were written by earlier work on
+ *      this stream);
+ *   2. waits, with a bound of roughly a second, until its own flags[rank][q] >= epoch for every q;
+ *   3. loads every rank's state of each row with plain peer loads and merges them into out bf16 [rows][128].
+ * parts and flags are host arrays of `world` (<= 8) device pointers, the same on every rank. `epoch` must grow by
+ * one per call on every rank and start above the flags' initial contents (zero them and synchronise the ranks
+ * once). A rank may run ahead of a peer by at most one call, so alternate between two `parts` buffers from call
+ * to call. If the wait runs out, NCB_DEV_WAIT_TIMEOUT is set in *status and `out` is not meaningful; the kernel
+ * still returns. No counterpart in the reference, which runs on one GPU.
+ */
+int decode_attn_merge_peers(const void *const *parts, void *const *flags, int world, int rank, unsigned epoch,
+                            long long rows, void *out, void *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -500,6 +500,77 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
     }
 }
 
+/* ---- merge over peer memory ---------------------------------------------------------------------------------- */
+
+constexpr int MAX_PEERS = 8;
+constexpr uint32_t PEER_WAIT_POLLS = 1u << 22; /* x ~100 ns sleep each: roughly half a second */
+
+struct PeerArgs {
+    const float *parts[MAX_PEERS]; /* rank q's states [rows][PART], addressable from this GPU */
+    uint32_t *flags[MAX_PEERS];    /* rank q's flags [world]: flags[q][r] = last epoch rank r published */
+    int world, rank;
+    uint32_t epoch;
+    long long rows;
+    bf16 *out;
+    int *status;
+};
+
+/* One block per row, one warp per block; lane = four output dims. Every block publishes nothing but waits itself:
+ * block 0 does the publishing for the rank. Blocks only ever wait for other GPUs' kernels, never for one another. */
+__global__ void __launch_bounds__(32) k_merge_peers(PeerArgs a) {
+    const long long row = blockIdx.x;
+    const int lane = threadIdx.x;
+    asm volatile("griddepcontrol.wait;" ::: "memory"); /* this rank's states are complete and visible */
+    if (row == 0 && lane < a.world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flags[lane] + a.rank), "r"(a.epoch) : "memory");
+    }
+    if (lane < a.world) { /* lane q waits for rank q */
+        const uint32_t *mine = a.flags[a.rank] + lane;
+        bool ok = false;
+        for (uint32_t polls = 0; polls < PEER_WAIT_POLLS; polls++) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if ((int32_t)(seen - a.epoch) >= 0) {
+                ok = true;
+                break;
+            }
+            __nanosleep(100);
+        }
+        if (!ok) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+    }
+    __syncwarp();
+    float top = -INFINITY, lsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float mq[MAX_PEERS], lq[MAX_PEERS];
+    float4 oq[MAX_PEERS];
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; q++) { /* all loads first: they cross NVLink and overlap */
+        if (q < a.world) {
+            const float *s = a.parts[q] + row * PART;
+            mq[q] = __ldcv(s);
+            lq[q] = __ldcv(s + 1);
+            oq[q] = __ldcv(reinterpret_cast<const float4 *>(s + 4) + lane);
+            top = fmaxf(top, mq[q]);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; q++) {
+        if (q < a.world) {
+            const float c = mq[q] == -INFINITY ? 0.f : ex2(mq[q] - top);
+            lsum += c * lq[q];
+            acc.x += c * oq[q].x, acc.y += c * oq[q].y, acc.z += c * oq[q].z, acc.w += c * oq[q].w;
+        }
+    }
+    const bool any = lsum > 0.f;
+    const float x = any ? __fdiv_rn(acc.x, lsum) : 0.f, y = any ? __fdiv_rn(acc.y, lsum) : 0.f;
+    const float z = any ? __fdiv_rn(acc.z, lsum) : 0.f, w = any ? __fdiv_rn(acc.w, lsum) : 0.f;
+    uint2 u;
+    *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(x, y);
+    *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(z, w);
+    *reinterpret_cast<uint2 *>(a.out + row * HEAD_DIM + 4 * lane) = u;
+}
+
 /* ---- host side ---------------------------------------------------------------------------------------------- */
 
 static int sm_count() {
@@ -671,6 +742,33 @@ int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens,
                           void *status, void *stream) {
     return launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots, pages_per_slot,
                         max_kv_len, window, chunk_pages, softmax_scale, status, (cudaStream_t)stream);
+}
+
+int decode_attn_merge_peers(const void *const *parts, void *const *flags, int world, int rank, unsigned epoch,
+                            long long rows, void *out, void *status, void *stream) {
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world || rows < 0 || rows > 0x7fffffffLL)
+        return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    if (!parts || !flags || !out) return NCB_ERR_ARG;
+    PeerArgs a = {};
+    for (int q = 0; q < world; q++) {
+        if (!parts[q] || !flags[q]) return NCB_ERR_ARG;
+        if (((uintptr_t)parts[q] % 16) || ((uintptr_t)flags[q] % 4)) return NCB_ERR_ALIGN;
+        a.parts[q] = (const float *)parts[q];
+        a.flags[q] = (uint32_t *)flags[q];
+    }
+    if ((uintptr_t)out % 8) return NCB_ERR_ALIGN;
+    a.world = world, a.rank = rank, a.epoch = epoch, a.rows = rows, a.out = (bf16 *)out, a.status = (int *)status;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)rows);
+    config.blockDim = dim3(32);
+    config.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, k_merge_peers, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out, void *stream) {

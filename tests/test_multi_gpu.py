@@ -39,6 +39,13 @@ def worker(rank: int, world: int, port: int, result):
         want = oat.decode_attention(case["q"], case["k_bytes"], case["k_scale"], case["v_bytes"], case["v_scale"],
                                     128 ** -0.5)
         result.put((rank, *helpers.error_stats(helpers.bf16_bits(out.cpu()), want)))
+        # the fused exchange + merge over peer memory, several calls in a row (the two state buffers alternate)
+        peers = sharding.PeerStates(len(lens), Hq)
+        for _ in range(5):
+            fused = sharding.attend_kv_sharded_fused(q, cache, lens_t, max(max(local_lens), 1), peers)
+        torch.cuda.synchronize()
+        assert int(peers.status.item()) == 0
+        result.put((rank, *helpers.error_stats(helpers.bf16_bits(fused.cpu()), helpers.bf16_bits(out.cpu()))))
     finally:
         dist.destroy_process_group()
 
@@ -51,6 +58,6 @@ def test_kv_length_sharded_attention_two_ranks():
     ctx = mp.get_context("spawn")
     result = ctx.Queue()
     mp.spawn(worker, args=(2, port, result), nprocs=2, join=True)
-    for _ in range(2):
+    for _ in range(4):  # per rank: NCCL path vs checker, then fused path vs NCCL path
         rank, max_abs, mean_abs = result.get(timeout=10)
         assert max_abs <= 2e-2 and mean_abs <= 2e-3, (rank, max_abs, mean_abs)
