@@ -175,6 +175,25 @@ int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out,
 int decode_attn_merge_peers(const void *const *parts, void *const *flags, int world, int rank, unsigned epoch,
                             long long rows, void *out, void *status, void *stream);
 
+/* ---- library decode_step ------------------------------------------------------------------------------------
+ * The rest of a decode step for at most 16 rows; replaces the reference's Hopper-only slot GEMM k_wgmma with its
+ * epilogues (model/kernels/decode.cu:170-208,232-359), k_norm / k_rstd (decode.cu:415-456) and k_commit
+ * (decode.cu:678-688). All three are launched with programmatic stream serialisation. */
+
+/*
+ * y = epilogue(norm?(x) . W^T). x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3);
+ * resid bf16 [rows][N] for epilogue 1 (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding
+ * the product), 2 relu^2, 3 fp32 store. norm_input != 0 first applies the parameter-free RMS norm (eps
+ * FLT_EPSILON, rounded to bf16) to x. rows <= 16; K a multiple of 256, at most 5120 (2048 with norm_input); N a
+ * multiple of 8.
+ */
+int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
+                int epilogue, void *stream);
+/* h bf16 [rows][C] = rms_norm(embed[tokens]); embed bf16 [vocab][C]; tokens int64 [rows]; C a multiple of 8. */
+int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, int vocab, void *stream);
+/* tokens[row] (int64) = argmax of logits fp32 [rows][vocab], ties to the lowest id; pos[row] (int32) += 1. */
+int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int vocab, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,314 @@
+/*
+ * The rest of a decode step for small batches (at most 16 rows): weight-streaming GEMMs with fused RMS norm and
+ * epilogues, the embedding + first norm, and the greedy choice. Replaces, for sm_100a, the reference's Hopper-only
+ * slot GEMM k_wgmma with its STORE / RESID / RELU2 / ARGMAX epilogues (model/kernels/decode.cu:170-208,232-359) and
+ * its k_norm / k_rstd / k_commit (decode.cu:415-456,678-688). Model semantics are those of the reference's exported
+ * model (inference/modeling_nanochat.py:105-125,163-194): parameter-free RMS norm with eps FLT_EPSILON rounded to
+ * bf16, bf16 GEMM outputs, residual adds in bf16, relu^2 in bf16, fp32 logits.
+ *
+ * At 8 rows a d20 step reads 0.95 GB of weights and computes almost nothing: every GEMM is a stream of W with a
+ * handful of activation rows held on chip, bound by HBM and, at these sizes (3 to 170 MB per GEMM), by launch and
+ * ramp-up latency. So:
+ *   - y^T tile = W tile . x^T on mma.sync.m16n8k16 (bf16, fp32 accumulate) with the ROWS as the M dimension (16 slots,
+ *     rows 8..15 zero when there are at most 8) and 8 output features as N. W is the B operand and goes from global
+ *     memory straight to registers with one 16-byte load per thread and 32 k-values (a feature row is read in
+ *     64-byte runs by four lanes, every sector fully used); the MMA's k slots are permuted identically for A and B so
+ *     no shuffle or shared-memory staging is needed;
+ *   - a block owns 8 output features and splits K over its 8 warps; each warp issues all loads of its K slice before
+ *     the first MMA (5 to 20 independent 16-byte loads per thread in flight), partial tiles are summed through
+ *     shared memory;
+ *   - the RMS norm of the input is fused: activations stay in registers between the sum of squares (block-wide
+ *     through shared memory) and the MMAs, so a layer needs no separate norm kernel;
+ *   - epilogues: bf16 store, residual add, relu^2, or fp32 store (logits).
+ * These kernels wait for their predecessor with griddepcontrol.wait and are launched with programmatic stream
+ * serialisation, so inside a captured step the launch of each overlaps the tail of the one before.
+ */
+#include "ncb_common.cuh"
+
+constexpr int GEMM_WARPS = 8;
+constexpr int GEMM_THREADS = GEMM_WARPS * 32;
+constexpr int TILE_N = 8;         /* output features per block */
+constexpr int MAX_ROWS = 16;
+constexpr int MAX_K_ITERS = 20;   /* 32 k-values per iteration and warp: K <= 8 * 20 * 32 = 5120 */
+
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_RELU2 = 2, EPI_F32 = 3 };
+
+struct GemmArgs {
+    const bf16 *x;     /* [rows][K] */
+    const bf16 *w;     /* [N][K] */
+    const bf16 *resid; /* [rows][N] for EPI_RESID (may alias y) */
+    void *y;           /* [rows][N] bf16, or fp32 for EPI_F32 */
+    int rows, N, K, norm_input;
+};
+
+static __device__ __forceinline__ void mma_bf16(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+static __device__ __forceinline__ float sumsq_bf16x8(const uint4 &u) {
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&u);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        s += f.x * f.x + f.y * f.y;
+    }
+    return s;
+}
+
+static __device__ __forceinline__ uint4 scale_bf16x8(const uint4 &u, float r) {
+    uint4 out;
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&u);
+    __nv_bfloat162 *o = reinterpret_cast<__nv_bfloat162 *>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        o[i] = __floats2bfloat162_rn(f.x * r, f.y * r);
+    }
+    return out;
+}
+
+/* ITERS: 32-k iterations per warp (K = GEMM_WARPS * ITERS * 32 exactly); HI: rows 8..15 are in use. */
+template <int ITERS, bool HI, int EPI, bool NORM>
+__global__ void __launch_bounds__(GEMM_THREADS) k_skinny_gemm(GemmArgs a) {
+    __shared__ float part[GEMM_WARPS][16][TILE_N + 1];
+    __shared__ float ss[GEMM_WARPS][16];
+    __shared__ float rstd[16];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * TILE_N;
+    const int k_warp = warp * ITERS * 32;
+
+    /* the weights do not depend on the kernel before this one: start streaming them before waiting for it */
+    uint4 wv[ITERS];
+    const bf16 *wrow = a.w + (size_t)(n0 + g) * a.K + k_warp + 8 * t;
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) wv[i] = __ldcs(reinterpret_cast<const uint4 *>(wrow + 32 * i)); /* read once */
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    uint4 xlo[ITERS], xhi[HI ? ITERS : 1];
+    const bool lo_on = g < a.rows, hi_on = HI && g + 8 < a.rows;
+    const bf16 *xl = a.x + (size_t)g * a.K + k_warp + 8 * t, *xh = a.x + (size_t)(g + 8) * a.K + k_warp + 8 * t;
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        xlo[i] = lo_on ? *reinterpret_cast<const uint4 *>(xl + 32 * i) : make_uint4(0, 0, 0, 0);
+        if (HI) xhi[i] = hi_on ? *reinterpret_cast<const uint4 *>(xh + 32 * i) : make_uint4(0, 0, 0, 0);
+    }
+    if (NORM) { /* rows' 1 / sqrt(mean(x^2) + eps) over the full K, then x <- bf16(x * rstd) in registers */
+        float s_lo = 0.f, s_hi = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITERS; i++) {
+            s_lo += sumsq_bf16x8(xlo[i]);
+            if (HI) s_hi += sumsq_bf16x8(xhi[i]);
+        }
+        s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 1);
+        s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 2);
+        if (HI) {
+            s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 1);
+            s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 2);
+        }
+        if (t == 0) {
+            ss[warp][g] = s_lo;
+            ss[warp][g + 8] = HI ? s_hi : 0.f;
+        }
+        __syncthreads();
+        if (tid < 16) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < GEMM_WARPS; w++) s += ss[w][tid];
+            rstd[tid] = rsqrtf(s / (float)a.K + FLT_EPSILON);
+        }
+        __syncthreads();
+        const float r_lo = rstd[g], r_hi = rstd[g + 8];
+#pragma unroll
+        for (int i = 0; i < ITERS; i++) {
+            xlo[i] = scale_bf16x8(xlo[i], r_lo);
+            if (HI) xhi[i] = scale_bf16x8(xhi[i], r_hi);
+        }
+    }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        /* k slots (2t, 2t+1) and (2t+8, 2t+9) of the two MMAs take the thread's values 0..1, 2..3 and 4..5, 6..7 */
+        const uint32_t h0 = HI ? xhi[i].x : 0u, h1 = HI ? xhi[i].y : 0u, h2 = HI ? xhi[i].z : 0u, h3 = HI ? xhi[i].w : 0u;
+        mma_bf16(acc, xlo[i].x, h0, xlo[i].y, h1, wv[i].x, wv[i].y);
+        mma_bf16(acc, xlo[i].z, h2, xlo[i].w, h3, wv[i].z, wv[i].w);
+    }
+    /* C: acc[0], acc[1] = row g, features 2t, 2t+1; acc[2], acc[3] = row g+8 */
+    part[warp][g][2 * t] = acc[0];
+    part[warp][g][2 * t + 1] = acc[1];
+    part[warp][g + 8][2 * t] = acc[2];
+    part[warp][g + 8][2 * t + 1] = acc[3];
+    __syncthreads();
+    if (tid < 16 * TILE_N) {
+        const int row = tid / TILE_N, col = tid % TILE_N;
+        if (row < a.rows) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < GEMM_WARPS; w++) v += part[w][row][col];
+            const size_t at = (size_t)row * a.N + n0 + col;
+            if (EPI == EPI_F32) {
+                reinterpret_cast<float *>(a.y)[at] = v;
+            } else {
+                bf16 out = __float2bfloat16_rn(v);
+                if (EPI == EPI_RESID) out = __float2bfloat16_rn(__bfloat162float(a.resid[at]) + __bfloat162float(out));
+                if (EPI == EPI_RELU2) {
+                    const float r = fmaxf(__bfloat162float(out), 0.f);
+                    out = __float2bfloat16_rn(r * r);
+                }
+                reinterpret_cast<bf16 *>(a.y)[at] = out;
+            }
+        }
+    }
+}
+
+/* h[row] = rms_norm(embed[token[row]]), one warp per row (decode.cu:415-443 EMBED, with a bf16 table). */
+__global__ void __launch_bounds__(128) k_embed_norm(const bf16 *embed, const long long *tokens, bf16 *h, int rows, int C,
+                                                    int vocab) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    long long token = tokens[row];
+    if (token < 0 || token >= vocab) token = 0;
+    const bf16 *e = embed + (size_t)token * C;
+    float s = 0.f;
+    for (int i = lane * 8; i < C; i += 256) s += sumsq_bf16x8(*reinterpret_cast<const uint4 *>(e + i));
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float r = rsqrtf(s / (float)C + FLT_EPSILON);
+    for (int i = lane * 8; i < C; i += 256)
+        *reinterpret_cast<uint4 *>(h + (size_t)row * C + i) = scale_bf16x8(*reinterpret_cast<const uint4 *>(e + i), r);
+}
+
+/* tokens[row] = argmax(logits[row]) (ties to the lowest id, decode.cu:90-96), pos[row] += 1; one block per row. */
+__global__ void __launch_bounds__(1024) k_greedy(const float *logits, long long *tokens, int32_t *pos, int vocab) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float *z = logits + (size_t)row * vocab;
+    float v = -INFINITY;
+    int at = 0x7fffffff;
+    for (int i = tid; i < vocab; i += 1024) {
+        const float x = z[i];
+        if (x > v) v = x, at = i; /* ascending i: the first maximum wins */
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ov > v || (ov == v && oi < at)) v = ov, at = oi;
+    }
+    if (lane == 0) best_v[warp] = v, best_i[warp] = at;
+    __syncthreads();
+    if (warp == 0) {
+        v = best_v[lane], at = best_i[lane];
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ov > v || (ov == v && oi < at)) v = ov, at = oi;
+        }
+        if (lane == 0) {
+            tokens[row] = at == 0x7fffffff ? 0 : at;
+            pos[row] += 1;
+        }
+    }
+}
+
+/* ---- host side ---------------------------------------------------------------------------------------------- */
+
+template <typename... Args>
+static int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, args...) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+}
+
+template <int ITERS, bool HI, bool NORM> static int launch_gemm_epi(const GemmArgs &a, int epilogue, cudaStream_t stream) {
+    const dim3 grid(a.N / TILE_N), block(GEMM_THREADS);
+    switch (epilogue) {
+    case EPI_STORE: return launch_pdl(k_skinny_gemm<ITERS, HI, EPI_STORE, NORM>, grid, block, stream, a);
+    case EPI_RESID: return launch_pdl(k_skinny_gemm<ITERS, HI, EPI_RESID, NORM>, grid, block, stream, a);
+    case EPI_RELU2: return launch_pdl(k_skinny_gemm<ITERS, HI, EPI_RELU2, NORM>, grid, block, stream, a);
+    case EPI_F32: return launch_pdl(k_skinny_gemm<ITERS, HI, EPI_F32, NORM>, grid, block, stream, a);
+    default: return NCB_ERR_ARG;
+    }
+}
+
+template <int ITERS> static int launch_gemm_rows(const GemmArgs &a, int epilogue, cudaStream_t stream) {
+    constexpr bool CAN_NORM = ITERS <= 8; /* the fused norm keeps the whole K slice of x in registers */
+    if (a.norm_input) {
+        if (!CAN_NORM) return NCB_ERR_UNSUPPORTED;
+        return a.rows > 8 ? launch_gemm_epi<(CAN_NORM ? ITERS : 1), true, true>(a, epilogue, stream)
+                          : launch_gemm_epi<(CAN_NORM ? ITERS : 1), false, true>(a, epilogue, stream);
+    }
+    return a.rows > 8 ? launch_gemm_epi<ITERS, true, false>(a, epilogue, stream)
+                      : launch_gemm_epi<ITERS, false, false>(a, epilogue, stream);
+}
+
+extern "C" {
+
+/*
+ * y = epilogue(norm?(x) . W^T) for rows <= 16 activation rows.
+ *   x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3); resid bf16 [rows][N] for epilogue 1
+ *   (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding the product), 2 relu^2, 3 fp32.
+ *   norm_input != 0 applies the parameter-free RMS norm (eps FLT_EPSILON, rounded to bf16) to x first.
+ * K must be a multiple of 256 and at most 5120 (at most 2048 with norm_input), N a multiple of 8.
+ */
+int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
+                int epilogue, void *stream) {
+    if (rows < 0 || rows > MAX_ROWS || N <= 0 || K <= 0 || N % TILE_N || K % (GEMM_WARPS * 32)) return NCB_ERR_ARG;
+    if (K / (GEMM_WARPS * 32) > MAX_K_ITERS) return NCB_ERR_UNSUPPORTED;
+    if (rows == 0) return NCB_OK;
+    if (!x || !w || !y || (epilogue == EPI_RESID && !resid)) return NCB_ERR_ARG;
+    if (((uintptr_t)x | (uintptr_t)w) % 16 || (uintptr_t)y % 4) return NCB_ERR_ALIGN;
+    const GemmArgs a = {(const bf16 *)x, (const bf16 *)w, (const bf16 *)resid, y, rows, N, K, norm_input};
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (K / (GEMM_WARPS * 32)) {
+    case 1: return launch_gemm_rows<1>(a, epilogue, s);
+    case 2: return launch_gemm_rows<2>(a, epilogue, s);
+    case 3: return launch_gemm_rows<3>(a, epilogue, s);
+    case 4: return launch_gemm_rows<4>(a, epilogue, s);
+    case 5: return launch_gemm_rows<5>(a, epilogue, s);
+    case 6: return launch_gemm_rows<6>(a, epilogue, s);
+    case 8: return launch_gemm_rows<8>(a, epilogue, s);
+    case 10: return launch_gemm_rows<10>(a, epilogue, s);
+    case 12: return launch_gemm_rows<12>(a, epilogue, s);
+    case 16: return launch_gemm_rows<16>(a, epilogue, s);
+    case 20: return launch_gemm_rows<20>(a, epilogue, s);
+    default: return NCB_ERR_UNSUPPORTED;
+    }
+}
+
+/* h bf16 [rows][C] = rms_norm(embed[tokens]); tokens int64 [rows]; C a multiple of 8. */
+int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, int vocab, void *stream) {
+    if (rows < 0 || C <= 0 || C % 8 || vocab <= 0) return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    if (!embed || !tokens || !h) return NCB_ERR_ARG;
+    if (((uintptr_t)embed | (uintptr_t)h) % 16) return NCB_ERR_ALIGN;
+    return launch_pdl(k_embed_norm, dim3((rows + 3) / 4), dim3(128), (cudaStream_t)stream, (const bf16 *)embed,
+                      (const long long *)tokens, (bf16 *)h, rows, C, vocab);
+}
+
+/* tokens[row] = argmax(logits[row]) over fp32 [rows][vocab], ties to the lowest id; pos[row] += 1. */
+int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int vocab, void *stream) {
+    if (rows < 0 || vocab <= 0) return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    if (!logits || !tokens || !pos) return NCB_ERR_ARG;
+    return launch_pdl(k_greedy, dim3(rows), dim3(1024), (cudaStream_t)stream, (const float *)logits,
+                      (long long *)tokens, (int32_t *)pos, vocab);
+}
+
+} /* extern "C" */

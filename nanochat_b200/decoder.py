@@ -27,6 +27,7 @@ from torch import Tensor
 
 from . import attention as ops
 from .kv_cache import HEAD_DIM, Fp8KVCache
+from .native import check, cuda_library, pointer, stream
 
 EPS = 1.1920928955078125e-07  # FLT_EPSILON (reference model/ops/linear.py:20)
 
@@ -95,6 +96,7 @@ class Decoder:
         self.cos, self.sin = ops.rotary_table(self.capacity, cfg.rope_theta, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.windows = cfg.windows or [0] * cfg.n_layers
+        self.use_fused = True  # decode steps of <= 16 rows run on the decode_step kernels when the shapes allow
         self._graphs: dict[int, tuple] = {}
         self._workspaces: dict[tuple[int, int], Tensor] = {}
 
@@ -138,6 +140,58 @@ class Decoder:
         """The bf16 head GEMM with its fp32 accumulator kept as the output (modeling_nanochat.py:190-192)."""
         return torch.mm(hidden, self.w.lm_head.T, out_dtype=torch.float32)
 
+    # ---- the same pass for at most 16 rows with this package's own GEMM kernels --------------------------------
+
+    def fused_supported(self, rows: int) -> bool:
+        """The decode_step kernels cover at most 16 rows, hidden sizes up to 2048 (fused norm keeps a row slice in
+        registers) and intermediate sizes up to 5120, all multiples of 256, with the default residual mixing."""
+        cfg = self.cfg
+        return (rows <= 16 and cfg.hidden % 256 == 0 and cfg.hidden <= 2048 and cfg.intermediate % 256 == 0
+                and cfg.intermediate <= 5120 and (cfg.n_heads * HEAD_DIM) % 256 == 0
+                and cfg.n_heads * HEAD_DIM <= 5120 and cfg.vocab % 8 == 0
+                and all(l.resid_lambda == 1.0 and l.x0_lambda == 0.0 for l in self.w.layers))
+
+    def fused_buffers(self, rows: int) -> dict[str, Tensor]:
+        cfg, dev, bf = self.cfg, self.device, torch.bfloat16
+        return {"h": torch.empty((rows, cfg.hidden), dtype=bf, device=dev),
+                "qkv": torch.empty((rows, cfg.qkv_width), dtype=bf, device=dev),
+                "q": torch.empty((rows, cfg.n_heads, HEAD_DIM), dtype=bf, device=dev),
+                "att": torch.empty((rows, cfg.n_heads, HEAD_DIM), dtype=bf, device=dev),
+                "u": torch.empty((rows, cfg.intermediate), dtype=bf, device=dev),
+                "lens": torch.empty(rows, dtype=torch.int32, device=dev),
+                "logits": torch.empty((rows, cfg.vocab), dtype=torch.float32, device=dev)}
+
+    def fused_step(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int, buf: dict[str, Tensor],
+                   choose: bool = True) -> Tensor:
+        """One step for rows <= 16 on the decode_step kernels: fp32 logits in buf["logits"]; with `choose`, tokens
+        become the greedy choices and pos advances by one. 7 launches per layer: qkv GEMM (norm fused), append,
+        split attention, merge, o GEMM + residual, up GEMM (norm fused) + relu^2, down GEMM + residual."""
+        cfg, lib, s = self.cfg, cuda_library("decode_step"), stream()
+        rows, C, Fd, A = tokens.shape[0], cfg.hidden, cfg.intermediate, cfg.n_heads * HEAD_DIM
+        workspace = self._workspace(rows, max_kv_len)
+        h, qkv, att, u = buf["h"], buf["qkv"], buf["att"], buf["u"]
+
+        def gemm(x, w, resid, y, n, k, norm, epilogue):
+            check(lib.skinny_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue, s),
+                  "skinny_gemm")
+
+        torch.add(pos, 1, out=buf["lens"])
+        check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
+        for i, layer in enumerate(self.w.layers):
+            gemm(h, layer.wqkv, None, qkv, cfg.qkv_width, C, 1, 0)
+            ops.kv_append(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i], cfg.n_heads,
+                          slot_map=slot_map, q_out=buf["q"], status=self.status)
+            ops.decode_attention(buf["q"], self.caches[i], buf["lens"], max_kv_len, slot_map=slot_map,
+                                 window=self.windows[i], workspace=workspace, out=att, status=self.status)
+            gemm(att, layer.wo, h, h, C, A, 0, 1)
+            gemm(h, layer.wup, None, u, Fd, C, 1, 2)
+            gemm(u, layer.wdown, h, h, C, Fd, 0, 1)
+        gemm(h, self.w.lm_head, None, buf["logits"], cfg.vocab, C, 1, 3)
+        if choose:
+            check(lib.greedy_choice(pointer(buf["logits"]), pointer(tokens), pointer(pos), rows, cfg.vocab, s),
+                  "greedy_choice")
+        return buf["logits"]
+
     # ---- prefill ----------------------------------------------------------------------------------------------
 
     @torch.no_grad()
@@ -163,9 +217,14 @@ class Decoder:
         tokens = torch.zeros(batch, dtype=torch.long, device=dev)
         pos = torch.zeros(batch, dtype=torch.int32, device=dev)
         slot_map = torch.arange(batch, dtype=torch.int32, device=dev)
-        logits = torch.empty((batch, self.cfg.vocab), dtype=torch.float32, device=dev)
+        fused = self.use_fused and self.fused_supported(batch)
+        buf = self.fused_buffers(batch) if fused else None
+        logits = buf["logits"] if fused else torch.empty((batch, self.cfg.vocab), dtype=torch.float32, device=dev)
 
         def body():
+            if fused:
+                self.fused_step(tokens, pos, slot_map, self.capacity, buf)
+                return
             logits.copy_(self.head(self.hidden_rows(tokens, pos, slot_map, self.capacity)))
             tokens.copy_(logits.argmax(-1))  # ties to the lowest id, as decode.cu:90-96
             pos.add_(1)

@@ -23,7 +23,7 @@ KERNELS = PACKAGE / "csrc"
 INCLUDE = PACKAGE.parent / "include"
 NATIVE = PACKAGE / "_native"
 HEAD_DIM = 128
-LIBRARIES = ("kv_append", "decode_attn")
+LIBRARIES = ("kv_append", "decode_attn", "decode_step")
 
 c_ptr, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 SIGNATURES = {
@@ -42,6 +42,11 @@ SIGNATURES = {
         "decode_attn_fp8_split": ([c_ptr] * 5 + [c_ll] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_merge": ([c_ptr, c_int, c_ll, c_ptr, c_ptr], c_int),
         "decode_attn_merge_peers": ([c_ptr, c_ptr, c_int, c_int, ctypes.c_uint, c_ll, c_ptr, c_ptr, c_ptr], c_int),
+    },
+    "decode_step": {
+        "skinny_gemm": ([c_ptr] * 4 + [c_int] * 5 + [c_ptr], c_int),
+        "embed_norm": ([c_ptr] * 3 + [c_int] * 3 + [c_ptr], c_int),
+        "greedy_choice": ([c_ptr] * 3 + [c_int] * 2 + [c_ptr], c_int),
     },
 }
 STATUS = {0: "ok", 1: "invalid argument", 2: "misaligned pointer or stride", 3: "workspace too small",

@@ -46,6 +46,31 @@ def test_step_logits_match_cpu_restatement_and_reference():
     assert int(dec.status.item()) == 0
 
 
+@torch.no_grad()
+def test_fused_step_logits_match_cpu_restatement_and_reference():
+    """The same teacher-forced run on the decode_step kernels (own GEMMs with fused norm and epilogues)."""
+    dec, cfg, w = gpu_decoder()
+    assert dec.fused_supported(2)
+    slot_map = torch.arange(2, dtype=torch.int32, device="cuda")
+    pos = torch.zeros(2, dtype=torch.int32, device="cuda")
+    buf = dec.fused_buffers(2)
+
+    def step(tok):
+        logits = dec.fused_step(tok.cuda(), pos, slot_map, int(pos.max()) + 1, buf, choose=False).cpu()
+        pos.add_(1)
+        return logits
+
+    got = teacher_forced_logits(step)
+    oracle = OracleDecoder(cfg, w, n_seqs=2)
+    cpu = teacher_forced_logits(lambda tok: oracle.step(tok, [0, 1]))
+    err = np.abs(got - cpu)
+    assert err.max() < 1e-2 and err.mean() < 1.5e-3, (err.max(), err.mean())
+    ref = uncapped(GOLDEN["logits"], float(GOLDEN["softcap"]))
+    err = np.abs(got - ref)
+    assert err.max() < 2.5e-2 and err.mean() < 4e-3, (err.max(), err.mean())
+    assert int(dec.status.item()) == 0
+
+
 def test_generate_prefill_and_graph_decode_reproduce_reference_tokens():
     dec, _, _ = gpu_decoder()
     prompts = GOLDEN["prompt"].tolist()
@@ -70,11 +95,12 @@ def test_generate_prefill_and_graph_decode_reproduce_reference_tokens():
 def test_ragged_prompts_and_gqa_shapes_run_and_agree_with_rowwise_logits():
     """A GQA model with prompts of different lengths: generate() (prefill rows + graph decode) against the eager
     row-at-a-time path."""
-    cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=4, n_kv_heads=1, intermediate=1024, vocab=300, max_len=128)
+    cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=4, n_kv_heads=1, intermediate=1024, vocab=304, max_len=128)
     w = DecoderWeights.random_init(cfg, seed=5, device="cuda", std=0.05)
     gen = torch.Generator().manual_seed(6)
-    prompts = [torch.randint(0, 300, (n,), generator=gen).tolist() for n in (1, 9, 70)]
+    prompts = [torch.randint(0, 304, (n,), generator=gen).tolist() for n in (1, 9, 70)]
     dec = Decoder(cfg, w, 3)
+    assert dec.fused_supported(3)  # generate() decodes on the decode_step kernels, the check below on torch ops
     tokens, _ = dec.generate(prompts, 5)
     ref = Decoder(cfg, w, 3)
     with torch.no_grad():
