@@ -183,6 +183,9 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int G = a.Hq / a.Hkv;
 
+    /* launched with programmatic stream serialisation: everything this kernel reads (lens, q, the cache with the
+     * token appended a moment ago) comes from kernels before it */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int len = a.lens[b];
     const int slot = a.slot_map ? a.slot_map[b] : b;
     if (len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots) {
@@ -615,15 +618,25 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     AttnArgs a = {(const bf16 *)q, (const uint8_t *)kv_cache, (const int32_t *)lens, (const int32_t *)slot_map,
                   (float *)workspace, B, Hq, Hkv, n_slots, pages_per_slot, window, chunk_pages, max_chunks,
                   softmax_scale * 1.4426950408889634f, (int *)status};
-    const dim3 grid(max_chunks, Hkv, B);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(max_chunks, Hkv, B);
+    config.blockDim = dim3(THREADS);
+    config.dynamicSmemBytes = ATTN_SMEM;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    cudaError_t rc;
     if (Hq / Hkv <= 4) {
         if (prepare<1>() != cudaSuccess) return NCB_ERR_LAUNCH;
-        k_decode_attn<1><<<grid, THREADS, ATTN_SMEM, stream>>>(a);
+        rc = cudaLaunchKernelEx(&config, k_decode_attn<1>, a);
     } else {
         if (prepare<2>() != cudaSuccess) return NCB_ERR_LAUNCH;
-        k_decode_attn<2><<<grid, THREADS, ATTN_SMEM, stream>>>(a);
+        rc = cudaLaunchKernelEx(&config, k_decode_attn<2>, a);
     }
-    return cudaGetLastError() == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+    return rc == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 static int launch_merge(const MergeArgs &a, cudaStream_t stream) {

@@ -115,6 +115,10 @@ struct AppendArgs {
 };
 
 __global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
+    /* launched with programmatic stream serialisation: wait for the kernel that produced qkv and pos, then let the
+     * next kernel's launch overlap this one (it waits the same way before it reads the cache or q) */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int items = a.Hq + 2 * a.Hkv;
     const long long item = (long long)blockIdx.x * ITEMS_PER_BLOCK + threadIdx.x / LANES;
     if (item >= a.rows * items) return; /* whole 8-lane groups leave together */
@@ -204,8 +208,16 @@ int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const
                     (const float *)sin, (const int32_t *)pos, (const int32_t *)slot_map, (bf16 *)q_out,
                     (uint8_t *)kv_cache, rows, qkv_row_stride, Hq, Hkv, table_len, n_slots, pages_per_slot,
                     (int *)status};
-    k_kv_append<<<(unsigned)blocks, BLOCK, 0, (cudaStream_t)stream>>>(a);
-    return cudaGetLastError() == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)blocks);
+    config.blockDim = dim3(BLOCK);
+    config.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, k_kv_append, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 } /* extern "C" */
