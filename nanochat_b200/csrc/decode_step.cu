@@ -14,9 +14,10 @@
  *     memory straight to registers with one 16-byte load per thread and 32 k-values (a feature row is read in
  *     64-byte runs by four lanes, every sector fully used); the MMA's k slots are permuted identically for A and B so
  *     no shuffle or shared-memory staging is needed;
- *   - a block owns 8 output features and splits K over its 8 warps; each warp issues all loads of its K slice before
- *     the first MMA (5 to 20 independent 16-byte loads per thread in flight), partial tiles are summed through
- *     shared memory;
+ *   - a block owns tiles of 8 output features and splits K over its 8 warps; each warp issues all loads of its K
+ *     slice before the first MMA (5 to 20 independent 16-byte loads per thread in flight), partial tiles are summed
+ *     through shared memory; a block walks over several tiles when there are more tiles than resident blocks, with
+ *     the next tile's weights already streaming, so the activations are loaded and normed once per block;
  *   - the RMS norm of the input is fused: activations stay in registers between the sum of squares (block-wide
  *     through shared memory) and the MMAs, so a layer needs no separate norm kernel;
  *   - epilogues: bf16 store, residual add, relu^2, or fp32 store (logits).
@@ -72,21 +73,34 @@ static __device__ __forceinline__ uint4 scale_bf16x8(const uint4 &u, float r) {
     return out;
 }
 
-/* ITERS: 32-k iterations per warp (K = GEMM_WARPS * ITERS * 32 exactly); HI: rows 8..15 are in use. */
+/* ITERS: 32-k iterations per warp (K = GEMM_WARPS * ITERS * 32 exactly); HI: rows 8..15 are in use.
+ * A block keeps its activation slice (normed once) in registers and walks over the feature tiles
+ * blockIdx.x, blockIdx.x + gridDim.x, ...; while it reduces one tile the next tile's weights are already in flight
+ * (PREFETCH: only where two weight slices fit the register file). */
 template <int ITERS, bool HI, int EPI, bool NORM>
 __global__ void __launch_bounds__(GEMM_THREADS) k_skinny_gemm(GemmArgs a) {
+    constexpr bool PREFETCH = ITERS <= 8;
     __shared__ float part[GEMM_WARPS][16][TILE_N + 1];
     __shared__ float ss[GEMM_WARPS][16];
     __shared__ float rstd[16];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * TILE_N;
+    const int tiles = a.N / TILE_N;
     const int k_warp = warp * ITERS * 32;
+    const bf16 *wbase = a.w + (size_t)g * a.K + k_warp + 8 * t;
 
     /* the weights do not depend on the kernel before this one: start streaming them before waiting for it */
-    uint4 wv[ITERS];
-    const bf16 *wrow = a.w + (size_t)(n0 + g) * a.K + k_warp + 8 * t;
+    uint4 wv[ITERS], wnext[PREFETCH ? ITERS : 1];
+    int tile = blockIdx.x;
+    if (tile < tiles) {
+        const bf16 *wrow = wbase + (size_t)tile * TILE_N * a.K;
 #pragma unroll
-    for (int i = 0; i < ITERS; i++) wv[i] = __ldcs(reinterpret_cast<const uint4 *>(wrow + 32 * i)); /* read once */
+        for (int i = 0; i < ITERS; i++) wv[i] = __ldcs(reinterpret_cast<const uint4 *>(wrow + 32 * i)); /* read once */
+    }
+    if (PREFETCH && tile + (int)gridDim.x < tiles) {
+        const bf16 *wrow = wbase + (size_t)(tile + gridDim.x) * TILE_N * a.K;
+#pragma unroll
+        for (int i = 0; i < ITERS; i++) wnext[i] = __ldcs(reinterpret_cast<const uint4 *>(wrow + 32 * i));
+    }
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -131,39 +145,58 @@ __global__ void __launch_bounds__(GEMM_THREADS) k_skinny_gemm(GemmArgs a) {
             if (HI) xhi[i] = scale_bf16x8(xhi[i], r_hi);
         }
     }
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (; tile < tiles; tile += gridDim.x) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f}; /* two chains: MMA latency overlaps */
 #pragma unroll
-    for (int i = 0; i < ITERS; i++) {
-        /* k slots (2t, 2t+1) and (2t+8, 2t+9) of the two MMAs take the thread's values 0..1, 2..3 and 4..5, 6..7 */
-        const uint32_t h0 = HI ? xhi[i].x : 0u, h1 = HI ? xhi[i].y : 0u, h2 = HI ? xhi[i].z : 0u, h3 = HI ? xhi[i].w : 0u;
-        mma_bf16(acc, xlo[i].x, h0, xlo[i].y, h1, wv[i].x, wv[i].y);
-        mma_bf16(acc, xlo[i].z, h2, xlo[i].w, h3, wv[i].z, wv[i].w);
-    }
-    /* C: acc[0], acc[1] = row g, features 2t, 2t+1; acc[2], acc[3] = row g+8 */
-    part[warp][g][2 * t] = acc[0];
-    part[warp][g][2 * t + 1] = acc[1];
-    part[warp][g + 8][2 * t] = acc[2];
-    part[warp][g + 8][2 * t + 1] = acc[3];
-    __syncthreads();
-    if (tid < 16 * TILE_N) {
-        const int row = tid / TILE_N, col = tid % TILE_N;
-        if (row < a.rows) {
-            float v = 0.f;
+        for (int i = 0; i < ITERS; i++) {
+            /* k slots (2t, 2t+1) and (2t+8, 2t+9) of the two MMAs take the thread's values 0..1, 2..3 and 4..5, 6..7 */
+            const uint32_t h0 = HI ? xhi[i].x : 0u, h1 = HI ? xhi[i].y : 0u, h2 = HI ? xhi[i].z : 0u,
+                           h3 = HI ? xhi[i].w : 0u;
+            mma_bf16(acc, xlo[i].x, h0, xlo[i].y, h1, wv[i].x, wv[i].y);
+            mma_bf16(acc2, xlo[i].z, h2, xlo[i].w, h3, wv[i].z, wv[i].w);
+        }
+        /* the tile after next starts streaming now; the next one becomes current */
+        const int after = tile + (PREFETCH ? 2 : 1) * (int)gridDim.x;
+        if (PREFETCH) {
 #pragma unroll
-            for (int w = 0; w < GEMM_WARPS; w++) v += part[w][row][col];
-            const size_t at = (size_t)row * a.N + n0 + col;
-            if (EPI == EPI_F32) {
-                reinterpret_cast<float *>(a.y)[at] = v;
-            } else {
-                bf16 out = __float2bfloat16_rn(v);
-                if (EPI == EPI_RESID) out = __float2bfloat16_rn(__bfloat162float(a.resid[at]) + __bfloat162float(out));
-                if (EPI == EPI_RELU2) {
-                    const float r = fmaxf(__bfloat162float(out), 0.f);
-                    out = __float2bfloat16_rn(r * r);
-                }
-                reinterpret_cast<bf16 *>(a.y)[at] = out;
+            for (int i = 0; i < ITERS; i++) wv[i] = wnext[i];
+        }
+        if (after < tiles) {
+            const bf16 *wrow = wbase + (size_t)after * TILE_N * a.K;
+#pragma unroll
+            for (int i = 0; i < ITERS; i++) {
+                const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(wrow + 32 * i));
+                if (PREFETCH) wnext[i] = v; else wv[i] = v;
             }
         }
+        /* C: acc[0], acc[1] = row g, features 2t, 2t+1; acc[2], acc[3] = row g+8 */
+        part[warp][g][2 * t] = acc[0] + acc2[0];
+        part[warp][g][2 * t + 1] = acc[1] + acc2[1];
+        part[warp][g + 8][2 * t] = acc[2] + acc2[2];
+        part[warp][g + 8][2 * t + 1] = acc[3] + acc2[3];
+        __syncthreads();
+        if (tid < 16 * TILE_N) {
+            const int row = tid / TILE_N, col = tid % TILE_N;
+            if (row < a.rows) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < GEMM_WARPS; w++) v += part[w][row][col];
+                const size_t at = (size_t)row * a.N + (size_t)tile * TILE_N + col;
+                if (EPI == EPI_F32) {
+                    reinterpret_cast<float *>(a.y)[at] = v;
+                } else {
+                    bf16 out = __float2bfloat16_rn(v);
+                    if (EPI == EPI_RESID)
+                        out = __float2bfloat16_rn(__bfloat162float(a.resid[at]) + __bfloat162float(out));
+                    if (EPI == EPI_RELU2) {
+                        const float r = fmaxf(__bfloat162float(out), 0.f);
+                        out = __float2bfloat16_rn(r * r);
+                    }
+                    reinterpret_cast<bf16 *>(a.y)[at] = out;
+                }
+            }
+        }
+        __syncthreads(); /* the partial sums are consumed before the next tile overwrites them */
     }
 }
 
@@ -236,13 +269,31 @@ static int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream
     return cudaLaunchKernelEx(&config, kernel, args...) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
+/* Blocks for `tiles` feature tiles: everything resident at once when it fits, else an even number of tiles per
+ * block (640 tiles on 444 slots -> 320 blocks of 2) so that no block is left with one more than the others. */
+template <typename K> static int grid_for(K kernel, int tiles, bool prefetch) {
+    if (!prefetch) return tiles; /* without a second weight slice in registers a block's tiles would serialise */
+    static int slots = 0; /* per instantiation; the same on every device of a homogeneous box */
+    if (!slots) {
+        int device = 0, sms = 148, per_sm = 1;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, GEMM_THREADS, 0) != cudaSuccess || per_sm < 1)
+            per_sm = 1;
+        slots = sms * per_sm;
+    }
+    const int per_block = (tiles + slots - 1) / slots;
+    return (tiles + per_block - 1) / per_block;
+}
+
 template <int ITERS, bool HI, bool NORM> static int launch_gemm_epi(const GemmArgs &a, int epilogue, cudaStream_t stream) {
-    const dim3 grid(a.N / TILE_N), block(GEMM_THREADS);
+    const int tiles = a.N / TILE_N;
+    const dim3 block(GEMM_THREADS);
     switch (epilogue) {
-    case EPI_STORE: return launch_pdl(k_skinny_gemm<ITERS, HI, EPI_STORE, NORM>, grid, block, stream, a);
-    case EPI_RESID: return launch_pdl(k_skinny_gemm<ITERS, HI, EPI_RESID, NORM>, grid, block, stream, a);
-    case EPI_RELU2: return launch_pdl(k_skinny_gemm<ITERS, HI, EPI_RELU2, NORM>, grid, block, stream, a);
-    case EPI_F32: return launch_pdl(k_skinny_gemm<ITERS, HI, EPI_F32, NORM>, grid, block, stream, a);
+    case EPI_STORE: { auto k = k_skinny_gemm<ITERS, HI, EPI_STORE, NORM>; return launch_pdl(k, dim3(grid_for(k, tiles, ITERS <= 8)), block, stream, a); }
+    case EPI_RESID: { auto k = k_skinny_gemm<ITERS, HI, EPI_RESID, NORM>; return launch_pdl(k, dim3(grid_for(k, tiles, ITERS <= 8)), block, stream, a); }
+    case EPI_RELU2: { auto k = k_skinny_gemm<ITERS, HI, EPI_RELU2, NORM>; return launch_pdl(k, dim3(grid_for(k, tiles, ITERS <= 8)), block, stream, a); }
+    case EPI_F32: { auto k = k_skinny_gemm<ITERS, HI, EPI_F32, NORM>; return launch_pdl(k, dim3(grid_for(k, tiles, ITERS <= 8)), block, stream, a); }
     default: return NCB_ERR_ARG;
     }
 }
