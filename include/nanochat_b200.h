@@ -120,6 +120,22 @@ int decode_attn_fp8_partial(const void *q, const void *kv_cache, const void *len
                             float softmax_scale, void *status, void *stream);
 
 /*
+ * kv_append_fp8 and decode_attn_fp8 for one new token per sequence in the same two launches as decode_attn_fp8
+ * alone (replaces k_prologue + k_attn, decode.cu:859-863, as a pair): every block of the split-KV kernel first does
+ * the append's arithmetic for its own heads — q rows stay in shared memory, the block whose chunk holds the new
+ * position writes that kv head's k and v bytes and scales into the cache — and then attends over positions
+ * [max(0, pos[b] + 1 - window), pos[b] + 1). Same arithmetic as kv_append_fp8 (shared code), so the cache bytes are
+ * identical; q is not written out. Arguments as for the two entry points; `pos` int32 [B] takes the place of lens,
+ * max_kv_len bounds pos[b] + 1. Rows must address distinct slots (rows sharing a slot, as in prefill, need the
+ * separate entry points, where every row's append lands before any row attends).
+ */
+int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                         const void *pos, const void *slot_map, void *kv_cache, void *workspace,
+                         long long workspace_bytes, void *out, int B, int Hq, int Hkv, long long qkv_row_stride,
+                         int table_len, int n_slots, int pages_per_slot, int max_kv_len, int window, int chunk_pages,
+                         float softmax_scale, void *status, void *stream);
+
+/*
  * The first of decode_attn_fp8's two launches alone: the split-KV kernel, leaving one state per (b, h, chunk) in
  * the workspace. For timing that kernel by itself and for callers that merge elsewhere; same arguments and
  * checks as decode_attn_fp8 without `out`.

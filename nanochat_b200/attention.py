@@ -86,6 +86,36 @@ def decode_attention(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int
     return out
 
 
+def decode_step_attention(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tensor, sin: Tensor, pos: Tensor,
+                          cache: Fp8KVCache, Hq: int, max_kv_len: int, slot_map: Tensor | None = None,
+                          window: int = 0, chunk_pages: int = 0, softmax_scale: float | None = None,
+                          workspace: Tensor | None = None, out: Tensor | None = None,
+                          status: Tensor | None = None) -> Tensor:
+    """kv_append + decode_attention for one new token per sequence in two launches instead of three: the attention
+    kernel norms, rotates, quantises and stores the token's q, k, v itself, then attends over positions
+    [.., pos + 1). Same cache bytes and outputs as the two calls; q is not returned. Rows must address distinct
+    slots; max_kv_len bounds pos + 1."""
+    rows, Hkv = qkv.shape[0], cache.kv_heads
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(-1) == 1 and qkv.shape[1] == (Hq + 2 * Hkv) * HEAD_DIM
+    assert pos.dtype == torch.int32 and pos.shape == (rows,) and pos.is_contiguous()
+    assert cos.shape == sin.shape and cos.shape[1] == HEAD_DIM // 2 and cos.is_contiguous() and sin.is_contiguous()
+    assert q_gain.dtype == k_gain.dtype == cos.dtype == sin.dtype == torch.float32
+    assert slot_map is None or (slot_map.dtype == torch.int32 and slot_map.shape == (rows,))
+    need = workspace_bytes(rows, Hq, Hkv, min(max_kv_len, cache.capacity), chunk_pages)
+    if workspace is None:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=qkv.device)
+    if out is None:
+        out = torch.empty((rows, Hq, HEAD_DIM), dtype=torch.bfloat16, device=qkv.device)
+    scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
+    rc = cuda_library("decode_attn").decode_step_attn_fp8(
+        pointer(qkv), pointer(q_gain), pointer(k_gain), pointer(cos), pointer(sin), pointer(pos), pointer(slot_map),
+        pointer(cache.pages), pointer(workspace), workspace.numel(), pointer(out), rows, Hq, Hkv, qkv.stride(0),
+        cos.shape[0], cache.n_slots, cache.pages_per_slot, max_kv_len, window, chunk_pages, scale, pointer(status),
+        stream())
+    check(rc, "decode_step_attn_fp8")
+    return out
+
+
 def decode_attention_static(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int,
                             slot_map: Tensor | None = None, window: int = 0, chunk_pages: int = 0,
                             softmax_scale: float | None = None, out: Tensor | None = None,

@@ -8,8 +8,8 @@
  *
  *   - one thread block per (sequence, kv head, chunk of pages); a page (include/nanochat_b200.h) is one contiguous
  *     16,896-byte record fetched by ONE cp.async.bulk that signals an mbarrier. Each of the block's WARPS warps
- *     owns one shared-memory stage and one barrier: it waits for its page, consumes it, draws the chunk's next
- *     unassigned page from a shared counter and immediately issues it into the same stage. Warps never synchronise with each
+ *     owns one shared-memory stage and one barrier: it takes every WARPS-th page of the chunk, waits for it,
+ *     consumes it and immediately issues its next page into the same stage. Warps never synchronise with each
  *     other until the end, a barrier is only ever waited on by the warp that armed it (so its phases are observed
  *     strictly in order), and three blocks of four warps per SM keep twelve pages (about 200 KB) in flight or in
  *     use per SM while staggering the blocks' start-up and drain phases;
@@ -35,7 +35,7 @@
  */
 #include <mutex>
 
-#include "ncb_common.cuh"
+#include "kv_row.cuh"
 
 #ifndef NCB_WARPS
 #define NCB_WARPS 4
@@ -60,6 +60,12 @@ struct AttnArgs {
     int B, Hq, Hkv, n_slots, pages_per_slot, window, chunk_pages, max_chunks;
     float scale_log2; /* softmax scale * log2(e) */
     int *status;
+    int len_add; /* a sequence's length is lens[b] + len_add (1 when lens holds the new token's position) */
+    /* APPEND only: the new token's fused projection row and what its q/k row math needs (kv_append_fp8's inputs) */
+    const bf16 *qkv;
+    const float *q_gain, *k_gain, *cs, *sn;
+    long long qkv_row_stride;
+    int table_len;
 };
 
 /* ---- PTX wrappers ------------------------------------------------------------------------------------------- */
@@ -171,12 +177,17 @@ static __device__ __forceinline__ Span span_of(int len, int window, int chunk_pa
 
 /* ---- split-KV kernel ---------------------------------------------------------------------------------------- */
 
-template <int NT>
+/* APPEND: the block first does kv_append_fp8's work for its own heads of the new token (the q rows of its group
+ * into shared memory; if its chunk holds the new position, the k and v rows into the cache in global memory and
+ * into the landed page in shared memory), so a decode step needs no separate append launch and no round trip of q
+ * through global memory. Meant for one new token per sequence; rows that share a slot need the separate kernels. */
+template <int NT, bool APPEND>
 __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];       /* WARPS stages of one page; later the merge area */
     __shared__ __align__(8) uint64_t bars[WARPS];          /* one "page landed" barrier per warp */
     __shared__ float q_stage[4 * NT * HEAD_DIM], q_scale[4 * NT];
-    __shared__ int next_page; /* the chunk's next unassigned page: warps draw from it as they finish one */
+    __shared__ __align__(16) uint8_t new_kv[2][HEAD_DIM]; /* APPEND: the new token's k and v bytes, natural order */
+    __shared__ float new_scale[2];
     float *merge = reinterpret_cast<float *>(smem);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -186,10 +197,11 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     /* launched with programmatic stream serialisation: everything this kernel reads (lens, q, the cache with the
      * token appended a moment ago) comes from kernels before it */
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int len = a.lens[b];
+    const int len = a.lens[b] + a.len_add;
     const int slot = a.slot_map ? a.slot_map[b] : b;
-    if (len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots) {
-        if (tid == 0 && chunk == 0 && kvh == 0) flag(a.status, NCB_DEV_BAD_LENGTH);
+    if (len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots ||
+        (APPEND && (len < 1 || len > a.table_len))) {
+        if (tid == 0 && chunk == 0 && kvh == 0) flag(a.status, APPEND ? NCB_DEV_BAD_POSITION : NCB_DEV_BAD_LENGTH);
         return; /* the merge kernel makes the same test and writes zeros */
     }
     const Span sp = span_of(len, a.window, a.chunk_pages);
@@ -202,16 +214,55 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     uint8_t *page = smem + (size_t)warp * PAGE_BYTES; /* this warp's stage */
     const uint32_t page_u = smem_u32(page), bar = smem_u32(bars + warp);
 
-    if (tid == 0) next_page = WARPS; /* pages 0 .. WARPS - 1 start with warps 0 .. WARPS - 1 */
     if (lane == 0) { /* arm this warp's barrier and start its first page before anything else happens */
         mbar_init(bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         if (warp < n) page_load(page_u, pages + (size_t)warp * PAGE_BYTES, bar);
     }
-    /* the group's queries as fp32 and each head's scale amax / 448 */
-    const bf16 *q = a.q + ((size_t)b * a.Hq + (size_t)kvh * G) * HEAD_DIM;
-    for (int i = tid; i < G * HEAD_DIM; i += THREADS) q_stage[i] = __bfloat162float(q[i]);
+    /* the group's queries as fp32 (bf16 values) and each head's scale amax / 448 */
+    const int new_page = (len - 1) / PAGE_TOKENS - pg0; /* APPEND: the chunk page that receives the new token */
+    if (APPEND) {
+        const int item = tid / LANES, t8 = tid % LANES, o = t8 * VEC;
+        const bool owner = new_page >= 0 && new_page < n;
+        if (item < G + (owner ? 2 : 0)) { /* q heads of the group, then (owner only) this kv head's k and v */
+            const int p = len - 1;
+            const bf16 *row = a.qkv + (size_t)b * a.qkv_row_stride;
+            const int head = item < G ? kvh * G + item : item == G ? a.Hq + kvh : a.Hq + a.Hkv + kvh;
+            float x1[VEC], x2[VEC];
+            load_bf16x8(row + (size_t)head * HEAD_DIM + o, x1);
+            load_bf16x8(row + (size_t)head * HEAD_DIM + HALF + o, x2);
+            const size_t tab = (size_t)p * HALF;
+            if (item < G) {
+                norm_rotate(x1, x2, a.q_gain, a.cs + tab, a.sn + tab, o);
+#pragma unroll
+                for (int i = 0; i < VEC; i++) {
+                    q_stage[item * HEAD_DIM + o + i] = x1[i];
+                    q_stage[item * HEAD_DIM + HALF + o + i] = x2[i];
+                }
+            } else {
+                const bool is_k = item == G;
+                if (is_k) norm_rotate(x1, x2, a.k_gain, a.cs + tab, a.sn + tab, o);
+                uint8_t b1[VEC], b2[VEC];
+                const float scale = quantise(x1, x2, b1, b2);
+                const int j = p % PAGE_TOKENS;
+                uint8_t *home = const_cast<uint8_t *>(pages) + (size_t)new_page * PAGE_BYTES; /* the cache itself */
+                if (is_k) {
+                    store_k_row(home, j, t8, b1, b2);
+                    if (t8 == 0) reinterpret_cast<float *>(home + PAGE_KS)[j] = scale;
+                } else {
+                    store_v_row(home, j, t8, b1, b2);
+                    if (t8 == 0) reinterpret_cast<float *>(home + PAGE_VS)[j] = scale;
+                }
+                memcpy(new_kv[is_k ? 0 : 1] + o, b1, VEC);
+                memcpy(new_kv[is_k ? 0 : 1] + HALF + o, b2, VEC);
+                if (t8 == 0) new_scale[is_k ? 0 : 1] = scale;
+            }
+        }
+    } else {
+        const bf16 *q = a.q + ((size_t)b * a.Hq + (size_t)kvh * G) * HEAD_DIM;
+        for (int i = tid; i < G * HEAD_DIM; i += THREADS) q_stage[i] = __bfloat162float(q[i]);
+    }
     __syncthreads();
     for (int h = warp; h < G; h += WARPS) {
         float m = 0.f;
@@ -265,6 +316,20 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
             break;
         }
         const int key0 = (pg0 + i) * PAGE_TOKENS; /* the page's first position */
+        if (APPEND && i == new_page) {
+            /* the copy of this page raced with the stores of the new token above: whatever it caught of that row,
+             * put the row's final bytes and scales into the landed page */
+            const int j = (len - 1) % PAGE_TOKENS;
+            if (lane < 8)
+                *reinterpret_cast<uint4 *>(page + page_k_chunk(j, lane)) = *reinterpret_cast<const uint4 *>(new_kv[0] + 16 * lane);
+#pragma unroll
+            for (int e = 0; e < 4; e++) page[page_v_byte(j, 4 * lane + e)] = new_kv[1][4 * lane + e];
+            if (lane == 0) {
+                reinterpret_cast<float *>(page + PAGE_KS)[j] = new_scale[0];
+                reinterpret_cast<float *>(page + PAGE_VS)[j] = new_scale[1];
+            }
+            __syncwarp();
+        }
         const bool partial = key0 < sp.begin || key0 + PAGE_TOKENS > sp.len;
         if (partial) { /* zero the V bytes of positions outside [begin, len) */
 #pragma unroll
@@ -375,20 +440,12 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
             }
         }
         __syncwarp(); /* every lane has read the stage */
-        int next = n;
-        if (lane == 0) {
-#ifdef NCB_STATIC_PAGES
-            next = i + WARPS;
-#else
-            next = atomicAdd(&next_page, 1);
-#endif
-            if (next < n) {
-                /* order this warp's reads (and the masking writes) of the stage before the copy engine's writes */
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                page_load(page_u, pages + (size_t)next * PAGE_BYTES, bar);
-            }
+        i += WARPS; /* a fixed page-to-warp map keeps the summation order, hence the output bits, reproducible */
+        if (lane == 0 && i < n) {
+            /* order this warp's reads (and the masking writes) of the stage before the copy engine's writes */
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            page_load(page_u, pages + (size_t)i * PAGE_BYTES, bar);
         }
-        i = __shfl_sync(0xffffffffu, next, 0);
     }
     /* the merge kernel may start occupying free SM resources now; it still waits for this grid to finish */
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -434,7 +491,7 @@ struct MergeArgs {
     long long rows, part_stride, row_stride; /* state (row, p) at parts + row * row_stride + p * part_stride */
     int n_parts;                             /* > 0: fixed; 0: from lens (the split kernel's chunks) */
     const int32_t *lens, *slot_map;
-    int Hq, window, chunk_pages, n_slots, pages_per_slot, max_chunks;
+    int Hq, window, chunk_pages, n_slots, pages_per_slot, max_chunks, len_add;
     bf16 *out;       /* [rows][128] normalised, or NULL */
     float *part_out; /* [rows][PART] merged state, or NULL */
 };
@@ -453,7 +510,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     int n = a.n_parts;
     if (n == 0) {
-        const int b = (int)(row / a.Hq), len = a.lens[b], slot = a.slot_map ? a.slot_map[b] : b;
+        const int b = (int)(row / a.Hq), len = a.lens[b] + a.len_add, slot = a.slot_map ? a.slot_map[b] : b;
         if (!(len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots)) {
             n = min(span_of(len, a.window, a.chunk_pages).n_chunks, a.max_chunks);
         }
@@ -588,13 +645,20 @@ static int sm_count() {
 
 static int pages_of(int len) { return (len + PAGE_TOKENS - 1) / PAGE_TOKENS; }
 
-template <int NT> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
+/* The new token's inputs for the appending variant (kv_append_fp8's arguments). */
+struct AppendIn {
+    const void *qkv, *q_gain, *k_gain, *cos, *sin;
+    long long qkv_row_stride;
+    int table_len;
+};
+
+template <int NT, bool APPEND> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
     static bool done[64] = {};
     int device = 0;
     cudaError_t rc = cudaGetDevice(&device);
     if (rc != cudaSuccess) return rc;
     if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
-    rc = cudaFuncSetAttribute(k_decode_attn<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM);
+    rc = cudaFuncSetAttribute(k_decode_attn<NT, APPEND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM);
     if (rc == cudaSuccess && device >= 0 && device < 64) done[device] = true;
     return rc;
 }
@@ -602,7 +666,7 @@ template <int NT> static cudaError_t prepare() { /* opt in to the large dynamic 
 static int launch_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
                         long long workspace_bytes, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,
                         int max_kv_len, int window, int &chunk_pages, float softmax_scale, void *status,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const AppendIn *app = nullptr) {
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || n_slots <= 0 || pages_per_slot <= 0 || max_kv_len < 0 ||
         window < 0 || chunk_pages < 0 || !(softmax_scale > 0.f))
         return NCB_ERR_ARG;
@@ -611,13 +675,26 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
     if (chunk_pages == 0) chunk_pages = decode_attn_chunk_pages(B, Hkv, max_kv_len);
     if (B == 0) return NCB_OK;
-    if (!q || !kv_cache || !lens || !workspace) return NCB_ERR_ARG;
+    if ((!q && !app) || !kv_cache || !lens || !workspace) return NCB_ERR_ARG;
     if (((uintptr_t)q | (uintptr_t)kv_cache | (uintptr_t)workspace) % 16 != 0) return NCB_ERR_ALIGN;
+    if (app) {
+        if (!app->qkv || !app->q_gain || !app->k_gain || !app->cos || !app->sin || app->table_len <= 0 ||
+            app->qkv_row_stride < (long long)(Hq + 2 * Hkv) * HEAD_DIM)
+            return NCB_ERR_ARG;
+        const uintptr_t all = (uintptr_t)app->qkv | (uintptr_t)app->q_gain | (uintptr_t)app->k_gain |
+                              (uintptr_t)app->cos | (uintptr_t)app->sin;
+        if (all % 16 != 0 || app->qkv_row_stride % 8 != 0) return NCB_ERR_ALIGN;
+    }
     if (workspace_bytes < decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages)) return NCB_ERR_WORKSPACE;
     const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
     AttnArgs a = {(const bf16 *)q, (const uint8_t *)kv_cache, (const int32_t *)lens, (const int32_t *)slot_map,
                   (float *)workspace, B, Hq, Hkv, n_slots, pages_per_slot, window, chunk_pages, max_chunks,
-                  softmax_scale * 1.4426950408889634f, (int *)status};
+                  softmax_scale * 1.4426950408889634f, (int *)status, app ? 1 : 0};
+    if (app) {
+        a.qkv = (const bf16 *)app->qkv, a.q_gain = (const float *)app->q_gain, a.k_gain = (const float *)app->k_gain;
+        a.cs = (const float *)app->cos, a.sn = (const float *)app->sin;
+        a.qkv_row_stride = app->qkv_row_stride, a.table_len = app->table_len;
+    }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(max_chunks, Hkv, B);
     config.blockDim = dim3(THREADS);
@@ -629,12 +706,18 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     config.attrs = attribute;
     config.numAttrs = 1;
     cudaError_t rc;
-    if (Hq / Hkv <= 4) {
-        if (prepare<1>() != cudaSuccess) return NCB_ERR_LAUNCH;
-        rc = cudaLaunchKernelEx(&config, k_decode_attn<1>, a);
+    if (Hq / Hkv <= 4 && !app) {
+        if (prepare<1, false>() != cudaSuccess) return NCB_ERR_LAUNCH;
+        rc = cudaLaunchKernelEx(&config, k_decode_attn<1, false>, a);
+    } else if (!app) {
+        if (prepare<2, false>() != cudaSuccess) return NCB_ERR_LAUNCH;
+        rc = cudaLaunchKernelEx(&config, k_decode_attn<2, false>, a);
+    } else if (Hq / Hkv <= 4) {
+        if (prepare<1, true>() != cudaSuccess) return NCB_ERR_LAUNCH;
+        rc = cudaLaunchKernelEx(&config, k_decode_attn<1, true>, a);
     } else {
-        if (prepare<2>() != cudaSuccess) return NCB_ERR_LAUNCH;
-        rc = cudaLaunchKernelEx(&config, k_decode_attn<2>, a);
+        if (prepare<2, true>() != cudaSuccess) return NCB_ERR_LAUNCH;
+        rc = cudaLaunchKernelEx(&config, k_decode_attn<2, true>, a);
     }
     return rc == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
@@ -658,18 +741,18 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
 static int attend(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
                   long long workspace_bytes, void *out, void *part_out, int B, int Hq, int Hkv, int n_slots,
                   int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale, void *status,
-                  void *stream) {
+                  void *stream, const AppendIn *app = nullptr) {
     if (!out && !part_out) return NCB_ERR_ARG;
     if (((uintptr_t)out | (uintptr_t)part_out) % 16 != 0) return NCB_ERR_ALIGN;
     const int rc = launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots,
                                 pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status,
-                                (cudaStream_t)stream);
+                                (cudaStream_t)stream, app);
     if (rc != NCB_OK || B == 0) return rc;
     if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
     const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
     MergeArgs m = {(const float *)workspace, (long long)B * Hq, PART, (long long)max_chunks * PART, 0,
                    (const int32_t *)lens, (const int32_t *)slot_map, Hq, window, chunk_pages, n_slots, pages_per_slot,
-                   max_chunks, (bf16 *)out, (float *)part_out};
+                   max_chunks, app ? 1 : 0, (bf16 *)out, (float *)part_out};
     return launch_merge(m, (cudaStream_t)stream);
 }
 
@@ -749,6 +832,17 @@ int decode_attn_fp8_static(const void *q, const void *kv_cache, const void *lens
                   pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream);
 }
 
+int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                         const void *pos, const void *slot_map, void *kv_cache, void *workspace,
+                         long long workspace_bytes, void *out, int B, int Hq, int Hkv, long long qkv_row_stride,
+                         int table_len, int n_slots, int pages_per_slot, int max_kv_len, int window, int chunk_pages,
+                         float softmax_scale, void *status, void *stream) {
+    if (!out && B > 0) return NCB_ERR_ARG;
+    const AppendIn app = {qkv, q_gain, k_gain, cos, sin, qkv_row_stride, table_len};
+    return attend(nullptr, kv_cache, pos, slot_map, workspace, workspace_bytes, out, nullptr, B, Hq, Hkv, n_slots,
+                  pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream, &app);
+}
+
 int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
                           void *workspace, long long workspace_bytes, int B, int Hq, int Hkv, int n_slots,
                           int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale,
@@ -789,7 +883,7 @@ int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out,
     if (rows == 0) return NCB_OK;
     if (!parts || !out) return NCB_ERR_ARG;
     if (((uintptr_t)parts | (uintptr_t)out) % 16 != 0) return NCB_ERR_ALIGN;
-    MergeArgs m = {(const float *)parts, rows, rows * PART, PART, n_parts, nullptr, nullptr, 1, 0, 1, 1, 1, n_parts,
+    MergeArgs m = {(const float *)parts, rows, rows * PART, PART, n_parts, nullptr, nullptr, 1, 0, 1, 1, 1, n_parts, 0,
                    (bf16 *)out, nullptr};
     return launch_merge(m, (cudaStream_t)stream);
 }

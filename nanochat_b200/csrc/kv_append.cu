@@ -10,98 +10,10 @@
  * oracle/kv_append_oracle.c (no FMA contraction, sqrt + divide instead of rsqrtf), which makes q bits, cache
  * bytes and scales exact functions of the inputs.
  */
-#include "ncb_common.cuh"
+#include "kv_row.cuh"
 
-constexpr int LANES = 8;
-constexpr int VEC = 8;
 constexpr int BLOCK = 128;
 constexpr int ITEMS_PER_BLOCK = BLOCK / LANES;
-
-static __device__ __forceinline__ void load_bf16x8(const bf16 *p, float *v) {
-    const uint4 u = *reinterpret_cast<const uint4 *>(p);
-    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&u);
-#pragma unroll
-    for (int i = 0; i < VEC / 2; i++) {
-        const float2 f = __bfloat1622float2(h[i]);
-        v[2 * i] = f.x;
-        v[2 * i + 1] = f.y;
-    }
-}
-
-static __device__ __forceinline__ void load_f32x8(const float *p, float *v) {
-    *reinterpret_cast<float4 *>(v) = *reinterpret_cast<const float4 *>(p);
-    *reinterpret_cast<float4 *>(v + 4) = *reinterpret_cast<const float4 *>(p + 4);
-}
-
-/* The 8-lane group's shuffle mask and butterfly reductions (offsets 4, 2, 1). */
-static __device__ __forceinline__ unsigned group_mask() {
-    return 0xffu << ((threadIdx.x & 31) & ~(LANES - 1));
-}
-static __device__ __forceinline__ float group_sum(float v) {
-    const unsigned mask = group_mask();
-#pragma unroll
-    for (int o = LANES / 2; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(mask, v, o));
-    return v;
-}
-static __device__ __forceinline__ float group_max(float v) {
-    const unsigned mask = group_mask();
-#pragma unroll
-    for (int o = LANES / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(mask, v, o));
-    return v;
-}
-
-/* x1, x2 (this lane's 8 + 8 values) -> normed, gained, rotated values rounded to bf16 and widened again. */
-static __device__ __forceinline__ void norm_rotate(float *x1, float *x2, const float *gain, const float *cs,
-                                                   const float *sn, int o) {
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < VEC; i++)
-        ss = __fadd_rn(ss, __fadd_rn(__fmul_rn(x1[i], x1[i]), __fmul_rn(x2[i], x2[i])));
-    ss = group_sum(ss);
-    const float mean = __fdiv_rn(ss, (float)HEAD_DIM);
-    const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(mean, FLT_EPSILON)));
-    float g1[VEC], g2[VEC], c[VEC], s[VEC];
-    load_f32x8(gain + o, g1);
-    load_f32x8(gain + HALF + o, g2);
-    load_f32x8(cs + o, c);
-    load_f32x8(sn + o, s);
-#pragma unroll
-    for (int i = 0; i < VEC; i++) {
-        const float n1 = __fmul_rn(__fmul_rn(x1[i], r), g1[i]), n2 = __fmul_rn(__fmul_rn(x2[i], r), g2[i]);
-        const float y1 = __fadd_rn(__fmul_rn(n1, c[i]), __fmul_rn(n2, s[i]));
-        const float y2 = __fsub_rn(__fmul_rn(n2, c[i]), __fmul_rn(n1, s[i]));
-        x1[i] = __bfloat162float(__float2bfloat16_rn(y1));
-        x2[i] = __bfloat162float(__float2bfloat16_rn(y2));
-    }
-}
-
-static __device__ __forceinline__ uint4 pack_bf16x8(const float *v) {
-    uint4 u;
-    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&u);
-#pragma unroll
-    for (int i = 0; i < VEC / 2; i++) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    return u;
-}
-
-/* scale = amax / 448 over the group's 128 values; bytes = e4m3(x / scale); a zero row gives scale 0, bytes 0. */
-static __device__ __forceinline__ float quantise(const float *x1, const float *x2, uint8_t *b1, uint8_t *b2) {
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < VEC; i++) amax = fmaxf(amax, fmaxf(fabsf(x1[i]), fabsf(x2[i])));
-    amax = group_max(amax);
-    if (!(amax > 0.f)) {
-#pragma unroll
-        for (int i = 0; i < VEC; i++) b1[i] = b2[i] = 0;
-        return 0.f;
-    }
-    const float scale = __fdiv_rn(amax, 448.f);
-#pragma unroll
-    for (int i = 0; i < VEC; i++) {
-        b1[i] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(x1[i], scale), __NV_SATFINITE, __NV_E4M3);
-        b2[i] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(x2[i], scale), __NV_SATFINITE, __NV_E4M3);
-    }
-    return scale;
-}
 
 struct AppendArgs {
     const bf16 *qkv;
@@ -150,19 +62,10 @@ __global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
     const int j = p % PAGE_TOKENS;
     uint8_t *page = a.cache + (((size_t)slot * a.Hkv + head) * a.pages_per_slot + p / PAGE_TOKENS) * PAGE_BYTES;
     if (is_k) {
-        /* dims 8t..8t+7 sit in chunk t/2 at byte (t&1)*8; the partners in chunk 4 + t/2 */
-        uint2 lo, hi;
-        memcpy(&lo, b1, 8);
-        memcpy(&hi, b2, 8);
-        *reinterpret_cast<uint2 *>(page + page_k_chunk(j, t >> 1) + (t & 1) * 8) = lo;
-        *reinterpret_cast<uint2 *>(page + page_k_chunk(j, 4 + (t >> 1)) + (t & 1) * 8) = hi;
+        store_k_row(page, j, t, b1, b2);
         if (t == 0) reinterpret_cast<float *>(page + PAGE_KS)[j] = scale;
     } else {
-#pragma unroll
-        for (int i = 0; i < VEC; i++) {
-            page[page_v_byte(j, o + i)] = b1[i];
-            page[page_v_byte(j, HALF + o + i)] = b2[i];
-        }
+        store_v_row(page, j, t, b1, b2);
         if (t == 0) reinterpret_cast<float *>(page + PAGE_VS)[j] = scale;
     }
 }

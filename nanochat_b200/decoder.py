@@ -164,8 +164,8 @@ class Decoder:
     def fused_step(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int, buf: dict[str, Tensor],
                    choose: bool = True) -> Tensor:
         """One step for rows <= 16 on the decode_step kernels: fp32 logits in buf["logits"]; with `choose`, tokens
-        become the greedy choices and pos advances by one. 7 launches per layer: qkv GEMM (norm fused), append,
-        split attention, merge, o GEMM + residual, up GEMM (norm fused) + relu^2, down GEMM + residual."""
+        become the greedy choices and pos advances by one. 6 launches per layer: qkv GEMM (norm fused), split
+        attention (append fused), merge, o GEMM + residual, up GEMM (norm fused) + relu^2, down GEMM + residual."""
         cfg, lib, s = self.cfg, cuda_library("decode_step"), stream()
         rows, C, Fd, A = tokens.shape[0], cfg.hidden, cfg.intermediate, cfg.n_heads * HEAD_DIM
         workspace = self._workspace(rows, max_kv_len)
@@ -175,14 +175,12 @@ class Decoder:
             check(lib.skinny_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue, s),
                   "skinny_gemm")
 
-        torch.add(pos, 1, out=buf["lens"])
         check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
         for i, layer in enumerate(self.w.layers):
             gemm(h, layer.wqkv, None, qkv, cfg.qkv_width, C, 1, 0)
-            ops.kv_append(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i], cfg.n_heads,
-                          slot_map=slot_map, q_out=buf["q"], status=self.status)
-            ops.decode_attention(buf["q"], self.caches[i], buf["lens"], max_kv_len, slot_map=slot_map,
-                                 window=self.windows[i], workspace=workspace, out=att, status=self.status)
+            ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
+                                      cfg.n_heads, max_kv_len, slot_map=slot_map, window=self.windows[i],
+                                      workspace=workspace, out=att, status=self.status)
             gemm(att, layer.wo, h, h, C, A, 0, 1)
             gemm(h, layer.wup, None, u, Fd, C, 1, 2)
             gemm(u, layer.wdown, h, h, C, Fd, 0, 1)

@@ -4,7 +4,7 @@ The reference runs its whole step as captured graphs launched from Python throug
 (model/kernels/decode.cu:848-902,1000-1016,1107-1110; inference/decoder.py:285) because at decode sizes the step is
 bound by launch latency, not by kernels. This is the same idea for the part of the step this package owns:
 
-    pinned host qkv rows + positions --copy--> device --kv_append_fp8--> cache, q --decode_attn_fp8--> out
+    pinned host qkv rows + positions --copy--> device --decode_step_attn_fp8 (append + attend)--> cache, out
     --copy--> pinned host
 
 The caller writes `qkv_host` and `pos_host`, calls run(), and reads `out_host`. Sequence lengths are pos + 1 (the
@@ -54,12 +54,10 @@ class DecodeStep:
     def _enqueue(self) -> None:
         self.qkv.copy_(self.qkv_host, non_blocking=True)
         self.pos.copy_(self.pos_host, non_blocking=True)
-        ops.kv_append(self.qkv, self.q_gain, self.k_gain, self.cos, self.sin, self.pos, self.cache, self.Hq,
-                      slot_map=self.slot_map, q_out=self.q, status=self.status)
-        torch.add(self.pos, 1, out=self.lens)
-        ops.decode_attention(self.q, self.cache, self.lens, self.max_kv_len, slot_map=self.slot_map,
-                             window=self.window, chunk_pages=self.chunk_pages, softmax_scale=self.softmax_scale,
-                             workspace=self.workspace, out=self.out, status=self.status)
+        ops.decode_step_attention(self.qkv, self.q_gain, self.k_gain, self.cos, self.sin, self.pos, self.cache,
+                                  self.Hq, self.max_kv_len, slot_map=self.slot_map, window=self.window,
+                                  chunk_pages=self.chunk_pages, softmax_scale=self.softmax_scale,
+                                  workspace=self.workspace, out=self.out, status=self.status)
         self.out_host.copy_(self.out, non_blocking=True)
 
     def capture(self) -> None:

@@ -223,3 +223,42 @@ def test_decode_step_graph_matches_eager_operators():
         pos += 1
     step.check()
     assert torch.equal(caches[0].pages, caches[1].pages)
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (10, 10), (8, 1)])
+def test_fused_append_attention_equals_the_two_kernels(Hq, Hkv):
+    """decode_step_attn_fp8 (the attention kernel appends its own token) against kv_append_fp8 + decode_attn_fp8 over
+    several steps, across page and chunk boundaries, with a window and a slot map: same cache bytes, same outputs."""
+    gen = torch.Generator().manual_seed(1300 + Hq)
+    lens = [62, 127, 5, 300]
+    B = len(lens)
+    case = helpers.attention_case(1301, Hq, Hkv, lens)
+    slots = [2, 0, 3, 1]
+    cos, sin = ncb.rotary_table(384, 1e4, device="cuda")
+    gain = (1 + 0.1 * torch.randn(128, generator=gen)).cuda()
+    caches = [load_cache(case, 384, slots=slots, n_slots=4) for _ in range(2)]
+    slot_map = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    pos = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for step in range(5):
+        qkv = torch.randn(B, (Hq + 2 * Hkv) * 128, generator=gen).bfloat16().cuda()
+        window = 0 if step % 2 == 0 else 100
+        got = ncb.decode_step_attention(qkv, gain, gain, cos, sin, pos, caches[0], Hq, int(pos.max()) + 1,
+                                        slot_map=slot_map, window=window, chunk_pages=2, status=status)
+        q = ncb.kv_append(qkv, gain, gain, cos, sin, pos, caches[1], Hq, slot_map=slot_map, status=status)
+        want = ncb.decode_attention(q, caches[1], pos + 1, int(pos.max()) + 1, slot_map=slot_map, window=window,
+                                    chunk_pages=2, status=status)
+        torch.cuda.synchronize()
+        assert torch.equal(caches[0].pages, caches[1].pages), f"step {step}: cache bytes differ"
+        assert torch.equal(got, want), f"step {step}: outputs differ"
+        pos += 1
+    assert status.item() == 0
+    # an out-of-range position is refused and flagged, and its row comes back as zeros
+    bad = pos.clone()
+    bad[1] = 384
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * 128, generator=gen).bfloat16().cuda()
+    before = caches[0].pages.clone()
+    out = ncb.decode_step_attention(qkv, gain, gain, cos, sin, bad, caches[0], Hq, 384, slot_map=slot_map, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 1 and not out[1].any()
+    assert torch.equal(caches[0].pages[0], before[0])  # slot 0 belongs to the refused row
