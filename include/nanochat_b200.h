@@ -207,8 +207,10 @@ int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int ro
                 int epilogue, void *stream);
 /* h bf16 [rows][C] = rms_norm(embed[tokens]); embed bf16 [vocab][C]; tokens int64 [rows]; C a multiple of 8. */
 int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, int vocab, void *stream);
-/* tokens[row] (int64) = argmax of logits fp32 [rows][vocab], ties to the lowest id; pos[row] (int32) += 1. */
-int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int vocab, void *stream);
+/* tokens[row] (int64) = argmax of logits fp32 [rows][vocab], ties to the lowest id; pos[row] (int32) += 1; with
+ * trace (int64 [rows][trace_stride], may be NULL) also trace[row][new pos[row]] = the choice. */
+int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int vocab, void *trace, int trace_stride,
+                  void *stream);
 
 #ifdef __cplusplus
 }

@@ -78,8 +78,9 @@ static __device__ __forceinline__ uint4 scale_bf16x8(const uint4 &u, float r) {
  * blockIdx.x, blockIdx.x + gridDim.x, ...; while it reduces one tile the next tile's weights are already in flight
  * (PREFETCH: only where two weight slices fit the register file). */
 template <int ITERS, bool HI, int EPI, bool NORM>
-__global__ void __launch_bounds__(GEMM_THREADS) k_skinny_gemm(GemmArgs a) {
+__global__ void __launch_bounds__(GEMM_THREADS, ITERS > 8 ? 2 : 1) k_skinny_gemm(GemmArgs a) {
     constexpr bool PREFETCH = ITERS <= 8;
+    constexpr bool HOLD_X = NORM || PREFETCH; /* long K slices stream x with the MMAs to stay within 128 registers */
     __shared__ float part[GEMM_WARPS][16][TILE_N + 1];
     __shared__ float ss[GEMM_WARPS][16];
     __shared__ float rstd[16];
@@ -105,13 +106,15 @@ __global__ void __launch_bounds__(GEMM_THREADS) k_skinny_gemm(GemmArgs a) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    uint4 xlo[ITERS], xhi[HI ? ITERS : 1];
+    uint4 xlo[HOLD_X ? ITERS : 1], xhi[HI && HOLD_X ? ITERS : 1];
     const bool lo_on = g < a.rows, hi_on = HI && g + 8 < a.rows;
     const bf16 *xl = a.x + (size_t)g * a.K + k_warp + 8 * t, *xh = a.x + (size_t)(g + 8) * a.K + k_warp + 8 * t;
+    if (HOLD_X) {
 #pragma unroll
-    for (int i = 0; i < ITERS; i++) {
-        xlo[i] = lo_on ? *reinterpret_cast<const uint4 *>(xl + 32 * i) : make_uint4(0, 0, 0, 0);
-        if (HI) xhi[i] = hi_on ? *reinterpret_cast<const uint4 *>(xh + 32 * i) : make_uint4(0, 0, 0, 0);
+        for (int i = 0; i < ITERS; i++) {
+            xlo[i] = lo_on ? *reinterpret_cast<const uint4 *>(xl + 32 * i) : make_uint4(0, 0, 0, 0);
+            if (HI) xhi[i] = hi_on ? *reinterpret_cast<const uint4 *>(xh + 32 * i) : make_uint4(0, 0, 0, 0);
+        }
     }
     if (NORM) { /* rows' 1 / sqrt(mean(x^2) + eps) over the full K, then x <- bf16(x * rstd) in registers */
         float s_lo = 0.f, s_hi = 0.f;
@@ -150,10 +153,16 @@ __global__ void __launch_bounds__(GEMM_THREADS) k_skinny_gemm(GemmArgs a) {
 #pragma unroll
         for (int i = 0; i < ITERS; i++) {
             /* k slots (2t, 2t+1) and (2t+8, 2t+9) of the two MMAs take the thread's values 0..1, 2..3 and 4..5, 6..7 */
-            const uint32_t h0 = HI ? xhi[i].x : 0u, h1 = HI ? xhi[i].y : 0u, h2 = HI ? xhi[i].z : 0u,
-                           h3 = HI ? xhi[i].w : 0u;
-            mma_bf16(acc, xlo[i].x, h0, xlo[i].y, h1, wv[i].x, wv[i].y);
-            mma_bf16(acc2, xlo[i].z, h2, xlo[i].w, h3, wv[i].z, wv[i].w);
+            uint4 lo, hi = make_uint4(0, 0, 0, 0);
+            if (HOLD_X) {
+                lo = xlo[i];
+                if (HI) hi = xhi[i];
+            } else {
+                lo = lo_on ? *reinterpret_cast<const uint4 *>(xl + 32 * i) : make_uint4(0, 0, 0, 0);
+                if (HI && hi_on) hi = *reinterpret_cast<const uint4 *>(xh + 32 * i);
+            }
+            mma_bf16(acc, lo.x, hi.x, lo.y, hi.y, wv[i].x, wv[i].y);
+            mma_bf16(acc2, lo.z, hi.z, lo.w, hi.w, wv[i].z, wv[i].w);
         }
         /* the tile after next starts streaming now; the next one becomes current */
         const int after = tile + (PREFETCH ? 2 : 1) * (int)gridDim.x;
@@ -219,7 +228,8 @@ __global__ void __launch_bounds__(128) k_embed_norm(const bf16 *embed, const lon
 }
 
 /* tokens[row] = argmax(logits[row]) (ties to the lowest id, decode.cu:90-96), pos[row] += 1; one block per row. */
-__global__ void __launch_bounds__(1024) k_greedy(const float *logits, long long *tokens, int32_t *pos, int vocab) {
+__global__ void __launch_bounds__(1024) k_greedy(const float *logits, long long *tokens, int32_t *pos, int vocab,
+                                                 long long *trace, int trace_stride) {
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -247,8 +257,11 @@ __global__ void __launch_bounds__(1024) k_greedy(const float *logits, long long 
             if (ov > v || (ov == v && oi < at)) v = ov, at = oi;
         }
         if (lane == 0) {
-            tokens[row] = at == 0x7fffffff ? 0 : at;
-            pos[row] += 1;
+            const long long choice = at == 0x7fffffff ? 0 : at;
+            const int next = pos[row] + 1;
+            tokens[row] = choice;
+            pos[row] = next;
+            if (trace && next >= 0 && next < trace_stride) trace[(size_t)row * trace_stride + next] = choice;
         }
     }
 }
@@ -353,13 +366,15 @@ int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, 
                       (const long long *)tokens, (bf16 *)h, rows, C, vocab);
 }
 
-/* tokens[row] = argmax(logits[row]) over fp32 [rows][vocab], ties to the lowest id; pos[row] += 1. */
-int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int vocab, void *stream) {
+/* tokens[row] = argmax(logits[row]) over fp32 [rows][vocab], ties to the lowest id; pos[row] += 1; if trace (int64
+ * [rows][trace_stride]) is given, trace[row][new pos] = the choice, so a host can fetch a whole run at its end. */
+int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int vocab, void *trace, int trace_stride,
+                  void *stream) {
     if (rows < 0 || vocab <= 0) return NCB_ERR_ARG;
     if (rows == 0) return NCB_OK;
     if (!logits || !tokens || !pos) return NCB_ERR_ARG;
     return launch_pdl(k_greedy, dim3(rows), dim3(1024), (cudaStream_t)stream, (const float *)logits,
-                      (long long *)tokens, (int32_t *)pos, vocab);
+                      (long long *)tokens, (int32_t *)pos, vocab, (long long *)trace, trace_stride);
 }
 
 } /* extern "C" */

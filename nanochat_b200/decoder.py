@@ -158,7 +158,7 @@ class Decoder:
                 "q": torch.empty((rows, cfg.n_heads, HEAD_DIM), dtype=bf, device=dev),
                 "att": torch.empty((rows, cfg.n_heads, HEAD_DIM), dtype=bf, device=dev),
                 "u": torch.empty((rows, cfg.intermediate), dtype=bf, device=dev),
-                "lens": torch.empty(rows, dtype=torch.int32, device=dev),
+                "trace": torch.zeros((rows, self.capacity + 1), dtype=torch.long, device=dev),
                 "logits": torch.empty((rows, cfg.vocab), dtype=torch.float32, device=dev)}
 
     def fused_step(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int, buf: dict[str, Tensor],
@@ -186,8 +186,8 @@ class Decoder:
             gemm(u, layer.wdown, h, h, C, Fd, 0, 1)
         gemm(h, self.w.lm_head, None, buf["logits"], cfg.vocab, C, 1, 3)
         if choose:
-            check(lib.greedy_choice(pointer(buf["logits"]), pointer(tokens), pointer(pos), rows, cfg.vocab, s),
-                  "greedy_choice")
+            check(lib.greedy_choice(pointer(buf["logits"]), pointer(tokens), pointer(pos), rows, cfg.vocab,
+                                    pointer(buf["trace"]), buf["trace"].shape[1], s), "greedy_choice")
         return buf["logits"]
 
     # ---- prefill ----------------------------------------------------------------------------------------------
@@ -237,7 +237,7 @@ class Decoder:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 body()
-        self._graphs[batch] = (graph, stream, tokens, pos, logits)
+        self._graphs[batch] = (graph, stream, tokens, pos, logits, buf["trace"] if fused else None)
         return self._graphs[batch]
 
     @torch.no_grad()
@@ -247,19 +247,24 @@ class Decoder:
         B = len(prompts)
         assert B <= self.n_slots and all(len(p) >= 1 for p in prompts)
         assert max(len(p) for p in prompts) - 1 + max_new_tokens <= self.capacity
-        graph, stream, tokens, pos, logits = self._step_graph(B)
+        graph, stream, tokens, pos, logits, trace = self._step_graph(B)
         start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         with torch.cuda.stream(stream):
             start.record()
             self.prefill(prompts, list(range(B)))
             tokens.copy_(torch.tensor([p[-1] for p in prompts], dtype=torch.long), non_blocking=False)
             pos.copy_(torch.tensor([len(p) - 1 for p in prompts], dtype=torch.int32))
+            first = pos.clone()
             out = torch.empty((max_new_tokens, B), dtype=torch.long, device=self.device)
             mid.record()
             for t in range(max_new_tokens):
                 graph.replay()
-                out[t].copy_(tokens)
+                if trace is None:
+                    out[t].copy_(tokens)
             end.record()
+            if trace is not None:  # the fused step logged every choice at its position: one gather at the end
+                at = first.long()[None, :] + 1 + torch.arange(max_new_tokens, device=self.device)[:, None]
+                out = trace.gather(1, at.T).T.contiguous()
         stream.synchronize()
         code = int(self.status.item())
         if code:

@@ -48,7 +48,7 @@ SIGNATURES = {
     "decode_step": {
         "skinny_gemm": ([c_ptr] * 4 + [c_int] * 5 + [c_ptr], c_int),
         "embed_norm": ([c_ptr] * 3 + [c_int] * 3 + [c_ptr], c_int),
-        "greedy_choice": ([c_ptr] * 3 + [c_int] * 2 + [c_ptr], c_int),
+        "greedy_choice": ([c_ptr] * 3 + [c_int] * 2 + [c_ptr, c_int, c_ptr], c_int),
     },
 }
 STATUS = {0: "ok", 1: "invalid argument", 2: "misaligned pointer or stride", 3: "workspace too small",

@@ -80,7 +80,10 @@ def test_embed_norm_and_greedy_choice():
     logits[1, 40000] = logits[1, 123] = 50.0  # a tie: the lowest id wins
     logits[2, 65535] = 60.0
     pos = torch.tensor([3, 4, 5, 6, 7], dtype=torch.int32, device="cuda")
-    assert lib.greedy_choice(pointer(logits), pointer(tokens), pointer(pos), rows, 65536, stream()) == 0
+    trace = torch.full((rows, 16), -1, dtype=torch.long, device="cuda")
+    assert lib.greedy_choice(pointer(logits), pointer(tokens), pointer(pos), rows, 65536, pointer(trace), 16,
+                             stream()) == 0
     torch.cuda.synchronize()
     assert tokens.tolist() == logits.argmax(-1).tolist() and tokens[1] == 123 and tokens[2] == 65535
     assert pos.tolist() == [4, 5, 6, 7, 8]
+    assert [int(trace[r, pos[r]]) for r in range(rows)] == tokens.tolist() and int((trace >= 0).sum()) == rows
