@@ -13,7 +13,7 @@ One JSON line on rank 0. A step is one decode-attention pass (split-KV kernel + 
   value     whole-job algorithmic GB/s with the cache, q and lens resident in HBM:
             bytes = sum_b len_b * Hkv * 264 + B * Hq * 512 per step (K + V bytes, two fp32 scales, q in, out).
   e2e       the same metric through the public operators with HOST buffers: each step copies the new token's fused
-            qkv row and positions from pinned memory, runs kv_append_fp8 + decode_attn_fp8 and copies the output
+            qkv row and positions from pinned memory, runs the append + attention kernels and copies the output
             back to pinned memory, synchronising every step. The KV cache is decoder state that lives in HBM
             between steps (as in the reference's decoder), so it is not a per-step input.
   roofline  the split-KV kernel alone (CUDA events around a loop of decode_attn_fp8_split launches on the same
@@ -406,9 +406,9 @@ def main() -> None:
                     "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps,
                     "ms_per_step": float(e2e_s.item()) / e2e_steps * 1e3,
-                    "what": "DecodeStep.run(): pinned-host qkv rows + positions in, kv_append_fp8 + decode_attn_fp8 "
-                            "(one CUDA graph), output to pinned host, synchronised every step; the KV cache is "
-                            "resident decoder state"},
+                    "what": "DecodeStep.run(): pinned-host qkv rows + positions in, decode_step_attn_fp8 (append + "
+                            "attention; one CUDA graph with the copies), output to pinned host, synchronised every "
+                            "step; the KV cache is resident decoder state"},
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "k_decode_attn<1> (split-KV)", "achieved": split_gbs, "peak": peak,
                          "unit": UNIT, "frac": split_gbs / peak, "peak_kind": peak_kind,
