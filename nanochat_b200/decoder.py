@@ -28,6 +28,7 @@ from torch import Tensor
 from . import attention as ops
 from .kv_cache import HEAD_DIM, Fp8KVCache
 from .native import check, cuda_library, pointer, stream
+from .prompt_store import PromptStore
 
 EPS = 1.1920928955078125e-07  # FLT_EPSILON (reference model/ops/linear.py:20)
 
@@ -89,9 +90,13 @@ def rms_norm(x: Tensor) -> Tensor:
 class Decoder:
     """Greedy decoding of up to n_slots sequences with an fp8 KV cache per layer."""
 
-    def __init__(self, cfg: DecoderConfig, weights: DecoderWeights, n_slots: int, device: "torch.device | str" = "cuda"):
+    def __init__(self, cfg: DecoderConfig, weights: DecoderWeights, n_slots: int, device: "torch.device | str" = "cuda",
+                 prompt_store: int = 0):
+        """prompt_store: positions of pinned host memory for prompts already prefilled (0: none); a prompt seen
+        again is copied back into its slot instead of being prefilled (inference/decoder.py:193-232)."""
         self.cfg, self.w, self.n_slots, self.device = cfg, weights, n_slots, torch.device(device)
         self.caches = [Fp8KVCache(n_slots, cfg.n_kv_heads, cfg.max_len, device=device) for _ in range(cfg.n_layers)]
+        self.store = PromptStore(self.caches, prompt_store) if prompt_store > 0 else None
         self.capacity = self.caches[0].capacity
         self.cos, self.sin = ops.rotary_table(self.capacity, cfg.rope_theta, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -251,7 +256,11 @@ class Decoder:
         start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         with torch.cuda.stream(stream):
             start.record()
-            self.prefill(prompts, list(range(B)))
+            missing = [b for b in range(B) if self.store is None or not self.store.load(b, prompts[b])]
+            self.prefill([prompts[b] for b in missing], missing)
+            if self.store is not None:
+                for b in missing:
+                    self.store.save(b, prompts[b])
             tokens.copy_(torch.tensor([p[-1] for p in prompts], dtype=torch.long), non_blocking=False)
             pos.copy_(torch.tensor([len(p) - 1 for p in prompts], dtype=torch.int32))
             first = pos.clone()

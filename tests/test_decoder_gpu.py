@@ -119,3 +119,22 @@ def test_ragged_prompts_and_gqa_shapes_run_and_agree_with_rowwise_logits():
                 if margin < 2e-2:
                     break
                 assert tokens[b][t] == tok, (b, t)
+
+
+def test_prompt_store_round_trip_gives_the_same_stream():
+    """A prompt prefilled once is served from the pinned-host page store afterwards: same tokens, no prefill."""
+    cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=4, n_kv_heads=2, intermediate=1024, vocab=304, max_len=256)
+    w = DecoderWeights.random_init(cfg, seed=7, device="cuda", std=0.05)
+    gen = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 304, (n,), generator=gen).tolist() for n in (130, 2, 65)]
+    dec = Decoder(cfg, w, 3, prompt_store=1024)
+    first, _ = dec.generate(prompts, 6)
+    assert set(dec.store.stored) == {tuple(p) for p in prompts} and dec.store.used == 3 + 1 + 1
+    for cache in dec.caches:  # wipe the slots: the second run can only succeed from the store
+        cache.pages.zero_()
+    calls = []
+    original = dec.prefill
+    dec.prefill = lambda p, s, **kw: (calls.append(len(p)), original(p, s, **kw))
+    second, _ = dec.generate(list(reversed(prompts)), 6)  # other slots than the first time
+    assert calls == [0]
+    assert second == list(reversed(first))
