@@ -229,6 +229,49 @@ def bench_decoder(rank: int, world: int, device, new_tokens: int) -> dict:
             "prefill_s": prefill_s, "scaling": "weak (replicas)"}
 
 
+def bench_decoder_d32(rank: int, world: int, device, new_tokens: int) -> dict:
+    """Batched decode of a random-init d32-class model (32 layers, d_model 2048, 16 query / 4 KV heads, relu^2 MLP of
+    8192, vocab 65536): batch 32 per GPU (256 over 8 GPUs), ragged contexts uniform in [256, 8192] already in the fp8
+    caches (synthetic quantised K/V, the same pages in every layer), `new_tokens` greedy tokens. Every step appends
+    and attends in every layer. Rows above 16 run the GEMMs on cuBLAS."""
+    import torch.distributed as dist
+
+    import nanochat_b200 as ncb
+    from nanochat_b200.decoder import Decoder, DecoderConfig, DecoderWeights
+
+    B = 32
+    gen = torch.Generator().manual_seed(200 + rank)
+    ctx = torch.randint(256, 8193, (B,), generator=gen).tolist()
+    cfg = DecoderConfig(n_layers=32, hidden=2048, n_heads=16, n_kv_heads=4, intermediate=8192, vocab=65536,
+                        rope_theta=10000.0, max_len=8192 + new_tokens + 8)
+    decoder = Decoder(cfg, DecoderWeights.random_init(cfg, 1, device), B, device)
+    dgen = torch.Generator(device=device).manual_seed(300 + rank)
+    filled = ncb.Fp8KVCache(B, 4, cfg.max_len, device=device)
+    for slot, n in enumerate(ctx):
+        packed = []
+        for _ in range(2):
+            x = torch.randn(4, n, D, generator=dgen, device=device)
+            scale = x.abs().amax(-1) / 448.0
+            packed += [(x / scale[..., None]).to(torch.float8_e4m3fn).view(torch.uint8), scale]
+        filled.write(slot, *packed)
+    for cache in decoder.caches:
+        cache.pages.copy_(filled.pages)
+    del filled
+    first = torch.randint(0, 65536, (B,), generator=gen).tolist()
+    decoder.decode_from(first, ctx, 4)  # warm-up: graph capture, cuBLAS heuristics
+    _, seconds = decoder.decode_from(first, ctx, new_tokens)
+    stats = torch.tensor([seconds], device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    seconds = float(stats.item())
+    kv_bytes = sum(ctx) * 4 * 264 * cfg.n_layers
+    return {"workload": "random-init d32-class (32 layers, d 2048, Hq 16, Hkv 4), batch 32 per GPU, contexts uniform in "
+                        "[256, 8192] (synthetic cache contents), greedy, fp8 KV cache",
+            "new_tokens": new_tokens, "tokens_per_s": B * world * new_tokens / seconds,
+            "ms_per_step": seconds / new_tokens * 1e3, "kv_bytes_per_step_per_gpu": kv_bytes,
+            "scaling": "weak (batch-sharded replicas)"}
+
+
 def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
@@ -281,6 +324,7 @@ def main() -> None:
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--chunk-pages", type=int, default=0)
     ap.add_argument("--decoder", type=int, default=1, help="also time end-to-end greedy decoding of d20 (0: skip)")
+    ap.add_argument("--decoder-d32", type=int, default=1, help="also time batched decode of the d32-class model (0: skip)")
     ap.add_argument("--longctx", type=int, default=1, help="also time the KV-length-sharded long-context case (0: skip)")
     ap.add_argument("--e2e-steps", type=int, default=200, help="steps of the end-to-end loop (profiling runs shrink it)")
     args = ap.parse_args()
@@ -390,6 +434,7 @@ def main() -> None:
     del cache, decode, workspace
     longctx = bench_longctx(rank, world, device, min(args.steps, 100), 5, timed) if args.longctx else None
     decoder = bench_decoder(rank, world, device, 256) if args.decoder else None
+    decoder_d32 = bench_decoder_d32(rank, world, device, 128) if args.decoder_d32 else None
 
     if rank == 0:
         peak, peak_kind = peaks()
@@ -420,6 +465,8 @@ def main() -> None:
             line["longctx"] = longctx
         if decoder:
             line["decoder"] = decoder
+        if decoder_d32:
+            line["decoder_d32"] = decoder_d32
         if world == 1 and args.cpu_seconds > 0:
             line["cpu_baseline"] = time_cpu_reference(lens[:args.cpu_sample], args.cpu_seconds)
         print(json.dumps(line))

@@ -246,38 +246,51 @@ class Decoder:
         return self._graphs[batch]
 
     @torch.no_grad()
+    def decode_from(self, first_tokens: list[int], positions: list[int], steps: int) -> tuple[list[list[int]], float]:
+        """`steps` greedy steps for slots 0 .. B - 1 whose caches already hold positions 0 .. positions[b] - 1:
+        slot b's next input is first_tokens[b] at position positions[b]. Returns the chosen tokens and the seconds
+        the steps took on the device. Stream-ordered after work queued on the current stream."""
+        B = len(first_tokens)
+        assert B <= self.n_slots and max(positions) + steps <= self.capacity
+        graph, stream, tokens, pos, logits, trace = self._step_graph(B)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            tokens.copy_(torch.tensor(first_tokens, dtype=torch.long))
+            pos.copy_(torch.tensor(positions, dtype=torch.int32))
+            first = pos.clone()
+            out = torch.empty((steps, B), dtype=torch.long, device=self.device)
+            begin.record()
+            for t in range(steps):
+                graph.replay()
+                if trace is None:
+                    out[t].copy_(tokens)
+            end.record()
+            if trace is not None:  # the fused step logged every choice at its position: one gather at the end
+                at = first.long()[None, :] + 1 + torch.arange(steps, device=self.device)[:, None]
+                out = trace.gather(1, at.T).T.contiguous()
+        stream.synchronize()
+        code = int(self.status.item())
+        if code:
+            raise RuntimeError(f"device status {code:#x} (NCB_DEV_* bits)")
+        return out.T.tolist(), begin.elapsed_time(end) * 1e-3
+
+    @torch.no_grad()
     def generate(self, prompts: list[list[int]], max_new_tokens: int) -> tuple[list[list[int]], dict]:
         """Greedy continuation of every prompt (slot b = prompt b). Returns the new tokens and timings: prefill
         seconds, decode seconds (the max_new_tokens steps), tokens per second of the decode phase."""
         B = len(prompts)
         assert B <= self.n_slots and all(len(p) >= 1 for p in prompts)
         assert max(len(p) for p in prompts) - 1 + max_new_tokens <= self.capacity
-        graph, stream, tokens, pos, logits, trace = self._step_graph(B)
-        start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        with torch.cuda.stream(stream):
-            start.record()
-            missing = [b for b in range(B) if self.store is None or not self.store.load(b, prompts[b])]
-            self.prefill([prompts[b] for b in missing], missing)
-            if self.store is not None:
-                for b in missing:
-                    self.store.save(b, prompts[b])
-            tokens.copy_(torch.tensor([p[-1] for p in prompts], dtype=torch.long), non_blocking=False)
-            pos.copy_(torch.tensor([len(p) - 1 for p in prompts], dtype=torch.int32))
-            first = pos.clone()
-            out = torch.empty((max_new_tokens, B), dtype=torch.long, device=self.device)
-            mid.record()
-            for t in range(max_new_tokens):
-                graph.replay()
-                if trace is None:
-                    out[t].copy_(tokens)
-            end.record()
-            if trace is not None:  # the fused step logged every choice at its position: one gather at the end
-                at = first.long()[None, :] + 1 + torch.arange(max_new_tokens, device=self.device)[:, None]
-                out = trace.gather(1, at.T).T.contiguous()
-        stream.synchronize()
-        code = int(self.status.item())
-        if code:
-            raise RuntimeError(f"device status {code:#x} (NCB_DEV_* bits)")
-        decode_s = mid.elapsed_time(end) * 1e-3
-        return out.T.tolist(), {"prefill_s": start.elapsed_time(mid) * 1e-3, "decode_s": decode_s,
-                                "tokens_per_s": B * max_new_tokens / decode_s}
+        self._step_graph(B)  # capture (and its warm-up step) before the caches are filled
+        start, mid = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        missing = [b for b in range(B) if self.store is None or not self.store.load(b, prompts[b])]
+        self.prefill([prompts[b] for b in missing], missing)
+        if self.store is not None:
+            for b in missing:
+                self.store.save(b, prompts[b])
+        mid.record()
+        out, decode_s = self.decode_from([p[-1] for p in prompts], [len(p) - 1 for p in prompts], max_new_tokens)
+        return out, {"prefill_s": start.elapsed_time(mid) * 1e-3, "decode_s": decode_s,
+                     "tokens_per_s": B * max_new_tokens / decode_s}
