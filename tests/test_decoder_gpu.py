@@ -111,14 +111,17 @@ def test_ragged_prompts_and_gqa_shapes_run_and_agree_with_rowwise_logits():
                 logits = ref.logits_rows(torch.tensor([seq[t]], device="cuda"),
                                          torch.tensor([t], dtype=torch.int32, device="cuda"), slot, t + 1)
                 if t >= len(p) - 1:
-                    top = torch.sort(logits[0]).values
-                    nxt = int(logits.argmax())
-                    out.append((nxt, float(top[-1] - top[-2])))
-                    seq.append(nxt)
-            for t, (tok, margin) in enumerate(out):
-                if margin < 2e-2:
+                    out.append(logits[0].clone())
+                    seq.append(int(logits.argmax()))
+            agreed = 0
+            for t, z in enumerate(out):
+                if tokens[b][t] != int(z.argmax()):
+                    # the two paths round their GEMMs differently: a different choice is only legitimate at a
+                    # near-tie, after which the streams are no longer comparable
+                    assert float(z.max() - z[tokens[b][t]]) < 5e-2, (b, t)
                     break
-                assert tokens[b][t] == tok, (b, t)
+                agreed += 1
+            assert agreed >= 2, (b, agreed)
 
 
 def test_prompt_store_round_trip_gives_the_same_stream():
