@@ -702,7 +702,7 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL;
     config.attrs = attribute;
     config.numAttrs = 1;
     cudaError_t rc;
@@ -732,7 +732,7 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1; /* overlap its launch with the split kernel's tail */
+    attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL; /* overlap its launch with the split kernel's tail */
     config.attrs = attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, k_merge, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
@@ -872,7 +872,7 @@ int decode_attn_merge_peers(const void *const *parts, void *const *flags, int wo
     config.stream = (cudaStream_t)stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL;
     config.attrs = attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, k_merge_peers, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;

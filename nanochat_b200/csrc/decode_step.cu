@@ -276,7 +276,7 @@ static int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL;
     config.attrs = attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, kernel, args...) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;

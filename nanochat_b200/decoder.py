@@ -103,6 +103,7 @@ class Decoder:
         self.windows = cfg.windows or [0] * cfg.n_layers
         self.use_fused = True  # decode steps of <= 16 rows run on the decode_step kernels when the shapes allow
         self._graphs: dict[int, tuple] = {}
+        self._graph_tensors: dict[int, tuple] = {}
         self._workspaces: dict[tuple[int, int], Tensor] = {}
 
     # ---- one pass over `rows` tokens -------------------------------------------------------------------------
@@ -242,6 +243,8 @@ class Decoder:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 body()
+        # the graph holds raw pointers: every tensor its kernels touch must stay alive as long as the graph does
+        self._graph_tensors[batch] = (slot_map, buf)
         self._graphs[batch] = (graph, stream, tokens, pos, logits, buf["trace"] if fused else None)
         return self._graphs[batch]
 
