@@ -205,7 +205,7 @@ def bench_longctx(rank: int, world: int, device, steps: int, warmup: int, timed)
             "nccl_variant_ms_per_step": None if world == 1 else ms_nccl / steps}
 
 
-def bench_decoder(rank: int, world: int, device, new_tokens: int) -> dict:
+def bench_decoder(rank: int, world: int, device, new_tokens: int, profile: bool = False) -> dict:
     """End-to-end greedy decode of the random-init d20 model (20 layers, d_model 1280, 10 heads, vocab 65536, bf16
     weights ~ N(0, 0.02)): batch 8 per GPU, 512-token prompts, `new_tokens` generated tokens; every rank runs its own
     batch (replicated weights, no collective), tokens/s is the sum over ranks of the decode phase."""
@@ -219,7 +219,12 @@ def bench_decoder(rank: int, world: int, device, new_tokens: int) -> dict:
     gen = torch.Generator().manual_seed(100 + rank)
     prompts = torch.randint(0, 65536, (8, 512), generator=gen).tolist()
     decoder.generate(prompts, 8)  # warm-up: graph capture, cuBLAS heuristics
+    if profile:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
     _, t = decoder.generate(prompts, new_tokens)
+    if profile:
+        torch.cuda.profiler.stop()
     stats = torch.tensor([t["decode_s"], t["prefill_s"]], device=device)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
@@ -324,6 +329,9 @@ def main() -> None:
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--chunk-pages", type=int, default=0)
     ap.add_argument("--decoder", type=int, default=1, help="also time end-to-end greedy decoding of d20 (0: skip)")
+    ap.add_argument("--decoder-tokens", type=int, default=256, help="tokens generated per sequence in that run")
+    ap.add_argument("--profile-range", default="attention", choices=["attention", "decoder"],
+                    help="which timed loops cudaProfilerStart/Stop bracket (for `ncu --profile-from-start off`)")
     ap.add_argument("--decoder-d32", type=int, default=1, help="also time batched decode of the d32-class model (0: skip)")
     ap.add_argument("--longctx", type=int, default=1, help="also time the KV-length-sharded long-context case (0: skip)")
     ap.add_argument("--e2e-steps", type=int, default=200, help="steps of the end-to-end loop (profiling runs shrink it)")
@@ -394,7 +402,8 @@ def main() -> None:
     for _ in range(3):  # first-use costs (module load, attribute set-up) stay out of any profiled range
         step()
     torch.cuda.synchronize()
-    torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see exactly the loops below
+    if args.profile_range == "attention":
+        torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see exactly the loops below
     with ClockSampler(local) as clocks:
         ms_total = timed(step, args.steps, args.warmup)
     ms_split = timed(split, args.steps, 3)
@@ -421,7 +430,8 @@ def main() -> None:
         e2e_step()
     barrier()
     e2e_s = torch.tensor([time.perf_counter() - t0], device=device)
-    torch.cuda.profiler.stop()
+    if args.profile_range == "attention":
+        torch.cuda.profiler.stop()
     total_e2e_bytes = torch.tensor([float(e2e_bytes)], device=device)
     total_bytes = torch.tensor([float(algorithmic_bytes(lens))], device=device)
     if world > 1:
@@ -433,7 +443,8 @@ def main() -> None:
     h2d_bytes, d2h_bytes = decode.h2d_bytes, decode.d2h_bytes
     del cache, decode, workspace
     longctx = bench_longctx(rank, world, device, min(args.steps, 100), 5, timed) if args.longctx else None
-    decoder = bench_decoder(rank, world, device, 256) if args.decoder else None
+    decoder = bench_decoder(rank, world, device, args.decoder_tokens, args.profile_range == "decoder") \
+        if args.decoder else None
     decoder_d32 = bench_decoder_d32(rank, world, device, 128) if args.decoder_d32 else None
 
     if rank == 0:
