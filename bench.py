@@ -41,7 +41,7 @@ sys.path.insert(0, str(ROOT))
 HQ, HKV, D, BATCH = 32, 8, 128, 64
 METRIC, UNIT = "decode_attention_hbm_gbs", "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_decode_attn<1> launch on the target8k workload, from the
-# ncu capture summarised in profiles/decode_attn_split_target8k.md (1.1081 GB read + 7.5 MB written)
+# ncu capture summarised under profiles/ (1.1081 GB read + 7.5 MB written)
 TARGET8K_TRAFFIC_BYTES = 1_108_096_000 + 7_493_000
 
 

@@ -34,8 +34,6 @@ class DecodeStep:
         self.out_host = torch.zeros((batch, Hq, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
         self.qkv = torch.empty((batch, width), dtype=torch.bfloat16, device=dev)
         self.pos = torch.empty(batch, dtype=torch.int32, device=dev)
-        self.lens = torch.empty(batch, dtype=torch.int32, device=dev)
-        self.q = torch.empty((batch, Hq, HEAD_DIM), dtype=torch.bfloat16, device=dev)
         self.out = torch.empty((batch, Hq, HEAD_DIM), dtype=torch.bfloat16, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         need = ops.workspace_bytes(batch, Hq, Hkv, self.max_kv_len, self.chunk_pages)
