@@ -262,3 +262,56 @@ def test_fused_append_attention_equals_the_two_kernels(Hq, Hkv):
     torch.cuda.synchronize()
     assert status.item() == 1 and not out[1].any()
     assert torch.equal(caches[0].pages[0], before[0])  # slot 0 belongs to the refused row
+
+
+def _peer_call(parts, flags, rank, epoch, rows, out, status):
+    import ctypes
+    from nanochat_b200.native import cuda_library, pointer, stream
+    world = len(parts)
+    p = (ctypes.c_void_p * world)(*(t.data_ptr() for t in parts))
+    f = (ctypes.c_void_p * world)(*(t.data_ptr() for t in flags))
+    return cuda_library("decode_attn").decode_attn_merge_peers(p, f, world, rank, epoch, rows, pointer(out),
+                                                               pointer(status), stream())
+
+
+def test_peer_merge_on_one_gpu_with_flags_already_published():
+    """decode_attn_merge_peers with two 'ranks' whose buffers both live on this GPU and whose peer flag is already
+    at the epoch (no kernel waits for another): the result equals decode_attn_merge over the same states, and the
+    kernel publishes its own flag into both flag arrays."""
+    n, cuts = 700, [0, 320, 700]
+    case = helpers.attention_case(1400, 8, 2, [n, 100])
+    q = helpers.bits_bf16(case["q"]).cuda()
+    parts = []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        sl = {**case, "lens": [max(0, min(b, L) - min(a, L)) for L in case["lens"]]}
+        for key in ("k_bytes", "k_scale", "v_bytes", "v_scale"):
+            sl[key] = [x[:, a:b] for x in case[key]]
+        cache = load_cache(sl, max(max(sl["lens"]), 1))
+        lens = torch.tensor(sl["lens"], dtype=torch.int32, device="cuda")
+        parts.append(ncb.decode_attention_partial(q, cache, lens, max_kv_len=max(max(sl["lens"]), 1)))
+    want = ncb.merge_partials(torch.stack(parts))
+    flags = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(2)]
+    flags[0][1] = 7  # rank 1 has published epoch 7 into rank 0's flags
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.empty_like(want)
+    assert _peer_call(parts, flags, 0, 7, 2 * 8, out, status) == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0 and torch.equal(out, want)
+    assert flags[0].tolist() == [7, 7] and flags[1].tolist() == [7, 0]
+
+
+def test_peer_merge_wait_runs_out_and_reports():
+    """A peer that never publishes: the bounded wait gives up after about half a second, the status word carries
+    NCB_DEV_WAIT_TIMEOUT and the context stays usable."""
+    import time
+    parts = [torch.zeros((4, 132), dtype=torch.float32, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(2)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.empty((4, 128), dtype=torch.bfloat16, device="cuda")
+    t0 = time.perf_counter()
+    assert _peer_call(parts, flags, 0, 1, 4, out, status) == 0
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert status.item() == 2
+    assert 0.05 < waited < 10.0
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0  # the device still answers
