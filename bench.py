@@ -66,7 +66,7 @@ def peaks() -> tuple[float, str]:
 class ClockSampler:
     """SM clock and throttle reasons of one GPU, polled through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period: float = 0.01):
+    def __init__(self, index: int, period: float = 0.003):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self.period, self.stop_flag, self.thread = period, threading.Event(), None
         try:
@@ -85,15 +85,18 @@ class ClockSampler:
 
     def poll(self):
         while not self.stop_flag.is_set():
-            try:
-                self.samples.append(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
-                reasons = getattr(self.nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
-                    self.nvml.nvmlDeviceGetCurrentClocksThrottleReasons
-                bits = reasons(self.handle)
-                self.reasons.update(name for name, bit in self.NAMES.items() if bits & bit)
-            except Exception:
-                pass
+            self.sample()
             self.stop_flag.wait(self.period)
+
+    def sample(self):
+        try:
+            self.samples.append(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
+            reasons = getattr(self.nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                self.nvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            bits = reasons(self.handle)
+            self.reasons.update(name for name, bit in self.NAMES.items() if bits & bit)
+        except Exception:
+            pass
 
     def __enter__(self):
         if self.nvml:
@@ -215,7 +218,7 @@ def bench_decoder(rank: int, world: int, device, new_tokens: int, profile: bool 
 
     cfg = DecoderConfig(n_layers=20, hidden=1280, n_heads=10, n_kv_heads=10, intermediate=5120, vocab=65536,
                         rope_theta=10000.0, max_len=512 + new_tokens)
-    decoder = Decoder(cfg, DecoderWeights.random_init(cfg, 0, device), 8, device)
+    decoder = Decoder(cfg, DecoderWeights.random_init(cfg, 0, device, on_device=True), 8, device)
     gen = torch.Generator().manual_seed(100 + rank)
     prompts = torch.randint(0, 65536, (8, 512), generator=gen).tolist()
     decoder.generate(prompts, 8)  # warm-up: graph capture, cuBLAS heuristics
@@ -249,7 +252,7 @@ def bench_decoder_d32(rank: int, world: int, device, new_tokens: int) -> dict:
     ctx = torch.randint(256, 8193, (B,), generator=gen).tolist()
     cfg = DecoderConfig(n_layers=32, hidden=2048, n_heads=16, n_kv_heads=4, intermediate=8192, vocab=65536,
                         rope_theta=10000.0, max_len=8192 + new_tokens + 8)
-    decoder = Decoder(cfg, DecoderWeights.random_init(cfg, 1, device), B, device)
+    decoder = Decoder(cfg, DecoderWeights.random_init(cfg, 1, device, on_device=True), B, device)
     dgen = torch.Generator(device=device).manual_seed(300 + rank)
     filled = ncb.Fp8KVCache(B, 4, cfg.max_len, device=device)
     for slot, n in enumerate(ctx):
@@ -378,9 +381,9 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps: int, warmup: int) -> float:
+    def timed(fn, steps: int, warmup: int, during=None) -> float:
         """Milliseconds for `steps` calls after `warmup`: CUDA events on the launching stream, barrier and
-        synchronize on both sides, max over ranks."""
+        synchronize on both sides, max over ranks. `during` runs once while the queued steps still execute."""
         for _ in range(warmup):
             fn()
         barrier()
@@ -389,6 +392,8 @@ def main() -> None:
         for _ in range(steps):
             fn()
         end.record()
+        if during:
+            during()
         barrier()
         ms = torch.tensor([start.elapsed_time(end)], device=device)
         if world > 1:
@@ -405,7 +410,7 @@ def main() -> None:
     if args.profile_range == "attention":
         torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see exactly the loops below
     with ClockSampler(local) as clocks:
-        ms_total = timed(step, args.steps, args.warmup)
+        ms_total = timed(step, args.steps, args.warmup, during=clocks.sample if clocks.nvml else None)
     ms_split = timed(split, args.steps, 3)
 
     # ---- end to end through the public step object with host buffers

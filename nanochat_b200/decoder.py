@@ -69,13 +69,17 @@ class DecoderWeights:
     layers: list[LayerWeights]
 
     @staticmethod
-    def random_init(cfg: DecoderConfig, seed: int, device: "torch.device | str", std: float = 0.02) -> "DecoderWeights":
-        """bf16 weights drawn from N(0, std) on the CPU generator (identical on every machine), gains = 1."""
-        gen = torch.Generator().manual_seed(seed)
+    def random_init(cfg: DecoderConfig, seed: int, device: "torch.device | str", std: float = 0.02,
+                    on_device: bool = False) -> "DecoderWeights":
+        """bf16 weights drawn from N(0, std), gains = 1. By default on the CPU generator (identical on every
+        machine, which tests rely on); on_device draws with the device's generator instead, much faster for
+        billion-parameter benchmark models."""
+        where = device if on_device else "cpu"
+        gen = torch.Generator(device=where).manual_seed(seed)
         C, Fdim = cfg.hidden, cfg.intermediate
 
         def w(*shape):
-            return (torch.randn(*shape, generator=gen) * std).bfloat16().to(device)
+            return (torch.randn(*shape, generator=gen, device=where) * std).bfloat16().to(device)
 
         layers = [LayerWeights(w(cfg.qkv_width, C), w(C, cfg.n_heads * HEAD_DIM), w(Fdim, C), w(C, Fdim),
                                torch.ones(HEAD_DIM, device=device), torch.ones(HEAD_DIM, device=device))
