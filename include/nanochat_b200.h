@@ -207,6 +207,11 @@ int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int ro
                 int epilogue, void *stream);
 /* h bf16 [rows][C] = rms_norm(embed[tokens]); embed bf16 [vocab][C]; tokens int64 [rows]; C a multiple of 8. */
 int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, int vocab, void *stream);
+/* h bf16 [rows][C] += y (same shape, or NULL for no add), in bf16; n bf16 [rows][C] = rms_norm(h). Any number of
+ * rows; C a multiple of 8, at most 4096. The norm / residual steps between library GEMMs (decode.cu:415-456). */
+int add_rms_norm(void *h, const void *y, void *n, long long rows, int C, void *stream);
+/* u bf16 [count] = relu(u)^2 in place (the MLP activation, decode.cu:170-208 EPI_RELU2); count a multiple of 8. */
+int relu2_inplace(void *u, long long count, void *stream);
 /* tokens[row] (int64) = argmax of logits fp32 [rows][vocab], ties to the lowest id; pos[row] (int32) += 1; with
  * trace (int64 [rows][trace_stride], may be NULL) also trace[row][new pos[row]] = the choice. */
 int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int vocab, void *trace, int trace_stride,

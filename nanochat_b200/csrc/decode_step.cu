@@ -227,6 +227,67 @@ __global__ void __launch_bounds__(128) k_embed_norm(const bf16 *embed, const lon
         *reinterpret_cast<uint4 *>(h + (size_t)row * C + i) = scale_bf16x8(*reinterpret_cast<const uint4 *>(e + i), r);
 }
 
+/* h[row] += y[row] (bf16 add, skipped when y is NULL), n[row] = rms_norm(h[row]); one block of 256 threads per row,
+ * the row held in registers between the two passes (C <= 256 * 8 * ROW_VECS). For any number of rows: the norm and
+ * residual steps between library GEMMs when a pass has more than 16 rows (decode.cu:415-443 RESID_NORM / NORM). */
+constexpr int ROW_THREADS = 256, ROW_VECS = 2;
+__global__ void __launch_bounds__(ROW_THREADS) k_add_rms_norm(bf16 *h, const bf16 *y, bf16 *n, int C) {
+    __shared__ float warp_sums[ROW_THREADS / 32];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const size_t base = (size_t)blockIdx.x * C;
+    uint4 v[ROW_VECS];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < ROW_VECS; j++) {
+        const int i = (threadIdx.x + j * ROW_THREADS) * 8;
+        if (i < C) {
+            v[j] = *reinterpret_cast<const uint4 *>(h + base + i);
+            if (y) {
+                const uint4 w = *reinterpret_cast<const uint4 *>(y + base + i);
+                __nv_bfloat162 *a = reinterpret_cast<__nv_bfloat162 *>(&v[j]);
+                const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&w);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 fa = __bfloat1622float2(a[e]), fb = __bfloat1622float2(b[e]);
+                    a[e] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+                }
+                *reinterpret_cast<uint4 *>(h + base + i) = v[j];
+            }
+            s += sumsq_bf16x8(v[j]);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = s;
+    __syncthreads();
+    s = 0.f;
+#pragma unroll
+    for (int w = 0; w < ROW_THREADS / 32; w++) s += warp_sums[w];
+    const float r = rsqrtf(s / (float)C + FLT_EPSILON);
+#pragma unroll
+    for (int j = 0; j < ROW_VECS; j++) {
+        const int i = (threadIdx.x + j * ROW_THREADS) * 8;
+        if (i < C) *reinterpret_cast<uint4 *>(n + base + i) = scale_bf16x8(v[j], r);
+    }
+}
+
+/* u = relu(u)^2 in bf16, in place, 8 values per thread. */
+__global__ void __launch_bounds__(256) k_relu2(bf16 *u, long long count) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const long long i = ((long long)blockIdx.x * 256 + threadIdx.x) * 8;
+    if (i >= count) return;
+    uint4 v = *reinterpret_cast<const uint4 *>(u + i);
+    __nv_bfloat162 *a = reinterpret_cast<__nv_bfloat162 *>(&v);
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const float2 f = __bfloat1622float2(a[e]);
+        const float x = fmaxf(f.x, 0.f), z = fmaxf(f.y, 0.f);
+        a[e] = __floats2bfloat162_rn(x * x, z * z);
+    }
+    *reinterpret_cast<uint4 *>(u + i) = v;
+}
+
 /* tokens[row] = argmax(logits[row]) (ties to the lowest id, decode.cu:90-96), pos[row] += 1; one block per row. */
 __global__ void __launch_bounds__(1024) k_greedy(const float *logits, long long *tokens, int32_t *pos, int vocab,
                                                  long long *trace, int trace_stride) {
@@ -364,6 +425,27 @@ int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, 
     if (((uintptr_t)embed | (uintptr_t)h) % 16) return NCB_ERR_ALIGN;
     return launch_pdl(k_embed_norm, dim3((rows + 3) / 4), dim3(128), (cudaStream_t)stream, (const bf16 *)embed,
                       (const long long *)tokens, (bf16 *)h, rows, C, vocab);
+}
+
+/* h bf16 [rows][C] += y (same shape; NULL: no add), n = rms_norm(h). C a multiple of 8, at most 4096. */
+int add_rms_norm(void *h, const void *y, void *n, long long rows, int C, void *stream) {
+    if (rows < 0 || rows > 0x7fffffffLL || C <= 0 || C % 8 || C > ROW_THREADS * 8 * ROW_VECS) return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    if (!h || !n) return NCB_ERR_ARG;
+    if (((uintptr_t)h | (uintptr_t)y | (uintptr_t)n) % 16) return NCB_ERR_ALIGN;
+    return launch_pdl(k_add_rms_norm, dim3((unsigned)rows), dim3(ROW_THREADS), (cudaStream_t)stream, (bf16 *)h,
+                      (const bf16 *)y, (bf16 *)n, C);
+}
+
+/* u bf16 [count] = relu(u)^2 in place; count a multiple of 8. */
+int relu2_inplace(void *u, long long count, void *stream) {
+    if (count < 0 || count % 8) return NCB_ERR_ARG;
+    if (count == 0) return NCB_OK;
+    if (!u) return NCB_ERR_ARG;
+    if ((uintptr_t)u % 16) return NCB_ERR_ALIGN;
+    const long long blocks = (count / 8 + 255) / 256;
+    if (blocks > 0x7fffffffLL) return NCB_ERR_ARG;
+    return launch_pdl(k_relu2, dim3((unsigned)blocks), dim3(256), (cudaStream_t)stream, (bf16 *)u, count);
 }
 
 /* tokens[row] = argmax(logits[row]) over fp32 [rows][vocab], ties to the lowest id; pos[row] += 1; if trace (int64

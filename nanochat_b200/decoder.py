@@ -4,10 +4,11 @@ Stands where the reference's NativeDecoder / decode.cu step graph stands (infere
 model/kernels/decode.cu:848-891): per layer
     norm -> qkv GEMM -> [kv_append_fp8 -> decode_attn_fp8] -> o GEMM + residual -> norm -> up GEMM, relu^2 ->
     down GEMM + residual
-then the final norm, the lm_head GEMM and an argmax. The bracketed part is this package's kernels; the GEMMs are
-plain library GEMMs (torch.matmul -> cuBLAS) and the norms/activations are torch operators in this first cut —
-the reference's own GEMM kernel is Hopper-only wgmma (decode.cu:232-359) and has to be replaced either way. The
-whole step is captured in one CUDA graph per batch size, the reference's remedy for launch-bound decode steps.
+then the final norm, the lm_head GEMM and an argmax. Steps of at most 16 rows run entirely on this package's
+kernels (csrc/decode_step.cu: weight-streaming GEMMs with fused norm and epilogues); larger passes (bigger batches,
+prefill) keep the GEMMs on cuBLAS and run everything between them on this package's kernels — the reference's own
+GEMM kernel is Hopper-only wgmma (decode.cu:232-359) and has to be replaced either way. The whole step is captured
+in one CUDA graph per batch size, the reference's remedy for launch-bound decode steps.
 
 Model semantics follow the reference's exported model (inference/modeling_nanochat.py:113-195): parameter-free RMS
 norm with eps FLT_EPSILON, h = x0 = norm(embed), per layer h = resid_lambda h + x0_lambda x0 (fp32, rounded once),
@@ -120,9 +121,48 @@ class Decoder:
         return self._workspaces[key]
 
     def hidden_rows(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int,
-                    attend_last_layer: bool = True) -> Tensor:
+                    attend_last_layer: bool = True, distinct_slots: bool = False) -> Tensor:
         """Final-normed hidden states (rows, C) bf16 of `tokens` at positions `pos` of slots `slot_map`; appends
-        every row's k, v to the caches. max_kv_len bounds pos + 1."""
+        every row's k, v to the caches. max_kv_len bounds pos + 1. Any number of rows: GEMMs on cuBLAS, everything
+        between them on this package's kernels (embedding + norm, residual add + norm, relu^2, append, attention).
+        distinct_slots: no two rows share a slot (a decode step), so the attention kernel may append its own
+        token; prefill passes, where rows of one sequence read each other's positions, need the separate append."""
+        cfg, lib, s = self.cfg, cuda_library("decode_step"), stream()
+        rows, C = tokens.shape[0], cfg.hidden
+        default_mix = all(l.resid_lambda == 1.0 and l.x0_lambda == 0.0 for l in self.w.layers)
+        if not default_mix or C % 8 or C > 4096 or cfg.intermediate % 8:
+            return self._hidden_rows_torch(tokens, pos, slot_map, max_kv_len, attend_last_layer)
+        lens = pos + 1
+        workspace = self._workspace(rows, max_kv_len)
+        h = torch.empty((rows, C), dtype=torch.bfloat16, device=self.device)
+        n = torch.empty_like(h)
+        check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
+        check(lib.add_rms_norm(pointer(h), None, pointer(n), rows, C, s), "add_rms_norm")
+        for i, layer in enumerate(self.w.layers):
+            qkv = n @ layer.wqkv.T
+            if distinct_slots and (attend_last_layer or i < cfg.n_layers - 1):
+                att = ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos,
+                                                self.caches[i], cfg.n_heads, max_kv_len, slot_map=slot_map,
+                                                window=self.windows[i], workspace=workspace, status=self.status)
+            else:
+                q = ops.kv_append(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
+                                  cfg.n_heads, slot_map=slot_map, status=self.status)
+                if i == cfg.n_layers - 1 and not attend_last_layer:
+                    return h  # prefill: the last layer only has to fill its cache (decode.cu:862)
+                att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map,
+                                           window=self.windows[i], workspace=workspace, status=self.status)
+            y = att.view(rows, -1) @ layer.wo.T
+            check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
+            u = n @ layer.wup.T
+            check(lib.relu2_inplace(pointer(u), u.numel(), s), "relu2_inplace")
+            y = u @ layer.wdown.T
+            check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
+        return n
+
+    def _hidden_rows_torch(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int,
+                           attend_last_layer: bool = True) -> Tensor:
+        """hidden_rows with torch operators around the append/attention kernels: the general form (per-layer
+        residual / x0 mixing, any hidden size)."""
         cfg = self.cfg
         rows = tokens.shape[0]
         lens = pos + 1
@@ -233,7 +273,7 @@ class Decoder:
             if fused:
                 self.fused_step(tokens, pos, slot_map, self.capacity, buf)
                 return
-            logits.copy_(self.head(self.hidden_rows(tokens, pos, slot_map, self.capacity)))
+            logits.copy_(self.head(self.hidden_rows(tokens, pos, slot_map, self.capacity, distinct_slots=True)))
             tokens.copy_(logits.argmax(-1))  # ties to the lowest id, as decode.cu:90-96
             pos.add_(1)
 

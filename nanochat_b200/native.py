@@ -48,6 +48,8 @@ SIGNATURES = {
     "decode_step": {
         "skinny_gemm": ([c_ptr] * 4 + [c_int] * 5 + [c_ptr], c_int),
         "embed_norm": ([c_ptr] * 3 + [c_int] * 3 + [c_ptr], c_int),
+        "add_rms_norm": ([c_ptr] * 3 + [c_ll, c_int, c_ptr], c_int),
+        "relu2_inplace": ([c_ptr, c_ll, c_ptr], c_int),
         "greedy_choice": ([c_ptr] * 3 + [c_int] * 2 + [c_ptr, c_int, c_ptr], c_int),
     },
 }

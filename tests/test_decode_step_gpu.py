@@ -87,3 +87,25 @@ def test_embed_norm_and_greedy_choice():
     assert tokens.tolist() == logits.argmax(-1).tolist() and tokens[1] == 123 and tokens[2] == 65535
     assert pos.tolist() == [4, 5, 6, 7, 8]
     assert [int(trace[r, pos[r]]) for r in range(rows)] == tokens.tolist() and int((trace >= 0).sum()) == rows
+
+
+@pytest.mark.parametrize("rows,C", [(1, 256), (33, 1280), (1024, 2048), (5, 4096), (7, 8)])
+def test_add_rms_norm_and_relu2_match_torch(rows, C):
+    gen = torch.Generator().manual_seed(rows + C)
+    h = torch.randn(rows, C, generator=gen).bfloat16().cuda()
+    y = torch.randn(rows, C, generator=gen).bfloat16().cuda()
+    lib = cuda_library("decode_step")
+    for add in (True, False):
+        h1, n = h.clone(), torch.empty_like(h)
+        assert lib.add_rms_norm(pointer(h1), pointer(y if add else None), pointer(n), rows, C, stream()) == 0
+        want_h = (h.float() + y.float()).bfloat16() if add else h
+        want_n = F.rms_norm(want_h, (C,), eps=EPS)
+        torch.cuda.synchronize()
+        assert torch.equal(h1, want_h)
+        assert (n.float() - want_n.float()).abs().max() <= 2 ** -7 * want_n.float().abs().max()
+        assert (n != want_n).float().mean() < 0.01
+    u = torch.randn(rows, C, generator=gen).bfloat16().cuda()
+    want = F.relu(u).float().square().bfloat16()
+    assert lib.relu2_inplace(pointer(u), u.numel(), stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(u, want)
