@@ -217,6 +217,20 @@ int relu2_inplace(void *u, long long count, void *stream);
 int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int vocab, void *trace, int trace_stride,
                   void *stream);
 
+/*
+ * The reference's sampled choice (decode.cu:90-120,195-203,364-411): per row, temperature 0 takes the argmax of the
+ * raw logits; otherwise logits are capped (softcap * tanh(s / softcap), softcap 0: none), optionally cut to the
+ * nucleus of mass top_p (keep e >= e*, the least e whose cumulative mass from below exceeds (1 - top_p) of the
+ * total; bisection on IEEE bits) and sampled by Gumbel-max with Philox4x32-10 noise at counter (token id,
+ * pos - first), key seed. Ties to the lowest id; `allow` (uint32 [rows][vocab / 32], may be NULL) masks tokens.
+ * tokens[row] = choice, pos[row] += 1, trace as greedy_choice (-1 logged if nothing is allowed).
+ * logits fp32 [rows][vocab]; probs fp32 [rows][vocab] scratch; temperature, top_p fp32 [rows]; seed uint64 [rows];
+ * first int32 [rows]; vocab a multiple of 32.
+ */
+int sample_choice(const void *logits, void *probs, const void *temperature, const void *top_p, const void *seed,
+                  const void *first, const void *allow, float softcap, void *tokens, void *pos, int rows, int vocab,
+                  void *trace, int trace_stride, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

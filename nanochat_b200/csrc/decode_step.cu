@@ -327,6 +327,139 @@ __global__ void __launch_bounds__(1024) k_greedy(const float *logits, long long 
     }
 }
 
+/* ---- sampling -------------------------------------------------------------------------------------------------
+ * The reference's choice rule (decode.cu:90-120 keys and Gumbel noise, :195-203 temperature and cap, :364-411
+ * nucleus): temperature 0 takes the argmax of the raw logits; otherwise the logits are capped (c tanh(s / c)),
+ * optionally cut to the nucleus of mass top_p (transformers' TopPLogitsWarper: keep e >= e*, the least e whose
+ * cumulative mass from below exceeds (1 - top_p) of the total, found by bisection on the IEEE bits of e in [0, 1])
+ * and sampled by Gumbel-max: argmax of s / T - log(-log u), u from Philox4x32-10 at counter (token id, step), key
+ * seed. Ties go to the lowest id. An optional bit mask restricts the choice to allowed tokens. */
+
+static __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+    for (int round = 0; round < 10; round++) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+        k.x += 0x9E3779B9u;
+        k.y += 0xBB67AE85u;
+    }
+    return c;
+}
+
+/* -log(-log(u)), u in (0, 1) from 52 random bits, exact in double. */
+static __device__ __forceinline__ float gumbel(unsigned long long seed, int step, int token) {
+    const uint4 x = philox4x32_10(make_uint4((uint32_t)token, (uint32_t)step, 0u, 0u),
+                                  make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+    const unsigned long long r = ((unsigned long long)x.x << 32 | x.y) >> 12;
+    return (float)-log(-log(ldexp(2.0 * (double)r + 1.0, -53)));
+}
+
+constexpr int SAMPLE_THREADS = 1024;
+
+static __device__ float block_sum_ordered(float v, float *scratch) { /* fixed order: lanes, then warps 0..31 */
+    for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.f;
+    for (int w = 0; w < SAMPLE_THREADS / 32; w++) s = __fadd_rn(s, scratch[w]);
+    return s;
+}
+
+struct SampleArgs {
+    const float *logits;       /* [rows][vocab] */
+    float *probs;              /* [rows][vocab] scratch for the nucleus */
+    const float *temperature, *top_p; /* [rows] */
+    const unsigned long long *seed;   /* [rows] */
+    const int32_t *first;      /* [rows]: the position of each row's first generated token's input (step = pos - first) */
+    const uint32_t *allow;     /* [rows][vocab / 32] or NULL */
+    long long *tokens;
+    int32_t *pos;
+    long long *trace;
+    int vocab, trace_stride;
+    float softcap;
+};
+
+__global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
+    __shared__ float scratch[SAMPLE_THREADS / 32];
+    __shared__ float best_v[SAMPLE_THREADS / 32];
+    __shared__ int best_i[SAMPLE_THREADS / 32];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, V = a.vocab;
+    const float *s = a.logits + (size_t)b * V;
+    float *e = a.probs + (size_t)b * V;
+    const uint32_t *allow = a.allow ? a.allow + (size_t)b * (V / 32) : nullptr;
+    const float T = a.temperature[b], top_p = a.top_p[b];
+    const bool sampled = T > 0.f, nucleus = sampled && top_p < 1.f;
+    const int step = a.pos[b] - a.first[b];
+    const unsigned long long seed = a.seed[b];
+    auto ok = [&](int r) { return !allow || ((allow[r >> 5] >> (r & 31)) & 1u); };
+    auto value = [&](int r) { /* the score the choice works on, before noise */
+        const float z = s[r];
+        if (!sampled) return z;
+        const float capped = a.softcap > 0.f ? __fmul_rn(a.softcap, tanhf(__fdiv_rn(z, a.softcap))) : z;
+        return __fdiv_rn(capped, T);
+    };
+    float least = 0.f;
+    if (nucleus) {
+        float m = -INFINITY;
+        for (int r = tid; r < V; r += SAMPLE_THREADS)
+            if (ok(r)) m = fmaxf(m, value(r));
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) scratch[warp] = m;
+        __syncthreads();
+        m = -INFINITY;
+        for (int w = 0; w < SAMPLE_THREADS / 32; w++) m = fmaxf(m, scratch[w]);
+        float sum = 0.f;
+        for (int r = tid; r < V; r += SAMPLE_THREADS) {
+            e[r] = ok(r) ? expf(__fsub_rn(value(r), m)) : 0.f;
+            sum = __fadd_rn(sum, e[r]);
+        }
+        const float drop = __fmul_rn(__fsub_rn(1.f, top_p), block_sum_ordered(sum, scratch));
+        uint32_t lo = 0u, hi = __float_as_uint(1.f); /* the least bits u with C(u) > drop */
+        while (lo < hi) {
+            const uint32_t mid = lo + (hi - lo) / 2;
+            const float x = __uint_as_float(mid);
+            float below = 0.f;
+            for (int r = tid; r < V; r += SAMPLE_THREADS)
+                if (e[r] <= x) below = __fadd_rn(below, e[r]);
+            if (block_sum_ordered(below, scratch) > drop) hi = mid; else lo = mid + 1;
+        }
+        least = __uint_as_float(lo);
+    }
+    float v = -INFINITY;
+    int at = 0x7fffffff;
+    for (int r = tid; r < V; r += SAMPLE_THREADS) {
+        if (!ok(r) || (nucleus && e[r] < least)) continue;
+        const float x = sampled ? __fadd_rn(value(r), gumbel(seed, step, r)) : value(r);
+        if (x > v || at == 0x7fffffff) v = x, at = r; /* ascending r: the first maximum wins */
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+        if (oi != 0x7fffffff && (at == 0x7fffffff || ov > v || (ov == v && oi < at))) v = ov, at = oi;
+    }
+    if (lane == 0) best_v[warp] = v, best_i[warp] = at;
+    __syncthreads();
+    if (warp == 0) {
+        v = best_v[lane], at = best_i[lane];
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+            if (oi != 0x7fffffff && (at == 0x7fffffff || ov > v || (ov == v && oi < at))) v = ov, at = oi;
+        }
+        if (lane == 0) {
+            const long long choice = at == 0x7fffffff ? -1 : at; /* -1: the mask allows nothing */
+            const int next = a.pos[b] + 1;
+            a.tokens[b] = choice < 0 ? 0 : choice;
+            a.pos[b] = next;
+            if (a.trace && next >= 0 && next < a.trace_stride) a.trace[(size_t)b * a.trace_stride + next] = choice;
+        }
+    }
+}
+
 /* ---- host side ---------------------------------------------------------------------------------------------- */
 
 template <typename... Args>
@@ -457,6 +590,25 @@ int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int voc
     if (!logits || !tokens || !pos) return NCB_ERR_ARG;
     return launch_pdl(k_greedy, dim3(rows), dim3(1024), (cudaStream_t)stream, (const float *)logits,
                       (long long *)tokens, (int32_t *)pos, vocab, (long long *)trace, trace_stride);
+}
+
+/*
+ * tokens[row] = the reference's choice for logits fp32 [rows][vocab] (see "sampling" above); pos[row] += 1; the
+ * choice is logged in trace like greedy_choice does (-1 when the mask allows no token).
+ *   temperature, top_p fp32 [rows]; seed uint64 [rows]; first int32 [rows] (step = pos - first picks the noise);
+ *   allow uint32 [rows][vocab / 32] or NULL; probs fp32 [rows][vocab] scratch (used when top_p < 1);
+ *   softcap: the logit cap c applied to sampled rows (0: none). vocab a multiple of 32.
+ */
+int sample_choice(const void *logits, void *probs, const void *temperature, const void *top_p, const void *seed,
+                  const void *first, const void *allow, float softcap, void *tokens, void *pos, int rows, int vocab,
+                  void *trace, int trace_stride, void *stream) {
+    if (rows < 0 || vocab <= 0 || vocab % 32 || softcap < 0.f) return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    if (!logits || !probs || !temperature || !top_p || !seed || !first || !tokens || !pos) return NCB_ERR_ARG;
+    const SampleArgs a = {(const float *)logits, (float *)probs, (const float *)temperature, (const float *)top_p,
+                          (const unsigned long long *)seed, (const int32_t *)first, (const uint32_t *)allow,
+                          (long long *)tokens, (int32_t *)pos, (long long *)trace, vocab, trace_stride, softcap};
+    return launch_pdl(k_sample, dim3(rows), dim3(SAMPLE_THREADS), (cudaStream_t)stream, a);
 }
 
 } /* extern "C" */

@@ -50,6 +50,7 @@ SIGNATURES = {
         "embed_norm": ([c_ptr] * 3 + [c_int] * 3 + [c_ptr], c_int),
         "add_rms_norm": ([c_ptr] * 3 + [c_ll, c_int, c_ptr], c_int),
         "relu2_inplace": ([c_ptr, c_ll, c_ptr], c_int),
+        "sample_choice": ([c_ptr] * 7 + [c_float, c_ptr, c_ptr, c_int, c_int, c_ptr, c_int, c_ptr], c_int),
         "greedy_choice": ([c_ptr] * 3 + [c_int] * 2 + [c_ptr, c_int, c_ptr], c_int),
     },
 }
