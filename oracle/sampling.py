@@ -59,6 +59,8 @@ def choose(logits: np.ndarray, temperature: float, top_p: float, seed: int, step
     if temperature <= 0:
         z = np.where(ok, logits.astype(np.float32), -np.inf)
         return {"token": int(np.argmax(z)) if ok.any() else -1, "keys": z, "kept": ok}
+    if not ok.any():
+        return {"token": -1, "keys": np.full(V, -np.inf, np.float32), "kept": ok}
     s = scores(logits, temperature, softcap)
     kept, e, least = ok.copy(), None, None
     if top_p < 1:
