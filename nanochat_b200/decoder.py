@@ -96,9 +96,11 @@ class Decoder:
     """Greedy decoding of up to n_slots sequences with an fp8 KV cache per layer."""
 
     def __init__(self, cfg: DecoderConfig, weights: DecoderWeights, n_slots: int, device: "torch.device | str" = "cuda",
-                 prompt_store: int = 0):
+                 prompt_store: int = 0, softcap: float = 0.0):
         """prompt_store: positions of pinned host memory for prompts already prefilled (0: none); a prompt seen
-        again is copied back into its slot instead of being prefilled (inference/decoder.py:193-232)."""
+        again is copied back into its slot instead of being prefilled (inference/decoder.py:193-232). softcap: the
+        output-logit cap c applied (c tanh(z / c)) before sampling; greedy choices need none (decode.cu:195)."""
+        self.softcap = float(softcap)
         self.cfg, self.w, self.n_slots, self.device = cfg, weights, n_slots, torch.device(device)
         self.caches = [Fp8KVCache(n_slots, cfg.n_kv_heads, cfg.max_len, device=device) for _ in range(cfg.n_layers)]
         self.store = PromptStore(self.caches, prompt_store) if prompt_store > 0 else None
@@ -257,79 +259,105 @@ class Decoder:
 
     # ---- decode -----------------------------------------------------------------------------------------------
 
-    def _step_graph(self, batch: int):
-        """The captured step for `batch` slots 0 .. batch - 1: tokens, pos (device) -> argmax tokens; pos += 1."""
-        if batch in self._graphs:
-            return self._graphs[batch]
-        dev = self.device
+    def _step_graph(self, batch: int, sampled: bool = False):
+        """The captured step for `batch` slots 0 .. batch - 1: tokens, pos (device) -> chosen tokens; pos += 1; every
+        choice is logged at its position in a (batch, capacity + 1) trace. `sampled` steps choose by temperature /
+        nucleus / Gumbel-max (sample_choice) from per-slot controls, the others take the argmax."""
+        key = (batch, sampled)
+        if key in self._graphs:
+            return self._graphs[key]
+        dev, lib, V = self.device, cuda_library("decode_step"), self.cfg.vocab
         tokens = torch.zeros(batch, dtype=torch.long, device=dev)
         pos = torch.zeros(batch, dtype=torch.int32, device=dev)
         slot_map = torch.arange(batch, dtype=torch.int32, device=dev)
         fused = self.use_fused and self.fused_supported(batch)
-        buf = self.fused_buffers(batch) if fused else None
-        logits = buf["logits"] if fused else torch.empty((batch, self.cfg.vocab), dtype=torch.float32, device=dev)
+        buf = self.fused_buffers(batch) if fused else {
+            "logits": torch.empty((batch, V), dtype=torch.float32, device=dev),
+            "trace": torch.zeros((batch, self.capacity + 1), dtype=torch.long, device=dev)}
+        logits, trace = buf["logits"], buf["trace"]
+        ctl = None
+        if sampled:
+            assert V % 32 == 0, "sampling needs a vocabulary that is a multiple of 32"
+            ctl = {"temperature": torch.zeros(batch, dtype=torch.float32, device=dev),
+                   "top_p": torch.ones(batch, dtype=torch.float32, device=dev),
+                   "seed": torch.zeros(batch, dtype=torch.long, device=dev),
+                   "first": torch.zeros(batch, dtype=torch.int32, device=dev),
+                   "probs": torch.empty((batch, V), dtype=torch.float32, device=dev)}
 
         def body():
             if fused:
-                self.fused_step(tokens, pos, slot_map, self.capacity, buf)
-                return
-            logits.copy_(self.head(self.hidden_rows(tokens, pos, slot_map, self.capacity, distinct_slots=True)))
-            tokens.copy_(logits.argmax(-1))  # ties to the lowest id, as decode.cu:90-96
-            pos.add_(1)
+                self.fused_step(tokens, pos, slot_map, self.capacity, buf, choose=False)
+            else:
+                logits.copy_(self.head(self.hidden_rows(tokens, pos, slot_map, self.capacity, distinct_slots=True)))
+            if sampled:
+                check(lib.sample_choice(pointer(logits), pointer(ctl["probs"]), pointer(ctl["temperature"]),
+                                        pointer(ctl["top_p"]), pointer(ctl["seed"]), pointer(ctl["first"]), None,
+                                        self.softcap, pointer(tokens), pointer(pos), batch, V, pointer(trace),
+                                        trace.shape[1], stream()), "sample_choice")
+            else:
+                check(lib.greedy_choice(pointer(logits), pointer(tokens), pointer(pos), batch, V, pointer(trace),
+                                        trace.shape[1], stream()), "greedy_choice")
 
-        stream = torch.cuda.Stream(dev)
-        stream.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(stream):
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
             body()  # eager warm-up: first-use set-up outside capture; it writes position 0, rewritten on replay
             pos.zero_()
             tokens.zero_()
-            stream.synchronize()
+            side.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
+            with torch.cuda.graph(graph, stream=side):
                 body()
         # the graph holds raw pointers: every tensor its kernels touch must stay alive as long as the graph does
-        self._graph_tensors[batch] = (slot_map, buf)
-        self._graphs[batch] = (graph, stream, tokens, pos, logits, buf["trace"] if fused else None)
-        return self._graphs[batch]
+        self._graph_tensors[key] = (slot_map, buf, ctl)
+        self._graphs[key] = (graph, side, tokens, pos, logits, trace, ctl)
+        return self._graphs[key]
 
     @torch.no_grad()
-    def decode_from(self, first_tokens: list[int], positions: list[int], steps: int) -> tuple[list[list[int]], float]:
-        """`steps` greedy steps for slots 0 .. B - 1 whose caches already hold positions 0 .. positions[b] - 1:
-        slot b's next input is first_tokens[b] at position positions[b]. Returns the chosen tokens and the seconds
-        the steps took on the device. Stream-ordered after work queued on the current stream."""
+    def decode_from(self, first_tokens: list[int], positions: list[int], steps: int, temperature: float = 0.0,
+                    top_p: float = 1.0, seeds: list[int] | None = None) -> tuple[list[list[int]], float]:
+        """`steps` steps for slots 0 .. B - 1 whose caches already hold positions 0 .. positions[b] - 1: slot b's
+        next input is first_tokens[b] at position positions[b]. Greedy at temperature 0, else sampled as the
+        reference samples (capped logits / temperature, nucleus top_p, Gumbel-max noise keyed by seeds[b] and the
+        step; the cap is the decoder's `softcap`). Returns the chosen tokens and the seconds the steps took on the
+        device. Stream-ordered after work queued on the current stream."""
         B = len(first_tokens)
         assert B <= self.n_slots and max(positions) + steps <= self.capacity
-        graph, stream, tokens, pos, logits, trace = self._step_graph(B)
+        sampled = temperature > 0.0
+        graph, side, tokens, pos, logits, trace, ctl = self._step_graph(B, sampled)
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        stream.wait_stream(torch.cuda.current_stream(self.device))
-        with torch.cuda.stream(stream):
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
             tokens.copy_(torch.tensor(first_tokens, dtype=torch.long))
             pos.copy_(torch.tensor(positions, dtype=torch.int32))
             first = pos.clone()
-            out = torch.empty((steps, B), dtype=torch.long, device=self.device)
+            if sampled:
+                ctl["temperature"].fill_(temperature)
+                ctl["top_p"].fill_(top_p)
+                ctl["seed"].copy_(torch.tensor(seeds if seeds is not None else list(range(B)), dtype=torch.long))
+                ctl["first"].copy_(first)
             begin.record()
-            for t in range(steps):
+            for _ in range(steps):
                 graph.replay()
-                if trace is None:
-                    out[t].copy_(tokens)
             end.record()
-            if trace is not None:  # the fused step logged every choice at its position: one gather at the end
-                at = first.long()[None, :] + 1 + torch.arange(steps, device=self.device)[:, None]
-                out = trace.gather(1, at.T).T.contiguous()
-        stream.synchronize()
+            at = first.long()[:, None] + 1 + torch.arange(steps, device=self.device)[None, :]
+            out = trace.gather(1, at)  # every choice was logged at its position: one gather at the end
+        side.synchronize()
         code = int(self.status.item())
         if code:
             raise RuntimeError(f"device status {code:#x} (NCB_DEV_* bits)")
-        return out.T.tolist(), begin.elapsed_time(end) * 1e-3
+        return out.tolist(), begin.elapsed_time(end) * 1e-3
 
     @torch.no_grad()
-    def generate(self, prompts: list[list[int]], max_new_tokens: int) -> tuple[list[list[int]], dict]:
-        """Greedy continuation of every prompt (slot b = prompt b). Returns the new tokens and timings: prefill
-        seconds, decode seconds (the max_new_tokens steps), tokens per second of the decode phase."""
+    def generate(self, prompts: list[list[int]], max_new_tokens: int, temperature: float = 0.0, top_p: float = 1.0,
+                 seeds: list[int] | None = None) -> tuple[list[list[int]], dict]:
+        """Continuation of every prompt (slot b = prompt b), greedy or sampled (see decode_from). Returns the new
+        tokens and timings: prefill seconds, decode seconds (the max_new_tokens steps), tokens per second of the
+        decode phase."""
         B = len(prompts)
         assert B <= self.n_slots and all(len(p) >= 1 for p in prompts)
         assert max(len(p) for p in prompts) - 1 + max_new_tokens <= self.capacity
-        self._step_graph(B)  # capture (and its warm-up step) before the caches are filled
+        self._step_graph(B, temperature > 0.0)  # capture (and its warm-up step) before the caches are filled
         start, mid = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         missing = [b for b in range(B) if self.store is None or not self.store.load(b, prompts[b])]
@@ -338,6 +366,7 @@ class Decoder:
             for b in missing:
                 self.store.save(b, prompts[b])
         mid.record()
-        out, decode_s = self.decode_from([p[-1] for p in prompts], [len(p) - 1 for p in prompts], max_new_tokens)
+        out, decode_s = self.decode_from([p[-1] for p in prompts], [len(p) - 1 for p in prompts], max_new_tokens,
+                                         temperature, top_p, seeds)
         return out, {"prefill_s": start.elapsed_time(mid) * 1e-3, "decode_s": decode_s,
                      "tokens_per_s": B * max_new_tokens / decode_s}

@@ -141,3 +141,30 @@ def test_prompt_store_round_trip_gives_the_same_stream():
     second, _ = dec.generate(list(reversed(prompts)), 6)  # other slots than the first time
     assert calls == [0]
     assert second == list(reversed(first))
+
+
+def test_sampled_generation_is_reproducible_and_follows_the_choice_rule():
+    """Sampled decoding: the same seeds give the same stream, other seeds another; the first sampled token equals
+    the checker's choice for the step's logits."""
+    from oracle import sampling
+    cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=4, n_kv_heads=2, intermediate=1024, vocab=320, max_len=128)
+    w = DecoderWeights.random_init(cfg, seed=9, device="cuda", std=0.05)
+    gen = torch.Generator().manual_seed(10)
+    prompts = [torch.randint(0, 320, (n,), generator=gen).tolist() for n in (5, 20)]
+    dec = Decoder(cfg, w, 2, softcap=15.0)
+    a, _ = dec.generate(prompts, 8, temperature=0.9, top_p=0.8, seeds=[11, 12])
+    b, _ = dec.generate(prompts, 8, temperature=0.9, top_p=0.8, seeds=[11, 12])
+    c, _ = dec.generate(prompts, 8, temperature=0.9, top_p=0.8, seeds=[13, 14])
+    g, _ = dec.generate(prompts, 8)
+    assert a == b and a != c and a != g
+    # step 0 of each sequence against the checker, on the logits of the eager path
+    ref = Decoder(cfg, w, 2)
+    with torch.no_grad():
+        ref.prefill(prompts, [0, 1])
+        for s_, (p, seed) in enumerate(zip(prompts, (11, 12))):
+            logits = ref.logits_rows(torch.tensor([p[-1]], device="cuda"),
+                                     torch.tensor([len(p) - 1], dtype=torch.int32, device="cuda"),
+                                     torch.tensor([s_], dtype=torch.int32, device="cuda"), len(p))[0].cpu().numpy()
+            want = sampling.choose(logits, 0.9, 0.8, seed, 0, 15.0)
+            got = a[s_][0]
+            assert got == want["token"] or (want["kept"][got] and want["keys"][want["token"]] - want["keys"][got] < 5e-2)
