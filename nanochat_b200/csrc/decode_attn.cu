@@ -43,7 +43,6 @@
 constexpr int WARPS = NCB_WARPS; /* = stages per block; 12 stages of 16,896 B fit one SM's shared memory */
 constexpr int BLOCKS_PER_SM = 12 / WARPS;
 constexpr int THREADS = WARPS * 32;
-constexpr int PART = NCB_PART_FLOATS;
 constexpr uint32_t WAIT_TRIES = 1u << 19; /* x <= 2 us suspend hint each: about one second */
 constexpr float P_SCALE = 256.f;          /* folded probabilities in (0, 1] -> e4m3 range, exact power of two */
 constexpr float LO_SCALE = 16.f;          /* second term's gain: the first term's rounding error is <= 2^-4 ulp-wise */
@@ -134,11 +133,6 @@ static __device__ __forceinline__ void split4(const float *x, uint32_t &hi, uint
     hi = h01 | (h23 << 16);
     lo = l01 | (l23 << 16);
 }
-static __device__ __forceinline__ float ex2(float x) { /* exp2, -inf -> 0 */
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 static __device__ __forceinline__ float lg2(float x) { /* log2, 0 -> -inf */
     float y;
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -154,25 +148,6 @@ static __device__ __forceinline__ float head_sum(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 4);
     v += __shfl_xor_sync(0xffffffffu, v, 8);
     return v + __shfl_xor_sync(0xffffffffu, v, 16);
-}
-
-/* Where a sequence's attended positions and pages lie; shared by the split and merge kernels. */
-struct Span {
-    int begin, len, first_page, last_page; /* positions [begin, len), pages [first_page, last_page) */
-    int n_chunks, chunk;                   /* the pages cut into n_chunks runs of `chunk` pages (the last may be shorter) */
-};
-/* chunk_pages is an upper bound: a sequence takes the fewest chunks that respect it and then evens them out, so no
- * block is left with a stub (129 pages at 27 per chunk are 5 chunks of 26, 26, 26, 26, 25). */
-static __device__ __forceinline__ Span span_of(int len, int window, int chunk_pages) {
-    Span s;
-    s.len = len;
-    s.begin = (window > 0 && len > window) ? len - window : 0;
-    s.first_page = s.begin / PAGE_TOKENS;
-    s.last_page = (len + PAGE_TOKENS - 1) / PAGE_TOKENS;
-    const int pages = s.last_page - s.first_page;
-    s.n_chunks = (pages + chunk_pages - 1) / chunk_pages;
-    s.chunk = s.n_chunks > 0 ? (pages + s.n_chunks - 1) / s.n_chunks : 0;
-    return s;
 }
 
 /* ---- split-KV kernel ---------------------------------------------------------------------------------------- */
@@ -783,11 +758,11 @@ extern "C" {
 int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len) {
     if (B <= 0 || Hkv <= 0 || max_kv_len <= 0) return 1;
     /* aim at about four blocks per resident slot (BLOCKS_PER_SM per SM) when every sequence is max_kv_len long,
-     * at most 32 pages each (measured: longer chunks gain nothing and unbalance ragged batches); small problems get
-     * one page per warp (WARPS pages per block) or, below one block per slot, as many blocks as there are pages */
+     * at most 32 pages each (measured: longer chunks gain nothing and unbalance ragged batches) and at least one
+     * page per warp (measured on small batches: blocks with idle warps cost more than the lost parallelism) */
     const long long total = (long long)B * Hkv * pages_of(max_kv_len), slots = (long long)BLOCKS_PER_SM * sm_count();
     long long c = total / (4 * slots);
-    if (c < WARPS) c = min((long long)WARPS, max(1LL, total / slots));
+    if (c < WARPS) c = WARPS;
     if (c > 32) c = 32;
     return (int)c;
 }
@@ -841,6 +816,18 @@ int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain
     const AppendIn app = {qkv, q_gain, k_gain, cos, sin, qkv_row_stride, table_len};
     return attend(nullptr, kv_cache, pos, slot_map, workspace, workspace_bytes, out, nullptr, B, Hq, Hkv, n_slots,
                   pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream, &app);
+}
+
+int decode_step_attn_fp8_split(const void *qkv, const void *q_gain, const void *k_gain, const void *cos,
+                               const void *sin, const void *pos, const void *slot_map, void *kv_cache,
+                               void *workspace, long long workspace_bytes, int B, int Hq, int Hkv,
+                               long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot,
+                               int max_kv_len, int window, int chunk_pages, float softmax_scale, void *status,
+                               void *stream) {
+    const AppendIn app = {qkv, q_gain, k_gain, cos, sin, qkv_row_stride, table_len};
+    return launch_split(nullptr, kv_cache, pos, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots,
+                        pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, (cudaStream_t)stream,
+                        &app);
 }
 
 int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map,

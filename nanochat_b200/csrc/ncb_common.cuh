@@ -44,3 +44,31 @@ static __host__ __device__ __forceinline__ int page_v_byte(int j, int d) {
 static __device__ __forceinline__ void flag(int *status, int bit) {
     if (status) atomicOr(status, bit);
 }
+
+constexpr int PART = NCB_PART_FLOATS; /* one (m, l, 2 pad, o[128]) attention state, fp32 */
+
+static __device__ __forceinline__ float ex2(float x) { /* exp2, -inf -> 0 */
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+/* Where a sequence's attended positions and pages lie; shared by the split kernel and everything that merges its states. */
+struct Span {
+    int begin, len, first_page, last_page; /* positions [begin, len), pages [first_page, last_page) */
+    int n_chunks, chunk;                   /* the pages cut into n_chunks runs of `chunk` pages (the last may be shorter) */
+};
+/* chunk_pages is an upper bound: a sequence takes the fewest chunks that respect it and then evens them out, so no
+ * block is left with a stub (129 pages at 27 per chunk are 5 chunks of 26, 26, 26, 26, 25). */
+static __device__ __forceinline__ Span span_of(int len, int window, int chunk_pages) {
+    Span s;
+    s.len = len;
+    s.begin = (window > 0 && len > window) ? len - window : 0;
+    s.first_page = s.begin / PAGE_TOKENS;
+    s.last_page = (len + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    const int pages = s.last_page - s.first_page;
+    s.n_chunks = (pages + chunk_pages - 1) / chunk_pages;
+    s.chunk = s.n_chunks > 0 ? (pages + s.n_chunks - 1) / s.n_chunks : 0;
+    return s;
+}
+
