@@ -135,15 +135,6 @@ int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain
                          int table_len, int n_slots, int pages_per_slot, int max_kv_len, int window, int chunk_pages,
                          float softmax_scale, void *status, void *stream);
 
-/* decode_step_attn_fp8's first launch alone (append + split-KV attention, states left in the workspace), for a caller
- * that merges elsewhere, e.g. skinny_gemm_merged. */
-int decode_step_attn_fp8_split(const void *qkv, const void *q_gain, const void *k_gain, const void *cos,
-                               const void *sin, const void *pos, const void *slot_map, void *kv_cache,
-                               void *workspace, long long workspace_bytes, int B, int Hq, int Hkv,
-                               long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot,
-                               int max_kv_len, int window, int chunk_pages, float softmax_scale, void *status,
-                               void *stream);
-
 /*
  * The first of decode_attn_fp8's two launches alone: the split-KV kernel, leaving one state per (b, h, chunk) in
  * the workspace. For timing that kernel by itself and for callers that merge elsewhere; same arguments and
@@ -214,16 +205,6 @@ int decode_attn_merge_peers(const void *const *parts, void *const *flags, int wo
  */
 int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
                 int epilogue, void *stream);
-/*
- * The o projection straight from the attention states: skinny_gemm with the residual epilogue whose input rows are
- * the merge of the states a split-only attention call left in `parts` (its workspace), so the step needs no merge
- * launch (the merge of decode.cu:661-674 moved into the consumer). lens, len_add (1 if lens holds positions),
- * window, chunk_pages (resolved, not 0), max_kv_len and pages_per_slot are that call's. K = Hq * 128 a multiple of
- * 256, at most 2048; rows <= 16.
- */
-int skinny_gemm_merged(const void *parts, const void *lens, int len_add, int Hq, int max_kv_len, int window,
-                       int chunk_pages, int pages_per_slot, const void *w, const void *resid, void *y, int rows, int N,
-                       void *stream);
 /* h bf16 [rows][C] = rms_norm(embed[tokens]); embed bf16 [vocab][C]; tokens int64 [rows]; C a multiple of 8. */
 int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, int vocab, void *stream);
 /* h bf16 [rows][C] += y (same shape, or NULL for no add), in bf16; n bf16 [rows][C] = rms_norm(h). Any number of

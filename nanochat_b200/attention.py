@@ -116,24 +116,6 @@ def decode_step_attention(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tens
     return out
 
 
-def decode_step_attention_split(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tensor, sin: Tensor, pos: Tensor,
-                                cache: Fp8KVCache, Hq: int, max_kv_len: int, chunk_pages: int, workspace: Tensor,
-                                slot_map: Tensor | None = None, window: int = 0,
-                                softmax_scale: float | None = None, status: Tensor | None = None) -> None:
-    """Only the first launch of decode_step_attention: the token is appended and the per-chunk states are left in
-    `workspace` for a consumer that merges them itself (skinny_gemm_merged). chunk_pages must be resolved
-    (chunk_pages_for), since the consumer needs the same value."""
-    rows, Hkv = qkv.shape[0], cache.kv_heads
-    assert chunk_pages > 0 and qkv.dtype == torch.bfloat16 and qkv.stride(-1) == 1
-    assert pos.dtype == torch.int32 and pos.shape == (rows,) and pos.is_contiguous()
-    scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
-    rc = cuda_library("decode_attn").decode_step_attn_fp8_split(
-        pointer(qkv), pointer(q_gain), pointer(k_gain), pointer(cos), pointer(sin), pointer(pos), pointer(slot_map),
-        pointer(cache.pages), pointer(workspace), workspace.numel(), rows, Hq, Hkv, qkv.stride(0), cos.shape[0],
-        cache.n_slots, cache.pages_per_slot, max_kv_len, window, chunk_pages, scale, pointer(status), stream())
-    check(rc, "decode_step_attn_fp8_split")
-
-
 def decode_attention_static(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int,
                             slot_map: Tensor | None = None, window: int = 0, chunk_pages: int = 0,
                             softmax_scale: float | None = None, out: Tensor | None = None,

@@ -818,18 +818,6 @@ int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain
                   pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream, &app);
 }
 
-int decode_step_attn_fp8_split(const void *qkv, const void *q_gain, const void *k_gain, const void *cos,
-                               const void *sin, const void *pos, const void *slot_map, void *kv_cache,
-                               void *workspace, long long workspace_bytes, int B, int Hq, int Hkv,
-                               long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot,
-                               int max_kv_len, int window, int chunk_pages, float softmax_scale, void *status,
-                               void *stream) {
-    const AppendIn app = {qkv, q_gain, k_gain, cos, sin, qkv_row_stride, table_len};
-    return launch_split(nullptr, kv_cache, pos, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots,
-                        pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, (cudaStream_t)stream,
-                        &app);
-}
-
 int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
                           void *workspace, long long workspace_bytes, int B, int Hq, int Hkv, int n_slots,
                           int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale,

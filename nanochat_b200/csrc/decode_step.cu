@@ -34,48 +34,13 @@ constexpr int MAX_K_ITERS = 20;   /* 32 k-values per iteration and warp: K <= 8 
 
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_RELU2 = 2, EPI_F32 = 3 };
 
-/* XMERGE: the GEMM's input rows are not in memory yet but are the merge of the split-KV attention states
- * (what k_merge would have written): x[row][head * 128 + d] = bf16(sum_p w_p o_p[d] / sum_p w_p l_p). */
-struct XMerge {
-    const float *parts;  /* [rows][Hq][max_chunks][PART] */
-    const int32_t *lens; /* [rows]; the length is lens[row] + len_add */
-    int len_add, Hq, max_chunks, chunk_pages, window, pages_per_slot;
-};
-
 struct GemmArgs {
     const bf16 *x;     /* [rows][K] */
     const bf16 *w;     /* [N][K] */
     const bf16 *resid; /* [rows][N] for EPI_RESID (may alias y) */
     void *y;           /* [rows][N] bf16, or fp32 for EPI_F32 */
     int rows, N, K, norm_input;
-    XMerge xm;
 };
-
-/* Eight consecutive merged attention outputs of `row` starting at input feature k (a multiple of 8). */
-static __device__ __forceinline__ uint4 merged_x8(const XMerge &m, int row, int k) {
-    const int head = k >> 7, d = k & 127, len = m.lens[row] + m.len_add;
-    int n = 0;
-    if (len >= 0 && len <= m.pages_per_slot * PAGE_TOKENS) n = min(span_of(len, m.window, m.chunk_pages).n_chunks, m.max_chunks);
-    const float *st = m.parts + ((size_t)row * m.Hq + head) * m.max_chunks * PART;
-    float top = -INFINITY;
-    for (int p = 0; p < n; p++) top = fmaxf(top, st[p * PART]);
-    float lsum = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int p = 0; p < n; p++) {
-        const float *s = st + p * PART;
-        const float c = s[0] == -INFINITY ? 0.f : ex2(s[0] - top);
-        const float4 a = *reinterpret_cast<const float4 *>(s + 4 + d), b = *reinterpret_cast<const float4 *>(s + 8 + d);
-        lsum += c * s[1];
-        acc[0] += c * a.x, acc[1] += c * a.y, acc[2] += c * a.z, acc[3] += c * a.w;
-        acc[4] += c * b.x, acc[5] += c * b.y, acc[6] += c * b.z, acc[7] += c * b.w;
-    }
-    uint4 out;
-    __nv_bfloat162 *o = reinterpret_cast<__nv_bfloat162 *>(&out);
-    const bool any = lsum > 0.f;
-#pragma unroll
-    for (int e = 0; e < 4; e++)
-        o[e] = __floats2bfloat162_rn(any ? __fdiv_rn(acc[2 * e], lsum) : 0.f, any ? __fdiv_rn(acc[2 * e + 1], lsum) : 0.f);
-    return out;
-}
 
 static __device__ __forceinline__ void mma_bf16(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                 uint32_t b0, uint32_t b1) {
@@ -112,7 +77,7 @@ static __device__ __forceinline__ uint4 scale_bf16x8(const uint4 &u, float r) {
  * A block keeps its activation slice (normed once) in registers and walks over the feature tiles
  * blockIdx.x, blockIdx.x + gridDim.x, ...; while it reduces one tile the next tile's weights are already in flight
  * (PREFETCH: only where two weight slices fit the register file). */
-template <int ITERS, bool HI, int EPI, bool NORM, bool XMERGE = false>
+template <int ITERS, bool HI, int EPI, bool NORM>
 __global__ void __launch_bounds__(GEMM_THREADS, ITERS > 8 ? 2 : 1) k_skinny_gemm(GemmArgs a) {
     constexpr bool PREFETCH = ITERS <= 8;
     constexpr bool HOLD_X = NORM || PREFETCH; /* long K slices stream x with the MMAs to stay within 128 registers */
@@ -147,13 +112,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, ITERS > 8 ? 2 : 1) k_skinny_gemm
     if (HOLD_X) {
 #pragma unroll
         for (int i = 0; i < ITERS; i++) {
-            if (XMERGE) {
-                xlo[i] = lo_on ? merged_x8(a.xm, g, k_warp + 8 * t + 32 * i) : make_uint4(0, 0, 0, 0);
-                if (HI) xhi[i] = hi_on ? merged_x8(a.xm, g + 8, k_warp + 8 * t + 32 * i) : make_uint4(0, 0, 0, 0);
-            } else {
-                xlo[i] = lo_on ? *reinterpret_cast<const uint4 *>(xl + 32 * i) : make_uint4(0, 0, 0, 0);
-                if (HI) xhi[i] = hi_on ? *reinterpret_cast<const uint4 *>(xh + 32 * i) : make_uint4(0, 0, 0, 0);
-            }
+            xlo[i] = lo_on ? *reinterpret_cast<const uint4 *>(xl + 32 * i) : make_uint4(0, 0, 0, 0);
+            if (HI) xhi[i] = hi_on ? *reinterpret_cast<const uint4 *>(xh + 32 * i) : make_uint4(0, 0, 0, 0);
         }
     }
     if (NORM) { /* rows' 1 / sqrt(mean(x^2) + eps) over the full K, then x <- bf16(x * rstd) in registers */
@@ -588,45 +548,6 @@ int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int ro
     case 20: return launch_gemm_rows<20>(a, epilogue, s);
     default: return NCB_ERR_UNSUPPORTED;
     }
-}
-
-/*
- * skinny_gemm with epilogue 1 (residual add) whose input rows are the merged split-KV attention states instead of a
- * tensor in memory: the o projection right after decode_attn_fp8_split / decode_step_attn_fp8_split, without the
- * merge launch in between. parts is that call's workspace, lens / len_add / window / chunk_pages / max_kv_len its
- * arguments (chunk_pages already resolved, not 0). K = Hq * 128 must be a multiple of 256 and at most 2048.
- */
-int skinny_gemm_merged(const void *parts, const void *lens, int len_add, int Hq, int max_kv_len, int window,
-                       int chunk_pages, int pages_per_slot, const void *w, const void *resid, void *y, int rows, int N,
-                       void *stream) {
-    const int K = Hq * HEAD_DIM;
-    if (rows < 0 || rows > MAX_ROWS || Hq <= 0 || N <= 0 || N % TILE_N || K % (GEMM_WARPS * 32) || chunk_pages <= 0 ||
-        max_kv_len < 0 || window < 0 || pages_per_slot <= 0)
-        return NCB_ERR_ARG;
-    if (K / (GEMM_WARPS * 32) > 8) return NCB_ERR_UNSUPPORTED;
-    if (rows == 0) return NCB_OK;
-    if (!parts || !lens || !w || !resid || !y) return NCB_ERR_ARG;
-    if (((uintptr_t)parts | (uintptr_t)w) % 16 || (uintptr_t)y % 2) return NCB_ERR_ALIGN;
-    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
-    const int pages = (max_kv_len + PAGE_TOKENS - 1) / PAGE_TOKENS;
-    GemmArgs a = {nullptr, (const bf16 *)w, (const bf16 *)resid, y, rows, N, K, 0,
-                  {(const float *)parts, (const int32_t *)lens, len_add, Hq, max(1, (pages + chunk_pages - 1) / chunk_pages),
-                   chunk_pages, window, pages_per_slot}};
-    const dim3 block(GEMM_THREADS);
-    const int tiles = N / TILE_N;
-    cudaStream_t s = (cudaStream_t)stream;
-#define NCB_MERGED_CASE(I)                                                                                      \
-    case I: {                                                                                                   \
-        if (rows > 8) { auto k = k_skinny_gemm<I, true, EPI_RESID, false, true>; return launch_pdl(k, dim3(grid_for(k, tiles, true)), block, s, a); } \
-        auto k = k_skinny_gemm<I, false, EPI_RESID, false, true>;                                               \
-        return launch_pdl(k, dim3(grid_for(k, tiles, true)), block, s, a);                                      \
-    }
-    switch (K / (GEMM_WARPS * 32)) {
-        NCB_MERGED_CASE(1) NCB_MERGED_CASE(2) NCB_MERGED_CASE(3) NCB_MERGED_CASE(4) NCB_MERGED_CASE(5)
-        NCB_MERGED_CASE(6) NCB_MERGED_CASE(8)
-    default: return NCB_ERR_UNSUPPORTED;
-    }
-#undef NCB_MERGED_CASE
 }
 
 /* h bf16 [rows][C] = rms_norm(embed[tokens]); tokens int64 [rows]; C a multiple of 8. */

@@ -108,7 +108,6 @@ class Decoder:
         self.cos, self.sin = ops.rotary_table(self.capacity, cfg.rope_theta, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.windows = cfg.windows or [0] * cfg.n_layers
-        self.merge_in_o = True  # the o projection merges the attention states itself (one launch fewer per layer)
         self.use_fused = True  # decode steps of <= 16 rows run on the decode_step kernels when the shapes allow
         self._graphs: dict[int, tuple] = {}
         self._graph_tensors: dict[int, tuple] = {}
@@ -217,15 +216,12 @@ class Decoder:
     def fused_step(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int, buf: dict[str, Tensor],
                    choose: bool = True) -> Tensor:
         """One step for rows <= 16 on the decode_step kernels: fp32 logits in buf["logits"]; with `choose`, tokens
-        become the greedy choices and pos advances by one. 5 launches per layer: qkv GEMM (norm fused), split
-        attention (append fused), o GEMM + residual (merging the attention states itself), up GEMM (norm fused) +
-        relu^2, down GEMM + residual."""
+        become the greedy choices and pos advances by one. 6 launches per layer: qkv GEMM (norm fused), split
+        attention (append fused), merge, o GEMM + residual, up GEMM (norm fused) + relu^2, down GEMM + residual."""
         cfg, lib, s = self.cfg, cuda_library("decode_step"), stream()
         rows, C, Fd, A = tokens.shape[0], cfg.hidden, cfg.intermediate, cfg.n_heads * HEAD_DIM
         workspace = self._workspace(rows, max_kv_len)
         h, qkv, att, u = buf["h"], buf["qkv"], buf["att"], buf["u"]
-        chunk = ops.chunk_pages_for(rows, cfg.n_kv_heads, min(max_kv_len, self.capacity))
-        merged_o = self.merge_in_o and A <= 2048
 
         def gemm(x, w, resid, y, n, k, norm, epilogue):
             check(lib.skinny_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue, s),
@@ -234,18 +230,10 @@ class Decoder:
         check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
         for i, layer in enumerate(self.w.layers):
             gemm(h, layer.wqkv, None, qkv, cfg.qkv_width, C, 1, 0)
-            if merged_o:  # append + split attention, then the o projection merges the states itself
-                ops.decode_step_attention_split(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos,
-                                                self.caches[i], cfg.n_heads, max_kv_len, chunk, workspace,
-                                                slot_map=slot_map, window=self.windows[i], status=self.status)
-                check(lib.skinny_gemm_merged(pointer(workspace), pointer(pos), 1, cfg.n_heads, max_kv_len,
-                                             self.windows[i], chunk, self.caches[i].pages_per_slot, pointer(layer.wo),
-                                             pointer(h), pointer(h), rows, C, s), "skinny_gemm_merged")
-            else:
-                ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
-                                          cfg.n_heads, max_kv_len, slot_map=slot_map, window=self.windows[i],
-                                          workspace=workspace, out=att, status=self.status)
-                gemm(att, layer.wo, h, h, C, A, 0, 1)
+            ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
+                                      cfg.n_heads, max_kv_len, slot_map=slot_map, window=self.windows[i],
+                                      workspace=workspace, out=att, status=self.status)
+            gemm(att, layer.wo, h, h, C, A, 0, 1)
             gemm(h, layer.wup, None, u, Fd, C, 1, 2)
             gemm(u, layer.wdown, h, h, C, Fd, 0, 1)
         gemm(h, self.w.lm_head, None, buf["logits"], cfg.vocab, C, 1, 3)

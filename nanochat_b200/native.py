@@ -41,15 +41,12 @@ SIGNATURES = {
         "decode_attn_fp8_static": ([c_ptr] * 5 + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_step_attn_fp8": ([c_ptr] * 9 + [c_ll, c_ptr, c_int, c_int, c_int, c_ll] + [c_int] * 6
                                  + [c_float, c_ptr, c_ptr], c_int),
-        "decode_step_attn_fp8_split": ([c_ptr] * 9 + [c_ll, c_int, c_int, c_int, c_ll] + [c_int] * 6
-                                       + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_fp8_split": ([c_ptr] * 5 + [c_ll] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_merge": ([c_ptr, c_int, c_ll, c_ptr, c_ptr], c_int),
         "decode_attn_merge_peers": ([c_ptr, c_ptr, c_int, c_int, ctypes.c_uint, c_ll, c_ptr, c_ptr, c_ptr], c_int),
     },
     "decode_step": {
         "skinny_gemm": ([c_ptr] * 4 + [c_int] * 5 + [c_ptr], c_int),
-        "skinny_gemm_merged": ([c_ptr, c_ptr] + [c_int] * 6 + [c_ptr] * 3 + [c_int, c_int, c_ptr], c_int),
         "embed_norm": ([c_ptr] * 3 + [c_int] * 3 + [c_ptr], c_int),
         "add_rms_norm": ([c_ptr] * 3 + [c_ll, c_int, c_ptr], c_int),
         "relu2_inplace": ([c_ptr, c_ll, c_ptr], c_int),

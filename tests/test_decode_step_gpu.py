@@ -109,38 +109,3 @@ def test_add_rms_norm_and_relu2_match_torch(rows, C):
     assert lib.relu2_inplace(pointer(u), u.numel(), stream()) == 0
     torch.cuda.synchronize()
     assert torch.equal(u, want)
-
-
-@pytest.mark.parametrize("Hq,Hkv,rows", [(10, 10, 8), (4, 1, 3), (16, 4, 12)])
-def test_o_projection_from_attention_states_equals_merge_then_gemm(Hq, Hkv, rows):
-    """skinny_gemm_merged after a split-only append+attention call against decode_step_attention (split + merge)
-    followed by skinny_gemm with the residual epilogue."""
-    import nanochat_b200 as ncb
-    from nanochat_b200 import attention as ops
-    gen = torch.Generator().manual_seed(Hq * 7 + rows)
-    lens = torch.randint(1, 700, (rows,), generator=gen).tolist()
-    C = 1280
-    cache_a, cache_b = ncb.Fp8KVCache(rows, Hkv, 768), ncb.Fp8KVCache(rows, Hkv, 768)
-    filler = (torch.randint(0, 120, cache_a.pages.shape, generator=gen, dtype=torch.uint8)).cuda()  # finite e4m3, small scales
-    cache_a.pages.copy_(filler); cache_b.pages.copy_(filler)
-    cos, sin = ncb.rotary_table(768, 1e4, device="cuda")
-    ones = torch.ones(128, device="cuda")
-    qkv = torch.randn(rows, (Hq + 2 * Hkv) * 128, generator=gen).bfloat16().cuda()
-    pos = torch.tensor(lens, dtype=torch.int32, device="cuda")
-    wo = (torch.randn(C, Hq * 128, generator=gen) * 0.05).bfloat16().cuda()
-    h = torch.randn(rows, C, generator=gen).bfloat16().cuda()
-    for window in (0, 130):
-        chunk = ops.chunk_pages_for(rows, Hkv, 768)
-        ws = torch.empty(ncb.workspace_bytes(rows, Hq, Hkv, 768, chunk), dtype=torch.uint8, device="cuda")
-        att = ncb.decode_step_attention(qkv, ones, ones, cos, sin, pos, cache_a, Hq, 768, window=window, chunk_pages=chunk)
-        want = gemm(att.view(rows, -1), wo, h, rows, C, Hq * 128, 0, 1)
-        ops.decode_step_attention_split(qkv, ones, ones, cos, sin, pos, cache_b, Hq, 768, chunk, ws, window=window)
-        got = h.clone()
-        rc = cuda_library("decode_step").skinny_gemm_merged(pointer(ws), pointer(pos), 1, Hq, 768, window, chunk,
-                                                            cache_b.pages_per_slot, pointer(wo), pointer(got),
-                                                            pointer(got), rows, C, stream())
-        assert rc == 0
-        torch.cuda.synchronize()
-        assert torch.equal(cache_a.pages, cache_b.pages)
-        err = (got.float() - want.float()).abs()
-        assert err.max() <= 2 ** -6 * want.float().abs().max() and (got != want).float().mean() < 0.02
