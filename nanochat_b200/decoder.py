@@ -207,7 +207,6 @@ class Decoder:
         cfg, dev, bf = self.cfg, self.device, torch.bfloat16
         return {"h": torch.empty((rows, cfg.hidden), dtype=bf, device=dev),
                 "qkv": torch.empty((rows, cfg.qkv_width), dtype=bf, device=dev),
-                "q": torch.empty((rows, cfg.n_heads, HEAD_DIM), dtype=bf, device=dev),
                 "att": torch.empty((rows, cfg.n_heads, HEAD_DIM), dtype=bf, device=dev),
                 "u": torch.empty((rows, cfg.intermediate), dtype=bf, device=dev),
                 "trace": torch.zeros((rows, self.capacity + 1), dtype=torch.long, device=dev),

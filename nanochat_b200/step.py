@@ -70,12 +70,13 @@ class DecodeStep:
                 self._enqueue()
 
     def run(self) -> None:
-        """Append the tokens in qkv_host at pos_host and attend; out_host holds the result on return."""
+        """Append the tokens in qkv_host at pos_host and attend; out_host holds the result on return. The graph is
+        launched on the caller's current stream (ordered after the caller's earlier work there), then that stream
+        is synchronised."""
         if self.graph is None:
             self.capture()
-        with torch.cuda.stream(self.stream):
-            self.graph.replay()
-        self.stream.synchronize()
+        self.graph.replay()
+        torch.cuda.current_stream(self.cache.device).synchronize()
 
     def check(self) -> None:
         """Raise if a kernel flagged a bad position / length or a wait that ran out (reads the device word)."""
