@@ -53,8 +53,10 @@ def kv_slices(n: int, world: int) -> list[tuple[int, int]]:
 
 
 def append_owner(position: int, slices: Sequence[tuple[int, int]]) -> int:
-    """The rank whose slice ends at `position` (the next position to write): the last rank with a non-empty slice,
-    or the first rank whose slice can still grow within its last page."""
+    """The rank that appends the token at global `position`: the rank whose slice contains it, else the last rank
+    with a non-empty slice (the tail grows there), else rank 0. The owner writes at its LOCAL position
+    (position - slice begin) but the rotary angle is the global position's: pass kv_append the rotary tables shifted
+    by the slice's begin (cos[begin:], sin[begin:]) so that table row `local position` is the global one."""
     for r, (begin, end) in enumerate(slices):
         if begin <= position < end:
             return r
