@@ -360,7 +360,7 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=device)
 
     lens_all = workload_lens(args.workload, BATCH * world)
-    mine = shard_batch(lens_all, world)[rank]
+    mine = shard_batch(lens_all, world, longest_first=True)[rank]
     lens = [lens_all[i] for i in mine]
     B = len(lens)
     e2e_steps = max(1, min(args.steps, args.e2e_steps))

@@ -25,9 +25,11 @@ from .kv_cache import PAGE_TOKENS
 from .native import check, cuda_library, pointer, stream
 
 
-def shard_batch(lens: Sequence[int], world: int) -> list[list[int]]:
-    """Indices of `lens` per rank: longest-processing-time greedy on the lengths, ties to the lower rank, each
-    rank's list in ascending index order. Every index appears exactly once."""
+def shard_batch(lens: Sequence[int], world: int, longest_first: bool = False) -> list[list[int]]:
+    """Indices of `lens` per rank: longest-processing-time greedy on the lengths, ties to the lower rank. Every
+    index appears exactly once. Each rank's list is in ascending index order, or with longest_first in descending
+    length order: thread blocks are dispatched in batch order, so a ragged batch that starts with its longest
+    sequences ends with short ones and leaves a shorter idle tail on the GPU."""
     assert world >= 1
     load = [0] * world
     shards: list[list[int]] = [[] for _ in range(world)]
@@ -35,6 +37,8 @@ def shard_batch(lens: Sequence[int], world: int) -> list[list[int]]:
         r = min(range(world), key=lambda r: (load[r], len(shards[r]), r))
         shards[r].append(i)
         load[r] += lens[i]
+    if longest_first:
+        return [sorted(s, key=lambda i: (-lens[i], i)) for s in shards]
     return [sorted(s) for s in shards]
 
 

@@ -25,6 +25,9 @@ def test_shard_batch_partitions_and_balances():
         loads = [sum(lens[i] for i in s) for s in shards]
         assert max(loads) - min(loads) <= max(lens)  # the LPT bound
         assert max(loads) <= 1.05 * sum(lens) / world
+    ordered = sharding.shard_batch(lens, 2, longest_first=True)
+    assert [sorted(s) for s in ordered] == sharding.shard_batch(lens, 2)
+    assert all(lens[a] >= lens[b] for s in ordered for a, b in zip(s[:-1], s[1:]))
     assert sharding.shard_batch([], 3) == [[], [], []]
     assert sharding.shard_batch([5, 5, 5], 2) == [[0, 2], [1]]
 
