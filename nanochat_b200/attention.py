@@ -116,6 +116,50 @@ def decode_step_attention(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tens
     return out
 
 
+def prefill_groups(slots: list[int], positions: list[int], Hq: int, Hkv: int) -> tuple[list[int], list[int]]:
+    """Group consecutive rows of a prefill pass for prefill_attention: a group is a run of rows of one slot with
+    positions ascending by one, at most 8 / (Hq / Hkv) long. Returns (group_start with the end sentinel, span_lens:
+    for every row the length pos + 1 of its group's last row)."""
+    limit = max(1, 8 // (Hq // Hkv))
+    starts, span = [0], [0] * len(slots)
+    for r in range(1, len(slots) + 1):
+        first = starts[-1]
+        if r == len(slots) or r - first == limit or slots[r] != slots[first] or positions[r] != positions[r - 1] + 1:
+            for i in range(first, r):
+                span[i] = positions[r - 1] + 1
+            if r < len(slots):
+                starts.append(r)
+    return starts + [len(slots)], span
+
+
+def prefill_attention(q: Tensor, cache: Fp8KVCache, slots: list[int], positions: list[int], slot_map: Tensor,
+                      lens: Tensor, softmax_scale: float | None = None, out: Tensor | None = None,
+                      status: Tensor | None = None) -> Tensor:
+    """Attention for a prefill pass: q (rows, Hq, 128) bf16 of rows whose slots and positions the host knows (lists)
+    and whose k, v are already appended; row r attends positions [0, positions[r]] of slots[r]. Rows of one prompt
+    should be consecutive and ascending: they are processed in groups that read the prompt's cache once.
+    slot_map, lens: the same slots and positions + 1 as int32 device tensors. Returns (rows, Hq, 128) bf16."""
+    rows, Hq, Hkv = q.shape[0], q.shape[1], cache.kv_heads
+    assert len(slots) == len(positions) == rows and q.dtype == torch.bfloat16 and q.is_contiguous()
+    starts, span = prefill_groups(slots, positions, Hq, Hkv)
+    dev = q.device
+    group_start = torch.tensor(starts, dtype=torch.int32, device=dev)
+    span_lens = torch.tensor(span, dtype=torch.int32, device=dev)
+    max_kv_len = min(max(positions) + 1, cache.capacity)
+    n_groups = len(starts) - 1
+    chunk = chunk_pages_for(n_groups, Hkv, max_kv_len)
+    workspace = torch.empty(max(16, workspace_bytes(rows, Hq, Hkv, max_kv_len, chunk)), dtype=torch.uint8, device=dev)
+    if out is None:
+        out = torch.empty_like(q)
+    scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
+    rc = cuda_library("decode_attn").prefill_attn_fp8(
+        pointer(q), pointer(cache.pages), pointer(lens), pointer(span_lens), pointer(slot_map), pointer(group_start),
+        n_groups, pointer(workspace), workspace.numel(), pointer(out), rows, Hq, Hkv, cache.n_slots,
+        cache.pages_per_slot, max_kv_len, chunk, scale, pointer(status), stream())
+    check(rc, "prefill_attn_fp8")
+    return out
+
+
 def decode_attention_static(q: Tensor, cache: Fp8KVCache, lens: Tensor, max_kv_len: int,
                             slot_map: Tensor | None = None, window: int = 0, chunk_pages: int = 0,
                             softmax_scale: float | None = None, out: Tensor | None = None,

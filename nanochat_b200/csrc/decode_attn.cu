@@ -65,6 +65,9 @@ struct AttnArgs {
     const float *q_gain, *k_gain, *cs, *sn;
     long long qkv_row_stride;
     int table_len;
+    /* MULTI only: block z works on rows group_start[z] .. group_start[z + 1] - 1, which share a slot and hold
+     * ascending positions; lens is per row then, and parts are indexed by row */
+    const int32_t *group_start;
 };
 
 /* ---- PTX wrappers ------------------------------------------------------------------------------------------- */
@@ -156,7 +159,11 @@ static __device__ __forceinline__ float head_sum(float v) {
  * into shared memory; if its chunk holds the new position, the k and v rows into the cache in global memory and
  * into the landed page in shared memory), so a decode step needs no separate append launch and no round trip of q
  * through global memory. Meant for one new token per sequence; rows that share a slot need the separate kernels. */
-template <int NT, bool APPEND>
+/* MULTI (prefill): the N columns hold several ROWS of one sequence instead of only the heads of one row: block z
+ * takes up to 4 NT / G consecutive rows of a slot (query "slots" = rows x heads of the kv group), loads each page of
+ * the sequence once for all of them and masks every slot at its own row's length. Not combined with APPEND or a
+ * window. */
+template <int NT, bool APPEND, bool MULTI = false>
 __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];       /* WARPS stages of one page; later the merge area */
     __shared__ __align__(8) uint64_t bars[WARPS];          /* one "page landed" barrier per warp */
@@ -166,13 +173,17 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     float *merge = reinterpret_cast<float *>(smem);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int chunk = blockIdx.x, kvh = blockIdx.y;
     const int G = a.Hq / a.Hkv;
 
     /* launched with programmatic stream serialisation: everything this kernel reads (lens, q, the cache with the
      * token appended a moment ago) comes from kernels before it */
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int len = a.lens[b] + a.len_add;
+    /* b: the first (or only) row of this block; S: its query slots (rows x heads of the kv group) */
+    const int b = MULTI ? a.group_start[blockIdx.z] : (int)blockIdx.z;
+    const int group_rows = MULTI ? min(a.group_start[blockIdx.z + 1] - b, 4 * NT / G) : 1;
+    const int S = group_rows * G;
+    const int len = a.lens[b + group_rows - 1] + a.len_add; /* the longest row's: rows ascend in position */
     const int slot = a.slot_map ? a.slot_map[b] : b;
     if (len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots ||
         (APPEND && (len < 1 || len > a.table_len))) {
@@ -235,11 +246,13 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
             }
         }
     } else {
-        const bf16 *q = a.q + ((size_t)b * a.Hq + (size_t)kvh * G) * HEAD_DIM;
-        for (int i = tid; i < G * HEAD_DIM; i += THREADS) q_stage[i] = __bfloat162float(q[i]);
+        for (int i = tid; i < S * HEAD_DIM; i += THREADS) { /* slot = row-in-group * G + head-in-group */
+            const int sl = i / HEAD_DIM, d = i % HEAD_DIM;
+            q_stage[i] = __bfloat162float(a.q[((size_t)(b + sl / G) * a.Hq + (size_t)kvh * G + sl % G) * HEAD_DIM + d]);
+        }
     }
     __syncthreads();
-    for (int h = warp; h < G; h += WARPS) {
+    for (int h = warp; h < S; h += WARPS) {
         float m = 0.f;
         for (int i = lane; i < HEAD_DIM; i += 32) m = fmaxf(m, fabsf(q_stage[h * HEAD_DIM + i]));
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -254,8 +267,8 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         const int hc = 4 * nt + (g >> 1), hs = 4 * nt + t; /* the head of this lane's B column / C columns */
-        const float sc = hc < G ? q_scale[hc] : 0.f, inv = sc > 0.f ? 1.f / sc : 0.f;
-        qfac[nt] = (hs < G ? q_scale[hs] : 0.f) * a.scale_log2;
+        const float sc = hc < S ? q_scale[hc] : 0.f, inv = sc > 0.f ? 1.f / sc : 0.f;
+        qfac[nt] = (hs < S ? q_scale[hs] : 0.f) * a.scale_log2;
 #pragma unroll
         for (int ks = 0; ks < 4; ks++)
 #pragma unroll
@@ -264,11 +277,16 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
                 uint32_t hi, lo;
 #pragma unroll
                 for (int i = 0; i < 4; i++)
-                    x[i] = hc < G ? q_stage[hc * HEAD_DIM + 32 * ks + 16 * half + 4 * t + i] * inv : 0.f;
+                    x[i] = hc < S ? q_stage[hc * HEAD_DIM + 32 * ks + 16 * half + 4 * t + i] * inv : 0.f;
                 split4(x, hi, lo);
                 qf[nt][ks][half] = (g & 1) ? lo : hi;
             }
     }
+
+    int slot_len[NT]; /* MULTI: the length of the row behind this lane's slot of each tile */
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+        slot_len[nt] = (MULTI && 4 * nt + t < S) ? a.lens[b + (4 * nt + t) / G] + a.len_add : len;
 
     /* the warp's running state: per tile, head t's maximum (log2 units), this lane's share of the sum, and O^T
      * fragments (dims 16 dt + g, + 8; columns = head t's two terms) */
@@ -371,10 +389,13 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
             for (int nt = 0; nt < NT; nt++) {
                 float x[4], top = -INFINITY;
 #pragma unroll
+                bool ok[4]; /* this slot may see position j: inside the span and, for MULTI, inside its own row */
+#pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const float raw = sc[nt][j >> 1][2 * (j & 1)] + sc[nt][j >> 1][2 * (j & 1) + 1] * (1.f / LO_SCALE);
                     x[j] = raw * (ksc[j] * qfac[nt]);
-                    top = fmaxf(top, valid[j] ? x[j] + lv[j] : -INFINITY);
+                    ok[j] = valid[j] && (!MULTI || first + 4 * g + j < slot_len[nt]);
+                    top = fmaxf(top, ok[j] ? x[j] + lv[j] : -INFINITY);
                 }
                 top = fmaxf(head_max(top), m[nt]);
                 if (__any_sync(0xffffffffu, top > m[nt])) { /* some head's maximum moved: rescale */
@@ -389,7 +410,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
                 float p[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const bool on = valid[j] && top != -INFINITY;
+                    const bool on = ok[j] && top != -INFINITY;
                     const float e = on ? ex2(x[j] - top) : 0.f;
                     l[nt] += e;
                     p[j] = on ? e * (vsc[j] * P_SCALE) : 0.f;
@@ -440,7 +461,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     }
     __syncthreads();
     if (tid < HEAD_DIM) { /* merge the warps' states per head; thread = dim */
-        for (int h = 0; h < G; h++) {
+        for (int h = 0; h < S; h++) {
             float top = -INFINITY;
 #pragma unroll
             for (int w = 0; w < WARPS; w++) top = fmaxf(top, merge[(w * 4 * NT + h) * PART]);
@@ -452,7 +473,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
                 lsum += c * st[1];
                 o += c * st[4 + tid];
             }
-            float *out = a.parts + (((size_t)b * a.Hq + (size_t)kvh * G + h) * a.max_chunks + chunk) * PART;
+            float *out = a.parts + (((size_t)(b + h / G) * a.Hq + (size_t)kvh * G + h % G) * a.max_chunks + chunk) * PART;
             if (tid == 0) out[0] = top, out[1] = lsum;
             out[4 + tid] = o;
         }
@@ -625,15 +646,19 @@ struct AppendIn {
     const void *qkv, *q_gain, *k_gain, *cos, *sin;
     long long qkv_row_stride;
     int table_len;
+    /* MULTI only: block z works on rows group_start[z] .. group_start[z + 1] - 1, which share a slot and hold
+     * ascending positions; lens is per row then, and parts are indexed by row */
+    const int32_t *group_start;
 };
 
-template <int NT, bool APPEND> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
+template <int NT, bool APPEND, bool MULTI = false> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
     static bool done[64] = {};
     int device = 0;
     cudaError_t rc = cudaGetDevice(&device);
     if (rc != cudaSuccess) return rc;
     if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
-    rc = cudaFuncSetAttribute(k_decode_attn<NT, APPEND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM);
+    rc = cudaFuncSetAttribute(k_decode_attn<NT, APPEND, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)ATTN_SMEM);
     if (rc == cudaSuccess && device >= 0 && device < 64) done[device] = true;
     return rc;
 }
@@ -641,12 +666,13 @@ template <int NT, bool APPEND> static cudaError_t prepare() { /* opt in to the l
 static int launch_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
                         long long workspace_bytes, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,
                         int max_kv_len, int window, int &chunk_pages, float softmax_scale, void *status,
-                        cudaStream_t stream, const AppendIn *app = nullptr) {
+                        cudaStream_t stream, const AppendIn *app = nullptr, const void *group_start = nullptr,
+                        int n_groups = 0) {
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || n_slots <= 0 || pages_per_slot <= 0 || max_kv_len < 0 ||
         window < 0 || chunk_pages < 0 || !(softmax_scale > 0.f))
         return NCB_ERR_ARG;
     if (Hq / Hkv > 8) return NCB_ERR_UNSUPPORTED;
-    if (B > 65535 || Hkv > 65535) return NCB_ERR_ARG;
+    if ((B > 65535 && !group_start) || Hkv > 65535) return NCB_ERR_ARG;
     if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
     if (chunk_pages == 0) chunk_pages = decode_attn_chunk_pages(B, Hkv, max_kv_len);
     if (B == 0) return NCB_OK;
@@ -670,8 +696,9 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
         a.cs = (const float *)app->cos, a.sn = (const float *)app->sin;
         a.qkv_row_stride = app->qkv_row_stride, a.table_len = app->table_len;
     }
+    a.group_start = (const int32_t *)group_start;
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(max_chunks, Hkv, B);
+    config.gridDim = dim3(max_chunks, Hkv, group_start ? n_groups : B);
     config.blockDim = dim3(THREADS);
     config.dynamicSmemBytes = ATTN_SMEM;
     config.stream = stream;
@@ -681,7 +708,11 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     config.attrs = attribute;
     config.numAttrs = 1;
     cudaError_t rc;
-    if (Hq / Hkv <= 4 && !app) {
+    if (group_start) { /* several rows per block: always two column tiles, 8 / G rows */
+        if (app || window || n_groups <= 0 || n_groups > 65535) return NCB_ERR_ARG;
+        if (prepare<2, false, true>() != cudaSuccess) return NCB_ERR_LAUNCH;
+        rc = cudaLaunchKernelEx(&config, k_decode_attn<2, false, true>, a);
+    } else if (Hq / Hkv <= 4 && !app) {
         if (prepare<1, false>() != cudaSuccess) return NCB_ERR_LAUNCH;
         rc = cudaLaunchKernelEx(&config, k_decode_attn<1, false>, a);
     } else if (!app) {
@@ -816,6 +847,26 @@ int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain
     const AppendIn app = {qkv, q_gain, k_gain, cos, sin, qkv_row_stride, table_len};
     return attend(nullptr, kv_cache, pos, slot_map, workspace, workspace_bytes, out, nullptr, B, Hq, Hkv, n_slots,
                   pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream, &app);
+}
+
+int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *span_lens,
+                     const void *slot_map, const void *group_start, int n_groups, void *workspace,
+                     long long workspace_bytes, void *out, int rows, int Hq, int Hkv, int n_slots, int pages_per_slot,
+                     int max_kv_len, int chunk_pages, float softmax_scale, void *status, void *stream) {
+    if (!out || !group_start || !span_lens || !slot_map || chunk_pages <= 0 || n_groups <= 0) return NCB_ERR_ARG;
+    if ((uintptr_t)out % 16 != 0) return NCB_ERR_ALIGN;
+    int chunk = chunk_pages;
+    const int rc = launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, rows, Hq, Hkv, n_slots,
+                                pages_per_slot, max_kv_len, 0, chunk, softmax_scale, status, (cudaStream_t)stream, nullptr,
+                                group_start, n_groups);
+    if (rc != NCB_OK || rows == 0) return rc;
+    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
+    const int max_chunks = max(1, (pages_of(max_kv_len) + chunk - 1) / chunk);
+    /* every row's states follow its group's chunking, so the merge takes each row's length from span_lens */
+    MergeArgs m = {(const float *)workspace, (long long)rows * Hq, PART, (long long)max_chunks * PART, 0,
+                   (const int32_t *)span_lens, (const int32_t *)slot_map, Hq, 0, chunk, n_slots, pages_per_slot,
+                   max_chunks, 0, (bf16 *)out, nullptr};
+    return launch_merge(m, (cudaStream_t)stream);
 }
 
 int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map,

@@ -123,12 +123,15 @@ class Decoder:
         return self._workspaces[key]
 
     def hidden_rows(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int,
-                    attend_last_layer: bool = True, distinct_slots: bool = False) -> Tensor:
+                    attend_last_layer: bool = True, distinct_slots: bool = False,
+                    host_rows: tuple[list[int], list[int]] | None = None) -> Tensor:
         """Final-normed hidden states (rows, C) bf16 of `tokens` at positions `pos` of slots `slot_map`; appends
         every row's k, v to the caches. max_kv_len bounds pos + 1. Any number of rows: GEMMs on cuBLAS, everything
         between them on this package's kernels (embedding + norm, residual add + norm, relu^2, append, attention).
         distinct_slots: no two rows share a slot (a decode step), so the attention kernel may append its own
-        token; prefill passes, where rows of one sequence read each other's positions, need the separate append."""
+        token; prefill passes, where rows of one sequence read each other's positions, need the separate append.
+        host_rows: the rows' (slots, positions) as host lists, when the caller has them (prefill): attention then
+        runs in groups of consecutive rows that read a prompt's cache once per group instead of once per row."""
         cfg, lib, s = self.cfg, cuda_library("decode_step"), stream()
         rows, C = tokens.shape[0], cfg.hidden
         default_mix = all(l.resid_lambda == 1.0 and l.x0_lambda == 0.0 for l in self.w.layers)
@@ -151,8 +154,12 @@ class Decoder:
                                   cfg.n_heads, slot_map=slot_map, status=self.status)
                 if i == cfg.n_layers - 1 and not attend_last_layer:
                     return h  # prefill: the last layer only has to fill its cache (decode.cu:862)
-                att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map,
-                                           window=self.windows[i], workspace=workspace, status=self.status)
+                if host_rows is not None and self.windows[i] == 0:
+                    att = ops.prefill_attention(q, self.caches[i], host_rows[0], host_rows[1], slot_map, lens,
+                                                status=self.status)
+                else:
+                    att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map,
+                                               window=self.windows[i], workspace=workspace, status=self.status)
             y = att.view(rows, -1) @ layer.wo.T
             check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
             u = n @ layer.wup.T
@@ -254,7 +261,8 @@ class Decoder:
             slot_map = torch.tensor([s for s, _, _ in part], dtype=torch.int32, device=self.device)
             pos = torch.tensor([t for _, t, _ in part], dtype=torch.int32, device=self.device)
             tokens = torch.tensor([k for _, _, k in part], dtype=torch.long, device=self.device)
-            self.hidden_rows(tokens, pos, slot_map, max(t for _, t, _ in part) + 1, attend_last_layer=False)
+            self.hidden_rows(tokens, pos, slot_map, max(t for _, t, _ in part) + 1, attend_last_layer=False,
+                             host_rows=([s for s, _, _ in part], [t for _, t, _ in part]))
 
     # ---- decode -----------------------------------------------------------------------------------------------
 

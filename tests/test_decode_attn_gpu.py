@@ -315,3 +315,37 @@ def test_peer_merge_wait_runs_out_and_reports():
     assert status.item() == 2
     assert 0.05 < waited < 10.0
     assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0  # the device still answers
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(10, 10), (8, 2), (4, 1), (16, 2)])
+def test_prefill_attention_groups_rows_and_matches_the_row_wise_path(Hq, Hkv):
+    """prefill_attn_fp8 (rows of a prompt share each page load) against decode_attn_fp8 run row by row and against
+    the float64 checker: causal prefixes of three prompts of different lengths in one pass, group boundaries in the
+    middle of prompts and across page edges."""
+    lens = [150, 9, 70]
+    case = helpers.attention_case(1500 + Hq, Hq, Hkv, lens)
+    cache = load_cache(case, 160, slots=[2, 0, 1], n_slots=3)
+    gen = torch.Generator().manual_seed(1501)
+    slots, positions = [], []
+    for slot, n in zip([2, 0, 1], lens):
+        slots += [slot] * n
+        positions += list(range(n))
+    rows = len(slots)
+    q = torch.randn(rows, Hq, 128, generator=gen).bfloat16().cuda()
+    slot_map = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    lens_t = torch.tensor(positions, dtype=torch.int32, device="cuda") + 1
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ncb.attention.prefill_attention(q, cache, slots, positions, slot_map, lens_t, status=status)
+    want = ncb.decode_attention(q, cache, lens_t, max(lens), slot_map=slot_map, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    d = (got.float() - want.float()).abs()
+    assert float(d.max()) <= 8e-3 and float(d.mean()) <= 2e-4, (float(d.max()), float(d.mean()))
+    # a few rows against the checker: the causal prefix of each prompt
+    seq_of = {2: 0, 0: 1, 1: 2}
+    for r in (0, 63, 64, 149, 150, 158, 159, rows - 1):
+        b, n = seq_of[slots[r]], positions[r] + 1
+        ref = oat.decode_attention(helpers.bf16_bits(q[r:r + 1].cpu()), [case["k_bytes"][b][:, :n]],
+                                   [case["k_scale"][b][:, :n]], [case["v_bytes"][b][:, :n]], [case["v_scale"][b][:, :n]], SCALE)
+        max_abs, mean_abs = helpers.error_stats(helpers.bf16_bits(got[r:r + 1].cpu()), ref)
+        assert max_abs <= 2e-2 and mean_abs <= 2e-3, (r, max_abs, mean_abs)
