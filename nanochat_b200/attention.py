@@ -132,30 +132,41 @@ def prefill_groups(slots: list[int], positions: list[int], Hq: int, Hkv: int) ->
     return starts + [len(slots)], span
 
 
-def prefill_attention(q: Tensor, cache: Fp8KVCache, slots: list[int], positions: list[int], slot_map: Tensor,
-                      lens: Tensor, softmax_scale: float | None = None, out: Tensor | None = None,
-                      status: Tensor | None = None) -> Tensor:
-    """Attention for a prefill pass: q (rows, Hq, 128) bf16 of rows whose slots and positions the host knows (lists)
-    and whose k, v are already appended; row r attends positions [0, positions[r]] of slots[r]. Rows of one prompt
-    should be consecutive and ascending: they are processed in groups that read the prompt's cache once.
-    slot_map, lens: the same slots and positions + 1 as int32 device tensors. Returns (rows, Hq, 128) bf16."""
-    rows, Hq, Hkv = q.shape[0], q.shape[1], cache.kv_heads
-    assert len(slots) == len(positions) == rows and q.dtype == torch.bfloat16 and q.is_contiguous()
-    starts, span = prefill_groups(slots, positions, Hq, Hkv)
-    dev = q.device
-    group_start = torch.tensor(starts, dtype=torch.int32, device=dev)
-    span_lens = torch.tensor(span, dtype=torch.int32, device=dev)
-    max_kv_len = min(max(positions) + 1, cache.capacity)
-    n_groups = len(starts) - 1
-    chunk = chunk_pages_for(n_groups, Hkv, max_kv_len)
-    workspace = torch.empty(max(16, workspace_bytes(rows, Hq, Hkv, max_kv_len, chunk)), dtype=torch.uint8, device=dev)
+class PrefillPlan:
+    """What prefill_attention needs besides q for one pass of rows, built once per pass and shared by the layers:
+    the row groups, each row's group length, the rows' slots and lengths on the device, the chunk size and a
+    workspace."""
+
+    def __init__(self, slots: list[int], positions: list[int], Hq: int, cache: Fp8KVCache, device):
+        Hkv = cache.kv_heads
+        starts, span = prefill_groups(slots, positions, Hq, Hkv)
+        self.rows, self.n_groups = len(slots), len(starts) - 1
+        self.group_start = torch.tensor(starts, dtype=torch.int32, device=device)
+        self.span_lens = torch.tensor(span, dtype=torch.int32, device=device)
+        self.slot_map = torch.tensor(slots, dtype=torch.int32, device=device)
+        self.lens = torch.tensor(positions, dtype=torch.int32, device=device) + 1
+        self.max_kv_len = min(max(positions) + 1, cache.capacity)
+        self.chunk = chunk_pages_for(self.n_groups, Hkv, self.max_kv_len)
+        need = workspace_bytes(self.rows, Hq, Hkv, self.max_kv_len, self.chunk)
+        self.workspace = torch.empty(max(16, need), dtype=torch.uint8, device=device)
+
+
+def prefill_attention(q: Tensor, cache: Fp8KVCache, plan: PrefillPlan, softmax_scale: float | None = None,
+                      out: Tensor | None = None, status: Tensor | None = None) -> Tensor:
+    """Attention for a prefill pass: q (rows, Hq, 128) bf16 of the rows the plan was built for, whose k, v are
+    already appended; row r attends positions [0, positions[r]] of slots[r]. Rows of one prompt should be
+    consecutive and ascending: they are processed in groups that read the prompt's cache once. Returns
+    (rows, Hq, 128) bf16."""
+    rows, Hq = q.shape[0], q.shape[1]
+    assert rows == plan.rows and q.dtype == torch.bfloat16 and q.is_contiguous()
     if out is None:
         out = torch.empty_like(q)
     scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
     rc = cuda_library("decode_attn").prefill_attn_fp8(
-        pointer(q), pointer(cache.pages), pointer(lens), pointer(span_lens), pointer(slot_map), pointer(group_start),
-        n_groups, pointer(workspace), workspace.numel(), pointer(out), rows, Hq, Hkv, cache.n_slots,
-        cache.pages_per_slot, max_kv_len, chunk, scale, pointer(status), stream())
+        pointer(q), pointer(cache.pages), pointer(plan.lens), pointer(plan.span_lens), pointer(plan.slot_map),
+        pointer(plan.group_start), plan.n_groups, pointer(plan.workspace), plan.workspace.numel(), pointer(out), rows,
+        Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, plan.max_kv_len, plan.chunk, scale, pointer(status),
+        stream())
     check(rc, "prefill_attn_fp8")
     return out
 

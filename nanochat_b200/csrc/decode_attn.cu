@@ -388,7 +388,6 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
                 float x[4], top = -INFINITY;
-#pragma unroll
                 bool ok[4]; /* this slot may see position j: inside the span and, for MULTI, inside its own row */
 #pragma unroll
                 for (int j = 0; j < 4; j++) {

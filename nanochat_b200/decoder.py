@@ -139,6 +139,9 @@ class Decoder:
             return self._hidden_rows_torch(tokens, pos, slot_map, max_kv_len, attend_last_layer)
         lens = pos + 1
         workspace = self._workspace(rows, max_kv_len)
+        plan = None
+        if host_rows is not None and not any(self.windows):
+            plan = ops.PrefillPlan(host_rows[0], host_rows[1], cfg.n_heads, self.caches[0], self.device)
         h = torch.empty((rows, C), dtype=torch.bfloat16, device=self.device)
         n = torch.empty_like(h)
         check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
@@ -154,9 +157,8 @@ class Decoder:
                                   cfg.n_heads, slot_map=slot_map, status=self.status)
                 if i == cfg.n_layers - 1 and not attend_last_layer:
                     return h  # prefill: the last layer only has to fill its cache (decode.cu:862)
-                if host_rows is not None and self.windows[i] == 0:
-                    att = ops.prefill_attention(q, self.caches[i], host_rows[0], host_rows[1], slot_map, lens,
-                                                status=self.status)
+                if plan is not None:
+                    att = ops.prefill_attention(q, self.caches[i], plan, status=self.status)
                 else:
                     att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map,
                                                window=self.windows[i], workspace=workspace, status=self.status)

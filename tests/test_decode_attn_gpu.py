@@ -335,7 +335,8 @@ def test_prefill_attention_groups_rows_and_matches_the_row_wise_path(Hq, Hkv):
     slot_map = torch.tensor(slots, dtype=torch.int32, device="cuda")
     lens_t = torch.tensor(positions, dtype=torch.int32, device="cuda") + 1
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    got = ncb.attention.prefill_attention(q, cache, slots, positions, slot_map, lens_t, status=status)
+    plan = ncb.attention.PrefillPlan(slots, positions, Hq, cache, "cuda")
+    got = ncb.attention.prefill_attention(q, cache, plan, status=status)
     want = ncb.decode_attention(q, cache, lens_t, max(lens), slot_map=slot_map, status=status)
     torch.cuda.synchronize()
     assert status.item() == 0
