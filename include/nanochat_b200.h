@@ -247,6 +247,27 @@ int sample_choice(const void *logits, void *probs, const void *temperature, cons
                   const void *first, const void *allow, float softcap, void *tokens, void *pos, int rows, int vocab,
                   void *trace, int trace_stride, void *stream);
 
+/* ---- library stream_gemm ------------------------------------------------------------------------------------
+ * The same GEMM for 1 to 128 rows on the tcgen05 tensor cores (TMA-staged weight stream, accumulators in tensor
+ * memory, K split over a thread-block cluster and reduced through distributed shared memory); replaces k_wgmma with
+ * its epilogues (model/kernels/decode.cu:170-208,232-359) and k_norm / k_rstd (decode.cu:415-456) for decode batches
+ * above 16 sequences per GPU. */
+
+/* The K split (blocks per cluster) stream_gemm chooses for a [N][K] weight matrix when called with split 0;
+ * 0 for shapes it does not take. */
+int stream_gemm_split(int N, int K);
+
+/*
+ * y = epilogue(norm?(x) . W^T). x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3);
+ * resid bf16 [rows][N] for epilogue 1 (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding
+ * the product), 2 relu^2, 3 fp32 store. norm_input != 0 applies the parameter-free RMS norm (eps FLT_EPSILON) to x,
+ * as a per-row scale of the fp32 product. rows <= 128; N a multiple of 128; K a multiple of 64; x, w 16-byte
+ * aligned. split: 1..8 blocks share one feature tile's K range (at most K / 64), 0 = automatic. status: optional
+ * device word for NCB_DEV_WAIT_TIMEOUT. Launched with programmatic stream serialisation.
+ */
+int stream_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
+                int epilogue, int split, int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

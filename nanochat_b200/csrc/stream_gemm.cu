@@ -1,0 +1,513 @@
+/*
+ * y = epilogue(norm?(x) . W^T) for 1 to 128 activation rows as a weight stream on Blackwell's tcgen05 tensor cores.
+ * Serves decode steps of 17 to 128 sequences per GPU (the d32-class batch of 32 per GPU), where the reference runs
+ * its Hopper-only slot GEMM k_wgmma with the STORE / RESID / RELU2 epilogues (model/kernels/decode.cu:170-208,232-359)
+ * and separate k_norm / k_rstd launches (decode.cu:415-456). Same model semantics as decode_step.cu: parameter-free
+ * RMS norm with eps FLT_EPSILON, bf16 GEMM outputs, residual add and relu^2 in bf16, fp32 logits.
+ *
+ * The weights are the only traffic that matters (a 2048 x 8192 projection is 33.5 MB against 128 KB of activations),
+ * so the GEMM is "swapped": D[128 features][rows] = W tile (A operand, M = 128) . x^T (B operand, N = rows padded to
+ * 32 / 64 / 128), both K-major, fp32 accumulators in tensor memory. One block:
+ *   - thread 0 streams W and x k-blocks (64 k-values = one 128-byte swizzled row per feature) into a ring of
+ *     shared-memory stages with cp.async.bulk.tensor (TMA, 128-byte swizzle, no multicast); weight loads for the
+ *     first ring fill are issued BEFORE griddepcontrol.wait, so in a captured step the stream starts under the
+ *     predecessor's tail;
+ *   - thread 32 issues tcgen05.mma.cta_group::1.kind::f16 (4 per k-block) and releases stages with tcgen05.commit;
+ *   - warps 2, 3 sum the squares of the staged x boxes for the fused norm. The norm has no gain, so
+ *     norm(x) . W^T = rstd[row] * (x . W^T): the scale is applied to the fp32 accumulators in the epilogue.
+ * K is split over a thread-block cluster of up to 8 blocks so that short-and-wide projections (16 feature tiles of
+ * a 2048 x 2048 matrix) still cover the GPU; after the main loop every block parks its accumulators in its own
+ * shared memory, and block r of the cluster reduces rows r, r + S, ... over all blocks through distributed shared
+ * memory in a fixed order (deterministic), applies the epilogue and stores. No workspace, no atomics.
+ * Every mbarrier wait is bounded; on expiry NCB_DEV_WAIT_TIMEOUT is flagged and the block still walks through both
+ * cluster barriers and frees its tensor memory.
+ */
+#include "ncb_common.cuh"
+
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int TILE_F = 128;                      /* output features per block = MMA M */
+constexpr int KBLK = 64;                         /* k-values per box: 64 bf16 = one 128-byte swizzle row */
+constexpr int A_BOX_BYTES = TILE_F * KBLK * 2;   /* 16 KB of weights per box */
+#ifndef SG_KSUB
+#define SG_KSUB 1
+#endif
+#ifndef SG_RING_KB
+#define SG_RING_KB 100
+#endif
+constexpr int THREADS = 128;
+constexpr int MAX_SPLIT = 8;                     /* portable cluster size */
+constexpr long long WAIT_CYCLES = 4000000000ll;  /* bound of every barrier wait */
+
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_RELU2 = 2, EPI_F32 = 3 };
+
+template <int NP> struct Shape {
+    /* A stage holds KSUB consecutive boxes of W (a feature row contributes KSUB x 128 contiguous bytes, so DRAM
+     * pages are visited for longer runs) and the matching boxes of x. */
+    static constexpr int KSUB = NP == 128 && SG_KSUB > 2 ? 2 : SG_KSUB;
+    static constexpr int B_BOX_BYTES = NP * KBLK * 2;
+    static constexpr int BOX_BYTES = A_BOX_BYTES + B_BOX_BYTES;
+    static constexpr int STAGE_BYTES = KSUB * BOX_BYTES;
+    static constexpr int STAGES = SG_RING_KB * 1024 / STAGE_BYTES < 8 ? SG_RING_KB * 1024 / STAGE_BYTES : 8;
+    static_assert(STAGES >= 2, "at least two stages");
+    static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int PARK_BYTES = NP * TILE_F * 4; /* fp32 accumulators parked over the ring after the main loop */
+    static_assert(PARK_BYTES <= RING_BYTES, "the parked accumulators reuse the ring");
+    static constexpr int TAIL_BYTES = 256 + NP * 4; /* barriers, tensor-memory slot, per-row sums of squares */
+    static constexpr int SMEM_BYTES = 1024 + RING_BYTES + TAIL_BYTES; /* 1024: the ring is aligned by hand */
+};
+
+struct GemmArgs {
+    const bf16 *x;     /* [rows][K] */
+    const bf16 *resid; /* [rows][N] for EPI_RESID (may alias y) */
+    void *y;           /* [rows][N] bf16, or fp32 for EPI_F32 */
+    int rows, N, K, norm_input;
+    int *status;
+};
+
+/* ---- PTX wrappers ------------------------------------------------------------------------------------------- */
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+/* True once the barrier's phase of the given parity has completed. Polls without a suspend hint (one thread feeds the
+ * whole pipeline, so a late wake-up stalls it) and gives up after WAIT_CYCLES of the SM clock, about two seconds. */
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    const long long start = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (done) return true;
+        if (clock64() - start > WAIT_CYCLES) return false;
+    }
+}
+/* One box of a 2-d tensor map into shared memory; (c0, c1) = (k, row) element coordinates, c0 a multiple of 64. */
+__device__ __forceinline__ void tma_load(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+                 : "memory");
+}
+/* Shared-memory matrix descriptor of a K-major tile of 128-byte rows with the 128-byte swizzle: 8-row groups are
+ * 1024 bytes apart (stride byte offset), the leading byte offset is unused for this layout, descriptor version 1. */
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+/* D[tmem] (+)= A[smem] . B[smem]^T, bf16 operands, fp32 accumulate, M 128, N from the instruction descriptor, K 16. */
+__device__ __forceinline__ void umma_bf16(uint32_t tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+/* The barrier gets one arrival when every MMA issued so far by this thread has completed. */
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+/* 32 consecutive fp32 columns of this thread's tensor-memory lane. */
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float *v) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+                   "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                   "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float sumsq_bf16x8(const uint4 &u) {
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&u);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        s += f.x * f.x + f.y * f.y;
+    }
+    return s;
+}
+
+#ifdef SG_TRACE /* experiments only: `status` is a long long [blocks][8] buffer of %globaltimer stamps */
+#define STAMP(slot)                                                                                      \
+    do {                                                                                                 \
+        long long t_;                                                                                    \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                           \
+        reinterpret_cast<long long *>(a.status)[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; \
+    } while (0)
+#undef NCB_DEV_WAIT_TIMEOUT
+#define NCB_DEV_WAIT_TIMEOUT 0
+#else
+#define STAMP(slot)
+#endif
+
+/* ---- the kernel ---------------------------------------------------------------------------------------------- */
+
+/* Grid (S, N / 128), cluster (S, 1, 1): block (s, t) multiplies feature tile t by k-blocks [s kb / S, (s + 1) kb / S). */
+template <int NP, int EPI>
+__global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__ CUtensorMap map_w,
+                                                         const __grid_constant__ CUtensorMap map_x, const GemmArgs a) {
+    using Sh = Shape<NP>;
+    constexpr int STAGES = Sh::STAGES;
+    extern __shared__ uint8_t raw[];
+    const uint32_t raw_addr = smem_u32(raw);
+    const uint32_t ring = (raw_addr + 1023u) & ~1023u; /* swizzled tiles sit on 1024-byte boundaries */
+    uint8_t *ring_ptr = raw + (ring - raw_addr);
+    uint8_t *tail = ring_ptr + Sh::RING_BYTES;
+    const uint32_t bars = ring + Sh::RING_BYTES; /* full[STAGES], empty[STAGES], accumulators complete */
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 128);
+    float *sumsq = reinterpret_cast<float *>(tail + 256); /* [NP] this block's K slice */
+    float *park = reinterpret_cast<float *>(ring_ptr);    /* [NP][128] after the main loop */
+    auto full = [&](int s) { return bars + 8u * s; };
+    auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = gridDim.x, rank = blockIdx.x, tile = blockIdx.y;
+    const int kb_total = a.K / KBLK;
+    const int kb0 = (int)((long long)rank * kb_total / S), kb1 = (int)((long long)(rank + 1) * kb_total / S);
+    const int nkb = kb1 - kb0;
+    cg::cluster_group cluster = cg::this_cluster();
+
+    if (tid == 0) {
+        STAMP(0);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), a.norm_input ? 3 : 1); /* the MMAs' commit + the two norm warps */
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    }
+    if (warp == 1) { /* NP columns of tensor memory: lane = feature, column = row */
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(NP)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); /* the successor may start streaming its weights */
+
+    constexpr int KSUB = Sh::KSUB;
+    const int nst = (nkb + KSUB - 1) / KSUB; /* stages of up to KSUB boxes; stage i holds boxes [i KSUB, ...) */
+    auto boxes_of = [&](int i) { return nkb - i * KSUB < KSUB ? nkb - i * KSUB : KSUB; };
+    auto load_w = [&](int i) {
+        const int s = i % STAGES, n = boxes_of(i);
+        mbar_expect_tx(full(s), n * Sh::BOX_BYTES);
+        for (int b = 0; b < n; b++)
+            tma_load(ring + s * Sh::STAGE_BYTES + b * A_BOX_BYTES, &map_w, (kb0 + i * KSUB + b) * KBLK, tile * TILE_F, full(s));
+    };
+    auto load_x = [&](int i) {
+        const int s = i % STAGES, n = boxes_of(i);
+        for (int b = 0; b < n; b++)
+            tma_load(ring + s * Sh::STAGE_BYTES + KSUB * A_BOX_BYTES + b * Sh::B_BOX_BYTES, &map_x,
+                     (kb0 + i * KSUB + b) * KBLK, 0, full(s));
+    };
+    if (warp == 0) {
+        if (lane == 0) { /* producer */
+            const int pre = nst < STAGES ? nst : STAGES;
+            for (int i = 0; i < pre; i++) load_w(i); /* weights do not depend on the predecessor */
+            STAMP(1);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            STAMP(2);
+            for (int i = 0; i < pre; i++) load_x(i);
+            for (int i = pre; i < nst; i++) {
+                if (!mbar_wait(empty(i % STAGES), ((i / STAGES) & 1) ^ 1)) {
+                    flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+                    break;
+                }
+                load_w(i);
+                load_x(i);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) { /* MMA issuer */
+            constexpr uint32_t IDESC = (1u << 4) /* fp32 accumulators */ | (1u << 7) /* A bf16 */ | (1u << 10) /* B bf16 */
+                                       | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(TILE_F >> 4) << 24); /* both K-major */
+            bool ok = true;
+            for (int i = 0; i < nst; i++) {
+                const int s = i % STAGES, n = boxes_of(i);
+                ok = mbar_wait(full(s), (i / STAGES) & 1);
+                if (!ok) break;
+                if (i == 0) STAMP(3);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = ring + s * Sh::STAGE_BYTES, b_addr = a_addr + KSUB * A_BOX_BYTES;
+                for (int b = 0; b < n; b++) {
+#pragma unroll
+                    for (int k = 0; k < KBLK / 16; k++) /* 16 k-values = 32 bytes further along the swizzled row */
+                        umma_bf16(tmem, umma_desc(a_addr + b * A_BOX_BYTES + k * 32),
+                                  umma_desc(b_addr + b * Sh::B_BOX_BYTES + k * 32), IDESC, (i | b | k) != 0);
+                }
+                umma_commit(empty(s));
+            }
+            if (!ok) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+            umma_commit(accum_bar);
+            STAMP(4);
+        }
+    }
+    if (tid != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (warp >= 2 && a.norm_input) {
+        /* Sums of squares of x[:, this block's K slice] from the staged x boxes: warp 2 takes the lower half of the
+         * rows, warp 3 the upper; 8 lanes read one row's 128 bytes (the swizzle only permutes 16-byte chunks inside
+         * a row), so a warp covers 4 rows per load. Each warp releases a stage with its own arrival. */
+        constexpr int ROWS_W = NP / 2, PER = ROWS_W / 4;
+        float acc[PER];
+#pragma unroll
+        for (int i = 0; i < PER; i++) acc[i] = 0.f;
+        const int row0 = (warp - 2) * ROWS_W + (lane >> 3);
+        for (int i = 0; i < nst; i++) {
+            const int s = i % STAGES, n = boxes_of(i);
+            if (!mbar_wait(full(s), (i / STAGES) & 1)) {
+                flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+                break;
+            }
+            const uint8_t *xs = ring_ptr + s * Sh::STAGE_BYTES + KSUB * A_BOX_BYTES + (lane & 7) * 16;
+            for (int b = 0; b < n; b++) {
+#pragma unroll
+                for (int j = 0; j < PER; j++)
+                    acc[j] += sumsq_bf16x8(*reinterpret_cast<const uint4 *>(xs + b * Sh::B_BOX_BYTES + (row0 + 4 * j) * 128));
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty(s)) : "memory");
+        }
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            float v = acc[j];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            if ((lane & 7) == 0) sumsq[row0 + 4 * j] = v;
+        }
+    }
+    __syncthreads(); /* the norm warps have read their last x box: the ring may now be overwritten */
+
+    /* every thread: accumulators complete -> park lane (= feature) tid's NP columns (= rows) in shared memory */
+    if (!mbar_wait(accum_bar, 0)) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+    if (tid == 0) STAMP(5);
+    __syncwarp(); /* the tensor-memory loads below are warp-wide */
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+    for (int c = 0; c < NP / 32; c++) {
+        float v[32];
+        tmem_load32(tmem + ((uint32_t)(warp * 32) << 16) + c * 32, v);
+#pragma unroll
+        for (int j = 0; j < 32; j++) park[(c * 32 + j) * TILE_F + tid] = v[j];
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster.sync(); /* all blocks' accumulators and sums of squares are parked */
+    if (tid == 0) STAMP(6);
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NP) : "memory");
+
+    for (int r = rank; r < a.rows; r += S) { /* this block's rows of the tile, summed over the cluster in order */
+        float pv[MAX_SPLIT], ps[MAX_SPLIT]; /* all remote loads in flight before the first add */
+#pragma unroll
+        for (int s = 0; s < MAX_SPLIT; s++) {
+            pv[s] = s < S ? cluster.map_shared_rank(park, s)[r * TILE_F + tid] : 0.f;
+            ps[s] = s < S && a.norm_input ? cluster.map_shared_rank(sumsq, s)[r] : 0.f;
+        }
+        float v = 0.f, ss = 0.f;
+#pragma unroll
+        for (int s = 0; s < MAX_SPLIT; s++) {
+            v += pv[s];
+            ss += ps[s];
+        }
+        if (a.norm_input) v *= rsqrtf(ss / (float)a.K + FLT_EPSILON);
+        const size_t at = (size_t)r * a.N + (size_t)tile * TILE_F + tid;
+        if (EPI == EPI_F32) {
+            reinterpret_cast<float *>(a.y)[at] = v;
+        } else {
+            bf16 out = __float2bfloat16_rn(v);
+            if (EPI == EPI_RESID) out = __float2bfloat16_rn(__bfloat162float(a.resid[at]) + __bfloat162float(out));
+            if (EPI == EPI_RELU2) {
+                const float p = fmaxf(__bfloat162float(out), 0.f);
+                out = __float2bfloat16_rn(p * p);
+            }
+            reinterpret_cast<bf16 *>(a.y)[at] = out;
+        }
+    }
+    if (tid == 0) STAMP(7);
+    cluster.sync(); /* nobody leaves while a peer still reads its shared memory */
+}
+
+/* ---- host side ---------------------------------------------------------------------------------------------- */
+
+typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+/* The driver's tensor-map encoder, looked up through the runtime so that the library does not link libcuda. */
+EncodeTiled encoder() {
+    static EncodeTiled fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiled)p;
+    }();
+    return fn;
+}
+
+/* Tensor map of a row-major bf16 matrix [rows][K] read in boxes of box_rows x 64 with the 128-byte swizzle; rows of
+ * a box beyond the matrix read as zero. A map depends only on (pointer, shape, box), so maps are cached. */
+bool tensor_map(const void *base, int rows, int K, int box_rows, CUtensorMap *out) {
+    struct Key {
+        const void *p;
+        int rows, K, box;
+        bool operator==(const Key &o) const { return p == o.p && rows == o.rows && K == o.K && box == o.box; }
+    };
+    struct Hash {
+        size_t operator()(const Key &k) const {
+            size_t h = (size_t)(uintptr_t)k.p;
+            h = h * 1000003u ^ (size_t)k.rows;
+            h = h * 1000003u ^ (size_t)k.K;
+            return h * 1000003u ^ (size_t)k.box;
+        }
+    };
+    static std::mutex lock;
+    static std::unordered_map<Key, CUtensorMap, Hash> cache;
+    const Key key = {base, rows, K, box_rows};
+    std::lock_guard<std::mutex> guard(lock);
+    auto hit = cache.find(key);
+    if (hit != cache.end()) {
+        *out = hit->second;
+        return true;
+    }
+    EncodeTiled encode = encoder();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {KBLK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    if (encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (cache.size() > 8192) cache.clear(); /* activations of eager callers come and go */
+    cache.emplace(key, *out);
+    return true;
+}
+
+/* K split S: enough blocks for every SM (two of the smaller shapes fit an SM), at least two k-blocks each. */
+int auto_split(int tiles, int kb) {
+    int s = 160 / tiles;
+    if (s > MAX_SPLIT) s = MAX_SPLIT;
+    if (s > kb / 2) s = kb / 2;
+    return s < 1 ? 1 : s;
+}
+
+template <int NP, int EPI>
+int launch(const CUtensorMap &map_w, const CUtensorMap &map_x, const GemmArgs &a, int split, cudaStream_t stream) {
+    auto kernel = k_stream_gemm<NP, EPI>;
+    static bool prepared = false; /* per instantiation; the attribute belongs to the function on every device */
+    static std::mutex lock;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        int device = 0;
+        static int prepared_device = -1;
+        cudaGetDevice(&device);
+        if (!prepared || prepared_device != device) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<NP>::SMEM_BYTES) !=
+                cudaSuccess)
+                return NCB_ERR_LAUNCH;
+            prepared = true;
+            prepared_device = device;
+        }
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(split, a.N / TILE_F);
+    config.blockDim = dim3(THREADS);
+    config.dynamicSmemBytes = Shape<NP>::SMEM_BYTES;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = split;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = NCB_PDL;
+    config.attrs = attribute;
+    config.numAttrs = 2;
+    return cudaLaunchKernelEx(&config, kernel, map_w, map_x, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+}
+
+template <int NP>
+int launch_epi(const CUtensorMap &map_w, const CUtensorMap &map_x, const GemmArgs &a, int epilogue, int split,
+               cudaStream_t stream) {
+    switch (epilogue) {
+    case EPI_STORE: return launch<NP, EPI_STORE>(map_w, map_x, a, split, stream);
+    case EPI_RESID: return launch<NP, EPI_RESID>(map_w, map_x, a, split, stream);
+    case EPI_RELU2: return launch<NP, EPI_RELU2>(map_w, map_x, a, split, stream);
+    case EPI_F32: return launch<NP, EPI_F32>(map_w, map_x, a, split, stream);
+    default: return NCB_ERR_ARG;
+    }
+}
+
+} /* namespace */
+
+extern "C" {
+
+/* The K split stream_gemm chooses for a [N][K] weight matrix when called with split 0. */
+int stream_gemm_split(int N, int K) {
+    if (N <= 0 || K <= 0 || N % TILE_F || K % KBLK) return 0;
+    return auto_split(N / TILE_F, K / KBLK);
+}
+
+/*
+ * y = epilogue(norm?(x) . W^T) for rows <= 128 activation rows on the tcgen05 tensor cores.
+ *   x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3); resid bf16 [rows][N] for epilogue 1
+ *   (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding the product), 2 relu^2, 3 fp32.
+ *   norm_input != 0 applies the parameter-free RMS norm (eps FLT_EPSILON) to x, as a per-row scale of the fp32
+ *   product. split: blocks per cluster that share a feature tile's K range (1..8, at most K / 64), 0 = automatic.
+ *   status: optional device word, NCB_DEV_WAIT_TIMEOUT is or-ed in if a bounded wait expired.
+ * N must be a multiple of 128, K of 64; x and w 16-byte aligned.
+ */
+int stream_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
+                int epilogue, int split, int *status, void *stream) {
+    if (rows < 0 || rows > 128 || N <= 0 || K <= 0 || N % TILE_F || K % KBLK) return NCB_ERR_ARG;
+    if (epilogue < EPI_STORE || epilogue > EPI_F32 || split < 0 || split > MAX_SPLIT || split > K / KBLK) return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    if (!x || !w || !y || (epilogue == EPI_RESID && !resid)) return NCB_ERR_ARG;
+    if (((uintptr_t)x | (uintptr_t)w) % 16 || (uintptr_t)y % 4) return NCB_ERR_ALIGN;
+    if (split == 0) split = auto_split(N / TILE_F, K / KBLK);
+    const int np = rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
+    CUtensorMap map_w, map_x;
+    if (!tensor_map(w, N, K, TILE_F, &map_w) || !tensor_map(x, rows, K, np, &map_x)) return NCB_ERR_LAUNCH;
+    const GemmArgs a = {(const bf16 *)x, (const bf16 *)resid, y, rows, N, K, norm_input, status};
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (np) {
+    case 32: return launch_epi<32>(map_w, map_x, a, epilogue, split, s);
+    case 64: return launch_epi<64>(map_w, map_x, a, epilogue, split, s);
+    default: return launch_epi<128>(map_w, map_x, a, epilogue, split, s);
+    }
+}
+
+} /* extern "C" */

@@ -108,7 +108,8 @@ class Decoder:
         self.cos, self.sin = ops.rotary_table(self.capacity, cfg.rope_theta, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.windows = cfg.windows or [0] * cfg.n_layers
-        self.use_fused = True  # decode steps of <= 16 rows run on the decode_step kernels when the shapes allow
+        self.use_fused = True  # decode steps of <= 128 rows run on this package's GEMM kernels when the shapes allow
+        self.use_stream_gemm = True  # ... of 17 to 128 rows on the tcgen05 stream_gemm (else cuBLAS)
         self._graphs: dict[int, tuple] = {}
         self._graph_tensors: dict[int, tuple] = {}
         self._workspaces: dict[tuple[int, int], Tensor] = {}
@@ -204,13 +205,20 @@ class Decoder:
     # ---- the same pass for at most 16 rows with this package's own GEMM kernels --------------------------------
 
     def fused_supported(self, rows: int) -> bool:
-        """The decode_step kernels cover at most 16 rows, hidden sizes up to 2048 (fused norm keeps a row slice in
-        registers) and intermediate sizes up to 5120, all multiples of 256, with the default residual mixing."""
+        """Steps of at most 16 rows run on the decode_step GEMM (hidden sizes up to 2048, since its fused norm keeps
+        a row slice in registers, intermediate sizes up to 5120, all multiples of 256); steps of 17 to 128 rows on
+        the tcgen05 stream_gemm (every GEMM width a multiple of 128, every depth of 64). Both need the default
+        residual mixing."""
         cfg = self.cfg
-        return (rows <= 16 and cfg.hidden % 256 == 0 and cfg.hidden <= 2048 and cfg.intermediate % 256 == 0
-                and cfg.intermediate <= 5120 and (cfg.n_heads * HEAD_DIM) % 256 == 0
-                and cfg.n_heads * HEAD_DIM <= 5120 and cfg.vocab % 8 == 0
-                and all(l.resid_lambda == 1.0 and l.x0_lambda == 0.0 for l in self.w.layers))
+        if not all(l.resid_lambda == 1.0 and l.x0_lambda == 0.0 for l in self.w.layers):
+            return False
+        if rows <= 16:
+            return (cfg.hidden % 256 == 0 and cfg.hidden <= 2048 and cfg.intermediate % 256 == 0
+                    and cfg.intermediate <= 5120 and (cfg.n_heads * HEAD_DIM) % 256 == 0
+                    and cfg.n_heads * HEAD_DIM <= 5120 and cfg.vocab % 8 == 0)
+        return (rows <= 128 and self.use_stream_gemm
+                and all(n % 128 == 0 for n in (cfg.hidden, cfg.intermediate, cfg.qkv_width, cfg.vocab))
+                and all(k % 64 == 0 for k in (cfg.hidden, cfg.intermediate)))
 
     def fused_buffers(self, rows: int) -> dict[str, Tensor]:
         cfg, dev, bf = self.cfg, self.device, torch.bfloat16
@@ -223,7 +231,7 @@ class Decoder:
 
     def fused_step(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int, buf: dict[str, Tensor],
                    choose: bool = True) -> Tensor:
-        """One step for rows <= 16 on the decode_step kernels: fp32 logits in buf["logits"]; with `choose`, tokens
+        """One step for rows <= 128 on this package's kernels (GEMMs: decode_step's for rows <= 16, stream_gemm above): fp32 logits in buf["logits"]; with `choose`, tokens
         become the greedy choices and pos advances by one. 6 launches per layer: qkv GEMM (norm fused), split
         attention (append fused), merge, o GEMM + residual, up GEMM (norm fused) + relu^2, down GEMM + residual."""
         cfg, lib, s = self.cfg, cuda_library("decode_step"), stream()
@@ -231,9 +239,15 @@ class Decoder:
         workspace = self._workspace(rows, max_kv_len)
         h, qkv, att, u = buf["h"], buf["qkv"], buf["att"], buf["u"]
 
+        wide = cuda_library("stream_gemm") if rows > 16 else None
+
         def gemm(x, w, resid, y, n, k, norm, epilogue):
-            check(lib.skinny_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue, s),
-                  "skinny_gemm")
+            if wide is not None:
+                check(wide.stream_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue,
+                                       0, pointer(self.status), s), "stream_gemm")
+            else:
+                check(lib.skinny_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue,
+                                      s), "skinny_gemm")
 
         check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
         for i, layer in enumerate(self.w.layers):
