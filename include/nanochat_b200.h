@@ -261,12 +261,14 @@ int stream_gemm_split(int N, int K);
  * y = epilogue(norm?(x) . W^T). x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3);
  * resid bf16 [rows][N] for epilogue 1 (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding
  * the product), 2 relu^2, 3 fp32 store. norm_input != 0 applies the parameter-free RMS norm (eps FLT_EPSILON) to x,
- * as a per-row scale of the fp32 product. rows <= 128; N a multiple of 128; K a multiple of 64; x, w 16-byte
- * aligned. split: 1..8 blocks share one feature tile's K range (at most K / 64), 0 = automatic. status: optional
- * device word for NCB_DEV_WAIT_TIMEOUT. Launched with programmatic stream serialisation.
+ * as a per-row scale of the fp32 product. rows <= 128; N a multiple of 128; K a multiple of 64; x, w, y, resid
+ * 16-byte aligned. split: 1..8 blocks share one feature tile's K range (at most K / 64), 0 = automatic. next_w, next_bytes:
+ * optional (NULL, 0): the weights the next call on this stream will read, 16-byte aligned and a multiple of 16
+ * bytes; they are prefetched into L2 while this call runs. status: optional device word for NCB_DEV_WAIT_TIMEOUT.
+ * Launched with programmatic stream serialisation.
  */
 int stream_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
-                int epilogue, int split, int *status, void *stream);
+                int epilogue, int split, const void *next_w, long long next_bytes, int *status, void *stream);
 
 #ifdef __cplusplus
 }

@@ -70,6 +70,8 @@ struct GemmArgs {
     const bf16 *resid; /* [rows][N] for EPI_RESID (may alias y) */
     void *y;           /* [rows][N] bf16, or fp32 for EPI_F32 */
     int rows, N, K, norm_input;
+    const uint8_t *next_w; /* optional: bytes the NEXT kernel will stream, pulled into L2 while this one runs */
+    long long next_bytes;
     int *status;
 };
 
@@ -104,6 +106,10 @@ __device__ __forceinline__ void tma_load(uint32_t dst, const CUtensorMap *map, i
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
                  : "memory");
+}
+/* A contiguous run of global memory into L2; 16-byte aligned, a multiple of 16 bytes. */
+__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 /* Shared-memory matrix descriptor of a K-major tile of 128-byte rows with the 128-byte swizzle: 8-row groups are
  * 1024 bytes apart (stride byte offset), the leading byte offset is unused for this layout, descriptor version 1. */
@@ -234,6 +240,13 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
         if (lane == 0) { /* producer */
             const int pre = nst < STAGES ? nst : STAGES;
             for (int i = 0; i < pre; i++) load_w(i); /* weights do not depend on the predecessor */
+            if (a.next_w) { /* this block's share of the next kernel's weights, in 32 KB runs */
+                const long long blocks = (long long)gridDim.x * gridDim.y, me = (long long)tile * gridDim.x + rank;
+                const long long share = ((a.next_bytes + blocks - 1) / blocks + 15) & ~15ll;
+                const long long from = me * share, to = from + share < a.next_bytes ? from + share : a.next_bytes;
+                for (long long at = from; at < to; at += 32768)
+                    l2_prefetch(a.next_w + at, (uint32_t)(to - at < 32768 ? to - at : 32768));
+            }
             STAMP(1);
             asm volatile("griddepcontrol.wait;" ::: "memory");
             STAMP(2);
@@ -308,11 +321,58 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
     }
     __syncthreads(); /* the norm warps have read their last x box: the ring may now be overwritten */
 
-    /* every thread: accumulators complete -> park lane (= feature) tid's NP columns (= rows) in shared memory */
+    /* every thread: accumulators complete; thread tid holds feature tid (tensor-memory lane) of every row (column) */
     if (!mbar_wait(accum_bar, 0)) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
     if (tid == 0) STAMP(5);
     __syncwarp(); /* the tensor-memory loads below are warp-wide */
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const size_t col = (size_t)tile * TILE_F + tid;
+    auto finish_value = [&](float v, float resid) { /* fp32 product (already normed) -> the bf16 epilogues */
+        bf16 out = __float2bfloat16_rn(v);
+        if (EPI == EPI_RESID) out = __float2bfloat16_rn(resid + __bfloat162float(out));
+        if (EPI == EPI_RELU2) {
+            const float p = fmaxf(__bfloat162float(out), 0.f);
+            out = __float2bfloat16_rn(p * p);
+        }
+        return out;
+    };
+    auto finish = [&](float v, float resid, size_t at) {
+        if (EPI == EPI_F32)
+            reinterpret_cast<float *>(a.y)[at] = v;
+        else
+            reinterpret_cast<bf16 *>(a.y)[at] = finish_value(v, resid);
+    };
+    const float inv_k = 1.f / (float)a.K;
+
+    if (S == 1) { /* no partner: straight from tensor memory to y, 32 rows at a time, loads before stores */
+#pragma unroll 1
+        for (int c = 0; c < NP / 32; c++) {
+            if (c * 32 >= a.rows) break;
+            float v[32], res[32];
+            tmem_load32(tmem + ((uint32_t)(warp * 32) << 16) + c * 32, v);
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const int r = c * 32 + j;
+                res[j] = EPI == EPI_RESID && r < a.rows ? __bfloat162float(a.resid[(size_t)r * a.N + col]) : 0.f;
+                if (a.norm_input) v[j] *= rsqrtf(sumsq[r] * inv_k + FLT_EPSILON);
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const int r = c * 32 + j;
+                if (r < a.rows) finish(v[j], res[j], (size_t)r * a.N + col);
+            }
+        }
+        if (tid == 0) STAMP(6);
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (warp == 1)
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NP) : "memory");
+        if (tid == 0) STAMP(7);
+        return;
+    }
+
+    /* K split over the cluster: park the partial accumulators, then block `rank` sums rows rank, rank + S, ... over
+     * all blocks in a fixed order through distributed shared memory, four rows' loads in flight at a time */
 #pragma unroll
     for (int c = 0; c < NP / 32; c++) {
         float v[32];
@@ -325,32 +385,58 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
     if (tid == 0) STAMP(6);
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NP) : "memory");
-
-    for (int r = rank; r < a.rows; r += S) { /* this block's rows of the tile, summed over the cluster in order */
-        float pv[MAX_SPLIT], ps[MAX_SPLIT]; /* all remote loads in flight before the first add */
+    /* 32 threads cover a row's 128 features with 16-byte remote loads; the block's four warps take four of its rows
+     * at a time, and all of a thread's loads (two row groups x S peers) are issued before the first add */
+    const float *peer_park[MAX_SPLIT], *peer_sumsq[MAX_SPLIT];
 #pragma unroll
-        for (int s = 0; s < MAX_SPLIT; s++) {
-            pv[s] = s < S ? cluster.map_shared_rank(park, s)[r * TILE_F + tid] : 0.f;
-            ps[s] = s < S && a.norm_input ? cluster.map_shared_rank(sumsq, s)[r] : 0.f;
-        }
-        float v = 0.f, ss = 0.f;
+    for (int s = 0; s < MAX_SPLIT; s++) {
+        peer_park[s] = cluster.map_shared_rank(park, s < S ? s : 0) + lane * 4;
+        peer_sumsq[s] = cluster.map_shared_rank(sumsq, s < S ? s : 0);
+    }
+    const size_t col4 = (size_t)tile * TILE_F + lane * 4;
+    constexpr int RB = 2;
+    for (int r0 = rank + warp * S; r0 < a.rows; r0 += 4 * S * RB) {
+        float4 pv[RB][MAX_SPLIT];
+        float ps[RB][MAX_SPLIT];
+        uint2 res[RB];
 #pragma unroll
-        for (int s = 0; s < MAX_SPLIT; s++) {
-            v += pv[s];
-            ss += ps[s];
-        }
-        if (a.norm_input) v *= rsqrtf(ss / (float)a.K + FLT_EPSILON);
-        const size_t at = (size_t)r * a.N + (size_t)tile * TILE_F + tid;
-        if (EPI == EPI_F32) {
-            reinterpret_cast<float *>(a.y)[at] = v;
-        } else {
-            bf16 out = __float2bfloat16_rn(v);
-            if (EPI == EPI_RESID) out = __float2bfloat16_rn(__bfloat162float(a.resid[at]) + __bfloat162float(out));
-            if (EPI == EPI_RELU2) {
-                const float p = fmaxf(__bfloat162float(out), 0.f);
-                out = __float2bfloat16_rn(p * p);
+        for (int i = 0; i < RB; i++) {
+            const int r = r0 + i * 4 * S;
+            const bool ok = r < a.rows;
+#pragma unroll
+            for (int s = 0; s < MAX_SPLIT; s++) {
+                pv[i][s] = ok && s < S ? *reinterpret_cast<const float4 *>(peer_park[s] + r * TILE_F) : make_float4(0.f, 0.f, 0.f, 0.f);
+                ps[i][s] = ok && s < S && a.norm_input ? peer_sumsq[s][r] : 0.f;
             }
-            reinterpret_cast<bf16 *>(a.y)[at] = out;
+            res[i] = EPI == EPI_RESID && ok ? *reinterpret_cast<const uint2 *>(a.resid + (size_t)r * a.N + col4) : make_uint2(0u, 0u);
+        }
+#pragma unroll
+        for (int i = 0; i < RB; i++) {
+            const int r = r0 + i * 4 * S;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            float ss = 0.f;
+#pragma unroll
+            for (int s = 0; s < MAX_SPLIT; s++) {
+                v.x += pv[i][s].x, v.y += pv[i][s].y, v.z += pv[i][s].z, v.w += pv[i][s].w;
+                ss += ps[i][s];
+            }
+            if (a.norm_input) {
+                const float rstd = rsqrtf(ss * inv_k + FLT_EPSILON);
+                v.x *= rstd, v.y *= rstd, v.z *= rstd, v.w *= rstd;
+            }
+            if (r >= a.rows) continue;
+            const size_t at = (size_t)r * a.N + col4;
+            if (EPI == EPI_F32) {
+                *reinterpret_cast<float4 *>(reinterpret_cast<float *>(a.y) + at) = v;
+            } else {
+                const __nv_bfloat162 *rr = reinterpret_cast<const __nv_bfloat162 *>(&res[i]);
+                const float2 r01 = __bfloat1622float2(rr[0]), r23 = __bfloat1622float2(rr[1]);
+                uint2 out;
+                __nv_bfloat162 *oo = reinterpret_cast<__nv_bfloat162 *>(&out);
+                oo[0] = __halves2bfloat162(finish_value(v.x, r01.x), finish_value(v.y, r01.y));
+                oo[1] = __halves2bfloat162(finish_value(v.z, r23.x), finish_value(v.w, r23.y));
+                *reinterpret_cast<uint2 *>(reinterpret_cast<bf16 *>(a.y) + at) = out;
+            }
         }
     }
     if (tid == 0) STAMP(7);
@@ -487,21 +573,25 @@ int stream_gemm_split(int N, int K) {
  *   (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding the product), 2 relu^2, 3 fp32.
  *   norm_input != 0 applies the parameter-free RMS norm (eps FLT_EPSILON) to x, as a per-row scale of the fp32
  *   product. split: blocks per cluster that share a feature tile's K range (1..8, at most K / 64), 0 = automatic.
- *   status: optional device word, NCB_DEV_WAIT_TIMEOUT is or-ed in if a bounded wait expired.
- * N must be a multiple of 128, K of 64; x and w 16-byte aligned.
+ *   next_w, next_bytes: optional; the weights the NEXT call on this stream will read (16-byte aligned, a multiple
+ *   of 16 bytes). They are prefetched into L2 while this call runs, so a chain of short GEMMs keeps HBM busy across
+ *   kernel boundaries. status: optional device word, NCB_DEV_WAIT_TIMEOUT is or-ed in if a bounded wait expired.
+ * N must be a multiple of 128, K of 64; x, w, y and resid 16-byte aligned.
  */
 int stream_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
-                int epilogue, int split, int *status, void *stream) {
+                int epilogue, int split, const void *next_w, long long next_bytes, int *status, void *stream) {
     if (rows < 0 || rows > 128 || N <= 0 || K <= 0 || N % TILE_F || K % KBLK) return NCB_ERR_ARG;
     if (epilogue < EPI_STORE || epilogue > EPI_F32 || split < 0 || split > MAX_SPLIT || split > K / KBLK) return NCB_ERR_ARG;
     if (rows == 0) return NCB_OK;
     if (!x || !w || !y || (epilogue == EPI_RESID && !resid)) return NCB_ERR_ARG;
-    if (((uintptr_t)x | (uintptr_t)w) % 16 || (uintptr_t)y % 4) return NCB_ERR_ALIGN;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)resid) % 16) return NCB_ERR_ALIGN;
+    if (next_w && ((uintptr_t)next_w % 16 || next_bytes % 16 || next_bytes < 0)) return NCB_ERR_ALIGN;
     if (split == 0) split = auto_split(N / TILE_F, K / KBLK);
     const int np = rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
     CUtensorMap map_w, map_x;
     if (!tensor_map(w, N, K, TILE_F, &map_w) || !tensor_map(x, rows, K, np, &map_x)) return NCB_ERR_LAUNCH;
-    const GemmArgs a = {(const bf16 *)x, (const bf16 *)resid, y, rows, N, K, norm_input, status};
+    const GemmArgs a = {(const bf16 *)x, (const bf16 *)resid, y, rows, N, K, norm_input,
+                        next_bytes > 0 ? (const uint8_t *)next_w : nullptr, next_bytes, status};
     cudaStream_t s = (cudaStream_t)stream;
     switch (np) {
     case 32: return launch_epi<32>(map_w, map_x, a, epilogue, split, s);

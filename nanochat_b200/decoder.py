@@ -241,23 +241,26 @@ class Decoder:
 
         wide = cuda_library("stream_gemm") if rows > 16 else None
 
-        def gemm(x, w, resid, y, n, k, norm, epilogue):
+        def gemm(x, w, resid, y, n, k, norm, epilogue, then=None):
+            """`then`: the weights of the next GEMM on the stream, prefetched into L2 meanwhile (stream_gemm only)."""
             if wide is not None:
                 check(wide.stream_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue,
-                                       0, pointer(self.status), s), "stream_gemm")
+                                       0, pointer(then), 0 if then is None else then.numel() * 2, pointer(self.status),
+                                       s), "stream_gemm")
             else:
                 check(lib.skinny_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue,
                                       s), "skinny_gemm")
 
         check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
-        for i, layer in enumerate(self.w.layers):
-            gemm(h, layer.wqkv, None, qkv, cfg.qkv_width, C, 1, 0)
+        layers = self.w.layers
+        for i, layer in enumerate(layers):
+            gemm(h, layer.wqkv, None, qkv, cfg.qkv_width, C, 1, 0, then=layer.wo)
             ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
                                       cfg.n_heads, max_kv_len, slot_map=slot_map, window=self.windows[i],
                                       workspace=workspace, out=att, status=self.status)
-            gemm(att, layer.wo, h, h, C, A, 0, 1)
-            gemm(h, layer.wup, None, u, Fd, C, 1, 2)
-            gemm(u, layer.wdown, h, h, C, Fd, 0, 1)
+            gemm(att, layer.wo, h, h, C, A, 0, 1, then=layer.wup)
+            gemm(h, layer.wup, None, u, Fd, C, 1, 2, then=layer.wdown)
+            gemm(u, layer.wdown, h, h, C, Fd, 0, 1, then=layers[i + 1].wqkv if i + 1 < len(layers) else None)
         gemm(h, self.w.lm_head, None, buf["logits"], cfg.vocab, C, 1, 3)
         if choose:
             check(lib.greedy_choice(pointer(buf["logits"]), pointer(tokens), pointer(pos), rows, cfg.vocab,

@@ -56,7 +56,7 @@ SIGNATURES = {
     },
     "stream_gemm": {
         "stream_gemm_split": ([c_int, c_int], c_int),
-        "stream_gemm": ([c_ptr] * 4 + [c_int] * 6 + [c_ptr, c_ptr], c_int),
+        "stream_gemm": ([c_ptr] * 4 + [c_int] * 6 + [c_ptr, c_ll, c_ptr, c_ptr], c_int),
     },
 }
 STATUS = {0: "ok", 1: "invalid argument", 2: "misaligned pointer or stride", 3: "workspace too small",

@@ -192,7 +192,9 @@ def test_wide_fused_step_on_stream_gemm_matches_the_cublas_path(rows):
         pos.add_(1)
         err = (got - want).abs()
         scale = float(want.abs().max())
-        assert err.max() < 2e-2 * max(scale, 1.0) and err.mean() < 2e-3 * max(scale, 1.0), (t, float(err.max()), scale)
+        # the two differ by bf16 roundings of every activation (here the norm scales the fp32 product instead of
+        # rounding the normed input), which three layers turn into about 0.3 % of the largest logit
+        assert err.max() < 3e-2 * max(scale, 1.0) and err.mean() < 5e-3 * max(scale, 1.0), (t, float(err.max()), scale)
     for a, b in zip(ours.caches, ref.caches):  # appended bytes only differ where a bf16 input rounded differently
         same = (a.pages == b.pages).float().mean()
         assert same > 0.98, float(same)

@@ -10,15 +10,16 @@ pytestmark = pytest.mark.gpu
 EPS = 1.1920928955078125e-07
 
 
-def gemm(x, w, resid, norm, epilogue, split=0, status=None):
+def gemm(x, w, resid, norm, epilogue, split=0, status=None, next_w=None):
     rows, K = x.shape
     N = w.shape[0]
     y = torch.empty((rows, N), dtype=torch.float32 if epilogue == 3 else torch.bfloat16, device="cuda")
     if epilogue == 1:
         y.copy_(resid)  # in place, as the decoder uses it
     rc = cuda_library("stream_gemm").stream_gemm(pointer(x), pointer(w), pointer(y if epilogue == 1 else None),
-                                                 pointer(y), rows, N, K, norm, epilogue, split, pointer(status),
-                                                 stream())
+                                                 pointer(y), rows, N, K, norm, epilogue, split, pointer(next_w),
+                                                 0 if next_w is None else next_w.numel() * next_w.element_size(),
+                                                 pointer(status), stream())
     assert rc == 0
     return y
 
@@ -78,6 +79,19 @@ def test_a_split_is_deterministic():
         assert torch.equal(gemm(x, w, None, 1, 3), first)
 
 
+def test_prefetching_the_next_weights_changes_nothing():
+    gen = torch.Generator().manual_seed(13)
+    x = torch.randn(32, 2048, generator=gen).bfloat16().cuda()
+    w = (torch.randn(2048, 2048, generator=gen) * 0.05).bfloat16().cuda()
+    nxt = (torch.randn(8192 * 2048 + 8, generator=gen) * 0.05).bfloat16().cuda()  # not a multiple of the block count
+    plain = gemm(x, w, None, 1, 0)
+    assert torch.equal(gemm(x, w, None, 1, 0, next_w=nxt), plain)
+    assert torch.equal(gemm(x, w, None, 1, 0, split=1, next_w=nxt[:8]), gemm(x, w, None, 1, 0, split=1))
+    lib = cuda_library("stream_gemm")
+    p = pointer(x)
+    assert lib.stream_gemm(p, p, None, p, 4, 128, 256, 0, 0, 0, p, 24, None, None) == 2  # not a multiple of 16 bytes
+
+
 def test_head_sized_gemm_keeps_fp32_logits():
     gen = torch.Generator().manual_seed(11)
     x = torch.randn(32, 2048, generator=gen).bfloat16().cuda()
@@ -92,11 +106,11 @@ def test_stream_gemm_rejects_unsupported_shapes():
     lib = cuda_library("stream_gemm")
     x = torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda")
     p = pointer(x)
-    assert lib.stream_gemm(p, p, None, p, 129, 128, 256, 0, 0, 0, None, None) == 1   # more than 128 rows
-    assert lib.stream_gemm(p, p, None, p, 4, 100, 256, 0, 0, 0, None, None) == 1     # N not a multiple of 128
-    assert lib.stream_gemm(p, p, None, p, 4, 128, 100, 0, 0, 0, None, None) == 1     # K not a multiple of 64
-    assert lib.stream_gemm(p, p, None, p, 4, 128, 128, 0, 0, 3, None, None) == 1     # more blocks than k-blocks
-    assert lib.stream_gemm(p, p, None, p, 4, 128, 256, 0, 1, 0, None, None) == 1     # residual epilogue, no residual
-    assert lib.stream_gemm(p, p, None, p, 0, 128, 256, 0, 0, 0, None, None) == 0     # nothing to do
+    assert lib.stream_gemm(p, p, None, p, 129, 128, 256, 0, 0, 0, None, 0, None, None) == 1   # more than 128 rows
+    assert lib.stream_gemm(p, p, None, p, 4, 100, 256, 0, 0, 0, None, 0, None, None) == 1     # N not a multiple of 128
+    assert lib.stream_gemm(p, p, None, p, 4, 128, 100, 0, 0, 0, None, 0, None, None) == 1     # K not a multiple of 64
+    assert lib.stream_gemm(p, p, None, p, 4, 128, 128, 0, 0, 3, None, 0, None, None) == 1     # more blocks than k-blocks
+    assert lib.stream_gemm(p, p, None, p, 4, 128, 256, 0, 1, 0, None, 0, None, None) == 1     # residual epilogue, no residual
+    assert lib.stream_gemm(p, p, None, p, 0, 128, 256, 0, 0, 0, None, 0, None, None) == 0     # nothing to do
     assert lib.stream_gemm_split(2048, 2048) == 8 and lib.stream_gemm_split(65536, 2048) == 1
     assert lib.stream_gemm_split(100, 2048) == 0
