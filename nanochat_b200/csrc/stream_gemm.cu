@@ -240,14 +240,6 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
         if (lane == 0) { /* producer */
             const int pre = nst < STAGES ? nst : STAGES;
             for (int i = 0; i < pre; i++) load_w(i); /* weights do not depend on the predecessor */
-            if (a.next_w) { /* this block's share of the next kernel's weights, in 32 KB runs */
-                const long long blocks = (long long)gridDim.x * gridDim.y, me = (long long)tile * gridDim.x + rank;
-                const long long share = ((a.next_bytes + blocks - 1) / blocks + 15) & ~15ll;
-                const long long from = me * share, to = from + share < a.next_bytes ? from + share : a.next_bytes;
-                for (long long at = from; at < to; at += 32768)
-                    l2_prefetch(a.next_w + at, (uint32_t)(to - at < 32768 ? to - at : 32768));
-            }
-            STAMP(1);
             asm volatile("griddepcontrol.wait;" ::: "memory");
             STAMP(2);
             for (int i = 0; i < pre; i++) load_x(i);
@@ -259,6 +251,15 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
                 load_w(i);
                 load_x(i);
             }
+            if (a.next_w) { /* all of this block's loads are issued: its share of the NEXT kernel's weights starts
+                               * towards L2 now (32 KB runs) and arrives under the epilogues and the next launch */
+                const long long blocks = (long long)gridDim.x * gridDim.y, me = (long long)tile * gridDim.x + rank;
+                const long long share = ((a.next_bytes + blocks - 1) / blocks + 15) & ~15ll;
+                const long long from = me * share, to = from + share < a.next_bytes ? from + share : a.next_bytes;
+                for (long long at = from; at < to; at += 32768)
+                    l2_prefetch(a.next_w + at, (uint32_t)(to - at < 32768 ? to - at : 32768));
+            }
+            STAMP(1);
         }
     } else if (warp == 1) {
         if (lane == 0) { /* MMA issuer */
@@ -502,12 +503,11 @@ bool tensor_map(const void *base, int rows, int K, int box_rows, CUtensorMap *ou
     return true;
 }
 
-/* K split S: enough blocks for every SM (two of the smaller shapes fit an SM), at least two k-blocks each. */
+/* K split S: enough blocks for every SM without a second wave, at least two k-blocks each. */
 int auto_split(int tiles, int kb) {
-    int s = 160 / tiles;
-    if (s > MAX_SPLIT) s = MAX_SPLIT;
-    if (s > kb / 2) s = kb / 2;
-    return s < 1 ? 1 : s;
+    int s = MAX_SPLIT; /* measured: powers of two, as many blocks as fit the GPU at two per SM (296 on a B200) */
+    while (s > 1 && (tiles * s > 296 || s > kb / 2)) s >>= 1;
+    return s;
 }
 
 template <int NP, int EPI>
