@@ -372,7 +372,7 @@ def main() -> None:
     lens_t = torch.tensor(lens, dtype=torch.int32, device=device)
     max_kv = max(lens)
     status = torch.zeros(1, dtype=torch.int32, device=device)
-    chunk = args.chunk_pages or ops.chunk_pages_for(B, HKV, max_kv)
+    chunk = args.chunk_pages or ops.plan_chunk_pages(lens, HKV, max_kv)  # the host knows this step's lengths
     workspace = torch.empty(ncb.workspace_bytes(B, HQ, HKV, max_kv + headroom, chunk), dtype=torch.uint8, device=device)
     out = torch.empty_like(q)
 

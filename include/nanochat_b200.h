@@ -84,8 +84,14 @@ int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const
 
 /* ---- library decode_attn ------------------------------------------------------------------------------------ */
 
-/* Pages one thread block covers when chunk_pages == 0 is passed below; depends only on these three values. */
+/* Pages one thread block covers when chunk_pages == 0 is passed below; depends only on these three values (every
+ * sequence is taken as max_kv_len long). */
 int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len);
+/* The same choice for lengths the HOST knows (lens: host int32[B], clipped to [0, max_kv_len]; NULL = all at
+ * max_kv_len): a model of how the split kernel's blocks fill the GPU picks the chunk size that avoids a nearly
+ * empty last wave of blocks. Pass the result as chunk_pages (and to decode_attn_workspace_bytes); worth it for
+ * ragged batches whose lengths change slowly, such as the steps of one captured decode loop. */
+int decode_attn_plan_chunk_pages(const int *lens, int B, int Hkv, int max_kv_len, int window);
 /* Workspace bytes for the split partials; chunk_pages == 0 selects decode_attn_chunk_pages(). */
 long long decode_attn_workspace_bytes(int B, int Hq, int max_kv_len, int Hkv, int chunk_pages);
 

@@ -48,6 +48,16 @@ def chunk_pages_for(B: int, Hkv: int, max_kv_len: int) -> int:
     return cuda_library("decode_attn").decode_attn_chunk_pages(B, Hkv, max_kv_len)
 
 
+def plan_chunk_pages(lens: list[int], Hkv: int, max_kv_len: int, window: int = 0) -> int:
+    """chunk_pages for lengths the host knows: the library's model of how the split kernel's blocks fill the GPU
+    picks the size that leaves no nearly empty last wave. For ragged batches whose lengths change slowly."""
+    import ctypes
+
+    arr = (ctypes.c_int * len(lens))(*lens)
+    return cuda_library("decode_attn").decode_attn_plan_chunk_pages(ctypes.cast(arr, ctypes.c_void_p), len(lens), Hkv,
+                                                                   max_kv_len, window)
+
+
 def workspace_bytes(B: int, Hq: int, Hkv: int, max_kv_len: int, chunk_pages: int = 0) -> int:
     return cuda_library("decode_attn").decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages)
 

@@ -33,7 +33,11 @@
  * NCB_DEV_WAIT_TIMEOUT in the caller's status word, waits once more (bounded again) for its copy in flight, stops
  * consuming and falls through to the block's final barriers.
  */
+#include <algorithm>
+#include <functional>
 #include <mutex>
+#include <unordered_map>
+#include <vector>
 
 #include "kv_row.cuh"
 
@@ -783,18 +787,71 @@ static int static_scratch(void **ptr) {
     return NCB_OK;
 }
 
+/*
+ * Chunk size by a model of how the split kernel's blocks fill the GPU. Blocks are dispatched in grid order (chunk
+ * fastest, then kv head, then sequence) to `slots` resident places; a block with p pages takes BLOCK_US + PAGE_US *
+ * ceil(p / WARPS) (its warps walk their pages one after the other), a block beyond its sequence's chunks IDLE_US.
+ * The modelled makespan tracks the measured kernel time up to a constant (the bytes' own streaming time) across
+ * chunk sizes, batch shapes and ragged lengths, including the steps where one more wave of blocks appears; the
+ * chunk size with the smallest makespan wins, the larger one on ties (fewer states to merge). lens == NULL takes
+ * every sequence as max_kv_len long. Chunks stay between one page per warp and 32 pages (longer ones gain nothing
+ * and unbalance ragged batches).
+ */
+static int plan_chunk_pages(const int *lens, int B, int Hkv, int max_kv_len, int window) {
+    constexpr double BLOCK_US = 2.0, PAGE_US = 1.2, IDLE_US = 0.3;
+    const int slots = BLOCKS_PER_SM * sm_count(), max_pages = pages_of(max_kv_len);
+    if (max_pages <= WARPS) return WARPS;
+    std::vector<int> pages(B);
+    for (int b = 0; b < B; b++) {
+        int len = lens ? lens[b] : max_kv_len;
+        len = len < 0 ? 0 : len > max_kv_len ? max_kv_len : len;
+        const int begin = (window > 0 && len > window) ? len - window : 0;
+        pages[b] = pages_of(len) - begin / PAGE_TOKENS;
+    }
+    int best = WARPS;
+    double best_cost = 0.;
+    std::vector<double> heap;
+    for (int c = WARPS; c <= 32; c++) {
+        const int max_chunks = (max_pages + c - 1) / c;
+        if ((long long)B * Hkv * max_chunks > (1ll << 18)) continue; /* keep the model itself cheap */
+        heap.assign(slots, 0.);
+        double end = 0.;
+        for (int b = 0; b < B; b++) {
+            const int n = (pages[b] + c - 1) / c, each = n ? (pages[b] + n - 1) / n : 0;
+            for (int h = 0; h < Hkv; h++)
+                for (int i = 0; i < max_chunks; i++) {
+                    const int first = i * each, p = i < n ? (pages[b] - first < each ? pages[b] - first : each) : 0;
+                    std::pop_heap(heap.begin(), heap.end(), std::greater<double>());
+                    double &t = heap.back();
+                    t += p > 0 ? BLOCK_US + PAGE_US * ((p + WARPS - 1) / WARPS) : IDLE_US;
+                    if (t > end) end = t;
+                    std::push_heap(heap.begin(), heap.end(), std::greater<double>());
+                }
+        }
+        if (c == WARPS || end <= best_cost) best = c, best_cost = end;
+    }
+    return best;
+}
+
 extern "C" {
+
+int decode_attn_plan_chunk_pages(const int *lens, int B, int Hkv, int max_kv_len, int window) {
+    if (B <= 0 || Hkv <= 0 || max_kv_len <= 0) return 1;
+    return plan_chunk_pages(lens, B, Hkv, max_kv_len, window);
+}
 
 int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len) {
     if (B <= 0 || Hkv <= 0 || max_kv_len <= 0) return 1;
-    /* aim at about four blocks per resident slot (BLOCKS_PER_SM per SM) when every sequence is max_kv_len long,
-     * at most 32 pages each (measured: longer chunks gain nothing and unbalance ragged batches) and at least one
-     * page per warp (measured on small batches: blocks with idle warps cost more than the lost parallelism) */
-    const long long total = (long long)B * Hkv * pages_of(max_kv_len), slots = (long long)BLOCKS_PER_SM * sm_count();
-    long long c = total / (4 * slots);
-    if (c < WARPS) c = WARPS;
-    if (c > 32) c = 32;
-    return (int)c;
+    /* every sequence taken as max_kv_len long; remembered, since eager callers ask on every call */
+    static std::mutex lock;
+    static std::unordered_map<unsigned long long, int> known;
+    const unsigned long long key = ((unsigned long long)B << 40) ^ ((unsigned long long)Hkv << 32) ^ (unsigned)max_kv_len;
+    std::lock_guard<std::mutex> guard(lock);
+    auto hit = known.find(key);
+    if (hit != known.end()) return hit->second;
+    const int c = plan_chunk_pages(nullptr, B, Hkv, max_kv_len, 0);
+    if (known.size() < 4096) known.emplace(key, c);
+    return c;
 }
 
 long long decode_attn_workspace_bytes(int B, int Hq, int max_kv_len, int Hkv, int chunk_pages) {

@@ -110,6 +110,7 @@ class Decoder:
         self.windows = cfg.windows or [0] * cfg.n_layers
         self.use_fused = True  # decode steps of <= 128 rows run on this package's GEMM kernels when the shapes allow
         self.use_stream_gemm = True  # ... of 17 to 128 rows on the tcgen05 stream_gemm (else cuBLAS)
+        self.chunk_pages = 0  # attention chunk size of decode steps; 0: the library's choice for full-length slots
         self.prefetch_next = True  # stream_gemm also pulls the next GEMM's weights into L2 (d32-class step: -1.3 %)
         self._graphs: dict[int, tuple] = {}
         self._graph_tensors: dict[int, tuple] = {}
@@ -118,9 +119,9 @@ class Decoder:
     # ---- one pass over `rows` tokens -------------------------------------------------------------------------
 
     def _workspace(self, rows: int, max_kv_len: int) -> Tensor:
-        key = (rows, max_kv_len)
+        key = (rows, max_kv_len, self.chunk_pages)
         if key not in self._workspaces:
-            need = ops.workspace_bytes(rows, self.cfg.n_heads, self.cfg.n_kv_heads, max_kv_len)
+            need = ops.workspace_bytes(rows, self.cfg.n_heads, self.cfg.n_kv_heads, max_kv_len, self.chunk_pages)
             self._workspaces[key] = torch.empty(max(need, 16), dtype=torch.uint8, device=self.device)
         return self._workspaces[key]
 
@@ -153,7 +154,8 @@ class Decoder:
             if distinct_slots and (attend_last_layer or i < cfg.n_layers - 1):
                 att = ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos,
                                                 self.caches[i], cfg.n_heads, max_kv_len, slot_map=slot_map,
-                                                window=self.windows[i], workspace=workspace, status=self.status)
+                                                window=self.windows[i], chunk_pages=self.chunk_pages,
+                                                workspace=workspace, status=self.status)
             else:
                 q = ops.kv_append(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
                                   cfg.n_heads, slot_map=slot_map, status=self.status)
@@ -163,7 +165,8 @@ class Decoder:
                     att = ops.prefill_attention(q, self.caches[i], plan, status=self.status)
                 else:
                     att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map,
-                                               window=self.windows[i], workspace=workspace, status=self.status)
+                                               window=self.windows[i], chunk_pages=self.chunk_pages,
+                                               workspace=workspace, status=self.status)
             y = att.view(rows, -1) @ layer.wo.T
             check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
             u = n @ layer.wup.T
@@ -259,7 +262,7 @@ class Decoder:
             gemm(h, layer.wqkv, None, qkv, cfg.qkv_width, C, 1, 0, then=layer.wo)
             ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
                                       cfg.n_heads, max_kv_len, slot_map=slot_map, window=self.windows[i],
-                                      workspace=workspace, out=att, status=self.status)
+                                      chunk_pages=self.chunk_pages, workspace=workspace, out=att, status=self.status)
             gemm(att, layer.wo, h, h, C, A, 0, 1, then=layer.wup)
             gemm(h, layer.wup, None, u, Fd, C, 1, 2, then=layer.wdown)
             gemm(u, layer.wdown, h, h, C, Fd, 0, 1, then=layers[i + 1].wqkv if i + 1 < len(layers) else None)
@@ -287,13 +290,15 @@ class Decoder:
 
     # ---- decode -----------------------------------------------------------------------------------------------
 
-    def _step_graph(self, batch: int, sampled: bool = False):
+    def _step_graph(self, batch: int, sampled: bool = False, chunk_pages: int = 0):
         """The captured step for `batch` slots 0 .. batch - 1: tokens, pos (device) -> chosen tokens; pos += 1; every
         choice is logged at its position in a (batch, capacity + 1) trace. `sampled` steps choose by temperature /
-        nucleus / Gumbel-max (sample_choice) from per-slot controls, the others take the argmax."""
-        key = (batch, sampled)
+        nucleus / Gumbel-max (sample_choice) from per-slot controls, the others take the argmax. `chunk_pages` is
+        the attention chunk size baked into the graph (0: the library's choice for full-length slots)."""
+        key = (batch, sampled, chunk_pages)
         if key in self._graphs:
             return self._graphs[key]
+        self.chunk_pages = chunk_pages
         dev, lib, V = self.device, cuda_library("decode_step"), self.cfg.vocab
         tokens = torch.zeros(batch, dtype=torch.long, device=dev)
         pos = torch.zeros(batch, dtype=torch.int32, device=dev)
@@ -336,10 +341,18 @@ class Decoder:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 body()
+        self.chunk_pages = 0
         # the graph holds raw pointers: every tensor its kernels touch must stay alive as long as the graph does
         self._graph_tensors[key] = (slot_map, buf, ctl)
         self._graphs[key] = (graph, side, tokens, pos, logits, trace, ctl)
         return self._graphs[key]
+
+    def planned_chunk(self, positions: list[int], steps: int) -> int:
+        """The attention chunk size for `steps` decode steps starting at these positions: the library's block-fill
+        model on the lengths half way through the run (they change by one per step, the choice is baked into the
+        captured step)."""
+        lens = [min(p + 1 + steps // 2, self.capacity) for p in positions]
+        return ops.plan_chunk_pages(lens, self.cfg.n_kv_heads, self.capacity)
 
     @torch.no_grad()
     def decode_from(self, first_tokens: list[int], positions: list[int], steps: int, temperature: float = 0.0,
@@ -352,7 +365,7 @@ class Decoder:
         B = len(first_tokens)
         assert B <= self.n_slots and max(positions) + steps <= self.capacity
         sampled = temperature > 0.0
-        graph, side, tokens, pos, logits, trace, ctl = self._step_graph(B, sampled)
+        graph, side, tokens, pos, logits, trace, ctl = self._step_graph(B, sampled, self.planned_chunk(positions, steps))
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
@@ -385,7 +398,8 @@ class Decoder:
         B = len(prompts)
         assert B <= self.n_slots and all(len(p) >= 1 for p in prompts)
         assert max(len(p) for p in prompts) - 1 + max_new_tokens <= self.capacity
-        self._step_graph(B, temperature > 0.0)  # capture (and its warm-up step) before the caches are filled
+        # capture (and its warm-up step) before the caches are filled
+        self._step_graph(B, temperature > 0.0, self.planned_chunk([len(p) - 1 for p in prompts], max_new_tokens))
         start, mid = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         missing = [b for b in range(B) if self.store is None or not self.store.load(b, prompts[b])]

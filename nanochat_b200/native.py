@@ -35,6 +35,7 @@ SIGNATURES = {
     },
     "decode_attn": {
         "decode_attn_chunk_pages": ([c_int, c_int, c_int], c_int),
+        "decode_attn_plan_chunk_pages": ([c_ptr, c_int, c_int, c_int, c_int], c_int),
         "decode_attn_workspace_bytes": ([c_int, c_int, c_int, c_int, c_int], c_ll),
         "decode_attn_fp8": ([c_ptr] * 5 + [c_ll, c_ptr] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_fp8_partial": ([c_ptr] * 5 + [c_ll, c_ptr] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),

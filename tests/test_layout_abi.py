@@ -133,3 +133,19 @@ def test_stream_gemm_validates_and_chooses_its_split_on_the_host():
     assert [lib.stream_gemm_split(n, k) for n, k in ((2048, 2048), (8192, 2048), (65536, 2048), (3072, 2048),
                                                     (5120, 1280), (1280, 5120), (128, 128), (100, 2048))] \
         == [8, 4, 1, 8, 4, 8, 1, 0]
+
+
+def test_planned_chunk_follows_the_block_fill_model():
+    """decode_attn_plan_chunk_pages is host-only: bounded, equal to the default for uniform full-length batches, and
+    it avoids the sizes that leave a nearly empty last wave of blocks."""
+    att = native.cuda_library("decode_attn")
+    uniform = (ctypes.c_int * 16)(*([8192] * 16))
+    assert att.decode_attn_plan_chunk_pages(uniform, 16, 8, 8192, 0) == att.decode_attn_chunk_pages(16, 8, 8192)
+    assert att.decode_attn_plan_chunk_pages(None, 16, 8, 8192, 0) == att.decode_attn_chunk_pages(16, 8, 8192)
+    assert att.decode_attn_chunk_pages(64, 8, 8192) == 32      # 2,048 blocks of 32 pages: the measured optimum
+    assert att.decode_attn_chunk_pages(8, 10, 776) == 4        # small batches: one page per warp
+    short = (ctypes.c_int * 4)(100, 0, 8192, -5)               # out-of-range lengths are clipped, not trusted
+    assert 4 <= att.decode_attn_plan_chunk_pages(short, 4, 2, 4096, 0) <= 32
+    windowed = (ctypes.c_int * 2)(8192, 8192)
+    # a 256-position window is 4 pages, one chunk whatever the bound: the largest bound launches the fewest idle blocks
+    assert att.decode_attn_plan_chunk_pages(windowed, 2, 1, 8192, 256) == 32
