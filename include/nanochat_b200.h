@@ -254,20 +254,20 @@ int sample_choice(const void *logits, void *probs, const void *temperature, cons
                   void *trace, int trace_stride, void *stream);
 
 /* ---- library stream_gemm ------------------------------------------------------------------------------------
- * The same GEMM for 1 to 128 rows on the tcgen05 tensor cores (TMA-staged weight stream, accumulators in tensor
+ * The same GEMM for 1 to 256 rows on the tcgen05 tensor cores (TMA-staged weight stream, accumulators in tensor
  * memory, K split over a thread-block cluster and reduced through distributed shared memory); replaces k_wgmma with
  * its epilogues (model/kernels/decode.cu:170-208,232-359) and k_norm / k_rstd (decode.cu:415-456) for decode batches
  * above 16 sequences per GPU. */
 
-/* The K split (blocks per cluster) stream_gemm chooses for a [N][K] weight matrix when called with split 0;
- * 0 for shapes it does not take. */
-int stream_gemm_split(int N, int K);
+/* The K split (blocks per cluster) stream_gemm chooses for `rows` rows and a [N][K] weight matrix when called with
+ * split 0; 0 for shapes it does not take. */
+int stream_gemm_split(int rows, int N, int K);
 
 /*
  * y = epilogue(norm?(x) . W^T). x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3);
  * resid bf16 [rows][N] for epilogue 1 (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding
  * the product), 2 relu^2, 3 fp32 store. norm_input != 0 applies the parameter-free RMS norm (eps FLT_EPSILON) to x,
- * as a per-row scale of the fp32 product. rows <= 128; N a multiple of 128; K a multiple of 64; x, w, y, resid
+ * as a per-row scale of the fp32 product. rows <= 256; N a multiple of 128; K a multiple of 64; x, w, y, resid
  * 16-byte aligned. split: 1..8 blocks share one feature tile's K range (at most K / 64), 0 = automatic. next_w, next_bytes:
  * optional (NULL, 0): the weights the next call on this stream will read, 16-byte aligned and a multiple of 16
  * bytes; they are prefetched into L2 while this call runs. status: optional device word for NCB_DEV_WAIT_TIMEOUT.

@@ -1,13 +1,13 @@
 /*
- * y = epilogue(norm?(x) . W^T) for 1 to 128 activation rows as a weight stream on Blackwell's tcgen05 tensor cores.
- * Serves decode steps of 17 to 128 sequences per GPU (the d32-class batch of 32 per GPU), where the reference runs
+ * y = epilogue(norm?(x) . W^T) for 1 to 256 activation rows as a weight stream on Blackwell's tcgen05 tensor cores.
+ * Serves decode steps of 17 to 256 sequences per GPU (the d32-class batch of 32 per GPU), where the reference runs
  * its Hopper-only slot GEMM k_wgmma with the STORE / RESID / RELU2 epilogues (model/kernels/decode.cu:170-208,232-359)
  * and separate k_norm / k_rstd launches (decode.cu:415-456). Same model semantics as decode_step.cu: parameter-free
  * RMS norm with eps FLT_EPSILON, bf16 GEMM outputs, residual add and relu^2 in bf16, fp32 logits.
  *
  * The weights are the only traffic that matters (a 2048 x 8192 projection is 33.5 MB against 128 KB of activations),
  * so the GEMM is "swapped": D[128 features][rows] = W tile (A operand, M = 128) . x^T (B operand, N = rows padded to
- * 32 / 64 / 128), both K-major, fp32 accumulators in tensor memory. One block:
+ * 32 / 64 / 128 / 256), both K-major, fp32 accumulators in tensor memory. One block:
  *   - thread 0 streams W and x k-blocks (64 k-values = one 128-byte swizzled row per feature) into a ring of
  *     shared-memory stages with cp.async.bulk.tensor (TMA, 128-byte swizzle, no multicast); weight loads for the
  *     first ring fill are issued BEFORE griddepcontrol.wait, so in a captured step the stream starts under the
@@ -37,9 +37,6 @@ namespace {
 constexpr int TILE_F = 128;                      /* output features per block = MMA M */
 constexpr int KBLK = 64;                         /* k-values per box: 64 bf16 = one 128-byte swizzle row */
 constexpr int A_BOX_BYTES = TILE_F * KBLK * 2;   /* 16 KB of weights per box */
-#ifndef SG_KSUB
-#define SG_KSUB 1
-#endif
 #ifndef SG_RING_KB
 #define SG_RING_KB 100
 #endif
@@ -50,13 +47,14 @@ constexpr long long WAIT_CYCLES = 4000000000ll;  /* bound of every barrier wait 
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_RELU2 = 2, EPI_F32 = 3 };
 
 template <int NP> struct Shape {
-    /* A stage holds KSUB consecutive boxes of W (a feature row contributes KSUB x 128 contiguous bytes, so DRAM
-     * pages are visited for longer runs) and the matching boxes of x. */
-    static constexpr int KSUB = NP == 128 && SG_KSUB > 2 ? 2 : SG_KSUB;
+    /* A stage holds KSUB consecutive boxes of W and the matching boxes of x. Wider stages (2 or 4 boxes, i.e. 256
+     * or 512 contiguous bytes per feature row and stage) measured no faster than 1. */
+    static constexpr int KSUB = 1;
     static constexpr int B_BOX_BYTES = NP * KBLK * 2;
     static constexpr int BOX_BYTES = A_BOX_BYTES + B_BOX_BYTES;
     static constexpr int STAGE_BYTES = KSUB * BOX_BYTES;
-    static constexpr int STAGES = SG_RING_KB * 1024 / STAGE_BYTES < 8 ? SG_RING_KB * 1024 / STAGE_BYTES : 8;
+    static constexpr int RING_KB = NP == 256 ? 144 : SG_RING_KB; /* 256 rows park 128 KB of accumulators */
+    static constexpr int STAGES = RING_KB * 1024 / STAGE_BYTES < 8 ? RING_KB * 1024 / STAGE_BYTES : 8;
     static_assert(STAGES >= 2, "at least two stages");
     static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
     static constexpr int PARK_BYTES = NP * TILE_F * 4; /* fp32 accumulators parked over the ring after the main loop */
@@ -504,9 +502,10 @@ bool tensor_map(const void *base, int rows, int K, int box_rows, CUtensorMap *ou
 }
 
 /* K split S: enough blocks for every SM without a second wave, at least two k-blocks each. */
-int auto_split(int tiles, int kb) {
-    int s = MAX_SPLIT; /* measured: powers of two, as many blocks as fit the GPU at two per SM (296 on a B200) */
-    while (s > 1 && (tiles * s > 296 || s > kb / 2)) s >>= 1;
+int auto_split(int rows, int tiles, int kb) {
+    const int slots = rows > 128 ? 148 : 296; /* 256-row blocks need an SM each, the others fit two per SM (B200) */
+    int s = MAX_SPLIT;                        /* measured: powers of two, as many blocks as fit in one wave */
+    while (s > 1 && (tiles * s > slots || s > kb / 2)) s >>= 1;
     return s;
 }
 
@@ -561,14 +560,14 @@ int launch_epi(const CUtensorMap &map_w, const CUtensorMap &map_x, const GemmArg
 
 extern "C" {
 
-/* The K split stream_gemm chooses for a [N][K] weight matrix when called with split 0. */
-int stream_gemm_split(int N, int K) {
-    if (N <= 0 || K <= 0 || N % TILE_F || K % KBLK) return 0;
-    return auto_split(N / TILE_F, K / KBLK);
+/* The K split stream_gemm chooses for `rows` rows and a [N][K] weight matrix when called with split 0. */
+int stream_gemm_split(int rows, int N, int K) {
+    if (rows < 0 || rows > 256 || N <= 0 || K <= 0 || N % TILE_F || K % KBLK) return 0;
+    return auto_split(rows, N / TILE_F, K / KBLK);
 }
 
 /*
- * y = epilogue(norm?(x) . W^T) for rows <= 128 activation rows on the tcgen05 tensor cores.
+ * y = epilogue(norm?(x) . W^T) for rows <= 256 activation rows on the tcgen05 tensor cores.
  *   x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3); resid bf16 [rows][N] for epilogue 1
  *   (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding the product), 2 relu^2, 3 fp32.
  *   norm_input != 0 applies the parameter-free RMS norm (eps FLT_EPSILON) to x, as a per-row scale of the fp32
@@ -580,14 +579,14 @@ int stream_gemm_split(int N, int K) {
  */
 int stream_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
                 int epilogue, int split, const void *next_w, long long next_bytes, int *status, void *stream) {
-    if (rows < 0 || rows > 128 || N <= 0 || K <= 0 || N % TILE_F || K % KBLK) return NCB_ERR_ARG;
+    if (rows < 0 || rows > 256 || N <= 0 || K <= 0 || N % TILE_F || K % KBLK) return NCB_ERR_ARG;
     if (epilogue < EPI_STORE || epilogue > EPI_F32 || split < 0 || split > MAX_SPLIT || split > K / KBLK) return NCB_ERR_ARG;
     if (rows == 0) return NCB_OK;
     if (!x || !w || !y || (epilogue == EPI_RESID && !resid)) return NCB_ERR_ARG;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)resid) % 16) return NCB_ERR_ALIGN;
     if (next_w && ((uintptr_t)next_w % 16 || next_bytes % 16 || next_bytes < 0)) return NCB_ERR_ALIGN;
-    if (split == 0) split = auto_split(N / TILE_F, K / KBLK);
-    const int np = rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
+    if (split == 0) split = auto_split(rows, N / TILE_F, K / KBLK);
+    const int np = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
     CUtensorMap map_w, map_x;
     if (!tensor_map(w, N, K, TILE_F, &map_w) || !tensor_map(x, rows, K, np, &map_x)) return NCB_ERR_LAUNCH;
     const GemmArgs a = {(const bf16 *)x, (const bf16 *)resid, y, rows, N, K, norm_input,
@@ -596,7 +595,8 @@ int stream_gemm(const void *x, const void *w, const void *resid, void *y, int ro
     switch (np) {
     case 32: return launch_epi<32>(map_w, map_x, a, epilogue, split, s);
     case 64: return launch_epi<64>(map_w, map_x, a, epilogue, split, s);
-    default: return launch_epi<128>(map_w, map_x, a, epilogue, split, s);
+    case 128: return launch_epi<128>(map_w, map_x, a, epilogue, split, s);
+    default: return launch_epi<256>(map_w, map_x, a, epilogue, split, s);
     }
 }
 

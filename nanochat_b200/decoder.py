@@ -108,8 +108,8 @@ class Decoder:
         self.cos, self.sin = ops.rotary_table(self.capacity, cfg.rope_theta, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.windows = cfg.windows or [0] * cfg.n_layers
-        self.use_fused = True  # decode steps of <= 128 rows run on this package's GEMM kernels when the shapes allow
-        self.use_stream_gemm = True  # ... of 17 to 128 rows on the tcgen05 stream_gemm (else cuBLAS)
+        self.use_fused = True  # decode steps of <= 256 rows run on this package's GEMM kernels when the shapes allow
+        self.use_stream_gemm = True  # ... of 17 to 256 rows on the tcgen05 stream_gemm (else cuBLAS)
         self.chunk_pages = 0  # attention chunk size of decode steps; 0: the library's choice for full-length slots
         self.prefetch_next = True  # stream_gemm also pulls the next GEMM's weights into L2 (d32-class step: -1.3 %)
         self._graphs: dict[int, tuple] = {}
@@ -210,7 +210,7 @@ class Decoder:
 
     def fused_supported(self, rows: int) -> bool:
         """Steps of at most 16 rows run on the decode_step GEMM (hidden sizes up to 2048, since its fused norm keeps
-        a row slice in registers, intermediate sizes up to 5120, all multiples of 256); steps of 17 to 128 rows on
+        a row slice in registers, intermediate sizes up to 5120, all multiples of 256); steps of 17 to 256 rows on
         the tcgen05 stream_gemm (every GEMM width a multiple of 128, every depth of 64). Both need the default
         residual mixing."""
         cfg = self.cfg
@@ -220,7 +220,7 @@ class Decoder:
             return (cfg.hidden % 256 == 0 and cfg.hidden <= 2048 and cfg.intermediate % 256 == 0
                     and cfg.intermediate <= 5120 and (cfg.n_heads * HEAD_DIM) % 256 == 0
                     and cfg.n_heads * HEAD_DIM <= 5120 and cfg.vocab % 8 == 0)
-        return (rows <= 128 and self.use_stream_gemm
+        return (rows <= 256 and self.use_stream_gemm
                 and all(n % 128 == 0 for n in (cfg.hidden, cfg.intermediate, cfg.qkv_width, cfg.vocab))
                 and all(k % 64 == 0 for k in (cfg.hidden, cfg.intermediate)))
 
@@ -235,7 +235,7 @@ class Decoder:
 
     def fused_step(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int, buf: dict[str, Tensor],
                    choose: bool = True) -> Tensor:
-        """One step for rows <= 128 on this package's kernels (GEMMs: decode_step's for rows <= 16, stream_gemm above): fp32 logits in buf["logits"]; with `choose`, tokens
+        """One step for rows <= 256 on this package's kernels (GEMMs: decode_step's for rows <= 16, stream_gemm above): fp32 logits in buf["logits"]; with `choose`, tokens
         become the greedy choices and pos advances by one. 6 launches per layer: qkv GEMM (norm fused), split
         attention (append fused), merge, o GEMM + residual, up GEMM (norm fused) + relu^2, down GEMM + residual."""
         cfg, lib, s = self.cfg, cuda_library("decode_step"), stream()

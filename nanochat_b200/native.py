@@ -56,7 +56,7 @@ SIGNATURES = {
         "greedy_choice": ([c_ptr] * 3 + [c_int] * 2 + [c_ptr, c_int, c_ptr], c_int),
     },
     "stream_gemm": {
-        "stream_gemm_split": ([c_int, c_int], c_int),
+        "stream_gemm_split": ([c_int, c_int, c_int], c_int),
         "stream_gemm": ([c_ptr] * 4 + [c_int] * 6 + [c_ptr, c_ll, c_ptr, c_ptr], c_int),
     },
 }

@@ -123,16 +123,18 @@ def test_chunk_choice_is_positive_and_bounded():
 def test_stream_gemm_validates_and_chooses_its_split_on_the_host():
     lib = native.cuda_library("stream_gemm")
     p, nul = ctypes.c_void_p(4096), ctypes.c_void_p(None)
-    assert lib.stream_gemm(p, p, nul, p, 129, 128, 256, 0, 0, 0, nul, 0, nul, nul) == 1   # more than 128 rows
+    assert lib.stream_gemm(p, p, nul, p, 257, 128, 256, 0, 0, 0, nul, 0, nul, nul) == 1   # more than 256 rows
     assert lib.stream_gemm(p, p, nul, p, 4, 100, 256, 0, 0, 0, nul, 0, nul, nul) == 1     # N not a multiple of 128
     assert lib.stream_gemm(p, p, nul, p, 4, 128, 100, 0, 0, 0, nul, 0, nul, nul) == 1     # K not a multiple of 64
     assert lib.stream_gemm(p, p, nul, p, 4, 128, 256, 0, 1, 0, nul, 0, nul, nul) == 1     # residual epilogue, no residual
     assert lib.stream_gemm(ctypes.c_void_p(4100), p, nul, p, 4, 128, 256, 0, 0, 0, nul, 0, nul, nul) == 2  # misaligned
     assert lib.stream_gemm(p, p, nul, p, 0, 128, 256, 0, 0, 0, nul, 0, nul, nul) == 0     # nothing to do
     # one wave of at most 296 blocks, powers of two, at least two k-blocks per block
-    assert [lib.stream_gemm_split(n, k) for n, k in ((2048, 2048), (8192, 2048), (65536, 2048), (3072, 2048),
-                                                    (5120, 1280), (1280, 5120), (128, 128), (100, 2048))] \
+    assert [lib.stream_gemm_split(32, n, k) for n, k in ((2048, 2048), (8192, 2048), (65536, 2048), (3072, 2048),
+                                                        (5120, 1280), (1280, 5120), (128, 128), (100, 2048))] \
         == [8, 4, 1, 8, 4, 8, 1, 0]
+    # blocks for more than 128 rows take an SM each: half as many fit
+    assert [lib.stream_gemm_split(256, n, k) for n, k in ((2048, 2048), (8192, 2048), (3072, 2048))] == [8, 2, 4]
 
 
 def test_planned_chunk_follows_the_block_fill_model():

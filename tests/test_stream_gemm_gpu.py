@@ -1,4 +1,4 @@
-"""stream_gemm (tcgen05 weight-streaming GEMM for up to 128 rows, K split over a cluster) through the C ABI against
+"""stream_gemm (tcgen05 weight-streaming GEMM for up to 256 rows, K split over a cluster) through the C ABI against
 a plain PyTorch fp32 reference of the same operation."""
 
 import pytest
@@ -46,7 +46,7 @@ def check(got, want):
     assert err.mean() <= 2e-4 * scale
 
 
-@pytest.mark.parametrize("rows", [1, 17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("rows", [1, 17, 32, 33, 64, 100, 128, 129, 256])
 @pytest.mark.parametrize("N,K,norm", [(3072, 2048, 1), (2048, 2048, 0), (8192, 2048, 1), (2048, 8192, 0), (128, 64, 1),
                                       (1280, 5120, 0), (3840, 1280, 1), (256, 192, 0)])
 @pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
@@ -106,11 +106,11 @@ def test_stream_gemm_rejects_unsupported_shapes():
     lib = cuda_library("stream_gemm")
     x = torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda")
     p = pointer(x)
-    assert lib.stream_gemm(p, p, None, p, 129, 128, 256, 0, 0, 0, None, 0, None, None) == 1   # more than 128 rows
+    assert lib.stream_gemm(p, p, None, p, 257, 128, 256, 0, 0, 0, None, 0, None, None) == 1   # more than 256 rows
     assert lib.stream_gemm(p, p, None, p, 4, 100, 256, 0, 0, 0, None, 0, None, None) == 1     # N not a multiple of 128
     assert lib.stream_gemm(p, p, None, p, 4, 128, 100, 0, 0, 0, None, 0, None, None) == 1     # K not a multiple of 64
     assert lib.stream_gemm(p, p, None, p, 4, 128, 128, 0, 0, 3, None, 0, None, None) == 1     # more blocks than k-blocks
     assert lib.stream_gemm(p, p, None, p, 4, 128, 256, 0, 1, 0, None, 0, None, None) == 1     # residual epilogue, no residual
     assert lib.stream_gemm(p, p, None, p, 0, 128, 256, 0, 0, 0, None, 0, None, None) == 0     # nothing to do
-    assert lib.stream_gemm_split(2048, 2048) == 8 and lib.stream_gemm_split(65536, 2048) == 1
-    assert lib.stream_gemm_split(100, 2048) == 0
+    assert lib.stream_gemm_split(32, 2048, 2048) == 8 and lib.stream_gemm_split(32, 65536, 2048) == 1
+    assert lib.stream_gemm_split(32, 100, 2048) == 0
