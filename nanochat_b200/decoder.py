@@ -108,8 +108,8 @@ class Decoder:
         self.cos, self.sin = ops.rotary_table(self.capacity, cfg.rope_theta, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.windows = cfg.windows or [0] * cfg.n_layers
-        self.use_fused = True  # decode steps of <= 256 rows run on this package's GEMM kernels when the shapes allow
-        self.use_stream_gemm = True  # ... of 17 to 256 rows on the tcgen05 stream_gemm (else cuBLAS)
+        self.use_fused = True  # decode steps of <= 64 rows run on this package's GEMM kernels when the shapes allow
+        self.use_stream_gemm = True  # ... of 17 to 64 rows on the tcgen05 stream_gemm (else cuBLAS)
         self.chunk_pages = 0  # attention chunk size of decode steps; 0: the library's choice for full-length slots
         self.prefetch_next = True  # stream_gemm also pulls the next GEMM's weights into L2 (d32-class step: -1.3 %)
         self._graphs: dict[int, tuple] = {}
@@ -210,7 +210,7 @@ class Decoder:
 
     def fused_supported(self, rows: int) -> bool:
         """Steps of at most 16 rows run on the decode_step GEMM (hidden sizes up to 2048, since its fused norm keeps
-        a row slice in registers, intermediate sizes up to 5120, all multiples of 256); steps of 17 to 256 rows on
+        a row slice in registers, intermediate sizes up to 5120, all multiples of 256); steps of 17 to 64 rows on
         the tcgen05 stream_gemm (every GEMM width a multiple of 128, every depth of 64). Both need the default
         residual mixing."""
         cfg = self.cfg
@@ -220,7 +220,7 @@ class Decoder:
             return (cfg.hidden % 256 == 0 and cfg.hidden <= 2048 and cfg.intermediate % 256 == 0
                     and cfg.intermediate <= 5120 and (cfg.n_heads * HEAD_DIM) % 256 == 0
                     and cfg.n_heads * HEAD_DIM <= 5120 and cfg.vocab % 8 == 0)
-        return (rows <= 256 and self.use_stream_gemm
+        return (rows <= 64 and self.use_stream_gemm  # the kernel takes 256 rows; cuBLAS is faster above about 64
                 and all(n % 128 == 0 for n in (cfg.hidden, cfg.intermediate, cfg.qkv_width, cfg.vocab))
                 and all(k % 64 == 0 for k in (cfg.hidden, cfg.intermediate)))
 

@@ -171,9 +171,9 @@ def test_sampled_generation_is_reproducible_and_follows_the_choice_rule():
 
 
 @torch.no_grad()
-@pytest.mark.parametrize("rows", [24, 40, 128, 200])
+@pytest.mark.parametrize("rows", [24, 40, 64])
 def test_wide_fused_step_on_stream_gemm_matches_the_cublas_path(rows):
-    """Steps of 17 to 256 rows: this package's tcgen05 GEMMs (fused norm, residual and relu^2 epilogues) against the
+    """Steps of 17 to 64 rows: this package's tcgen05 GEMMs (fused norm, residual and relu^2 epilogues) against the
     same steps with cuBLAS GEMMs and separate norm kernels, three teacher-forced positions per slot."""
     cfg = DecoderConfig(n_layers=3, hidden=512, n_heads=4, n_kv_heads=2, intermediate=1024, vocab=384, max_len=64)
     w = DecoderWeights.random_init(cfg, seed=21, device="cuda", std=0.05)
