@@ -208,21 +208,27 @@ class Decoder:
 
     # ---- the same pass for at most 16 rows with this package's own GEMM kernels --------------------------------
 
-    def fused_supported(self, rows: int) -> bool:
-        """Steps of at most 16 rows run on the decode_step GEMM (hidden sizes up to 2048, since its fused norm keeps
-        a row slice in registers, intermediate sizes up to 5120, all multiples of 256); steps of 17 to 64 rows on
-        the tcgen05 stream_gemm (every GEMM width a multiple of 128, every depth of 64). Both need the default
-        residual mixing."""
+    def gemm_kernel(self, rows: int) -> str | None:
+        """Which of this package's GEMM kernels runs a decode step of `rows` rows: "skinny" (decode_step.cu) for at
+        most 16 rows when the model fits it (hidden sizes up to 2048, since its fused norm keeps a row slice in
+        registers, intermediate sizes up to 5120, all multiples of 256), else "stream" (the tcgen05 stream_gemm) up to
+        64 rows when every GEMM width is a multiple of 128 and every depth of 64; None: cuBLAS and separate norm
+        kernels. Both need the default residual mixing."""
         cfg = self.cfg
         if not all(l.resid_lambda == 1.0 and l.x0_lambda == 0.0 for l in self.w.layers):
-            return False
-        if rows <= 16:
-            return (cfg.hidden % 256 == 0 and cfg.hidden <= 2048 and cfg.intermediate % 256 == 0
-                    and cfg.intermediate <= 5120 and (cfg.n_heads * HEAD_DIM) % 256 == 0
-                    and cfg.n_heads * HEAD_DIM <= 5120 and cfg.vocab % 8 == 0)
-        return (rows <= 64 and self.use_stream_gemm  # the kernel takes 256 rows; cuBLAS is faster above about 64
+            return None
+        if (rows <= 16 and cfg.hidden % 256 == 0 and cfg.hidden <= 2048 and cfg.intermediate % 256 == 0
+                and cfg.intermediate <= 5120 and (cfg.n_heads * HEAD_DIM) % 256 == 0
+                and cfg.n_heads * HEAD_DIM <= 5120 and cfg.vocab % 8 == 0):
+            return "skinny"
+        if (rows <= 64 and self.use_stream_gemm  # the kernel takes 256 rows; cuBLAS is faster above about 64
                 and all(n % 128 == 0 for n in (cfg.hidden, cfg.intermediate, cfg.qkv_width, cfg.vocab))
-                and all(k % 64 == 0 for k in (cfg.hidden, cfg.intermediate)))
+                and all(k % 64 == 0 for k in (cfg.hidden, cfg.intermediate, cfg.n_heads * HEAD_DIM))):
+            return "stream"
+        return None
+
+    def fused_supported(self, rows: int) -> bool:
+        return self.gemm_kernel(rows) is not None
 
     def fused_buffers(self, rows: int) -> dict[str, Tensor]:
         cfg, dev, bf = self.cfg, self.device, torch.bfloat16
@@ -235,7 +241,7 @@ class Decoder:
 
     def fused_step(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int, buf: dict[str, Tensor],
                    choose: bool = True) -> Tensor:
-        """One step for rows <= 256 on this package's kernels (GEMMs: decode_step's for rows <= 16, stream_gemm above): fp32 logits in buf["logits"]; with `choose`, tokens
+        """One step on this package's kernels (GEMMs: see gemm_kernel): fp32 logits in buf["logits"]; with `choose`, tokens
         become the greedy choices and pos advances by one. 6 launches per layer: qkv GEMM (norm fused), split
         attention (append fused), merge, o GEMM + residual, up GEMM (norm fused) + relu^2, down GEMM + residual."""
         cfg, lib, s = self.cfg, cuda_library("decode_step"), stream()
@@ -243,7 +249,7 @@ class Decoder:
         workspace = self._workspace(rows, max_kv_len)
         h, qkv, att, u = buf["h"], buf["qkv"], buf["att"], buf["u"]
 
-        wide = cuda_library("stream_gemm") if rows > 16 else None
+        wide = cuda_library("stream_gemm") if self.gemm_kernel(rows) == "stream" else None
 
         def gemm(x, w, resid, y, n, k, norm, epilogue, then=None):
             """`then`: the weights of the next GEMM on the stream, prefetched into L2 meanwhile (stream_gemm only)."""

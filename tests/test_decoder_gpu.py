@@ -171,14 +171,15 @@ def test_sampled_generation_is_reproducible_and_follows_the_choice_rule():
 
 
 @torch.no_grad()
-@pytest.mark.parametrize("rows", [24, 40, 64])
-def test_wide_fused_step_on_stream_gemm_matches_the_cublas_path(rows):
-    """Steps of 17 to 64 rows: this package's tcgen05 GEMMs (fused norm, residual and relu^2 epilogues) against the
+@pytest.mark.parametrize("rows,intermediate", [(24, 1024), (40, 1024), (64, 1024), (8, 5248)])
+def test_wide_fused_step_on_stream_gemm_matches_the_cublas_path(rows, intermediate):
+    """Steps of 17 to 64 rows (and smaller ones of models the skinny kernel does not take): this package's tcgen05 GEMMs (fused norm, residual and relu^2 epilogues) against the
     same steps with cuBLAS GEMMs and separate norm kernels, three teacher-forced positions per slot."""
-    cfg = DecoderConfig(n_layers=3, hidden=512, n_heads=4, n_kv_heads=2, intermediate=1024, vocab=384, max_len=64)
-    w = DecoderWeights.random_init(cfg, seed=21, device="cuda", std=0.05)
+    cfg = DecoderConfig(n_layers=3, hidden=512, n_heads=4, n_kv_heads=2, intermediate=intermediate, vocab=384,
+                        max_len=64)
+    w = DecoderWeights.random_init(cfg, seed=21, device="cuda", std=0.05 if intermediate == 1024 else 0.02)
     ours, ref = Decoder(cfg, w, rows), Decoder(cfg, w, rows)
-    assert ours.fused_supported(rows)
+    assert ours.gemm_kernel(rows) == "stream"  # also for few rows when the MLP is too deep for the skinny kernel
     ref.use_stream_gemm = False
     assert not ref.fused_supported(rows)
     gen = torch.Generator().manual_seed(rows)
