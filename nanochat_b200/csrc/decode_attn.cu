@@ -811,22 +811,34 @@ static int plan_chunk_pages(const int *lens, int B, int Hkv, int max_kv_len, int
     int best = WARPS;
     double best_cost = 0.;
     std::vector<double> heap;
+    /* launches of more than 32,768 blocks are many waves deep: whole waves of the mean sequence stand in for the
+     * dispatch simulation there, which keeps the planner itself under a few milliseconds */
+    const bool simulate = (long long)B * Hkv * ((max_pages + WARPS - 1) / WARPS) <= 32768;
+    long long total_pages = 0;
+    for (int b = 0; b < B; b++) total_pages += pages[b];
+    const int mean_pages = (int)((total_pages + B - 1) / B);
     for (int c = WARPS; c <= 32; c++) {
         const int max_chunks = (max_pages + c - 1) / c;
-        if ((long long)B * Hkv * max_chunks > (1ll << 18)) continue; /* keep the model itself cheap */
-        heap.assign(slots, 0.);
         double end = 0.;
-        for (int b = 0; b < B; b++) {
-            const int n = (pages[b] + c - 1) / c, each = n ? (pages[b] + n - 1) / n : 0;
-            for (int h = 0; h < Hkv; h++)
-                for (int i = 0; i < max_chunks; i++) {
-                    const int first = i * each, p = i < n ? (pages[b] - first < each ? pages[b] - first : each) : 0;
-                    std::pop_heap(heap.begin(), heap.end(), std::greater<double>());
-                    double &t = heap.back();
-                    t += p > 0 ? BLOCK_US + PAGE_US * ((p + WARPS - 1) / WARPS) : IDLE_US;
-                    if (t > end) end = t;
-                    std::push_heap(heap.begin(), heap.end(), std::greater<double>());
-                }
+        if (!simulate) {
+            const int n = (mean_pages + c - 1) / c, each = n ? (mean_pages + n - 1) / n : 0;
+            const long long busy = (long long)B * Hkv * n, idle = (long long)B * Hkv * (max_chunks - n);
+            end = (double)((busy + slots - 1) / slots) * (BLOCK_US + PAGE_US * ((each + WARPS - 1) / WARPS)) +
+                  (double)idle / slots * IDLE_US;
+        } else {
+            heap.assign(slots, 0.);
+            for (int b = 0; b < B; b++) {
+                const int n = (pages[b] + c - 1) / c, each = n ? (pages[b] + n - 1) / n : 0;
+                for (int h = 0; h < Hkv; h++)
+                    for (int i = 0; i < max_chunks; i++) {
+                        const int first = i * each, p = i < n ? (pages[b] - first < each ? pages[b] - first : each) : 0;
+                        std::pop_heap(heap.begin(), heap.end(), std::greater<double>());
+                        double &t = heap.back();
+                        t += p > 0 ? BLOCK_US + PAGE_US * ((p + WARPS - 1) / WARPS) : IDLE_US;
+                        if (t > end) end = t;
+                        std::push_heap(heap.begin(), heap.end(), std::greater<double>());
+                    }
+            }
         }
         if (c == WARPS || end <= best_cost) best = c, best_cost = end;
     }
