@@ -21,6 +21,11 @@ One JSON line on rank 0. A step is one decode-attention pass (split-KV kernel + 
   cpu_baseline  the reference's CPU attention (a torch restatement of inference/modeling_nanochat.py:48-56, see
             oracle/attention.py) on a bounded sample of the same workload, all host threads.
 
+  longctx, decoder, decoder_d32  extras in the same line: the long-context configuration (KV split by length over
+            the ranks), greedy decode tokens/s of the random-init d20 model (batch 8 per GPU, 512-token prompts; at
+            N = 1 with the CPU port of the reference's decoder timed beside it, `decoder.cpu_baseline`) and of the
+            d32-class model (batch 32 per GPU, ragged contexts).
+
 --impl reference times that CPU restatement alone, on the same config and metric.
 Data is synthetic: q ~ N(0,1) bf16; K, V ~ N(0,1) quantised per (token, head) with scale = amax / 448."""
 
@@ -235,6 +240,42 @@ def bench_decoder(rank: int, world: int, device, new_tokens: int, profile: bool 
     return {"workload": "random-init d20, batch 8 per GPU, prompt 512, greedy, fp8 KV cache", "new_tokens": new_tokens,
             "tokens_per_s": 8 * world * new_tokens / decode_s, "ms_per_step": decode_s / new_tokens * 1e3,
             "prefill_s": prefill_s, "scaling": "weak (replicas)"}
+
+
+def bench_decoder_cpu(steps: int) -> dict:
+    """The CPU port of the reference's decoder (oracle/decoder.py: the exported model's operators on torch CPU
+    bf16, op for op) on the d20 workload, all host threads: batch 8, 512 positions already in the caches (synthetic
+    fp8 contents), `steps` greedy steps timed after one warm-up step."""
+    import numpy as np
+
+    from oracle.decoder import OracleDecoder
+
+    threads = len(os.sched_getaffinity(0))
+    torch.set_num_threads(threads)
+    cfg = {"n_layers": 20, "hidden": 1280, "n_heads": 10, "n_kv_heads": 10, "intermediate": 5120, "vocab": 65536,
+           "rope_theta": 10000.0, "max_len": 512 + steps + 2}
+    gen = torch.Generator().manual_seed(0)
+    rnd = lambda *shape: (torch.randn(*shape, generator=gen) * 0.02).bfloat16()
+    C, F_, W = cfg["hidden"], cfg["intermediate"], (cfg["n_heads"] + 2 * cfg["n_kv_heads"]) * D
+    weights = {"embed": rnd(cfg["vocab"], C), "lm_head": rnd(cfg["vocab"], C),
+               "layers": [{"wqkv": rnd(W, C), "wo": rnd(C, cfg["n_heads"] * D), "wup": rnd(F_, C), "wdown": rnd(C, F_),
+                           "q_gain": torch.ones(D), "k_gain": torch.ones(D)} for _ in range(cfg["n_layers"])]}
+    oracle = OracleDecoder(cfg, weights, 8)
+    rng = np.random.default_rng(0)
+    for layer in oracle.cache:
+        for seq in layer:
+            for key in ("k", "v"):
+                seq[key + "_bytes"] = rng.integers(0, 120, (cfg["n_kv_heads"], 512, D), dtype=np.uint8)
+                seq[key + "_scale"] = rng.uniform(1e-3, 1e-2, (cfg["n_kv_heads"], 512)).astype(np.float32)
+    tokens = torch.randint(0, cfg["vocab"], (8,), generator=gen)
+    seqs = list(range(8))
+    tokens = oracle.step(tokens, seqs).argmax(-1)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tokens = oracle.step(tokens, seqs).argmax(-1)
+    dt = time.perf_counter() - t0
+    return {"tokens_per_s": 8 * steps / dt, "cores": threads, "kind": "port",
+            "sample": f"{steps} greedy steps of batch 8 at context 512 (one warm-up step before)"}
 
 
 def bench_decoder_d32(rank: int, world: int, device, new_tokens: int) -> dict:
@@ -485,6 +526,8 @@ def main() -> None:
             line["decoder_d32"] = decoder_d32
         if world == 1 and args.cpu_seconds > 0:
             line["cpu_baseline"] = time_cpu_reference(lens[:args.cpu_sample], args.cpu_seconds)
+            if decoder:
+                decoder["cpu_baseline"] = bench_decoder_cpu(3)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
