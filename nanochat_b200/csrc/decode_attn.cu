@@ -98,12 +98,25 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) 
     }
     return false;
 }
-/* One page from global to shared memory; the barrier receives the byte count when the copy has landed. */
+/* One page from global to shared memory; the barrier receives the byte count when the copy has landed. A page is
+ * read once per step, so with NCB_KV_EVICT_FIRST it is marked evict-first in L2: what else lives there across the
+ * launch (weights the neighbouring GEMMs prefetched, the split states) is not pushed out by the cache stream. */
+#ifndef NCB_KV_EVICT_FIRST
+#define NCB_KV_EVICT_FIRST 1
+#endif
 static __device__ __forceinline__ void page_load(uint32_t dst, const void *src, uint32_t bar) {
     mbar_expect_tx(bar, PAGE_BYTES);
+#if NCB_KV_EVICT_FIRST
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"((uint32_t)PAGE_BYTES), "r"(bar), "l"(policy)
+                 : "memory");
+#else
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"((uint32_t)PAGE_BYTES), "r"(bar)
                  : "memory");
+#endif
 }
 static __device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3,
                                                    uint32_t addr) {
