@@ -99,11 +99,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (clock64() - start > WAIT_CYCLES) return false;
     }
 }
-/* One box of a 2-d tensor map into shared memory; (c0, c1) = (k, row) element coordinates, c0 a multiple of 64. */
-__device__ __forceinline__ void tma_load(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+/* One box of a 2-d tensor map into shared memory; (c0, c1) = (k, row) element coordinates, c0 a multiple of 64.
+ * `policy` is an L2 eviction policy: weights are read once (evict first), activations by every block (evict last). */
+__device__ __forceinline__ void tma_load(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+                 "[%0], [%1, {%3, %4}], [%2], %5;"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
                  : "memory");
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
 }
 /* A contiguous run of global memory into L2; 16-byte aligned, a multiple of 16 bytes. */
 __device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
@@ -222,17 +234,18 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
     constexpr int KSUB = Sh::KSUB;
     const int nst = (nkb + KSUB - 1) / KSUB; /* stages of up to KSUB boxes; stage i holds boxes [i KSUB, ...) */
     auto boxes_of = [&](int i) { return nkb - i * KSUB < KSUB ? nkb - i * KSUB : KSUB; };
+    const uint64_t w_policy = policy_evict_first(), x_policy = policy_evict_last();
     auto load_w = [&](int i) {
         const int s = i % STAGES, n = boxes_of(i);
         mbar_expect_tx(full(s), n * Sh::BOX_BYTES);
         for (int b = 0; b < n; b++)
-            tma_load(ring + s * Sh::STAGE_BYTES + b * A_BOX_BYTES, &map_w, (kb0 + i * KSUB + b) * KBLK, tile * TILE_F, full(s));
+            tma_load(ring + s * Sh::STAGE_BYTES + b * A_BOX_BYTES, &map_w, (kb0 + i * KSUB + b) * KBLK, tile * TILE_F, full(s), w_policy);
     };
     auto load_x = [&](int i) {
         const int s = i % STAGES, n = boxes_of(i);
         for (int b = 0; b < n; b++)
             tma_load(ring + s * Sh::STAGE_BYTES + KSUB * A_BOX_BYTES + b * Sh::B_BOX_BYTES, &map_x,
-                     (kb0 + i * KSUB + b) * KBLK, 0, full(s));
+                     (kb0 + i * KSUB + b) * KBLK, 0, full(s), x_policy);
     };
     if (warp == 0) {
         if (lane == 0) { /* producer */
