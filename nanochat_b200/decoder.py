@@ -281,7 +281,7 @@ class Decoder:
     # ---- prefill ----------------------------------------------------------------------------------------------
 
     @torch.no_grad()
-    def prefill(self, prompts: list[list[int]], slots: list[int], rows_per_pass: int = 1024) -> None:
+    def prefill(self, prompts: list[list[int]], slots: list[int], rows_per_pass: int = 4096) -> None:
         """Cache positions 0 .. len - 2 of every prompt (its last token is the first decode input). Sequences are
         processed in passes of at most rows_per_pass rows; a pass holds whole position ranges in order, so every row
         finds the earlier positions of its sequence either in the cache or earlier in its own pass."""
