@@ -34,6 +34,8 @@
  * consuming and falls through to the block's final barriers.
  */
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <functional>
 #include <mutex>
 #include <unordered_map>
@@ -741,6 +743,9 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
         if (prepare<2, true>() != cudaSuccess) return NCB_ERR_LAUNCH;
         rc = cudaLaunchKernelEx(&config, k_decode_attn<2, true>, a);
     }
+    if (rc != cudaSuccess && getenv("NCB_DEBUG"))
+        fprintf(stderr, "k_decode_attn launch (grid %d x %d x %d, chunk %d): %s\n", max_chunks, Hkv,
+                group_start ? n_groups : B, chunk_pages, cudaGetErrorString(rc));
     return rc == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 

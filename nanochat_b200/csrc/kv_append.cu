@@ -5,15 +5,17 @@
  *
  * Work item = one head row of 128 values (a q, k or v head of one token), handled by 8 lanes; lane t owns dims
  * 8t..8t+7 and their rotation partners 64+8t..64+8t+7, the ownership of qk_row.cuh:11-12,44-50. A 128-thread block
- * holds 16 items. The kernel is bound by launch latency and a few KB of traffic per token, so it is written for
- * exactness: every fp32 operation is an explicit round-to-nearest intrinsic in the order of
+ * holds the same head row of 16 consecutive tokens, so that a prefill pass (runs of consecutive positions of one
+ * slot) can store its transposed V bytes as 16-byte chunks. At decode sizes the kernel is bound by launch latency
+ * and a few KB of traffic per token; it is written for exactness: every fp32 operation is an explicit round-to-nearest intrinsic in the order of
  * oracle/kv_append_oracle.c (no FMA contraction, sqrt + divide instead of rsqrtf), which makes q bits, cache
  * bytes and scales exact functions of the inputs.
  */
 #include "kv_row.cuh"
 
 constexpr int BLOCK = 128;
-constexpr int ITEMS_PER_BLOCK = BLOCK / LANES;
+constexpr int ROWS_PER_BLOCK = BLOCK / LANES; /* 16: one run of V positions that share 16-byte chunks */
+static_assert(ROWS_PER_BLOCK == 16 && BLOCK == HEAD_DIM, "a V run is 16 positions and the block has a thread per dim");
 
 struct AppendArgs {
     const bf16 *qkv;
@@ -26,22 +28,35 @@ struct AppendArgs {
     int *status;
 };
 
+/* Block (x, y) = rows 16 x .. 16 x + 15 of head row y (q heads, then k heads, then v heads); 8 lanes per row. */
 __global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
     /* launched with programmatic stream serialisation: wait for the kernel that produced qkv and pos, then let the
      * next kernel's launch overlap this one (it waits the same way before it reads the cache or q) */
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int items = a.Hq + 2 * a.Hkv;
-    const long long item = (long long)blockIdx.x * ITEMS_PER_BLOCK + threadIdx.x / LANES;
-    if (item >= a.rows * items) return; /* whole 8-lane groups leave together */
-    const long long row = item / items;
-    const int which = (int)(item % items), t = threadIdx.x % LANES, o = t * VEC;
-    const int p = a.pos[row];
-    const int slot = a.slot_map ? a.slot_map[row] : (int)row;
-    if (p < 0 || p >= a.table_len || p >= a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots) {
-        if (t == 0) flag(a.status, NCB_DEV_BAD_POSITION);
-        return;
+    __shared__ __align__(16) uint8_t vt[HEAD_DIM][ROWS_PER_BLOCK]; /* a V run transposed: [dim][position] */
+    const int which = blockIdx.y, g = threadIdx.x / LANES, t = threadIdx.x % LANES, o = t * VEC;
+    const long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK, row = row0 + g;
+    const bool live = row < a.rows;
+    int p = 0, slot = 0;
+    bool valid = false;
+    if (live) {
+        p = a.pos[row];
+        slot = a.slot_map ? a.slot_map[row] : (int)row;
+        valid = !(p < 0 || p >= a.table_len || p >= a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots);
+        if (!valid && t == 0 && which == 0) flag(a.status, NCB_DEV_BAD_POSITION);
     }
+    const bool is_k = which >= a.Hq && which < a.Hq + a.Hkv, is_v = which >= a.Hq + a.Hkv;
+    /* A prefill pass appends runs of consecutive positions of one slot. When the block's 16 rows are such a run and
+     * start on a 16-position boundary, their V bytes of one dim are 16 contiguous bytes of the page: they are
+     * transposed through shared memory and stored as 128 16-byte chunks (2 KB contiguous) instead of 2,048 single
+     * bytes. Any other block (decode steps, ragged edges) stores byte by byte. Same bytes either way. */
+    bool run = false;
+    if (is_v) {
+        const int p0 = a.pos[row0], slot0 = a.slot_map ? a.slot_map[row0] : (int)row0;
+        run = __syncthreads_and(live && valid && slot == slot0 && p == p0 + g && p0 % ROWS_PER_BLOCK == 0);
+    }
+    if (!live || !valid) return; /* never part of a run: no barrier follows for this thread */
     const bf16 *x = a.qkv + row * a.qkv_row_stride + (size_t)which * HEAD_DIM;
     float x1[VEC], x2[VEC];
     load_bf16x8(x + o, x1);
@@ -54,7 +69,6 @@ __global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
         *reinterpret_cast<uint4 *>(q + HALF + o) = pack_bf16x8(x2);
         return;
     }
-    const bool is_k = which < a.Hq + a.Hkv;
     const int head = is_k ? which - a.Hq : which - a.Hq - a.Hkv;
     if (is_k) norm_rotate(x1, x2, a.k_gain, a.cs + tab, a.sn + tab, o);
     uint8_t b1[VEC], b2[VEC];
@@ -64,10 +78,21 @@ __global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
     if (is_k) {
         store_k_row(page, j, t, b1, b2);
         if (t == 0) reinterpret_cast<float *>(page + PAGE_KS)[j] = scale;
-    } else {
-        store_v_row(page, j, t, b1, b2);
-        if (t == 0) reinterpret_cast<float *>(page + PAGE_VS)[j] = scale;
+        return;
     }
+    if (t == 0) reinterpret_cast<float *>(page + PAGE_VS)[j] = scale;
+    if (!run) {
+        store_v_row(page, j, t, b1, b2);
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; i++) {
+        vt[o + i][g] = b1[i];
+        vt[HALF + o + i][g] = b2[i];
+    }
+    __syncthreads(); /* every thread of the block is in the run */
+    const int d = threadIdx.x, j0 = j - g; /* the run's first in-page position; thread = dim */
+    *reinterpret_cast<uint4 *>(page + page_v_byte(j0, d)) = *reinterpret_cast<const uint4 *>(vt[d]);
 }
 
 extern "C" {
@@ -104,15 +129,14 @@ int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const
     const uintptr_t all = (uintptr_t)qkv | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)cos | (uintptr_t)sin |
                           (uintptr_t)q_out | (uintptr_t)kv_cache;
     if (all % 16 != 0 || qkv_row_stride % 8 != 0) return NCB_ERR_ALIGN;
-    const long long items = rows * (Hq + 2 * Hkv);
-    const long long blocks = (items + ITEMS_PER_BLOCK - 1) / ITEMS_PER_BLOCK;
-    if (blocks > 0x7fffffffLL) return NCB_ERR_ARG;
+    const long long blocks = (rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
+    if (blocks > 0x7fffffffLL || Hq + 2 * Hkv > 65535) return NCB_ERR_ARG;
     AppendArgs a = {(const bf16 *)qkv, (const float *)q_gain, (const float *)k_gain, (const float *)cos,
                     (const float *)sin, (const int32_t *)pos, (const int32_t *)slot_map, (bf16 *)q_out,
                     (uint8_t *)kv_cache, rows, qkv_row_stride, Hq, Hkv, table_len, n_slots, pages_per_slot,
                     (int *)status};
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)blocks);
+    config.gridDim = dim3((unsigned)blocks, (unsigned)(Hq + 2 * Hkv));
     config.blockDim = dim3(BLOCK);
     config.stream = (cudaStream_t)stream;
     cudaLaunchAttribute attribute[1];

@@ -20,6 +20,8 @@ Prefill runs prompt tokens as rows through the same kernels, every row attending
 (decode.cu:859-863,1041-1051; inference/decoder.py:211-222); the prompt's last token is the first decode step's
 input (decoder.py:196,207,215)."""
 
+import contextlib
+import gc
 from dataclasses import dataclass, field
 
 import torch
@@ -32,6 +34,21 @@ from .native import check, cuda_library, pointer, stream
 from .prompt_store import PromptStore
 
 EPS = 1.1920928955078125e-07  # FLT_EPSILON (reference model/ops/linear.py:20)
+
+
+@contextlib.contextmanager
+def no_collection():
+    """Python's cyclic garbage collector switched off for the duration of a stream capture: a collection that
+    happens to run inside the capture can finalise an old graph or memory pool, whose cudaFree invalidates the
+    capture ("operation failed due to a previous error during capture" at the next launch)."""
+    enabled = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if enabled:
+            gc.enable()
 
 
 @dataclass
@@ -345,7 +362,7 @@ class Decoder:
             tokens.zero_()
             side.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
+            with no_collection(), torch.cuda.graph(graph, stream=side):
                 body()
         self.chunk_pages = 0
         # the graph holds raw pointers: every tensor its kernels touch must stay alive as long as the graph does

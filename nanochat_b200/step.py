@@ -15,6 +15,7 @@ import torch
 from torch import Tensor
 
 from . import attention as ops
+from .decoder import no_collection
 from .kv_cache import HEAD_DIM, Fp8KVCache
 
 
@@ -66,7 +67,7 @@ class DecodeStep:
             self._enqueue()
             self.stream.synchronize()
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph, stream=self.stream):
+            with no_collection(), torch.cuda.graph(self.graph, stream=self.stream):
                 self._enqueue()
 
     def run(self) -> None:

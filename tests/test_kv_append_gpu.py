@@ -120,3 +120,21 @@ def test_native_error_on_bad_shapes():
     cos, sin = ncb.rotary_table(64, 1e4, device="cuda")
     with pytest.raises(ncb.NativeError):
         ncb.kv_append(qkv, ones, ones, cos, sin, torch.zeros(1, dtype=torch.int32, device="cuda"), cache, Hq=4)
+
+
+def test_prefill_runs_store_the_same_bytes_as_single_rows():
+    """Rows that form runs of consecutive positions of one slot (a prefill pass): blocks whose 16 rows are an aligned
+    run store V as 16-byte chunks, the ragged starts and ends and the slot changes byte by byte; every row must still
+    match the checker bit for bit, and nothing else in the cache may change."""
+    runs = [(0, 0, 100), (1, 5, 61), (2, 16, 48), (3, 63, 70), (1, 128, 145), (4, 32, 33)]  # (slot, first, end)
+    slots = [s for s, a, b in runs for _ in range(a, b)]
+    positions = [p for s, a, b in runs for p in range(a, b)]
+    cache, _ = run_case(seed=21, rows=len(slots), Hq=8, Hkv=2, max_len=192, n_slots=5, positions=positions,
+                        slots=slots)
+    host = ncb.Fp8KVCache(5, 2, 192, device="cpu", pages=cache.pages.cpu())
+    written = set(zip(slots, positions))
+    for slot in range(5):
+        k, ks, v, vs = host.read(slot, 192)
+        for p in range(192):
+            if (slot, p) not in written:
+                assert not k[:, p].any() and not v[:, p].any() and not ks[:, p].any() and not vs[:, p].any(), (slot, p)
