@@ -130,16 +130,20 @@ def prefill_groups(slots: list[int], positions: list[int], Hq: int, Hkv: int) ->
     """Group consecutive rows of a prefill pass for prefill_attention: a group is a run of rows of one slot with
     positions ascending by one, at most 8 / (Hq / Hkv) long. Returns (group_start with the end sentinel, span_lens:
     for every row the length pos + 1 of its group's last row)."""
-    limit = max(1, 8 // (Hq // Hkv))
-    starts, span = [0], [0] * len(slots)
-    for r in range(1, len(slots) + 1):
-        first = starts[-1]
-        if r == len(slots) or r - first == limit or slots[r] != slots[first] or positions[r] != positions[r - 1] + 1:
-            for i in range(first, r):
-                span[i] = positions[r - 1] + 1
-            if r < len(slots):
-                starts.append(r)
-    return starts + [len(slots)], span
+    import numpy as np
+
+    limit, n = max(1, 8 // (Hq // Hkv)), len(slots)
+    if n == 0:
+        return [0], []
+    s, p = np.asarray(slots, dtype=np.int64), np.asarray(positions, dtype=np.int64)
+    run_start = np.ones(n, dtype=bool)  # a run: one slot, positions ascending by one
+    run_start[1:] = (s[1:] != s[:-1]) | (p[1:] != p[:-1] + 1)
+    first_of_run = np.flatnonzero(run_start)[np.cumsum(run_start) - 1]
+    group_start = (np.arange(n) - first_of_run) % limit == 0  # runs are cut into groups of `limit` rows
+    starts = np.flatnonzero(group_start)
+    ends = np.append(starts[1:], n)
+    span = p[ends[np.cumsum(group_start) - 1] - 1] + 1
+    return starts.tolist() + [n], span.tolist()
 
 
 class PrefillPlan:

@@ -106,3 +106,34 @@ def test_gather_and_merge_over_two_gloo_ranks():
     result = ctx.Queue()
     mp.spawn(worker, args=(2, port, result), nprocs=2, join=True)
     assert result.get(timeout=10) < 4e-3  # only the bf16 rounding of the reference output remains
+
+
+def test_prefill_groups_cut_runs_into_groups_that_share_page_loads():
+    """prefill_groups against a row-by-row restatement of its rule on random passes."""
+    import random
+
+    from nanochat_b200.attention import prefill_groups
+
+    def by_rows(slots, positions, limit):
+        starts, span = [0], [0] * len(slots)
+        for r in range(1, len(slots) + 1):
+            first = starts[-1]
+            if (r == len(slots) or r - first == limit or slots[r] != slots[first]
+                    or positions[r] != positions[r - 1] + 1):
+                for i in range(first, r):
+                    span[i] = positions[r - 1] + 1
+                if r < len(slots):
+                    starts.append(r)
+        return starts + [len(slots)], span
+
+    rng = random.Random(0)
+    for Hq, Hkv in ((8, 8), (8, 2), (8, 1), (6, 2)):
+        for _ in range(20):
+            slots, positions = [], []
+            for _ in range(rng.randint(1, 6)):
+                slot, first, count = rng.randint(0, 3), rng.randint(0, 40), rng.randint(1, 30)
+                slots += [slot] * count
+                positions += list(range(first, first + count))
+            assert prefill_groups(slots, positions, Hq, Hkv) == by_rows(slots, positions, max(1, 8 // (Hq // Hkv)))
+    assert prefill_groups([], [], 8, 8) == ([0], [])
+    assert prefill_groups([3], [7], 8, 2) == ([0, 1], [8])
