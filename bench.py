@@ -278,7 +278,7 @@ def bench_decoder_cpu(steps: int) -> dict:
             "sample": f"{steps} greedy steps of batch 8 at context 512 (one warm-up step before)"}
 
 
-def bench_decoder_d32(rank: int, world: int, device, new_tokens: int) -> dict:
+def bench_decoder_d32(rank: int, world: int, device, new_tokens: int, profile: bool = False) -> dict:
     """Batched decode of a random-init d32-class model (32 layers, d_model 2048, 16 query / 4 KV heads, relu^2 MLP of
     8192, vocab 65536): batch 32 per GPU (256 over 8 GPUs), ragged contexts uniform in [256, 8192] already in the fp8
     caches (synthetic quantised K/V, the same pages in every layer), `new_tokens` greedy tokens. Every step appends
@@ -308,7 +308,13 @@ def bench_decoder_d32(rank: int, world: int, device, new_tokens: int) -> dict:
     del filled
     first = torch.randint(0, 65536, (B,), generator=gen).tolist()
     decoder.decode_from(first, ctx, 4)  # warm-up: graph capture, cuBLAS heuristics
+    if profile:  # the same graph must not be captured inside the range: lengths half way decide its chunk size
+        decoder.decode_from(first, ctx, new_tokens)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
     _, seconds = decoder.decode_from(first, ctx, new_tokens)
+    if profile:
+        torch.cuda.profiler.stop()
     stats = torch.tensor([seconds], device=device)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
@@ -374,7 +380,7 @@ def main() -> None:
     ap.add_argument("--chunk-pages", type=int, default=0)
     ap.add_argument("--decoder", type=int, default=1, help="also time end-to-end greedy decoding of d20 (0: skip)")
     ap.add_argument("--decoder-tokens", type=int, default=256, help="tokens generated per sequence in that run")
-    ap.add_argument("--profile-range", default="attention", choices=["attention", "decoder"],
+    ap.add_argument("--profile-range", default="attention", choices=["attention", "decoder", "decoder_d32"],
                     help="which timed loops cudaProfilerStart/Stop bracket (for `ncu --profile-from-start off`)")
     ap.add_argument("--decoder-d32", type=int, default=1, help="also time batched decode of the d32-class model (0: skip)")
     ap.add_argument("--longctx", type=int, default=1, help="also time the KV-length-sharded long-context case (0: skip)")
@@ -491,7 +497,9 @@ def main() -> None:
     longctx = bench_longctx(rank, world, device, min(args.steps, 100), 5, timed) if args.longctx else None
     decoder = bench_decoder(rank, world, device, args.decoder_tokens, args.profile_range == "decoder") \
         if args.decoder else None
-    decoder_d32 = bench_decoder_d32(rank, world, device, 128) if args.decoder_d32 else None
+    d32_profiled = args.profile_range == "decoder_d32"  # two steps are enough for a launch list
+    decoder_d32 = bench_decoder_d32(rank, world, device, 2 if d32_profiled else 128, d32_profiled) \
+        if args.decoder_d32 else None
 
     if rank == 0:
         peak, peak_kind = peaks()
