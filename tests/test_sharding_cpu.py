@@ -137,3 +137,25 @@ def test_prefill_groups_cut_runs_into_groups_that_share_page_loads():
             assert prefill_groups(slots, positions, Hq, Hkv) == by_rows(slots, positions, max(1, 8 // (Hq // Hkv)))
     assert prefill_groups([], [], 8, 8) == ([0], [])
     assert prefill_groups([3], [7], 8, 2) == ([0, 1], [8])
+
+
+def test_no_collection_restores_the_collector():
+    import gc
+
+    from nanochat_b200.decoder import no_collection
+
+    assert gc.isenabled()
+    with no_collection():
+        assert not gc.isenabled()
+    assert gc.isenabled()
+    gc.disable()
+    try:
+        with no_collection():
+            assert not gc.isenabled()
+        assert not gc.isenabled()  # it was off before: it stays off
+    finally:
+        gc.enable()
+    with pytest.raises(RuntimeError):
+        with no_collection():
+            raise RuntimeError("capture failed")
+    assert gc.isenabled()
