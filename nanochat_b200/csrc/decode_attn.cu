@@ -574,6 +574,44 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
     }
 }
 
+/* The same merge with one WARP per row, for prefill passes: tens of thousands of rows with one or two states each,
+ * where a block per row spends its time starting blocks. Lane = four output dims; states are folded in index order
+ * (a different summation order than k_merge: equal up to rounding, not bit for bit). */
+__global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_rows(MergeArgs a) {
+    const long long row = (long long)blockIdx.x * MERGE_WARPS + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (row >= a.rows) return;
+    int n = 0;
+    {
+        const int b = (int)(row / a.Hq), len = a.lens[b] + a.len_add, slot = a.slot_map ? a.slot_map[b] : b;
+        if (!(len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots))
+            n = min(span_of(len, a.window, a.chunk_pages).n_chunks, a.max_chunks);
+    }
+    const float *st = a.parts + row * a.row_stride;
+    float top = -INFINITY, lsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+    for (int p = 0; p < n; p++) {
+        const float *s = st + p * a.part_stride;
+        const float mp = s[0], lp = s[1];
+        const float4 o = *reinterpret_cast<const float4 *>(s + 4 + 4 * lane);
+        const float next = fmaxf(top, mp);
+        const float c0 = top == -INFINITY ? 0.f : ex2(top - next), c1 = mp == -INFINITY ? 0.f : ex2(mp - next);
+        lsum = lsum * c0 + lp * c1;
+        acc.x = acc.x * c0 + o.x * c1, acc.y = acc.y * c0 + o.y * c1;
+        acc.z = acc.z * c0 + o.z * c1, acc.w = acc.w * c0 + o.w * c1;
+        top = next;
+    }
+    const bool any = lsum > 0.f;
+    const float x = any ? __fdiv_rn(acc.x, lsum) : 0.f, y = any ? __fdiv_rn(acc.y, lsum) : 0.f;
+    const float z = any ? __fdiv_rn(acc.z, lsum) : 0.f, w = any ? __fdiv_rn(acc.w, lsum) : 0.f;
+    uint2 u;
+    *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(x, y);
+    *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(z, w);
+    *reinterpret_cast<uint2 *>(a.out + row * HEAD_DIM + 4 * lane) = u;
+}
+
 /* ---- merge over peer memory ---------------------------------------------------------------------------------- */
 
 constexpr int MAX_PEERS = 8;
@@ -749,9 +787,9 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     return rc == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
-static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
+static int launch_merge(const MergeArgs &a, cudaStream_t stream, bool warp_per_row = false) {
     if (a.rows == 0) return NCB_OK;
-    const long long blocks = a.rows; /* one block per row */
+    const long long blocks = warp_per_row ? (a.rows + MERGE_WARPS - 1) / MERGE_WARPS : a.rows; /* else a block per row */
     if (blocks > 0x7fffffffLL) return NCB_ERR_ARG;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)blocks);
@@ -762,7 +800,7 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
     attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL; /* overlap its launch with the split kernel's tail */
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, k_merge, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+    return cudaLaunchKernelEx(&config, warp_per_row ? k_merge_rows : k_merge, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 static int attend(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
@@ -952,7 +990,7 @@ int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, cons
     MergeArgs m = {(const float *)workspace, (long long)rows * Hq, PART, (long long)max_chunks * PART, 0,
                    (const int32_t *)span_lens, (const int32_t *)slot_map, Hq, 0, chunk, n_slots, pages_per_slot,
                    max_chunks, 0, (bf16 *)out, nullptr};
-    return launch_merge(m, (cudaStream_t)stream);
+    return launch_merge(m, (cudaStream_t)stream, true);
 }
 
 int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
