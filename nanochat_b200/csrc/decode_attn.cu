@@ -34,8 +34,6 @@
  * consuming and falls through to the block's final barriers.
  */
 #include <algorithm>
-#include <cstdio>
-#include <cstdlib>
 #include <functional>
 #include <mutex>
 #include <unordered_map>
@@ -43,10 +41,7 @@
 
 #include "kv_row.cuh"
 
-#ifndef NCB_WARPS
-#define NCB_WARPS 4
-#endif
-constexpr int WARPS = NCB_WARPS; /* = stages per block; 12 stages of 16,896 B fit one SM's shared memory */
+constexpr int WARPS = 4; /* = stages per block; 12 stages of 16,896 B fit one SM's shared memory */
 constexpr int BLOCKS_PER_SM = 12 / WARPS;
 constexpr int THREADS = WARPS * 32;
 constexpr uint32_t WAIT_TRIES = 1u << 19; /* x <= 2 us suspend hint each: about one second */
@@ -101,24 +96,15 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) 
     return false;
 }
 /* One page from global to shared memory; the barrier receives the byte count when the copy has landed. A page is
- * read once per step, so with NCB_KV_EVICT_FIRST it is marked evict-first in L2: what else lives there across the
- * launch (weights the neighbouring GEMMs prefetched, the split states) is not pushed out by the cache stream. */
-#ifndef NCB_KV_EVICT_FIRST
-#define NCB_KV_EVICT_FIRST 1
-#endif
+ * read once per step, so it is marked evict-first in L2: what else lives there across the launch (weights the
+ * neighbouring GEMMs prefetched, the split states) is not pushed out by the cache stream. */
 static __device__ __forceinline__ void page_load(uint32_t dst, const void *src, uint32_t bar) {
     mbar_expect_tx(bar, PAGE_BYTES);
-#if NCB_KV_EVICT_FIRST
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                  ::"r"(dst), "l"(src), "r"((uint32_t)PAGE_BYTES), "r"(bar), "l"(policy)
                  : "memory");
-#else
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"((uint32_t)PAGE_BYTES), "r"(bar)
-                 : "memory");
-#endif
 }
 static __device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3,
                                                    uint32_t addr) {
@@ -760,7 +746,7 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
     cudaError_t rc;
@@ -781,9 +767,6 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
         if (prepare<2, true>() != cudaSuccess) return NCB_ERR_LAUNCH;
         rc = cudaLaunchKernelEx(&config, k_decode_attn<2, true>, a);
     }
-    if (rc != cudaSuccess && getenv("NCB_DEBUG"))
-        fprintf(stderr, "k_decode_attn launch (grid %d x %d x %d, chunk %d): %s\n", max_chunks, Hkv,
-                group_start ? n_groups : B, chunk_pages, cudaGetErrorString(rc));
     return rc == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
@@ -797,7 +780,7 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream, bool warp_per_r
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL; /* overlap its launch with the split kernel's tail */
+    attribute[0].val.programmaticStreamSerializationAllowed = 1; /* overlap its launch with the split kernel's tail */
     config.attrs = attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, warp_per_row ? k_merge_rows : k_merge, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
@@ -1022,7 +1005,7 @@ int decode_attn_merge_peers(const void *const *parts, void *const *flags, int wo
     config.stream = (cudaStream_t)stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, k_merge_peers, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;

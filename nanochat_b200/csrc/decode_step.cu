@@ -347,7 +347,9 @@ static __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
     return c;
 }
 
-/* -log(-log(u)), u in (0, 1) from 52 random bits, exact in double. */
+/* -log(-log(u)), u in (0, 1) from 52 random bits, exact in double. Restates the reference's noise
+ * (model/kernels/decode.cu:100-105) so that a (seed, step, token) triple means the same draw: the counter layout, the
+ * 52-bit mantissa and the midpoint u = (2 r + 1) 2^-53 have to be the reference's. */
 static __device__ __forceinline__ float gumbel(unsigned long long seed, int step, int token) {
     const uint4 x = philox4x32_10(make_uint4((uint32_t)token, (uint32_t)step, 0u, 0u),
                                   make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
@@ -418,6 +420,9 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
             sum = __fadd_rn(sum, e[r]);
         }
         const float drop = __fmul_rn(__fsub_rn(1.f, top_p), block_sum_ordered(sum, scratch));
+        /* The nucleus threshold, restating the reference's rule (model/kernels/decode.cu:382-393): e lies in [0, 1], where
+         * IEEE bit patterns order like the values, so the least e* whose mass from below exceeds `drop` is found by
+         * bisection on the bits; sums in the fixed order of block_sum_ordered, so the result is reproducible. */
         uint32_t lo = 0u, hi = __float_as_uint(1.f); /* the least bits u with C(u) > drop */
         while (lo < hi) {
             const uint32_t mid = lo + (hi - lo) / 2;
@@ -470,7 +475,7 @@ static int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, kernel, args...) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;

@@ -141,7 +141,7 @@ int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const
     config.stream = (cudaStream_t)stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = NCB_PDL;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, k_kv_append, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;

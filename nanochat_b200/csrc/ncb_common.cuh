@@ -15,12 +15,6 @@
 
 typedef __nv_bfloat16 bf16;
 
-/* 1: kernels are launched with programmatic stream serialisation (each waits for its predecessor with
- * griddepcontrol.wait before touching its inputs); 0 falls back to plain stream order, for bisecting. */
-#ifndef NCB_PDL
-#define NCB_PDL 1
-#endif
-
 constexpr int HEAD_DIM = NCB_HEAD_DIM;
 constexpr int HALF = HEAD_DIM / 2;
 constexpr int PAGE_TOKENS = NCB_PAGE_TOKENS;

@@ -37,9 +37,7 @@ namespace {
 constexpr int TILE_F = 128;                      /* output features per block = MMA M */
 constexpr int KBLK = 64;                         /* k-values per box: 64 bf16 = one 128-byte swizzle row */
 constexpr int A_BOX_BYTES = TILE_F * KBLK * 2;   /* 16 KB of weights per box */
-#ifndef SG_RING_KB
-#define SG_RING_KB 100
-#endif
+constexpr int RING_KB_SMALL = 100;               /* ring of the <= 128-row shapes: two blocks per SM */
 constexpr int THREADS = 128;
 constexpr int MAX_SPLIT = 8;                     /* portable cluster size */
 constexpr long long WAIT_CYCLES = 4000000000ll;  /* bound of every barrier wait */
@@ -53,7 +51,7 @@ template <int NP> struct Shape {
     static constexpr int B_BOX_BYTES = NP * KBLK * 2;
     static constexpr int BOX_BYTES = A_BOX_BYTES + B_BOX_BYTES;
     static constexpr int STAGE_BYTES = KSUB * BOX_BYTES;
-    static constexpr int RING_KB = NP == 256 ? 144 : SG_RING_KB; /* 256 rows park 128 KB of accumulators */
+    static constexpr int RING_KB = NP == 256 ? 144 : RING_KB_SMALL; /* 256 rows park 128 KB of accumulators */
     static constexpr int STAGES = RING_KB * 1024 / STAGE_BYTES < 8 ? RING_KB * 1024 / STAGE_BYTES : 8;
     static_assert(STAGES >= 2, "at least two stages");
     static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
@@ -167,18 +165,6 @@ __device__ __forceinline__ float sumsq_bf16x8(const uint4 &u) {
     return s;
 }
 
-#ifdef SG_TRACE /* experiments only: `status` is a long long [blocks][8] buffer of %globaltimer stamps */
-#define STAMP(slot)                                                                                      \
-    do {                                                                                                 \
-        long long t_;                                                                                    \
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                           \
-        reinterpret_cast<long long *>(a.status)[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; \
-    } while (0)
-#undef NCB_DEV_WAIT_TIMEOUT
-#define NCB_DEV_WAIT_TIMEOUT 0
-#else
-#define STAMP(slot)
-#endif
 
 /* ---- the kernel ---------------------------------------------------------------------------------------------- */
 
@@ -209,7 +195,6 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
     cg::cluster_group cluster = cg::this_cluster();
 
     if (tid == 0) {
-        STAMP(0);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full(s), 1);
             mbar_init(empty(s), a.norm_input ? 3 : 1); /* the MMAs' commit + the two norm warps */
@@ -252,7 +237,6 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
             const int pre = nst < STAGES ? nst : STAGES;
             for (int i = 0; i < pre; i++) load_w(i); /* weights do not depend on the predecessor */
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            STAMP(2);
             for (int i = 0; i < pre; i++) load_x(i);
             for (int i = pre; i < nst; i++) {
                 if (!mbar_wait(empty(i % STAGES), ((i / STAGES) & 1) ^ 1)) {
@@ -270,7 +254,6 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
                 for (long long at = from; at < to; at += 32768)
                     l2_prefetch(a.next_w + at, (uint32_t)(to - at < 32768 ? to - at : 32768));
             }
-            STAMP(1);
         }
     } else if (warp == 1) {
         if (lane == 0) { /* MMA issuer */
@@ -281,7 +264,6 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
                 const int s = i % STAGES, n = boxes_of(i);
                 ok = mbar_wait(full(s), (i / STAGES) & 1);
                 if (!ok) break;
-                if (i == 0) STAMP(3);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_addr = ring + s * Sh::STAGE_BYTES, b_addr = a_addr + KSUB * A_BOX_BYTES;
                 for (int b = 0; b < n; b++) {
@@ -294,7 +276,6 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
             }
             if (!ok) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
             umma_commit(accum_bar);
-            STAMP(4);
         }
     }
     if (tid != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -335,7 +316,6 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
 
     /* every thread: accumulators complete; thread tid holds feature tid (tensor-memory lane) of every row (column) */
     if (!mbar_wait(accum_bar, 0)) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
-    if (tid == 0) STAMP(5);
     __syncwarp(); /* the tensor-memory loads below are warp-wide */
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const size_t col = (size_t)tile * TILE_F + tid;
@@ -374,12 +354,10 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
                 if (r < a.rows) finish(v[j], res[j], (size_t)r * a.N + col);
             }
         }
-        if (tid == 0) STAMP(6);
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         if (warp == 1)
             asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NP) : "memory");
-        if (tid == 0) STAMP(7);
         return;
     }
 
@@ -394,7 +372,6 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     cluster.sync(); /* all blocks' accumulators and sums of squares are parked */
-    if (tid == 0) STAMP(6);
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NP) : "memory");
     /* 32 threads cover a row's 128 features with 16-byte remote loads; the block's four warps take four of its rows
@@ -451,7 +428,6 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
             }
         }
     }
-    if (tid == 0) STAMP(7);
     cluster.sync(); /* nobody leaves while a peer still reads its shared memory */
 }
 
@@ -551,7 +527,7 @@ int launch(const CUtensorMap &map_w, const CUtensorMap &map_x, const GemmArgs &a
     attribute[0].val.clusterDim.y = 1;
     attribute[0].val.clusterDim.z = 1;
     attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[1].val.programmaticStreamSerializationAllowed = NCB_PDL;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 2;
     return cudaLaunchKernelEx(&config, kernel, map_w, map_x, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;

@@ -9,7 +9,6 @@ failed build raises, and so does a non-zero status from any entry point (check()
 import ctypes
 import functools
 import hashlib
-import os
 import subprocess
 import tempfile
 from pathlib import Path
@@ -69,11 +68,9 @@ class NativeError(RuntimeError):
 
 
 def command() -> list[str]:
-    """The nvcc command; NCB_NVCC_FLAGS (space-separated, e.g. "-DWARPS=4") adds flags for experiments and, being
-    part of the command, selects its own cached library."""
-    extra = os.environ.get("NCB_NVCC_FLAGS", "").split()
-    return ["nvcc", "-gencode=arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", *extra,
-            "-Xcompiler", "-fPIC", "-shared", "-o"]
+    """The nvcc command, up to the output path."""
+    return ["nvcc", "-gencode=arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-shared",
+            "-o"]
 
 
 def library_path(name: str) -> Path:
@@ -90,9 +87,8 @@ def build_library(name: str) -> Path:
     path = library_path(name)
     if not path.exists():
         NATIVE.mkdir(exist_ok=True)
-        if not os.environ.get("NCB_NVCC_FLAGS"):
-            for stale in NATIVE.glob(f"{name}-*.so"):
-                stale.unlink(missing_ok=True)
+        for stale in NATIVE.glob(f"{name}-*.so"):
+            stale.unlink(missing_ok=True)
         with tempfile.TemporaryDirectory(dir=NATIVE) as tmp:
             built = Path(tmp) / path.name
             subprocess.run([*command(), str(built), str(KERNELS / f"{name}.cu")], check=True)
