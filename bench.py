@@ -21,10 +21,18 @@ One JSON line on rank 0. A step is one decode-attention pass (split-KV kernel + 
   cpu_baseline  the reference's CPU attention (a torch restatement of inference/modeling_nanochat.py:48-56, see
             oracle/attention.py) on a bounded sample of the same workload, all host threads.
 
-  longctx, decoder, decoder_d32  extras in the same line: the long-context configuration (KV split by length over
-            the ranks), greedy decode tokens/s of the random-init d20 model (batch 8 per GPU, 512-token prompts; at
-            N = 1 with the CPU port of the reference's decoder timed beside it, `decoder.cpu_baseline`) and of the
-            d32-class model (batch 32 per GPU, ragged contexts).
+  parity    checks made inside this run, asserted before the line is printed: one sequence per rank has a constant
+            V row planted, so its output must be that vector whatever q and K are (max over ranks of the error), and
+            one sequence per rank is recomputed with plain torch fp32 operators on the dequantised cache.
+  ragged, longctx, decoder, decoder_d32  extras in the same line: the GQA sweep itself (ragged lengths, its own
+            roofline fraction); the long-context configuration (KV split by length over the ranks; fused exchange
+            against the NCCL variant on the same inputs, planted-constant-V property); greedy decode tokens/s of the
+            random-init d20 model (batch 8 per GPU, 512-token prompts; at N = 1 with the CPU port of the reference's
+            decoder timed beside it, `decoder.cpu_baseline`) and of the d32-class model (batch 32 per GPU, ragged
+            contexts).
+
+Every timed loop runs REPEATS times inside one invocation (each repeat: exactly --steps steps between two events,
+barrier and synchronize on both sides, max over ranks); the line carries the median repeat.
 
 --impl reference times that CPU restatement alone, on the same config and metric.
 Data is synthetic: q ~ N(0,1) bf16; K, V ~ N(0,1) quantised per (token, head) with scale = amax / 448."""
@@ -45,9 +53,22 @@ sys.path.insert(0, str(ROOT))
 
 HQ, HKV, D, BATCH = 32, 8, 128, 64
 METRIC, UNIT = "decode_attention_hbm_gbs", "GB/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_decode_attn<1> launch on the target8k workload, from the
-# ncu capture summarised under profiles/ (1.1080 GB read + 6.3 MB written)
-TARGET8K_TRAFFIC_BYTES = 1_108_042_000 + 6_277_000
+REPEATS = 5
+PATH_MAX_ABS, PATH_MEAN_ABS = 2e-2, 2e-3  # the path's tolerance on bf16 outputs
+
+
+def profiled_traffic() -> dict | None:
+    """dram__bytes_read.sum + dram__bytes_write.sum of one split-kernel launch on the target8k workload, read from
+    the tracked ncu summary (its `traffic_bytes_per_launch:` line, which also names the commit it was captured at)."""
+    import re
+
+    path = ROOT / "profiles" / "decode_attn_split_target8k.md"
+    if not path.exists():
+        return None
+    m = re.search(r"traffic_bytes_per_launch:\s*([0-9_,]+)\s*\(capture of commit ([0-9a-f]+)\)", path.read_text())
+    if not m:
+        return None
+    return {"bytes": int(m.group(1).replace("_", "").replace(",", "")), "commit": m.group(2)}
 
 
 def algorithmic_bytes(lens, Hq=HQ, Hkv=HKV) -> int:
@@ -65,7 +86,7 @@ def peaks() -> tuple[float, str]:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
         return float(json.loads(path.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s, an earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s; MEASURED_PEAKS.json is absent)"
 
 
 class ClockSampler:
@@ -151,66 +172,146 @@ def time_cpu_reference(lens, budget_s: float, seed: int = 1234) -> dict:
         times.append(time.perf_counter() - t0)
     warm = times[1:] if len(times) > 1 else times
     t = statistics.median(warm)
-    return {"value": algorithmic_bytes(lens) / t / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+    return {"value": algorithmic_bytes(lens) / t / 1e9, "unit": UNIT, "cores": threads, "cpu": cpu_model(), "kind": "port",
             "sample": f"{len(lens)} sequences of the workload ({sum(lens)} positions), bf16 K/V dequantised outside "
                       f"the timed region, {len(warm)} timed passes, median", "seconds_per_pass": t}
 
 
-def synthetic_cache(lens, max_len: int, seed: int, device):
-    """A cache filled with quantised N(0,1) keys and values, generated on the device."""
+def quantise_rows(x: torch.Tensor):
+    """(..., 128) fp32 -> (e4m3 bytes as uint8, fp32 scale = amax / 448): the cache's quantise rule, in torch."""
+    scale = x.abs().amax(-1) / 448.0
+    return (x / scale[..., None]).to(torch.float8_e4m3fn).view(torch.uint8), scale
+
+
+def synthetic_cache(lens, max_len: int, seed: int, device, constant_v: dict | None = None):
+    """A cache filled with quantised N(0,1) keys and values, generated on the device. constant_v = {slot: vector
+    fp32 (128,)} plants that vector as every V row of the slot: the slot's attention output must then be the
+    (dequantised) vector, whatever q and K are: a check that needs no second implementation."""
     import nanochat_b200 as ncb
 
     gen = torch.Generator(device=device).manual_seed(seed)
     cache = ncb.Fp8KVCache(len(lens), HKV, max_len, device=device)
     for slot, n in enumerate(lens):
         packed = []
-        for _ in range(2):
+        for which in range(2):
             x = torch.randn(HKV, n, D, generator=gen, device=device)
-            scale = x.abs().amax(-1) / 448.0
-            packed += [(x / scale[..., None]).to(torch.float8_e4m3fn).view(torch.uint8), scale]
+            if which == 1 and constant_v and slot in constant_v:
+                x = constant_v[slot].to(device).expand(HKV, n, D)
+            packed += list(quantise_rows(x))
         cache.write(slot, *packed)
     return cache
 
 
+def dequantised(vector: torch.Tensor) -> torch.Tensor:
+    b, s = quantise_rows(vector[None])
+    return (b.view(torch.float8_e4m3fn).float() * s[..., None])[0]
+
+
+def torch_attention_row(cache, slot: int, n: int, q_row: torch.Tensor) -> torch.Tensor:
+    """One sequence recomputed with plain torch fp32 operators on the dequantised cache: q_row (Hq, 128) bf16 ->
+    (Hq, 128) fp32. The check beside the planted-vector property; not an import of the CPU checker."""
+    k, ks, v, vs = cache.read(slot, n)
+    K = k.view(torch.float8_e4m3fn).float() * ks[..., None]
+    V = v.view(torch.float8_e4m3fn).float() * vs[..., None]
+    G = q_row.shape[0] // K.shape[0]
+    scores = torch.einsum("kgd,knd->kgn", q_row.float().view(K.shape[0], G, D), K) * D ** -0.5
+    return torch.einsum("kgn,knd->kgd", scores.softmax(-1), V).reshape(q_row.shape[0], D)
+
+
+def error_of(got: torch.Tensor, want: torch.Tensor) -> tuple[float, float]:
+    d = (got.float() - want.float()).abs()
+    return float(d.max()), float(d.mean())
+
+
+def captured(fn, device) -> torch.cuda.CUDAGraph:
+    """fn's launches as a CUDA graph: one eager run first (first-use set-up happens outside capture), then the
+    capture on a side stream. Replays launch on the caller's current stream."""
+    from nanochat_b200.decoder import no_collection
+
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        fn()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with no_collection(), torch.cuda.graph(graph, stream=side):
+            fn()
+    torch.cuda.current_stream(device).wait_stream(side)
+    return graph
+
+
 def bench_longctx(rank: int, world: int, device, steps: int, warmup: int, timed) -> dict:
     """Long-context decode attention: batch 4, Hq 32, Hkv 8, 131,072 positions per sequence. With N > 1 ranks every
-    sequence's positions are cut into N page-aligned slices; each rank attends over its slice, the un-normalised
-    (m, l, o) states are all-gathered over NCCL and merged locally. Total work is fixed (strong scaling)."""
+    sequence's positions are cut into N page-aligned slices; each rank runs the split-KV kernel over its slice and ONE
+    more kernel that merges its chunks, pushes the row states to every peer over NVLink and merges across ranks
+    (decode_attn_fp8_sharded; no collective library on the data path). Total work is fixed (strong scaling). The step
+    is a captured CUDA graph, as a decode loop would replay it. The NCCL variant (local merge, all-gather, merge; eager
+    launches) runs on the same inputs: its time is reported and its output compared. Sequence 1 has a constant V row
+    planted on every rank, so its merged output is known without gathering the slices."""
     import nanochat_b200 as ncb
+    from nanochat_b200 import attention as ops
     from nanochat_b200 import sharding
 
     B, N = 4, 131072
     begin, end = sharding.kv_slices(N, world)[rank]
-    n_local = end - begin
-    cache = synthetic_cache([n_local] * B, max(n_local, 1), seed=5000 + rank, device=device)
+    n_local = max(end - begin, 1)
+    vector = 0.25 * torch.randn(D, generator=torch.Generator().manual_seed(6100))  # the same on every rank
+    cache = synthetic_cache([n_local] * B, n_local, seed=5000 + rank, device=device, constant_v={1: vector})
     gen = torch.Generator(device=device).manual_seed(6000)  # q is replicated: same seed on every rank
     q = torch.randn(B, HQ, D, generator=gen, device=device).bfloat16()
     lens_t = torch.full((B,), n_local, dtype=torch.int32, device=device)
-    chunk = ncb.attention.chunk_pages_for(B, HKV, max(n_local, 1))
-    workspace = torch.empty(max(16, ncb.workspace_bytes(B, HQ, HKV, max(n_local, 1), chunk)), dtype=torch.uint8,
-                            device=device)
+    chunk = ops.chunk_pages_for(B, HKV, n_local)
+    workspace = torch.empty(max(16, ncb.workspace_bytes(B, HQ, HKV, n_local, chunk)), dtype=torch.uint8, device=device)
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    parity, ms_nccl, peers = {}, None, None
     if world == 1:
-        out = torch.empty_like(q)
-        step = lambda: ncb.decode_attention(q, cache, lens_t, n_local, chunk_pages=chunk, workspace=workspace, out=out)
+        eager = lambda: ncb.decode_attention(q, cache, lens_t, n_local, chunk_pages=chunk, workspace=workspace, out=out,
+                                             status=status)
     else:
         part = torch.empty((B, HQ, 132), dtype=torch.float32, device=device)
-        nccl_step = lambda: sharding.attend_kv_sharded(q, cache, lens_t, max(n_local, 1), chunk_pages=chunk,
-                                                       workspace=workspace, part=part)
+        nccl_step = lambda: sharding.attend_kv_sharded(q, cache, lens_t, n_local, chunk_pages=chunk,
+                                                       workspace=workspace, part=part, status=status)
         ms_nccl = timed(nccl_step, steps, warmup)
+        out_nccl = nccl_step().clone()
         peers = sharding.PeerStates(B, HQ)
-        out = torch.empty_like(q)
-        step = lambda: sharding.attend_kv_sharded_fused(q, cache, lens_t, max(n_local, 1), peers, out=out,
-                                                        chunk_pages=chunk, workspace=workspace)
-    ms = timed(step, steps, warmup)
+        eager = lambda: sharding.attend_kv_sharded_fused(q, cache, lens_t, n_local, peers, out=out, chunk_pages=chunk,
+                                                         workspace=workspace)
+    split_only = captured(lambda: ops.decode_attention_split(q, cache, lens_t, n_local, workspace, chunk_pages=chunk,
+                                                             status=status), device)
+    step = captured(eager, device)
+    ms = timed(step.replay, steps, warmup)
+    ms_split = timed(split_only.replay, steps, warmup)
+    step.replay()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, f"device status {int(status.item())}"
+    parity["property_max_abs"], parity["property_mean_abs"] = error_of(out[1], dequantised(vector).to(device).expand(HQ, D))
     if world > 1:
         assert int(peers.status.item()) == 0, "a peer wait ran out"
+        parity["fused_vs_nccl_max_abs"], parity["fused_vs_nccl_mean_abs"] = error_of(out, out_nccl)
+        everyone = [torch.empty_like(out) for _ in range(world)]
+        torch.distributed.all_gather(everyone, out)
+        parity["ranks_bit_identical"] = all(torch.equal(everyone[0], o) for o in everyone[1:])
+        assert parity["ranks_bit_identical"], "ranks disagree on the merged output"
+        assert parity["fused_vs_nccl_max_abs"] <= PATH_MAX_ABS and parity["fused_vs_nccl_mean_abs"] <= PATH_MEAN_ABS, parity
+    else:
+        ref = torch_attention_row(cache, 0, n_local, q[0])
+        parity["torch_fp32_seq0_max_abs"], parity["torch_fp32_seq0_mean_abs"] = error_of(out[0], ref)
+        assert parity["torch_fp32_seq0_max_abs"] <= PATH_MAX_ABS and parity["torch_fp32_seq0_mean_abs"] <= PATH_MEAN_ABS, parity
+    assert parity["property_max_abs"] <= PATH_MAX_ABS and parity["property_mean_abs"] <= PATH_MEAN_ABS, parity
+    parity["tolerance"] = {"max_abs": PATH_MAX_ABS, "mean_abs": PATH_MEAN_ABS}
     total = algorithmic_bytes([N] * B)
     return {"workload": "batch 4, Hq 32, Hkv 8, head_dim 128, 131072 positions per sequence, KV split by length over "
-                        f"{world} GPU(s)", "value": total * steps / (ms * 1e-3) / 1e9, "unit": UNIT,
-            "ms_per_step": ms / steps, "steps": steps, "scaling": "strong", "chunk_pages": chunk,
-            "collective": None if world == 1 else "none: decode_attn_merge_peers loads every rank's fp32 [4][32][132] "
-                                                  "states over NVLink after a bounded flag wait",
-            "nccl_variant_ms_per_step": None if world == 1 else ms_nccl / steps}
+                        f"{world} GPU(s)", "value": total / (ms * 1e-3) / 1e9, "unit": UNIT,
+            "ms_per_step": ms, "steps": steps, "scaling": "strong", "chunk_pages": chunk,
+            "launch": "one captured CUDA graph per step (split-KV kernel, then merge" +
+                      (" + exchange kernel)" if world > 1 else " kernel)"),
+            "breakdown_us": {"split_kernel_alone": ms_split * 1e3, "merge_and_exchange": (ms - ms_split) * 1e3,
+                             "per_gpu_slice_bytes": algorithmic_bytes([n_local] * B)},
+            "collective": None if world == 1 else "none: each rank's merge kernel pushes its fp32 [4][32][132] states "
+                          "into every peer's inbox over NVLink, then waits (bounded) on per-row flags",
+            "nccl_variant_ms_per_step": ms_nccl, "nccl_variant_launch": None if world == 1 else "eager launches: split, "
+            "merge, all_gather_into_tensor, merge", "parity": parity}
 
 
 def bench_decoder(rank: int, world: int, device, new_tokens: int, profile: bool = False) -> dict:
@@ -274,7 +375,7 @@ def bench_decoder_cpu(steps: int) -> dict:
     for _ in range(steps):
         tokens = oracle.step(tokens, seqs).argmax(-1)
     dt = time.perf_counter() - t0
-    return {"tokens_per_s": 8 * steps / dt, "cores": threads, "kind": "port",
+    return {"tokens_per_s": 8 * steps / dt, "cores": threads, "cpu": cpu_model(), "kind": "port",
             "sample": f"{steps} greedy steps of batch 8 at context 512 (one warm-up step before)"}
 
 
@@ -327,7 +428,19 @@ def bench_decoder_d32(rank: int, world: int, device, new_tokens: int, profile: b
             "scaling": "weak (batch-sharded replicas)"}
 
 
+def cpu_model() -> str:
+    try:
+        for line in Path("/proc/cpuinfo").read_text().splitlines():
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
 def run_reference(args, rank: int, world: int) -> None:
+    """The reference arm: the CPU port of the reference's attention on the host cores. It runs on rank 0 alone and
+    does not shard (the reference has no multi-GPU or multi-process path), so its value is the same at every N."""
     if rank != 0:
         return
     lens_all = workload_lens(args.workload, BATCH * world)
@@ -345,13 +458,16 @@ def run_reference(args, rank: int, world: int) -> None:
         step()
     dt = time.perf_counter() - t0
     value = algorithmic_bytes(sample) * args.steps / dt / 1e9
-    note = f"each step = {len(sample)} sequences of the workload ({sum(sample)} positions) on the host cores"
+    note = (f"each step = {len(sample)} sequences of the workload ({sum(sample)} positions; the GPU arm's step is the "
+            f"whole batch of {BATCH} per GPU: the metric is a rate, so the two compare) on the host cores")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "none (one host process on rank 0; the value does not grow with N)",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": config_of(args, world, extra={"reference_step": note}),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": note},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "cpu": cpu_model(), "kind": "port",
+                         "sample": note},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
 
@@ -383,6 +499,7 @@ def main() -> None:
     ap.add_argument("--profile-range", default="attention", choices=["attention", "decoder", "decoder_d32"],
                     help="which timed loops cudaProfilerStart/Stop bracket (for `ncu --profile-from-start off`)")
     ap.add_argument("--decoder-d32", type=int, default=1, help="also time batched decode of the d32-class model (0: skip)")
+    ap.add_argument("--ragged", type=int, default=1, help="also run the ragged GQA sweep as an extra (0: skip)")
     ap.add_argument("--longctx", type=int, default=1, help="also time the KV-length-sharded long-context case (0: skip)")
     ap.add_argument("--e2e-steps", type=int, default=200, help="steps of the end-to-end loop (profiling runs shrink it)")
     args = ap.parse_args()
@@ -406,94 +523,147 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    lens_all = workload_lens(args.workload, BATCH * world)
-    mine = shard_batch(lens_all, world, longest_first=True)[rank]
-    lens = [lens_all[i] for i in mine]
-    B = len(lens)
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    headroom = args.warmup + e2e_steps + 8
-    max_len = max(lens) + headroom
-    cache = synthetic_cache(lens, max_len, seed=1000 + rank, device=device)
-    gen = torch.Generator(device=device).manual_seed(2000 + rank)
-    q = torch.randn(B, HQ, D, generator=gen, device=device).bfloat16()
-    lens_t = torch.tensor(lens, dtype=torch.int32, device=device)
-    max_kv = max(lens)
-    status = torch.zeros(1, dtype=torch.int32, device=device)
-    chunk = args.chunk_pages or ops.plan_chunk_pages(lens, HKV, max_kv)  # the host knows this step's lengths
-    workspace = torch.empty(ncb.workspace_bytes(B, HQ, HKV, max_kv + headroom, chunk), dtype=torch.uint8, device=device)
-    out = torch.empty_like(q)
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
     def timed(fn, steps: int, warmup: int, during=None) -> float:
-        """Milliseconds for `steps` calls after `warmup`: CUDA events on the launching stream, barrier and
-        synchronize on both sides, max over ranks. `during` runs once while the queued steps still execute."""
+        """Milliseconds per step: after `warmup` calls, REPEATS timed loops of exactly `steps` calls each, every loop
+        between two CUDA events on the launching stream with a barrier and a synchronize on both sides and the max over
+        ranks taken; the median loop is returned. `during` runs once per loop while its queued steps still execute."""
         for _ in range(warmup):
             fn()
-        barrier()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            fn()
-        end.record()
-        if during:
-            during()
-        barrier()
-        ms = torch.tensor([start.elapsed_time(end)], device=device)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        loops = []
+        for _ in range(REPEATS):
+            barrier()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(steps):
+                fn()
+            end.record()
+            if during:
+                during()
+            barrier()
+            ms = torch.tensor([start.elapsed_time(end)], device=device)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            loops.append(float(ms.item()) / steps)
+        return statistics.median(loops)
 
-    step = lambda: ncb.decode_attention(q, cache, lens_t, max_kv, chunk_pages=chunk, workspace=workspace, out=out,
-                                        status=status)
-    split = lambda: ops.decode_attention_split(q, cache, lens_t, max_kv, workspace, chunk_pages=chunk, status=status)
-
-    for _ in range(3):  # first-use costs (module load, attribute set-up) stay out of any profiled range
+    def attention_workload(workload: str, with_e2e: bool, profiled: bool) -> dict:
+        """One decode-attention workload on this rank's share of the global batch: the step (split + merge), the split
+        kernel alone, the checks, and (with_e2e) the step through DecodeStep with host buffers."""
+        lens_all = workload_lens(workload, BATCH * world)
+        mine = shard_batch(lens_all, world, longest_first=True)[rank]
+        lens = [lens_all[i] for i in mine]
+        B = len(lens)
+        e2e_steps = max(1, min(args.steps, args.e2e_steps))
+        headroom = args.warmup + e2e_steps * REPEATS + 8 if with_e2e else 0
+        max_len = max(lens) + headroom
+        planted = min(range(B), key=lambda b: (abs(lens[b] - 8192), b))  # the slot whose V rows are one vector
+        vector = 0.25 * torch.randn(D, generator=torch.Generator().manual_seed(1500 + rank))
+        cache = synthetic_cache(lens, max_len, seed=1000 + rank, device=device, constant_v={planted: vector})
+        gen = torch.Generator(device=device).manual_seed(2000 + rank)
+        q = torch.randn(B, HQ, D, generator=gen, device=device).bfloat16()
+        lens_t = torch.tensor(lens, dtype=torch.int32, device=device)
+        max_kv = max(lens)
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+        chunk = args.chunk_pages or ops.plan_chunk_pages(lens, HKV, max_kv)  # the host knows this step's lengths
+        workspace = torch.empty(ncb.workspace_bytes(B, HQ, HKV, max_kv + headroom, chunk), dtype=torch.uint8,
+                                device=device)
+        out = torch.empty_like(q)
+        step = lambda: ncb.decode_attention(q, cache, lens_t, max_kv, chunk_pages=chunk, workspace=workspace, out=out,
+                                            status=status)
+        split = lambda: ops.decode_attention_split(q, cache, lens_t, max_kv, workspace, chunk_pages=chunk,
+                                                   status=status)
+        for _ in range(3):  # first-use costs (module load, attribute set-up) stay out of any profiled range
+            step()
+        torch.cuda.synchronize()
+        if profiled:
+            torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see exactly the loops below
+        with ClockSampler(local) as clocks:
+            ms_step = timed(step, args.steps, args.warmup, during=clocks.sample if clocks.nvml else None)
+        ms_split = timed(split, args.steps, 3)
         step()
-    torch.cuda.synchronize()
-    if args.profile_range == "attention":
-        torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see exactly the loops below
-    with ClockSampler(local) as clocks:
-        ms_total = timed(step, args.steps, args.warmup, during=clocks.sample if clocks.nvml else None)
-    ms_split = timed(split, args.steps, 3)
+        torch.cuda.synchronize()
+        # ---- checks on what the timed kernels computed
+        check_seq = 0 if planted != 0 else 1
+        errs = torch.tensor([*error_of(out[planted], dequantised(vector).to(device).expand(HQ, D)),
+                             *error_of(out[check_seq], torch_attention_row(cache, check_seq, lens[check_seq], q[check_seq]))],
+                            device=device)
+        res = {"lens": lens, "chunk": chunk, "ms_step": ms_step, "ms_split": ms_split, "clocks": clocks.summary()}
+        if with_e2e:
+            # ---- end to end through the public step object with host buffers
+            cos, sin = ncb.rotary_table(max_len, 1e4, device=device)
+            ones = torch.ones(D, device=device)
+            host_gen = torch.Generator().manual_seed(3000 + rank)
+            decode = ncb.DecodeStep(cache, HQ, cos, sin, ones, ones, B, chunk_pages=chunk)
+            decode.qkv_host.copy_(torch.randn(decode.qkv_host.shape, generator=host_gen).bfloat16())
+            decode.pos_host.copy_(torch.tensor(lens, dtype=torch.int32))
 
-    # ---- end to end through the public step object with host buffers
-    cos, sin = ncb.rotary_table(max_len, 1e4, device=device)
-    ones = torch.ones(D, device=device)
-    host_gen = torch.Generator().manual_seed(3000 + rank)
-    decode = ncb.DecodeStep(cache, HQ, cos, sin, ones, ones, B, chunk_pages=chunk)
-    decode.qkv_host.copy_(torch.randn(decode.qkv_host.shape, generator=host_gen).bfloat16())
-    decode.pos_host.copy_(torch.tensor(lens, dtype=torch.int32))
+            def e2e_step():
+                decode.run()  # pinned host in, graph replay (copies, append + attention), pinned host out, sync
+                decode.pos_host.add_(1)  # the next step's token goes one position further
 
-    def e2e_step():
-        decode.run()  # pinned host in, graph replay (copies, kv_append_fp8, decode_attn_fp8), pinned host out, sync
-        decode.pos_host.add_(1)  # the next step's token goes one position further
+            for _ in range(args.warmup):
+                e2e_step()
+            done, loops = args.warmup, []
+            for _ in range(REPEATS):
+                barrier()
+                # every timed step attends one position more than the one before
+                nbytes = sum(algorithmic_bytes([n + done + k + 1 for n in lens]) for k in range(e2e_steps))
+                t0 = time.perf_counter()
+                for _ in range(e2e_steps):
+                    e2e_step()
+                barrier()
+                t = torch.tensor([time.perf_counter() - t0, float(nbytes)], device=device)
+                if world > 1:
+                    seconds = t[:1].clone()
+                    dist.all_reduce(seconds, op=dist.ReduceOp.MAX)
+                    dist.all_reduce(t)
+                    t[0] = seconds[0]
+                loops.append((float(t[0]), float(t[1])))
+                done += e2e_steps
+            loops.sort(key=lambda x: x[0] / x[1])
+            seconds, nbytes = loops[len(loops) // 2]
+            decode.check()
+            res["e2e"] = {"value": nbytes / seconds / 1e9, "unit": UNIT, "h2d_bytes_per_step": decode.h2d_bytes,
+                          "d2h_bytes_per_step": decode.d2h_bytes, "steps": e2e_steps,
+                          "ms_per_step": seconds / e2e_steps * 1e3,
+                          "what": "DecodeStep.run(): pinned-host qkv rows + positions in, decode_step_attn_fp8 (append "
+                                  "+ attention; one CUDA graph with the copies), output to pinned host, synchronised "
+                                  "every step; the KV cache is resident decoder state"}
+            del decode
+        if profiled:
+            torch.cuda.profiler.stop()
+        total_bytes = torch.tensor([float(algorithmic_bytes(lens))], device=device)
+        if world > 1:
+            dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+            dist.all_reduce(total_bytes)
+        assert status.item() == 0, f"device status {status.item()}"
+        res["total_bytes"] = float(total_bytes.item())
+        res["parity"] = {"property_max_abs": float(errs[0]), "property_mean_abs": float(errs[1]),
+                         "torch_fp32_seq_max_abs": float(errs[2]), "torch_fp32_seq_mean_abs": float(errs[3]),
+                         "what": "max over ranks; property: one sequence per rank has a constant V row planted, its "
+                                 "output must be that vector; torch_fp32_seq: one sequence per rank recomputed with "
+                                 "plain torch fp32 operators on the dequantised cache",
+                         "tolerance": {"max_abs": PATH_MAX_ABS, "mean_abs": PATH_MEAN_ABS}}
+        assert errs[0] <= PATH_MAX_ABS and errs[1] <= PATH_MEAN_ABS and errs[2] <= PATH_MAX_ABS and errs[3] <= PATH_MEAN_ABS, \
+            res["parity"]
+        return res
 
-    for _ in range(args.warmup):
-        e2e_step()
-    barrier()
-    # every timed step attends one position more than the one before
-    e2e_bytes = sum(algorithmic_bytes([n + args.warmup + k + 1 for n in lens]) for k in range(e2e_steps))
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    barrier()
-    e2e_s = torch.tensor([time.perf_counter() - t0], device=device)
-    if args.profile_range == "attention":
-        torch.cuda.profiler.stop()
-    total_e2e_bytes = torch.tensor([float(e2e_bytes)], device=device)
-    total_bytes = torch.tensor([float(algorithmic_bytes(lens))], device=device)
-    if world > 1:
-        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-        dist.all_reduce(total_e2e_bytes)
-        dist.all_reduce(total_bytes)
-    assert status.item() == 0, f"device status {status.item()}"
-    decode.check()
-    h2d_bytes, d2h_bytes = decode.h2d_bytes, decode.d2h_bytes
-    del cache, decode, workspace
+    def roofline_of(res: dict, traffic) -> dict:
+        peak, peak_kind = peaks()
+        nbytes = algorithmic_bytes(res["lens"])
+        gbs = nbytes / (res["ms_split"] * 1e-3) / 1e9
+        return {"bound": "hbm", "kernel": "k_decode_attn<1> (split-KV)", "achieved": gbs, "peak": peak, "unit": UNIT,
+                "frac": gbs / peak, "peak_kind": peak_kind, "traffic": traffic["bytes"] if traffic else None,
+                "traffic_capture_commit": traffic["commit"] if traffic else None,
+                "us_per_launch": res["ms_split"] * 1e3, "algorithmic_bytes_per_launch": nbytes}
+
+    head = attention_workload(args.workload, True, args.profile_range == "attention")
+    ragged = attention_workload("ragged", False, False) if args.ragged and args.workload != "ragged" else None
     longctx = bench_longctx(rank, world, device, min(args.steps, 100), 5, timed) if args.longctx else None
     decoder = bench_decoder(rank, world, device, args.decoder_tokens, args.profile_range == "decoder") \
         if args.decoder else None
@@ -502,30 +672,24 @@ def main() -> None:
         if args.decoder_d32 else None
 
     if rank == 0:
-        peak, peak_kind = peaks()
-        step_bytes = float(total_bytes.item())
-        value = step_bytes * args.steps / (ms_total * 1e-3) / 1e9
-        split_gbs = algorithmic_bytes(lens) * args.steps / (ms_split * 1e-3) / 1e9
+        value = head["total_bytes"] / (head["ms_step"] * 1e-3) / 1e9
+        traffic = profiled_traffic() if args.workload == "target8k" and not args.chunk_pages else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": head["ms_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "e4m3 operands, fp32 accumulate and softmax", "data": "synthetic",
-            "config": config_of(args, world, extra={"chunk_pages": chunk, "pct_of_8TBs_per_gpu": value / world / 80.0}),
-            "clocks": clocks.summary(),
-            "e2e": {"value": float(total_e2e_bytes.item()) / float(e2e_s.item()) / 1e9, "unit": UNIT,
-                    "h2d_bytes_per_step": h2d_bytes,
-                    "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps,
-                    "ms_per_step": float(e2e_s.item()) / e2e_steps * 1e3,
-                    "what": "DecodeStep.run(): pinned-host qkv rows + positions in, decode_step_attn_fp8 (append + "
-                            "attention; one CUDA graph with the copies), output to pinned host, synchronised every "
-                            "step; the KV cache is resident decoder state"},
-            "gpu_launches": 2 * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "k_decode_attn<1> (split-KV)", "achieved": split_gbs, "peak": peak,
-                         "unit": UNIT, "frac": split_gbs / peak, "peak_kind": peak_kind,
-                         "traffic": TARGET8K_TRAFFIC_BYTES if args.workload == "target8k" and not args.chunk_pages else None,
-                         "us_per_launch": ms_split / args.steps * 1e3,
-                         "algorithmic_bytes_per_launch": algorithmic_bytes(lens)},
+            "config": config_of(args, world, extra={"chunk_pages": head["chunk"], "timed_loops": REPEATS,
+                                                    "pct_of_8TBs_per_gpu": value / world / 80.0}),
+            "clocks": head["clocks"], "e2e": head["e2e"], "gpu_launches": 2 * args.steps * REPEATS,
+            "roofline": roofline_of(head, traffic), "parity": head["parity"],
         }
+        if ragged:
+            rvalue = ragged["total_bytes"] / (ragged["ms_step"] * 1e-3) / 1e9
+            line["ragged"] = {"workload": config_of(argparse.Namespace(workload="ragged"), world)["workload"] +
+                                          ", sequences longest-first inside each GPU's batch",
+                              "value": rvalue, "unit": UNIT, "ms_per_step": ragged["ms_step"], "scaling": "weak",
+                              "chunk_pages": ragged["chunk"], "roofline": roofline_of(ragged, None),
+                              "parity": ragged["parity"]}
         if longctx:
             line["longctx"] = longctx
         if decoder:
@@ -533,7 +697,7 @@ def main() -> None:
         if decoder_d32:
             line["decoder_d32"] = decoder_d32
         if world == 1 and args.cpu_seconds > 0:
-            line["cpu_baseline"] = time_cpu_reference(lens[:args.cpu_sample], args.cpu_seconds)
+            line["cpu_baseline"] = time_cpu_reference(head["lens"][:args.cpu_sample], args.cpu_seconds)
             if decoder:
                 decoder["cpu_baseline"] = bench_decoder_cpu(3)
         print(json.dumps(line))

@@ -75,7 +75,10 @@ int kv_cache_pages(int max_len);
  *   status    int32 device word or NULL
  * Arithmetic: every fp32 operation individually rounded in the order fixed by oracle/kv_append_oracle.c, so q
  * bits, cache bytes and scales are exact functions of the inputs. Rows whose position >= pages_per_slot * 64 or
- * >= table_len, or whose slot >= n_slots, are skipped and flagged in *status.
+ * >= table_len, or whose slot is outside [0, n_slots), are skipped and flagged in *status. A NEGATIVE position marks
+ * an idle row: it is skipped silently (nothing written, nothing flagged), the counterpart of the reference's
+ * `active` slot mask (decode.cu:60-62,555), so that one captured step serves a batch whose slots finish at different
+ * times.
  */
 int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
                   const void *pos, const void *slot_map, void *q_out, void *kv_cache, long long rows, int Hq,
@@ -92,7 +95,9 @@ int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len);
  * empty last wave of blocks. Pass the result as chunk_pages (and to decode_attn_workspace_bytes); worth it for
  * ragged batches whose lengths change slowly, such as the steps of one captured decode loop. */
 int decode_attn_plan_chunk_pages(const int *lens, int B, int Hkv, int max_kv_len, int window);
-/* Workspace bytes for the split partials; chunk_pages == 0 selects decode_attn_chunk_pages(). */
+/* Workspace bytes for the split partials; chunk_pages == 0 selects decode_attn_chunk_pages(B, Hkv, max_kv_len). Pass
+ * the same max_kv_len here and to the attention entry point: they derive the same default chunk from it (the entry
+ * point clips max_kv_len to the cache's capacity only afterwards, which can only shrink the need). */
 long long decode_attn_workspace_bytes(int B, int Hq, int max_kv_len, int Hkv, int chunk_pages);
 
 /*
@@ -100,7 +105,8 @@ long long decode_attn_workspace_bytes(int B, int Hq, int max_kv_len, int Hkv, in
  * j in [max(0, lens[b] - window), lens[b]) of slot slot_map[b] (replaces k_attn, decode.cu:567-675; the current
  * token is read from the cache, where kv_append_fp8 put it, instead of from registers).
  *   q         bf16 [B][Hq][128]
- *   lens      int32 [B]: cached positions per sequence (0 gives a zero output row)
+ *   lens      int32 [B]: cached positions per sequence (0 gives a zero output row; so does a negative value, which
+ *             marks an idle row and is not flagged)
  *   slot_map  int32 [B] or NULL
  *   workspace >= decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages), 16-byte aligned; contents are
  *             scratch, calls sharing it must be stream-ordered
@@ -133,7 +139,8 @@ int decode_attn_fp8_partial(const void *q, const void *kv_cache, const void *len
  * [max(0, pos[b] + 1 - window), pos[b] + 1). Same arithmetic as kv_append_fp8 (shared code), so the cache bytes are
  * identical; q is not written out. Arguments as for the two entry points; `pos` int32 [B] takes the place of lens,
  * max_kv_len bounds pos[b] + 1. Rows must address distinct slots (rows sharing a slot, as in prefill, need the
- * separate entry points, where every row's append lands before any row attends).
+ * separate entry points, where every row's append lands before any row attends). pos[b] < 0 marks an idle row: no
+ * append, no attention, a zero output row, no status bit (the reference's inactive slots, decode.cu:555,573).
  */
 int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
                          const void *pos, const void *slot_map, void *kv_cache, void *workspace,
@@ -182,7 +189,8 @@ int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens,
  * The first call on each device looks up the array's device address (with that device current) and remembers it;
  * make that first call outside any stream capture. Every call on a device shares the one array: calls must be
  * stream-ordered with respect to each other, since two that overlap on the GPU would overwrite each other's
- * states. Nothing in the array has to start at zero; each call writes every state it later reads.
+ * states. Nothing in the array has to start at zero; each call writes every state it later reads. The remembered
+ * address belongs to the device's primary context: after cudaDeviceReset the library must be reloaded.
  */
 int decode_attn_fp8_static(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *out,
                            int B, int Hq, int Hkv, int n_slots, int pages_per_slot, int max_kv_len, int window,
@@ -196,22 +204,31 @@ int decode_attn_fp8_static(const void *q, const void *kv_cache, const void *lens
 int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out, void *stream);
 
 /*
- * decode_attn_merge across GPUs without a collective library: the exchange and the merge in ONE kernel over peer
- * memory (NVLink). Each rank r has left its rows' states in a buffer that every peer can address
- * (parts[r], fp32 [rows][NCB_PART_FLOATS], e.g. written by decode_attn_fp8_partial), and owns an array of
- * `world` uint32 flags that every peer can address (flags[r]). The kernel, on rank `rank`:
- *   1. publishes: stores `epoch` into flags[q][rank] of every rank q (its states were written by earlier work on
- *      this stream);
- *   2. waits, with a bound of roughly a second, until its own flags[rank][q] >= epoch for every q;
- *   3. loads every rank's state of each row with plain peer loads and merges them into out bf16 [rows][128].
- * parts and flags are host arrays of `world` (<= 8) device pointers, the same on every rank. `epoch` must grow by
- * one per call on every rank and start above the flags' initial contents (zero them and synchronise the ranks
- * once). A rank may run ahead of a peer by at most one call, so alternate between two `parts` buffers from call
- * to call. If the wait runs out, NCB_DEV_WAIT_TIMEOUT is set in *status and `out` is not meaningful; the kernel
- * still returns. No counterpart in the reference, which runs on one GPU.
+ * decode_attn_fp8 for sequences whose positions are sharded by length over the GPUs of one box (each rank's cache
+ * holds a contiguous slice of every sequence; lens are the LOCAL lengths): the split-KV launch, then ONE launch that
+ * merges this rank's chunk states, exchanges the (m, l, o) state of every row with the other ranks over peer memory
+ * (NVLink) and merges across ranks, so that every rank ends with the full out bf16 [B][Hq][128], bit-identical on all
+ * ranks (states are merged in rank order). No collective library on the data path. The merge rule of
+ * decode.cu:548,661-670 is associative, which is what makes the sharding exact. No counterpart in the reference,
+ * which runs on one GPU.
+ *   inbox   host array of `world` (<= 8) device pointers, the same on every rank: inbox[r] is rank r's buffer of
+ *           2 * world * B * Hq * NCB_PART_FLOATS floats, addressable from every GPU (peer-mapped / symmetric memory)
+ *   flags   host array of `world` device pointers: flags[r] is rank r's world * B * Hq uint32 words, peer-addressable,
+ *           zeroed once before the first call (and the ranks synchronised)
+ *   epoch   this rank's own two device uint32 words, zeroed once; the kernel advances the first by one per call, so
+ *           the launch arguments never change and a step can be captured in a CUDA graph and replayed
+ * Per row the second launch: stores the rank state into every rank's inbox (plain peer stores), publishes the row's
+ * flag to every rank (release, system scope), waits — bounded, about half a second — for every rank's flag of the same
+ * row in its own memory, and merges the `world` states from its own inbox. Every rank must make the same sequence of
+ * calls with the same B and Hq; a rank may run ahead of a peer by at most one call, and the inbox's two halves
+ * alternate between calls so nothing still being read is overwritten. If a wait runs out, NCB_DEV_WAIT_TIMEOUT is set
+ * in *status and `out` is not meaningful; the kernel still returns. Other arguments as decode_attn_fp8.
  */
-int decode_attn_merge_peers(const void *const *parts, void *const *flags, int world, int rank, unsigned epoch,
-                            long long rows, void *out, void *status, void *stream);
+int decode_attn_fp8_sharded(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
+                            void *workspace, long long workspace_bytes, void *out, int B, int Hq, int Hkv, int n_slots,
+                            int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale,
+                            const void *const *inbox, void *const *flags, int world, int rank, void *epoch,
+                            void *status, void *stream);
 
 /* ---- library decode_step ------------------------------------------------------------------------------------
  * The rest of a decode step for at most 16 rows; replaces the reference's Hopper-only slot GEMM k_wgmma with its
@@ -235,7 +252,8 @@ int add_rms_norm(void *h, const void *y, void *n, long long rows, int C, void *s
 /* u bf16 [count] = relu(u)^2 in place (the MLP activation, decode.cu:170-208 EPI_RELU2); count a multiple of 8. */
 int relu2_inplace(void *u, long long count, void *stream);
 /* tokens[row] (int64) = argmax of logits fp32 [rows][vocab], ties to the lowest id; pos[row] (int32) += 1; with
- * trace (int64 [rows][trace_stride], may be NULL) also trace[row][new pos[row]] = the choice. */
+ * trace (int64 [rows][trace_stride], may be NULL) also trace[row][new pos[row]] = the choice. Rows with pos[row] < 0
+ * are idle: token and position stay as they are. */
 int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int vocab, void *trace, int trace_stride,
                   void *stream);
 
@@ -245,7 +263,8 @@ int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int voc
  * nucleus of mass top_p (keep e >= e*, the least e whose cumulative mass from below exceeds (1 - top_p) of the
  * total; bisection on IEEE bits) and sampled by Gumbel-max with Philox4x32-10 noise at counter (token id,
  * pos - first), key seed. Ties to the lowest id; `allow` (uint32 [rows][vocab / 32], may be NULL) masks tokens.
- * tokens[row] = choice, pos[row] += 1, trace as greedy_choice (-1 logged if nothing is allowed).
+ * tokens[row] = choice, pos[row] += 1, trace as greedy_choice (-1 logged if nothing is allowed); idle rows
+ * (pos[row] < 0) are left alone.
  * logits fp32 [rows][vocab]; probs fp32 [rows][vocab] scratch; temperature, top_p fp32 [rows]; seed uint64 [rows];
  * first int32 [rows]; vocab a multiple of 32.
  */

@@ -100,11 +100,16 @@ def decode_step_attention(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tens
                           cache: Fp8KVCache, Hq: int, max_kv_len: int, slot_map: Tensor | None = None,
                           window: int = 0, chunk_pages: int = 0, softmax_scale: float | None = None,
                           workspace: Tensor | None = None, out: Tensor | None = None,
-                          status: Tensor | None = None) -> Tensor:
+                          status: Tensor | None = None, slots: "list[int] | None" = None) -> Tensor:
     """kv_append + decode_attention for one new token per sequence in two launches instead of three: the attention
     kernel norms, rotates, quantises and stores the token's q, k, v itself, then attends over positions
     [.., pos + 1). Same cache bytes and outputs as the two calls; q is not returned. Rows must address distinct
-    slots; max_kv_len bounds pos + 1."""
+    slots (two rows of one slot would race on its pages); a caller that has the slot list on the host passes it as
+    `slots` (the host copy of slot_map, idle rows included) and gets a ValueError for duplicates. max_kv_len bounds
+    pos + 1. Rows with pos < 0 are idle: nothing appended, a zero output row."""
+    if slots is not None and len(set(slots)) != len(slots):
+        raise ValueError(f"decode_step_attention: rows share a slot ({sorted(s for s in set(slots) if slots.count(s) > 1)}); "
+                         "use kv_append + decode_attention for rows of one sequence")
     rows, Hkv = qkv.shape[0], cache.kv_heads
     assert qkv.dtype == torch.bfloat16 and qkv.stride(-1) == 1 and qkv.shape[1] == (Hq + 2 * Hkv) * HEAD_DIM
     assert pos.dtype == torch.int32 and pos.shape == (rows,) and pos.is_contiguous()

@@ -36,7 +36,8 @@
 #include <algorithm>
 #include <functional>
 #include <mutex>
-#include <unordered_map>
+#include <map>
+#include <array>
 #include <vector>
 
 #include "kv_row.cuh"
@@ -160,6 +161,13 @@ static __device__ __forceinline__ float head_sum(float v) {
 
 /* ---- split-KV kernel ---------------------------------------------------------------------------------------- */
 
+/* A row the kernels refuse (and flag): its length or slot lies outside the cache or, where the row's own token is
+ * appended first, beyond the rotary table (table_len 0: no such check). The split and the merge kernels share the
+ * test, so a refused row has no states written and none merged: its output is a zero row. */
+static __device__ __forceinline__ bool row_rejected(int len, int slot, int pages_per_slot, int n_slots, int table_len) {
+    return len > pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= n_slots || (table_len > 0 && len > table_len);
+}
+
 /* APPEND: the block first does kv_append_fp8's work for its own heads of the new token (the q rows of its group
  * into shared memory; if its chunk holds the new position, the k and v rows into the cache in global memory and
  * into the landed page in shared memory), so a decode step needs no separate append launch and no round trip of q
@@ -188,10 +196,11 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     const int b = MULTI ? a.group_start[blockIdx.z] : (int)blockIdx.z;
     const int group_rows = MULTI ? min(a.group_start[blockIdx.z + 1] - b, 4 * NT / G) : 1;
     const int S = group_rows * G;
-    const int len = a.lens[b + group_rows - 1] + a.len_add; /* the longest row's: rows ascend in position */
+    const int given = a.lens[b + group_rows - 1]; /* the longest row's: rows ascend in position */
+    if (given < 0) return; /* an idle row: nothing appended, nothing attended, nothing flagged; the merge writes zeros */
+    const int len = given + a.len_add;
     const int slot = a.slot_map ? a.slot_map[b] : b;
-    if (len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots ||
-        (APPEND && (len < 1 || len > a.table_len))) {
+    if (row_rejected(len, slot, a.pages_per_slot, a.n_slots, APPEND ? a.table_len : 0)) {
         if (tid == 0 && chunk == 0 && kvh == 0) flag(a.status, APPEND ? NCB_DEV_BAD_POSITION : NCB_DEV_BAD_LENGTH);
         return; /* the merge kernel makes the same test and writes zeros */
     }
@@ -494,30 +503,34 @@ struct MergeArgs {
     int Hq, window, chunk_pages, n_slots, pages_per_slot, max_chunks, len_add;
     bf16 *out;       /* [rows][128] normalised, or NULL */
     float *part_out; /* [rows][PART] merged state, or NULL */
+    int table_len;   /* > 0: rows longer than this were refused by the appending split kernel */
 };
+
+/* How many chunk states the split kernel left for `row`: 0 for idle and refused rows. */
+static __device__ __forceinline__ int states_of(const MergeArgs &a, long long row) {
+    if (a.n_parts > 0) return a.n_parts;
+    const int b = (int)(row / a.Hq), given = a.lens[b], slot = a.slot_map ? a.slot_map[b] : b;
+    if (given < 0) return 0;
+    const int len = given + a.len_add;
+    if (row_rejected(len, slot, a.pages_per_slot, a.n_slots, a.table_len)) return 0;
+    return min(span_of(len, a.window, a.chunk_pages).n_chunks, a.max_chunks);
+}
 
 constexpr int MERGE_WARPS = 4;
 
-/* One block per row; warp w folds states w, w + 4, ... into a running state (its loads are independent of the fold,
- * so they overlap), then the four running states are merged through shared memory. Lane = four output dims. */
-__global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
+/* The states of one row folded by a block of MERGE_WARPS warps: warp w folds states w, w + 4, ... into a running
+ * state (its loads are independent of the fold, so they overlap), then warp 0 merges the four running states through
+ * shared memory. Lane = four output dims. Returns true in warp 0, whose lanes then hold the row's un-normalised state
+ * (top in log2 units, lsum, acc); the other warps are done. */
+static __device__ __forceinline__ bool merge_row_states(const MergeArgs &a, long long row, float &top, float &lsum,
+                                                        float4 &acc) {
     __shared__ float sm[MERGE_WARPS], sl[MERGE_WARPS];
     __shared__ float4 so[MERGE_WARPS][32];
-    const long long row = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    /* launched with programmatic stream serialisation: wait here until the grid before it (the split kernel, whose
-     * states this reads) has completed and its writes are visible; a no-op after an ordinary launch */
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    int n = a.n_parts;
-    if (n == 0) {
-        const int b = (int)(row / a.Hq), len = a.lens[b] + a.len_add, slot = a.slot_map ? a.slot_map[b] : b;
-        if (!(len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots)) {
-            n = min(span_of(len, a.window, a.chunk_pages).n_chunks, a.max_chunks);
-        }
-    }
+    const int n = states_of(a, row);
     const float *st = a.parts + row * a.row_stride;
-    float top = -INFINITY, lsum = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    top = -INFINITY, lsum = 0.f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 2
     for (int p = warp; p < n; p += MERGE_WARPS) {
         const float *s = st + p * a.part_stride;
@@ -533,7 +546,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
     if (lane == 0) sm[warp] = top, sl[warp] = lsum;
     so[warp][lane] = acc;
     __syncthreads();
-    if (warp != 0) return;
+    if (warp != 0) return false;
     top = fmaxf(fmaxf(sm[0], sm[1]), fmaxf(sm[2], sm[3]));
     lsum = 0.f;
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -544,20 +557,37 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
         lsum += c * sl[w];
         acc.x += c * o.x, acc.y += c * o.y, acc.z += c * o.z, acc.w += c * o.w;
     }
+    return true;
+}
+
+/* out[row][4 lane .. 4 lane + 3] = acc / lsum as bf16 (the reference's __fdiv_rn then round, decode.cu:674); a row
+ * without any position gives zeros. */
+static __device__ __forceinline__ void store_normalised(bf16 *out, long long row, int lane, float lsum, const float4 &acc) {
+    const bool any = lsum > 0.f;
+    const float x = any ? __fdiv_rn(acc.x, lsum) : 0.f, y = any ? __fdiv_rn(acc.y, lsum) : 0.f;
+    const float z = any ? __fdiv_rn(acc.z, lsum) : 0.f, w = any ? __fdiv_rn(acc.w, lsum) : 0.f;
+    uint2 u;
+    *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(x, y);
+    *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(z, w);
+    *reinterpret_cast<uint2 *>(out + row * HEAD_DIM + 4 * lane) = u;
+}
+
+/* One block per row. */
+__global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
+    const long long row = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    /* launched with programmatic stream serialisation: wait here until the grid before it (the split kernel, whose
+     * states this reads) has completed and its writes are visible; a no-op after an ordinary launch */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float top, lsum;
+    float4 acc;
+    if (!merge_row_states(a, row, top, lsum, acc)) return;
     if (a.part_out) {
         float *o = a.part_out + row * PART;
         if (lane == 0) *reinterpret_cast<float4 *>(o) = make_float4(top, lsum, 0.f, 0.f);
         *reinterpret_cast<float4 *>(o + 4 + 4 * lane) = acc;
     }
-    if (a.out) {
-        const bool any = lsum > 0.f;
-        const float x = any ? __fdiv_rn(acc.x, lsum) : 0.f, y = any ? __fdiv_rn(acc.y, lsum) : 0.f;
-        const float z = any ? __fdiv_rn(acc.z, lsum) : 0.f, w = any ? __fdiv_rn(acc.w, lsum) : 0.f;
-        uint2 u;
-        *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(x, y);
-        *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(z, w);
-        *reinterpret_cast<uint2 *>(a.out + row * HEAD_DIM + 4 * lane) = u;
-    }
+    if (a.out) store_normalised(a.out, row, lane, lsum, acc);
 }
 
 /* The same merge with one WARP per row, for prefill passes: tens of thousands of rows with one or two states each,
@@ -568,12 +598,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_rows(MergeArgs a) {
     const int lane = threadIdx.x & 31;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (row >= a.rows) return;
-    int n = 0;
-    {
-        const int b = (int)(row / a.Hq), len = a.lens[b] + a.len_add, slot = a.slot_map ? a.slot_map[b] : b;
-        if (!(len < 0 || len > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots))
-            n = min(span_of(len, a.window, a.chunk_pages).n_chunks, a.max_chunks);
-    }
+    const int n = states_of(a, row);
     const float *st = a.parts + row * a.row_stride;
     float top = -INFINITY, lsum = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -589,47 +614,62 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_rows(MergeArgs a) {
         acc.z = acc.z * c0 + o.z * c1, acc.w = acc.w * c0 + o.w * c1;
         top = next;
     }
-    const bool any = lsum > 0.f;
-    const float x = any ? __fdiv_rn(acc.x, lsum) : 0.f, y = any ? __fdiv_rn(acc.y, lsum) : 0.f;
-    const float z = any ? __fdiv_rn(acc.z, lsum) : 0.f, w = any ? __fdiv_rn(acc.w, lsum) : 0.f;
-    uint2 u;
-    *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(x, y);
-    *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(z, w);
-    *reinterpret_cast<uint2 *>(a.out + row * HEAD_DIM + 4 * lane) = u;
+    store_normalised(a.out, row, lane, lsum, acc);
 }
 
-/* ---- merge over peer memory ---------------------------------------------------------------------------------- */
+/* ---- merge + exchange over peer memory ------------------------------------------------------------------------ */
 
 constexpr int MAX_PEERS = 8;
 constexpr uint32_t PEER_WAIT_POLLS = 1u << 22; /* x ~100 ns sleep each: roughly half a second */
 
-struct PeerArgs {
-    const float *parts[MAX_PEERS]; /* rank q's states [rows][PART], addressable from this GPU */
-    uint32_t *flags[MAX_PEERS];    /* rank q's flags [world]: flags[q][r] = last epoch rank r published */
+/* Every rank owns an "inbox" [2][world][rows][PART] fp32 and flags [world][rows] uint32 that all peers can address,
+ * and a private device word pair `epoch` = (calls completed, blocks arrived in the current call). */
+struct ExchangeArgs {
+    MergeArgs local;            /* this rank's chunk states (the split kernel's workspace) */
+    float *inbox[MAX_PEERS];    /* rank q's inbox */
+    uint32_t *flags[MAX_PEERS]; /* rank q's flags: flags[q][r * rows + row] = last epoch rank r delivered `row` */
     int world, rank;
-    uint32_t epoch;
-    long long rows;
-    bf16 *out;
+    uint32_t *epoch;
     int *status;
 };
 
-/* One block per row, one warp per block; lane = four output dims. Every block publishes nothing but waits itself:
- * block 0 does the publishing for the rank. Blocks only ever wait for other GPUs' kernels, never for one another. */
-__global__ void __launch_bounds__(32) k_merge_peers(PeerArgs a) {
-    const long long row = blockIdx.x;
-    const int lane = threadIdx.x;
-    asm volatile("griddepcontrol.wait;" ::: "memory"); /* this rank's states are complete and visible */
-    if (row == 0 && lane < a.world) {
-        __threadfence_system();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flags[lane] + a.rank), "r"(a.epoch) : "memory");
+/* The chunk merge of k_merge and the cross-GPU exchange in one launch, one block per row: merge the row's local chunk
+ * states; PUSH the rank state into every rank's inbox (plain stores over NVLink, one direction, no read round trip);
+ * publish the row's flag to every rank; wait (bounded) until every rank's flag for this row has arrived here; merge
+ * the `world` states from this rank's own inbox in rank order, so every rank computes bit-identical outputs. Rows are
+ * independent: a block waits only for the same row's blocks on the other GPUs, never for blocks of its own grid.
+ * The call's number comes from a device word the kernel itself advances (the last block to finish bumps it), so
+ * the launch arguments never change and the step can be captured in a CUDA graph. Inboxes alternate between two
+ * halves by the call's parity: a rank can run at most one call ahead of a peer (it needs the peer's flags of call e to
+ * finish call e), so what it writes never lands in a half a slower peer still reads. */
+__global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_exchange(ExchangeArgs a) {
+    const long long row = blockIdx.x, rows = a.local.rows;
+    const int lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.wait;" ::: "memory"); /* this rank's chunk states are complete and visible */
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(a.epoch) + 1u;
+    float top, lsum;
+    float4 acc;
+    if (!merge_row_states(a.local, row, top, lsum, acc)) return;
+    const size_t half = (size_t)(epoch & 1u) * a.world * rows * PART;
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; q++) {
+        if (q < a.world) {
+            float *o = a.inbox[q] + half + ((size_t)a.rank * rows + row) * PART;
+            if (lane == 0) *reinterpret_cast<float4 *>(o) = make_float4(top, lsum, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(o + 4 + 4 * lane) = acc;
+        }
     }
-    if (lane < a.world) { /* lane q waits for rank q */
-        const uint32_t *mine = a.flags[a.rank] + lane;
+    __syncwarp(); /* the warp's stores precede the flags below */
+    if (lane < a.world) { /* lane q: deliver to rank q, then wait for rank q */
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flags[lane] + (size_t)a.rank * rows + row), "r"(epoch)
+                     : "memory");
+        const uint32_t *mine = a.flags[a.rank] + (size_t)lane * rows + row;
         bool ok = false;
         for (uint32_t polls = 0; polls < PEER_WAIT_POLLS; polls++) {
             uint32_t seen;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-            if ((int32_t)(seen - a.epoch) >= 0) {
+            if ((int32_t)(seen - epoch) >= 0) {
                 ok = true;
                 break;
             }
@@ -638,20 +678,22 @@ __global__ void __launch_bounds__(32) k_merge_peers(PeerArgs a) {
         if (!ok) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
     }
     __syncwarp();
-    float top = -INFINITY, lsum = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float *in = a.inbox[a.rank] + half + (size_t)row * PART;
     float mq[MAX_PEERS], lq[MAX_PEERS];
     float4 oq[MAX_PEERS];
+    top = -INFINITY;
 #pragma unroll
-    for (int q = 0; q < MAX_PEERS; q++) { /* all loads first: they cross NVLink and overlap */
+    for (int q = 0; q < MAX_PEERS; q++) { /* written by other GPUs: bypass this SM's L1 */
         if (q < a.world) {
-            const float *s = a.parts[q] + row * PART;
+            const float *s = in + (size_t)q * rows * PART;
             mq[q] = __ldcv(s);
             lq[q] = __ldcv(s + 1);
             oq[q] = __ldcv(reinterpret_cast<const float4 *>(s + 4) + lane);
             top = fmaxf(top, mq[q]);
         }
     }
+    lsum = 0.f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int q = 0; q < MAX_PEERS; q++) {
         if (q < a.world) {
@@ -660,25 +702,33 @@ __global__ void __launch_bounds__(32) k_merge_peers(PeerArgs a) {
             acc.x += c * oq[q].x, acc.y += c * oq[q].y, acc.z += c * oq[q].z, acc.w += c * oq[q].w;
         }
     }
-    const bool any = lsum > 0.f;
-    const float x = any ? __fdiv_rn(acc.x, lsum) : 0.f, y = any ? __fdiv_rn(acc.y, lsum) : 0.f;
-    const float z = any ? __fdiv_rn(acc.z, lsum) : 0.f, w = any ? __fdiv_rn(acc.w, lsum) : 0.f;
-    uint2 u;
-    *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(x, y);
-    *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(z, w);
-    *reinterpret_cast<uint2 *>(a.out + row * HEAD_DIM + 4 * lane) = u;
+    store_normalised(a.local.out, row, lane, lsum, acc);
+    if (lane == 0) { /* the last row to finish closes the call */
+        __threadfence();
+        if (atomicAdd(a.epoch + 1, 1u) == (uint32_t)rows - 1u) {
+            a.epoch[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(a.epoch) = epoch;
+        }
+    }
 }
 
 /* ---- host side ---------------------------------------------------------------------------------------------- */
 
-static int sm_count() {
-    static const int count = [] {
-        int device = 0, c = 0;
-        if (cudaGetDevice(&device) != cudaSuccess) return 148;
-        if (cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || c <= 0) return 148;
-        return c;
-    }();
-    return count;
+/* Host-side facts remembered per device ordinal, under one lock (entry points may be called from several threads). */
+static std::mutex g_device_lock;
+constexpr int MAX_DEVICES = 64;
+
+static int sm_count() { /* of the current device */
+    static int count[MAX_DEVICES] = {};
+    int device = 0, c = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return 148;
+    std::lock_guard<std::mutex> guard(g_device_lock);
+    if (!count[device]) {
+        if (cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || c <= 0) c = 148;
+        count[device] = c;
+    }
+    return count[device];
 }
 
 static int pages_of(int len) { return (len + PAGE_TOKENS - 1) / PAGE_TOKENS; }
@@ -694,14 +744,15 @@ struct AppendIn {
 };
 
 template <int NT, bool APPEND, bool MULTI = false> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
-    static bool done[64] = {};
+    static bool done[MAX_DEVICES] = {};
     int device = 0;
     cudaError_t rc = cudaGetDevice(&device);
     if (rc != cudaSuccess) return rc;
-    if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
+    std::lock_guard<std::mutex> guard(g_device_lock);
+    if (device >= 0 && device < MAX_DEVICES && done[device]) return cudaSuccess;
     rc = cudaFuncSetAttribute(k_decode_attn<NT, APPEND, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               (int)ATTN_SMEM);
-    if (rc == cudaSuccess && device >= 0 && device < 64) done[device] = true;
+    if (rc == cudaSuccess && device >= 0 && device < MAX_DEVICES) done[device] = true;
     return rc;
 }
 
@@ -715,8 +766,10 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
         return NCB_ERR_ARG;
     if (Hq / Hkv > 8) return NCB_ERR_UNSUPPORTED;
     if ((B > 65535 && !group_start) || Hkv > 65535) return NCB_ERR_ARG;
-    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
+    /* the default chunk follows the caller's max_kv_len, as decode_attn_workspace_bytes() computed it, before the
+     * bound is clipped to the cache: the workspace the caller sized is then never too small */
     if (chunk_pages == 0) chunk_pages = decode_attn_chunk_pages(B, Hkv, max_kv_len);
+    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
     if (B == 0) return NCB_OK;
     if ((!q && !app) || !kv_cache || !lens || !workspace) return NCB_ERR_ARG;
     if (((uintptr_t)q | (uintptr_t)kv_cache | (uintptr_t)workspace) % 16 != 0) return NCB_ERR_ALIGN;
@@ -786,10 +839,38 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream, bool warp_per_r
     return cudaLaunchKernelEx(&config, warp_per_row ? k_merge_rows : k_merge, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
+/* What the merge + exchange launch needs besides the local merge (decode_attn_fp8_sharded). */
+struct ExchangeIn {
+    const void *const *inbox;
+    void *const *flags;
+    int world, rank;
+    void *epoch;
+};
+
+static int launch_exchange(const MergeArgs &m, const ExchangeIn &x, void *status, cudaStream_t stream) {
+    ExchangeArgs a = {};
+    a.local = m;
+    for (int q = 0; q < x.world; q++) {
+        a.inbox[q] = (float *)x.inbox[q];
+        a.flags[q] = (uint32_t *)x.flags[q];
+    }
+    a.world = x.world, a.rank = x.rank, a.epoch = (uint32_t *)x.epoch, a.status = (int *)status;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)m.rows);
+    config.blockDim = dim3(MERGE_WARPS * 32);
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, k_merge_exchange, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+}
+
 static int attend(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
                   long long workspace_bytes, void *out, void *part_out, int B, int Hq, int Hkv, int n_slots,
                   int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale, void *status,
-                  void *stream, const AppendIn *app = nullptr) {
+                  void *stream, const AppendIn *app = nullptr, const ExchangeIn *exchange = nullptr) {
     if (!out && !part_out) return NCB_ERR_ARG;
     if (((uintptr_t)out | (uintptr_t)part_out) % 16 != 0) return NCB_ERR_ALIGN;
     const int rc = launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots,
@@ -800,7 +881,8 @@ static int attend(const void *q, const void *kv_cache, const void *lens, const v
     const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
     MergeArgs m = {(const float *)workspace, (long long)B * Hq, PART, (long long)max_chunks * PART, 0,
                    (const int32_t *)lens, (const int32_t *)slot_map, Hq, window, chunk_pages, n_slots, pages_per_slot,
-                   max_chunks, app ? 1 : 0, (bf16 *)out, (float *)part_out};
+                   max_chunks, app ? 1 : 0, (bf16 *)out, (float *)part_out, app ? app->table_len : 0};
+    if (exchange) return launch_exchange(m, *exchange, status, (cudaStream_t)stream);
     return launch_merge(m, (cudaStream_t)stream);
 }
 
@@ -812,11 +894,10 @@ static __device__ __align__(256) unsigned char g_static_scratch[NCB_STATIC_SCRAT
 
 /* The array's address on the current device, looked up once per device. */
 static int static_scratch(void **ptr) {
-    static std::mutex lock;
-    static void *address[64] = {};
+    static void *address[MAX_DEVICES] = {};
     int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return NCB_ERR_LAUNCH;
-    std::lock_guard<std::mutex> guard(lock);
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return NCB_ERR_LAUNCH;
+    std::lock_guard<std::mutex> guard(g_device_lock);
     if (!address[device]) {
         void *p = nullptr;
         if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return NCB_ERR_LAUNCH;
@@ -893,10 +974,11 @@ int decode_attn_plan_chunk_pages(const int *lens, int B, int Hkv, int max_kv_len
 
 int decode_attn_chunk_pages(int B, int Hkv, int max_kv_len) {
     if (B <= 0 || Hkv <= 0 || max_kv_len <= 0) return 1;
-    /* every sequence taken as max_kv_len long; remembered, since eager callers ask on every call */
+    /* every sequence taken as max_kv_len long; remembered, since eager callers ask on every call. The answer
+     * depends on the current device's SM count, so that is part of the key. */
     static std::mutex lock;
-    static std::unordered_map<unsigned long long, int> known;
-    const unsigned long long key = ((unsigned long long)B << 40) ^ ((unsigned long long)Hkv << 32) ^ (unsigned)max_kv_len;
+    static std::map<std::array<int, 4>, int> known;
+    const std::array<int, 4> key = {sm_count(), B, Hkv, max_kv_len};
     std::lock_guard<std::mutex> guard(lock);
     auto hit = known.find(key);
     if (hit != known.end()) return hit->second;
@@ -934,8 +1016,8 @@ int decode_attn_fp8_static(const void *q, const void *kv_cache, const void *lens
                            int chunk_pages, float softmax_scale, void *status, void *stream) {
     if (!out && B > 0) return NCB_ERR_ARG;
     if (B < 0 || Hq <= 0 || Hkv <= 0 || pages_per_slot <= 0 || max_kv_len < 0 || chunk_pages < 0) return NCB_ERR_ARG;
-    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
     if (chunk_pages == 0) chunk_pages = decode_attn_chunk_pages(B, Hkv, max_kv_len);
+    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
     const long long need = decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages);
     if (need > (long long)NCB_STATIC_SCRATCH_BYTES) return NCB_ERR_STATIC_LIMIT;
     void *scratch = nullptr;
@@ -972,7 +1054,7 @@ int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, cons
     /* every row's states follow its group's chunking, so the merge takes each row's length from span_lens */
     MergeArgs m = {(const float *)workspace, (long long)rows * Hq, PART, (long long)max_chunks * PART, 0,
                    (const int32_t *)span_lens, (const int32_t *)slot_map, Hq, 0, chunk, n_slots, pages_per_slot,
-                   max_chunks, 0, (bf16 *)out, nullptr};
+                   max_chunks, 0, (bf16 *)out, nullptr, 0};
     return launch_merge(m, (cudaStream_t)stream, true);
 }
 
@@ -984,31 +1066,22 @@ int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens,
                         max_kv_len, window, chunk_pages, softmax_scale, status, (cudaStream_t)stream);
 }
 
-int decode_attn_merge_peers(const void *const *parts, void *const *flags, int world, int rank, unsigned epoch,
-                            long long rows, void *out, void *status, void *stream) {
-    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world || rows < 0 || rows > 0x7fffffffLL)
-        return NCB_ERR_ARG;
-    if (rows == 0) return NCB_OK;
-    if (!parts || !flags || !out) return NCB_ERR_ARG;
-    PeerArgs a = {};
-    for (int q = 0; q < world; q++) {
-        if (!parts[q] || !flags[q]) return NCB_ERR_ARG;
-        if (((uintptr_t)parts[q] % 16) || ((uintptr_t)flags[q] % 4)) return NCB_ERR_ALIGN;
-        a.parts[q] = (const float *)parts[q];
-        a.flags[q] = (uint32_t *)flags[q];
+int decode_attn_fp8_sharded(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
+                            void *workspace, long long workspace_bytes, void *out, int B, int Hq, int Hkv, int n_slots,
+                            int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale,
+                            const void *const *inbox, void *const *flags, int world, int rank, void *epoch,
+                            void *status, void *stream) {
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world) return NCB_ERR_ARG;
+    if (B == 0) return NCB_OK; /* every rank passes the same B: nobody publishes, nobody waits */
+    if (!out || !inbox || !flags || !epoch) return NCB_ERR_ARG;
+    for (int r = 0; r < world; r++) {
+        if (!inbox[r] || !flags[r]) return NCB_ERR_ARG;
+        if (((uintptr_t)inbox[r] % 16) || ((uintptr_t)flags[r] % 4)) return NCB_ERR_ALIGN;
     }
-    if ((uintptr_t)out % 8) return NCB_ERR_ALIGN;
-    a.world = world, a.rank = rank, a.epoch = epoch, a.rows = rows, a.out = (bf16 *)out, a.status = (int *)status;
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)rows);
-    config.blockDim = dim3(32);
-    config.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute;
-    config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, k_merge_peers, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+    if ((uintptr_t)epoch % 8) return NCB_ERR_ALIGN;
+    const ExchangeIn x = {inbox, flags, world, rank, epoch};
+    return attend(q, kv_cache, lens, slot_map, workspace, workspace_bytes, out, nullptr, B, Hq, Hkv, n_slots,
+                  pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream, nullptr, &x);
 }
 
 int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out, void *stream) {
@@ -1017,7 +1090,7 @@ int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out,
     if (!parts || !out) return NCB_ERR_ARG;
     if (((uintptr_t)parts | (uintptr_t)out) % 16 != 0) return NCB_ERR_ALIGN;
     MergeArgs m = {(const float *)parts, rows, rows * PART, PART, n_parts, nullptr, nullptr, 1, 0, 1, 1, 1, n_parts, 0,
-                   (bf16 *)out, nullptr};
+                   (bf16 *)out, nullptr, 0};
     return launch_merge(m, (cudaStream_t)stream);
 }
 

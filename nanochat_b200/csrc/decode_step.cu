@@ -296,6 +296,7 @@ __global__ void __launch_bounds__(1024) k_greedy(const float *logits, long long 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (pos[row] < 0) return; /* an idle row (the whole block leaves): no choice, no advance */
     const float *z = logits + (size_t)row * vocab;
     float v = -INFINITY;
     int at = 0x7fffffff;
@@ -390,6 +391,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, V = a.vocab;
+    if (a.pos[b] < 0) return; /* an idle row (the whole block leaves): no choice, no advance */
     const float *s = a.logits + (size_t)b * V;
     float *e = a.probs + (size_t)b * V;
     const uint32_t *allow = a.allow ? a.allow + (size_t)b * (V / 32) : nullptr;

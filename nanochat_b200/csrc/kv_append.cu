@@ -44,7 +44,8 @@ __global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
         p = a.pos[row];
         slot = a.slot_map ? a.slot_map[row] : (int)row;
         valid = !(p < 0 || p >= a.table_len || p >= a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots);
-        if (!valid && t == 0 && which == 0) flag(a.status, NCB_DEV_BAD_POSITION);
+        /* a negative position marks an idle row (skipped silently); anything else outside the cache is flagged */
+        if (!valid && p >= 0 && t == 0 && which == 0) flag(a.status, NCB_DEV_BAD_POSITION);
     }
     const bool is_k = which >= a.Hq && which < a.Hq + a.Hkv, is_v = which >= a.Hq + a.Hkv;
     /* A prefill pass appends runs of consecutive positions of one slot. When the block's 16 rows are such a run and

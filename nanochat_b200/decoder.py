@@ -257,7 +257,7 @@ class Decoder:
                 "logits": torch.empty((rows, cfg.vocab), dtype=torch.float32, device=dev)}
 
     def fused_step(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int, buf: dict[str, Tensor],
-                   choose: bool = True) -> Tensor:
+                   choose: bool = True, slots: "list[int] | None" = None) -> Tensor:
         """One step on this package's kernels (GEMMs: see gemm_kernel): fp32 logits in buf["logits"]; with `choose`, tokens
         become the greedy choices and pos advances by one. 6 launches per layer: qkv GEMM (norm fused), split
         attention (append fused), merge, o GEMM + residual, up GEMM (norm fused) + relu^2, down GEMM + residual."""
@@ -285,7 +285,8 @@ class Decoder:
             gemm(h, layer.wqkv, None, qkv, cfg.qkv_width, C, 1, 0, then=layer.wo)
             ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
                                       cfg.n_heads, max_kv_len, slot_map=slot_map, window=self.windows[i],
-                                      chunk_pages=self.chunk_pages, workspace=workspace, out=att, status=self.status)
+                                      chunk_pages=self.chunk_pages, workspace=workspace, out=att, status=self.status,
+                                      slots=slots)
             gemm(att, layer.wo, h, h, C, A, 0, 1, then=layer.wup)
             gemm(h, layer.wup, None, u, Fd, C, 1, 2, then=layer.wdown)
             gemm(u, layer.wdown, h, h, C, Fd, 0, 1, then=layers[i + 1].wqkv if i + 1 < len(layers) else None)
@@ -357,7 +358,11 @@ class Decoder:
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
-            body()  # eager warm-up: first-use set-up outside capture; it writes position 0, rewritten on replay
+            # eager warm-up (first-use set-up has to happen outside capture) with every slot idle: a negative position
+            # appends nothing, attends nothing and advances nothing, so caches that already hold sequences (decode_from
+            # with a key not captured yet) are left as they are
+            pos.fill_(-1)
+            body()
             pos.zero_()
             tokens.zero_()
             side.synchronize()

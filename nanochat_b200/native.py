@@ -44,7 +44,8 @@ SIGNATURES = {
         "prefill_attn_fp8": ([c_ptr] * 6 + [c_int, c_ptr, c_ll, c_ptr] + [c_int] * 7 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_fp8_split": ([c_ptr] * 5 + [c_ll] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_merge": ([c_ptr, c_int, c_ll, c_ptr, c_ptr], c_int),
-        "decode_attn_merge_peers": ([c_ptr, c_ptr, c_int, c_int, ctypes.c_uint, c_ll, c_ptr, c_ptr, c_ptr], c_int),
+        "decode_attn_fp8_sharded": ([c_ptr] * 5 + [c_ll, c_ptr] + [c_int] * 8 + [c_float, c_ptr, c_ptr, c_int, c_int,
+                                                                               c_ptr, c_ptr, c_ptr], c_int),
     },
     "decode_step": {
         "skinny_gemm": ([c_ptr] * 4 + [c_int] * 5 + [c_ptr], c_int),

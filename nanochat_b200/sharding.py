@@ -10,8 +10,8 @@ the batch nor the placement, inference/decoder.py:124-125, which is what makes t
              (sequence, head); the states are all-gathered (NCCL over NVLink; 528 bytes per row and rank) and merged
              by the same kernel that merges chunks inside a GPU (the rule of model/kernels/decode.cu:548,661-670
              is associative). A new token is appended by the rank that owns the tail slice (append_owner).
-             attend_kv_sharded_fused replaces the NCCL all-gather + merge by one kernel that loads the peers'
-             states over NVLink itself (PeerStates)."""
+             attend_kv_sharded_fused replaces the local merge, the NCCL all-gather and the cross-rank merge by one
+             kernel that pushes the row states to the peers over NVLink itself (PeerStates)."""
 
 import ctypes
 from collections.abc import Sequence
@@ -77,15 +77,15 @@ def gather_states(part: Tensor, group: "dist.ProcessGroup | None" = None) -> Ten
 
 
 class PeerStates:
-    """Per-rank (m, l, o) states in memory every GPU of the group can address, for the fused exchange + merge
-    kernel (decode_attn_merge_peers): no collective library on the data path, each rank's merge kernel loads the
-    peers' states over NVLink itself after a bounded wait on per-rank epoch flags.
+    """What the fused exchange + merge (decode_attn_fp8_sharded) needs on every rank: an inbox and per-row flags in
+    memory every GPU of the group can address, and this rank's private call counter.
 
-    One symmetric allocation per rank: `world` uint32 flags (padded to 256 bytes), then two buffers of
-    (rows, 132) fp32 that calls alternate between, so a rank that runs one call ahead never overwrites states a
-    slower peer is still reading. Construction is collective (allocation, rendezvous, barrier)."""
-
-    FLAG_BYTES = 256
+    One symmetric allocation per rank: world * rows uint32 flags (padded to 256 bytes), then the inbox of
+    2 * world * rows states of 132 fp32 (two halves that calls alternate between). Each rank's merge kernel pushes
+    its row states into every rank's inbox with plain stores over NVLink, publishes per-row flags, waits (bounded)
+    for the peers' flags in its own memory and merges: no collective library on the data path. Construction is
+    collective (allocation, rendezvous, barrier); torch's symmetric memory is used for the allocation and the
+    pointer exchange only."""
 
     def __init__(self, batch: int, heads: int, group: "dist.ProcessGroup | None" = None,
                  device: "torch.device | None" = None):
@@ -93,46 +93,48 @@ class PeerStates:
 
         group = group or dist.group.WORLD
         device = device or torch.device("cuda", torch.cuda.current_device())
+        world = dist.get_world_size(group)
+        assert world <= 8
         self.batch, self.heads, self.rows = batch, heads, batch * heads
-        self.half_floats = self.rows * PART_FLOATS
-        floats = self.FLAG_BYTES // 4 + 2 * self.half_floats
+        self.flag_bytes = -(-world * self.rows * 4 // 256) * 256
+        floats = self.flag_bytes // 4 + 2 * world * self.rows * PART_FLOATS
         self.buffer = symm_mem.empty(floats, dtype=torch.float32, device=device)
         self.buffer.zero_()
         self.handle = symm_mem.rendezvous(self.buffer, group)
         self.world, self.rank = self.handle.world_size, self.handle.rank
-        assert self.world <= 8
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)  # (calls completed, rows arrived)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's flags are zero before anyone publishes
-        self.epoch = 0
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self._flags = (ctypes.c_void_p * self.world)(*self.handle.buffer_ptrs)
-
-    def next_part(self) -> Tensor:
-        """Advance to the next call and return this rank's (batch, heads, 132) state buffer for it."""
-        self.epoch += 1
-        at = self.FLAG_BYTES // 4 + (self.epoch % 2) * self.half_floats
-        return self.buffer[at:at + self.half_floats].view(self.batch, self.heads, PART_FLOATS)
-
-    def merge(self, out: Tensor | None = None) -> Tensor:
-        """Publish this rank's states of the current call, wait for every rank's, merge: (batch, heads, 128) bf16."""
-        if out is None:
-            out = torch.empty((self.batch, self.heads, 128), dtype=torch.bfloat16, device=self.buffer.device)
-        offset = self.FLAG_BYTES + (self.epoch % 2) * self.half_floats * 4
-        parts = (ctypes.c_void_p * self.world)(*(p + offset for p in self.handle.buffer_ptrs))
-        rc = cuda_library("decode_attn").decode_attn_merge_peers(
-            parts, self._flags, self.world, self.rank, self.epoch, self.rows, pointer(out), pointer(self.status),
-            stream())
-        check(rc, "decode_attn_merge_peers")
-        return out
+        self._inbox = (ctypes.c_void_p * self.world)(*(p + self.flag_bytes for p in self.handle.buffer_ptrs))
 
 
 def attend_kv_sharded_fused(q: Tensor, cache, local_lens: Tensor, max_local_len: int, peers: PeerStates,
-                            out: Tensor | None = None, **kwargs) -> Tensor:
-    """attend_kv_sharded with the all-gather and the merge replaced by one kernel over peer memory."""
-    from .attention import decode_attention_partial
+                            out: Tensor | None = None, slot_map: Tensor | None = None, window: int = 0,
+                            chunk_pages: int = 0, softmax_scale: float | None = None,
+                            workspace: Tensor | None = None) -> Tensor:
+    """attend_kv_sharded in two launches and without a collective: the split-KV kernel over this rank's slice, then
+    one kernel that merges the local chunks, exchanges the row states over peer memory and merges across ranks.
+    Every rank returns the full (B, Hq, 128) bf16 output, bit-identical across ranks. The call sequence must be the
+    same on every rank; it is safe to capture in a CUDA graph (the call counter lives on the device)."""
+    from .attention import workspace_bytes
 
-    decode_attention_partial(q, cache, local_lens, max_local_len, part=peers.next_part(), **kwargs)
-    return peers.merge(out)
+    B, Hq = q.shape[0], q.shape[1]
+    assert (B, Hq) == (peers.batch, peers.heads) and q.dtype == torch.bfloat16 and q.is_contiguous()
+    assert local_lens.dtype == torch.int32 and local_lens.shape == (B,) and local_lens.is_contiguous()
+    if workspace is None:
+        need = workspace_bytes(B, Hq, cache.kv_heads, min(max_local_len, cache.capacity), chunk_pages)
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    if out is None:
+        out = torch.empty_like(q)
+    rc = cuda_library("decode_attn").decode_attn_fp8_sharded(
+        pointer(q), pointer(cache.pages), pointer(local_lens), pointer(slot_map), pointer(workspace),
+        workspace.numel(), pointer(out), B, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, max_local_len,
+        window, chunk_pages, 128 ** -0.5 if softmax_scale is None else softmax_scale, peers._inbox, peers._flags,
+        peers.world, peers.rank, pointer(peers.epoch), pointer(peers.status), stream())
+    check(rc, "decode_attn_fp8_sharded")
+    return out
 
 
 def attend_kv_sharded(q: Tensor, cache, local_lens: Tensor, max_local_len: int,

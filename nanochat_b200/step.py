@@ -24,6 +24,8 @@ class DecodeStep:
                  batch: int, slot_map: Tensor | None = None, window: int = 0, chunk_pages: int = 0,
                  softmax_scale: float | None = None, max_kv_len: int | None = None):
         dev, Hkv = cache.device, cache.kv_heads
+        # the step appends inside the attention launch, which needs one row per slot: checked once, on the host
+        self.slots = list(range(batch)) if slot_map is None else slot_map.tolist()
         self.cache, self.Hq, self.batch = cache, Hq, batch
         self.cos, self.sin, self.q_gain, self.k_gain = cos, sin, q_gain, k_gain
         self.slot_map, self.window, self.softmax_scale = slot_map, window, softmax_scale
@@ -56,7 +58,7 @@ class DecodeStep:
         ops.decode_step_attention(self.qkv, self.q_gain, self.k_gain, self.cos, self.sin, self.pos, self.cache,
                                   self.Hq, self.max_kv_len, slot_map=self.slot_map, window=self.window,
                                   chunk_pages=self.chunk_pages, softmax_scale=self.softmax_scale,
-                                  workspace=self.workspace, out=self.out, status=self.status)
+                                  workspace=self.workspace, out=self.out, status=self.status, slots=self.slots)
         self.out_host.copy_(self.out, non_blocking=True)
 
     def capture(self) -> None:

@@ -262,58 +262,113 @@ def test_fused_append_attention_equals_the_two_kernels(Hq, Hkv):
     torch.cuda.synchronize()
     assert status.item() == 1 and not out[1].any()
     assert torch.equal(caches[0].pages[0], before[0])  # slot 0 belongs to the refused row
+    # a position inside the cache but past the rotary table is refused the same way: zeros, not stale states
+    status.zero_()
+    bad = pos.clone()
+    bad[1] = 320
+    out = torch.full((B, Hq, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ncb.decode_step_attention(qkv, gain, gain, cos[:320].contiguous(), sin[:320].contiguous(), bad, caches[0], Hq, 384,
+                              slot_map=slot_map, chunk_pages=2, out=out, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 1 and not out[1].any() and torch.isfinite(out.float()).all()
+    assert torch.equal(caches[0].pages[0], before[0])
+    # idle rows (negative position): no append, a zero output row, nothing flagged; the other rows as usual
+    status.zero_()
+    idle = pos.clone()
+    idle[0] = idle[2] = -1
+    before = caches[0].pages.clone()
+    out = ncb.decode_step_attention(qkv, gain, gain, cos, sin, idle, caches[0], Hq, int(pos.max()) + 1,
+                                    slot_map=slot_map, chunk_pages=2, status=status)
+    q = ncb.kv_append(qkv, gain, gain, cos, sin, idle, caches[1], Hq, slot_map=slot_map, status=status)
+    want = ncb.decode_attention(q, caches[1], torch.where(idle < 0, idle, idle + 1), int(pos.max()) + 1,
+                                slot_map=slot_map, chunk_pages=2, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and not out[0].any() and not out[2].any() and out[1].any() and out[3].any()
+    assert torch.equal(out, want)
+    for b in (0, 2):
+        assert torch.equal(caches[0].pages[slots[b]], before[slots[b]])
 
 
-def _peer_call(parts, flags, rank, epoch, rows, out, status):
-    import ctypes
-    from nanochat_b200.native import cuda_library, pointer, stream
-    world = len(parts)
-    p = (ctypes.c_void_p * world)(*(t.data_ptr() for t in parts))
-    f = (ctypes.c_void_p * world)(*(t.data_ptr() for t in flags))
-    return cuda_library("decode_attn").decode_attn_merge_peers(p, f, world, rank, epoch, rows, pointer(out),
-                                                               pointer(status), stream())
+class _OneGpuPeers:
+    """The buffers of `world` 'ranks' of decode_attn_fp8_sharded, all on this GPU: per rank an inbox
+    [2][world][rows][132] fp32 and flags [world][rows] uint32, plus rank 0's call counter."""
+
+    def __init__(self, world, rows):
+        import ctypes
+        self.world, self.rows = world, rows
+        self.inbox = [torch.zeros((2, world, rows, 132), dtype=torch.float32, device="cuda") for _ in range(world)]
+        self.flags = [torch.zeros((world, rows), dtype=torch.int32, device="cuda") for _ in range(world)]
+        self.epoch = torch.zeros(2, dtype=torch.int32, device="cuda")
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.p_inbox = (ctypes.c_void_p * world)(*(t.data_ptr() for t in self.inbox))
+        self.p_flags = (ctypes.c_void_p * world)(*(t.data_ptr() for t in self.flags))
+
+    def call(self, q, cache, lens, max_kv_len, rank=0, chunk_pages=2):
+        from nanochat_b200.native import cuda_library, pointer, stream
+        B, Hq = q.shape[0], q.shape[1]
+        need = ncb.workspace_bytes(B, Hq, cache.kv_heads, max_kv_len, chunk_pages)
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+        out = torch.full_like(q, float("nan"))
+        rc = cuda_library("decode_attn").decode_attn_fp8_sharded(
+            pointer(q), pointer(cache.pages), pointer(lens), None, pointer(workspace), workspace.numel(), pointer(out),
+            B, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, max_kv_len, 0, chunk_pages, SCALE,
+            self.p_inbox, self.p_flags, self.world, rank, pointer(self.epoch), pointer(self.status), stream())
+        return rc, out
 
 
-def test_peer_merge_on_one_gpu_with_flags_already_published():
-    """decode_attn_merge_peers with two 'ranks' whose buffers both live on this GPU and whose peer flag is already
-    at the epoch (no kernel waits for another): the result equals decode_attn_merge over the same states, and the
-    kernel publishes its own flag into both flag arrays."""
+def test_sharded_exchange_on_one_gpu_with_the_peer_already_delivered():
+    """decode_attn_fp8_sharded as rank 0 of two 'ranks' whose buffers both live on this GPU; the peer's states and
+    flags for the call are planted beforehand, so no kernel waits for another. The result equals decode_attn_merge
+    over the two slices' states bit for bit, the kernel delivers its own states and flags to both inboxes, advances
+    the call counter, and the next call uses the inbox's other half."""
     n, cuts = 700, [0, 320, 700]
     case = helpers.attention_case(1400, 8, 2, [n, 100])
     q = helpers.bits_bf16(case["q"]).cuda()
-    parts = []
+    parts, caches, lens_of = [], [], []
     for a, b in zip(cuts[:-1], cuts[1:]):
         sl = {**case, "lens": [max(0, min(b, L) - min(a, L)) for L in case["lens"]]}
         for key in ("k_bytes", "k_scale", "v_bytes", "v_scale"):
             sl[key] = [x[:, a:b] for x in case[key]]
         cache = load_cache(sl, max(max(sl["lens"]), 1))
         lens = torch.tensor(sl["lens"], dtype=torch.int32, device="cuda")
-        parts.append(ncb.decode_attention_partial(q, cache, lens, max_kv_len=max(max(sl["lens"]), 1)))
+        parts.append(ncb.decode_attention_partial(q, cache, lens, max_kv_len=max(max(sl["lens"]), 1), chunk_pages=2))
+        caches.append(cache)
+        lens_of.append(lens)
     want = ncb.merge_partials(torch.stack(parts))
-    flags = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(2)]
-    flags[0][1] = 7  # rank 1 has published epoch 7 into rank 0's flags
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    out = torch.empty_like(want)
-    assert _peer_call(parts, flags, 0, 7, 2 * 8, out, status) == 0
-    torch.cuda.synchronize()
-    assert status.item() == 0 and torch.equal(out, want)
-    assert flags[0].tolist() == [7, 7] and flags[1].tolist() == [7, 0]
+    rows = 2 * 8
+    peers = _OneGpuPeers(2, rows)
+    for call in (1, 2, 3):
+        peers.inbox[0][call % 2, 1] = parts[1].view(rows, 132)  # rank 1's states of this call, in rank 0's inbox
+        peers.flags[0][1] = call
+        rc, out = peers.call(q, caches[0], lens_of[0], 320)
+        torch.cuda.synchronize()
+        assert rc == 0 and peers.status.item() == 0
+        assert torch.equal(out, want), call
+        assert peers.epoch.tolist() == [call, 0]
+        assert peers.flags[0].tolist() == [[call] * rows] * 2 and peers.flags[1].tolist() == [[call] * rows, [0] * rows]
+        for inbox in peers.inbox:  # its own states went to both ranks, into the half of the call's parity
+            assert torch.equal(inbox[call % 2, 0], parts[0].view(rows, 132))
+    # the whole result against the float64 checker
+    check(case, helpers.bf16_bits(out.cpu()))
 
 
-def test_peer_merge_wait_runs_out_and_reports():
-    """A peer that never publishes: the bounded wait gives up after about half a second, the status word carries
-    NCB_DEV_WAIT_TIMEOUT and the context stays usable."""
+def test_sharded_exchange_wait_runs_out_and_reports():
+    """A peer that never delivers: the bounded wait gives up after about half a second, the status word carries
+    NCB_DEV_WAIT_TIMEOUT, the call counter still advances and the context stays usable."""
     import time
-    parts = [torch.zeros((4, 132), dtype=torch.float32, device="cuda") for _ in range(2)]
-    flags = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(2)]
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    out = torch.empty((4, 128), dtype=torch.bfloat16, device="cuda")
+    case = helpers.attention_case(1401, 4, 2, [70])
+    cache = load_cache(case, 128)
+    q = helpers.bits_bf16(case["q"]).cuda()
+    lens = torch.tensor([70], dtype=torch.int32, device="cuda")
+    peers = _OneGpuPeers(2, 4)
+    torch.cuda.synchronize()
     t0 = time.perf_counter()
-    assert _peer_call(parts, flags, 0, 1, 4, out, status) == 0
+    rc, _ = peers.call(q, cache, lens, 128)
     torch.cuda.synchronize()
     waited = time.perf_counter() - t0
-    assert status.item() == 2
+    assert rc == 0 and peers.status.item() == 2
     assert 0.05 < waited < 10.0
+    assert peers.epoch.tolist() == [1, 0]
     assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0  # the device still answers
 
 

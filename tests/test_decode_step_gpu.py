@@ -87,6 +87,16 @@ def test_embed_norm_and_greedy_choice():
     assert tokens.tolist() == logits.argmax(-1).tolist() and tokens[1] == 123 and tokens[2] == 65535
     assert pos.tolist() == [4, 5, 6, 7, 8]
     assert [int(trace[r, pos[r]]) for r in range(rows)] == tokens.tolist() and int((trace >= 0).sum()) == rows
+    # idle rows (negative position) keep their token and position and log nothing
+    pos = torch.tensor([3, -1, 5, -1, 7], dtype=torch.int32, device="cuda")
+    tokens.fill_(7)
+    trace.fill_(-1)
+    assert lib.greedy_choice(pointer(logits), pointer(tokens), pointer(pos), rows, 65536, pointer(trace), 16,
+                             stream()) == 0
+    torch.cuda.synchronize()
+    best = logits.argmax(-1).tolist()
+    assert tokens.tolist() == [best[0], 7, best[2], 7, best[4]] and pos.tolist() == [4, -1, 6, -1, 8]
+    assert int((trace >= 0).sum()) == 3
 
 
 @pytest.mark.parametrize("rows,C", [(1, 256), (33, 1280), (1024, 2048), (5, 4096), (7, 8)])

@@ -92,6 +92,36 @@ def test_generate_prefill_and_graph_decode_reproduce_reference_tokens():
     assert again == tokens
 
 
+def test_decode_from_with_an_uncaptured_key_leaves_live_caches_alone():
+    """decode_from on caches that already hold the prompts, with a step graph that is captured only then: the
+    capture's warm-up must not touch live positions (it runs with every slot idle). Same stream as generate(), which
+    captures before it prefills."""
+    dec, _, _ = gpu_decoder()
+    prompts = GOLDEN["prompt"].tolist()
+    want, _ = dec.generate(prompts, 6)
+    other, _, _ = gpu_decoder()
+    with torch.no_grad():
+        other.prefill(prompts, [0, 1])
+    filled = [c.pages.clone() for c in other.caches]
+    assert not other._graphs
+    got, _ = other.decode_from([p[-1] for p in prompts], [len(p) - 1 for p in prompts], 6)
+    assert got == want
+    n = len(prompts[0]) - 1  # the prefilled positions are untouched
+    for cache, before in zip(other.caches, filled):
+        now = ncb_cache_rows(cache, n)
+        assert all(torch.equal(a, b) for a, b in zip(now, ncb_cache_rows_from(before, cache, n)))
+
+
+def ncb_cache_rows(cache, n):
+    return [t.clone() for slot in range(2) for t in cache.read(slot, n)]
+
+
+def ncb_cache_rows_from(pages, like, n):
+    from nanochat_b200.kv_cache import Fp8KVCache
+    old = Fp8KVCache(like.n_slots, like.kv_heads, like.capacity, device=pages.device, pages=pages)
+    return ncb_cache_rows(old, n)
+
+
 def test_ragged_prompts_and_gqa_shapes_run_and_agree_with_rowwise_logits():
     """A GQA model with prompts of different lengths: generate() (prefill rows + graph decode) against the eager
     row-at-a-time path."""

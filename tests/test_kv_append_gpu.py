@@ -113,6 +113,22 @@ def test_out_of_range_rows_are_skipped_and_flagged():
     assert not host.pages[1].any()
 
 
+def test_idle_rows_are_skipped_silently():
+    """A negative position marks an idle row (a slot without a request): nothing written, nothing flagged."""
+    gen = torch.Generator().manual_seed(18)
+    Hq, Hkv = 2, 1
+    qkv = torch.randn(3, (Hq + 2 * Hkv) * HEAD_DIM, generator=gen).bfloat16()
+    ones = torch.ones(HEAD_DIM)
+    cos, sin = ncb.rotary_table(64, 1e4)
+    cache = ncb.Fp8KVCache(3, Hkv, 64)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pos = torch.tensor([5, -1, 3], dtype=torch.int32)
+    ncb.kv_append(qkv.cuda(), ones.cuda(), ones.cuda(), cos.cuda(), sin.cuda(), pos.cuda(), cache, Hq, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert cache.pages[0].any() and not cache.pages[1].any() and cache.pages[2].any()
+
+
 def test_native_error_on_bad_shapes():
     cache = ncb.Fp8KVCache(1, 3, 64)
     qkv = torch.zeros(1, (4 + 6) * HEAD_DIM, dtype=torch.bfloat16, device="cuda")

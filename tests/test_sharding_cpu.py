@@ -159,3 +159,16 @@ def test_no_collection_restores_the_collector():
         with no_collection():
             raise RuntimeError("capture failed")
     assert gc.isenabled()
+
+
+def test_decode_step_attention_refuses_rows_that_share_a_slot():
+    """The fused append + attention launch needs one row per slot; a caller that passes its host-side slot list gets
+    the duplicate reported before anything is launched (no GPU needed to see it)."""
+    import pytest
+    import torch
+
+    from nanochat_b200 import attention as ops
+    x = torch.zeros(3, 4 * 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="share a slot"):
+        ops.decode_step_attention(x, None, None, None, None, None, None, 2, 64, slots=[0, 1, 0])
+
