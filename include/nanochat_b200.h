@@ -263,8 +263,8 @@ int greedy_choice(const void *logits, void *tokens, void *pos, int rows, int voc
  * nucleus of mass top_p (keep e >= e*, the least e whose cumulative mass from below exceeds (1 - top_p) of the
  * total; bisection on IEEE bits) and sampled by Gumbel-max with Philox4x32-10 noise at counter (token id,
  * pos - first), key seed. Ties to the lowest id; `allow` (uint32 [rows][vocab / 32], may be NULL) masks tokens.
- * tokens[row] = choice, pos[row] += 1, trace as greedy_choice (-1 logged if nothing is allowed); idle rows
- * (pos[row] < 0) are left alone.
+ * tokens[row] = choice (-1 if the mask allows nothing; embed_norm reads a token outside the vocabulary as token 0),
+ * pos[row] += 1, trace as greedy_choice; idle rows (pos[row] < 0) are left alone.
  * logits fp32 [rows][vocab]; probs fp32 [rows][vocab] scratch; temperature, top_p fp32 [rows]; seed uint64 [rows];
  * first int32 [rows]; vocab a multiple of 32.
  */

@@ -460,7 +460,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample(SampleArgs a) {
         if (lane == 0) {
             const long long choice = at == 0x7fffffff ? -1 : at; /* -1: the mask allows nothing */
             const int next = a.pos[b] + 1;
-            a.tokens[b] = choice < 0 ? 0 : choice;
+            a.tokens[b] = choice; /* -1 reaches the host; as the next step's input the embedding reads it as token 0 */
             a.pos[b] = next;
             if (a.trace && next >= 0 && next < a.trace_stride) a.trace[(size_t)b * a.trace_stride + next] = choice;
         }

@@ -314,12 +314,14 @@ class Decoder:
 
     # ---- decode -----------------------------------------------------------------------------------------------
 
-    def _step_graph(self, batch: int, sampled: bool = False, chunk_pages: int = 0):
+    def _step_graph(self, batch: int, sampled: bool = False, chunk_pages: int = 0, masked: bool = False):
         """The captured step for `batch` slots 0 .. batch - 1: tokens, pos (device) -> chosen tokens; pos += 1; every
         choice is logged at its position in a (batch, capacity + 1) trace. `sampled` steps choose by temperature /
         nucleus / Gumbel-max (sample_choice) from per-slot controls, the others take the argmax. `chunk_pages` is
-        the attention chunk size baked into the graph (0: the library's choice for full-length slots)."""
-        key = (batch, sampled, chunk_pages)
+        the attention chunk size baked into the graph (0: the library's choice for full-length slots). `masked`
+        (sampled steps only) adds per-slot allowed-token bit masks, ctl["allow"] int32 (batch, vocab / 32), all ones
+        until a caller writes a row."""
+        key = (batch, sampled, chunk_pages, masked)
         if key in self._graphs:
             return self._graphs[key]
         self.chunk_pages = chunk_pages
@@ -340,15 +342,18 @@ class Decoder:
                    "seed": torch.zeros(batch, dtype=torch.long, device=dev),
                    "first": torch.zeros(batch, dtype=torch.int32, device=dev),
                    "probs": torch.empty((batch, V), dtype=torch.float32, device=dev)}
+            if masked:
+                ctl["allow"] = torch.full((batch, V // 32), -1, dtype=torch.int32, device=dev)
 
         def body():
             if fused:
-                self.fused_step(tokens, pos, slot_map, self.capacity, buf, choose=False)
+                self.fused_step(tokens, pos, slot_map, self.capacity, buf, choose=False, slots=list(range(batch)))
             else:
                 logits.copy_(self.head(self.hidden_rows(tokens, pos, slot_map, self.capacity, distinct_slots=True)))
             if sampled:
                 check(lib.sample_choice(pointer(logits), pointer(ctl["probs"]), pointer(ctl["temperature"]),
-                                        pointer(ctl["top_p"]), pointer(ctl["seed"]), pointer(ctl["first"]), None,
+                                        pointer(ctl["top_p"]), pointer(ctl["seed"]), pointer(ctl["first"]),
+                                        pointer(ctl.get("allow")),
                                         self.softcap, pointer(tokens), pointer(pos), batch, V, pointer(trace),
                                         trace.shape[1], stream()), "sample_choice")
             else:

@@ -196,7 +196,9 @@ def teacher_forced_against_the_cpu_decoder(cfg, seed, rows, steps, kernel):
     """`steps` positions of `rows` sequences through the fused step (this package's GEMM kernels, append fused into
     the attention launch) and through the CPU restatement, fed the same random tokens: fp32 logits compared. The two
     differ by bf16 roundings of activations (GEMM summation order; the tcgen05 kernel applies the norm as a scale of
-    the fp32 product), which the layers compound: the bound is 3 % of the largest logit, 0.5 % on average."""
+    the fp32 product): a one-ulp flip of a residual-stream element is 2^-9 of its value and every layer of a
+    random-init model adds and amplifies such flips, so the bound scales with depth: max 2 % + 0.2 % per layer of the
+    largest logit, a sixth of that on average (measured: 3 layers 0.9 % / 0.1 %, 20 layers 3.0 % / 0.5 %)."""
     from oracle.decoder import OracleDecoder
     w = cpu_weights(cfg, seed)
     dec = as_gpu(cfg, w, rows)
@@ -213,8 +215,8 @@ def teacher_forced_against_the_cpu_decoder(cfg, seed, rows, steps, kernel):
         want = oracle.step(tok, list(range(rows)))
         err = (got - want).abs()
         top = float(want.abs().max())
-        assert float(err.max()) <= 3e-2 * max(top, 1.0) and float(err.mean()) <= 5e-3 * max(top, 1.0), \
-            (t, float(err.max()), float(err.mean()), top)
+        bound = (2e-2 + 2e-3 * cfg["n_layers"]) * max(top, 1.0)
+        assert float(err.max()) <= bound and float(err.mean()) <= bound / 6, (t, float(err.max()), float(err.mean()), top)
     assert int(dec.status.item()) == 0
     # the appended cache rows: bit-exact wherever the bf16 qkv inputs agree, which is nearly everywhere
     host = ncb.Fp8KVCache(rows, cfg["n_kv_heads"], cfg["max_len"], device="cpu", pages=dec.caches[0].pages.cpu())
