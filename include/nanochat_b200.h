@@ -36,6 +36,7 @@ extern "C" {
 #define NCB_PAGE_BYTES 16896
 #define NCB_PART_FLOATS 132 /* one partial attention state: m, l, 2 pad, o[128]; fp32 */
 #define NCB_STATIC_SCRATCH_BYTES (8u << 20) /* the built-in scratch of decode_attn_fp8_static */
+#define NCB_PEER_STATE_BYTES 1056 /* one (m, l, o) state in a peer inbox of decode_attn_fp8_sharded */
 
 enum {
     NCB_OK = 0,
@@ -84,6 +85,24 @@ int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const
                   const void *pos, const void *slot_map, void *q_out, void *kv_cache, long long rows, int Hq,
                   int Hkv, long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot, void *status,
                   void *stream);
+
+/*
+ * kv_append_fp8 with the reference's optional value-embedding mix on v (attn_prologue, decode.cu:482-494; the
+ * reference's checkpoints have it on alternating layers, model/modeling.py:35-37): before it is quantised, each v
+ * head row becomes bf16(v + g ve[token]) with g = 2 sigmoid(ve_gate[kv head] . h).
+ *   h         bf16 [rows][C]: the layer's normed input rows (what the qkv projection read)
+ *   tokens    int64 [rows]: the rows' input tokens (outside [0, vocab): token 0, as embed_norm)
+ *   ve_table  bf16 [vocab][Hkv][128]; ve_gate fp32 [Hkv][C]; C a multiple of 256
+ * The dot product is summed in the reference's order (FMAs per warp lane over 8-element runs of 256-element chunks,
+ * then an xor butterfly), the sigmoid is evaluated in double precision and rounded once (the reference's fp32 expf
+ * is not reproducible on a CPU), products and sums individually rounded: v bytes and scales stay exact functions of
+ * the inputs (oracle/kv_append_oracle.c:oracle_kv_append_ve). ve_table == NULL is kv_append_fp8.
+ */
+int kv_append_fp8_ve(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                     const void *pos, const void *slot_map, void *q_out, void *kv_cache, long long rows, int Hq,
+                     int Hkv, long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot, const void *h,
+                     const void *tokens, const void *ve_table, const void *ve_gate, int C, int vocab, void *status,
+                     void *stream);
 
 /* ---- library decode_attn ------------------------------------------------------------------------------------ */
 
@@ -147,6 +166,15 @@ int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain
                          long long workspace_bytes, void *out, int B, int Hq, int Hkv, long long qkv_row_stride,
                          int table_len, int n_slots, int pages_per_slot, int max_kv_len, int window, int chunk_pages,
                          float softmax_scale, void *status, void *stream);
+
+/* decode_step_attn_fp8 with the value-embedding mix of kv_append_fp8_ve on the appended v rows (same arguments, same
+ * bytes). */
+int decode_step_attn_fp8_ve(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                            const void *pos, const void *slot_map, void *kv_cache, void *workspace,
+                            long long workspace_bytes, void *out, int B, int Hq, int Hkv, long long qkv_row_stride,
+                            int table_len, int n_slots, int pages_per_slot, int max_kv_len, int window,
+                            int chunk_pages, float softmax_scale, const void *h, const void *tokens,
+                            const void *ve_table, const void *ve_gate, int C, int vocab, void *status, void *stream);
 
 /*
  * Attention for a prefill pass (replaces k_attn over prompt rows, decode.cu:859-863,1041-1051): `rows` query rows,
@@ -212,23 +240,23 @@ int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out,
  * decode.cu:548,661-670 is associative, which is what makes the sharding exact. No counterpart in the reference,
  * which runs on one GPU.
  *   inbox   host array of `world` (<= 8) device pointers, the same on every rank: inbox[r] is rank r's buffer of
- *           2 * world * B * Hq * NCB_PART_FLOATS floats, addressable from every GPU (peer-mapped / symmetric memory)
- *   flags   host array of `world` device pointers: flags[r] is rank r's world * B * Hq uint32 words, peer-addressable,
- *           zeroed once before the first call (and the ranks synchronised)
+ *           2 * world * B * Hq * NCB_PEER_STATE_BYTES bytes, addressable from every GPU (peer-mapped / symmetric
+ *           memory), 16-byte aligned, zeroed once before the first call (and the ranks synchronised)
  *   epoch   this rank's own two device uint32 words, zeroed once; the kernel advances the first by one per call, so
  *           the launch arguments never change and a step can be captured in a CUDA graph and replayed
- * Per row the second launch: stores the rank state into every rank's inbox (plain peer stores), publishes the row's
- * flag to every rank (release, system scope), waits — bounded, about half a second — for every rank's flag of the same
- * row in its own memory, and merges the `world` states from its own inbox. Every rank must make the same sequence of
- * calls with the same B and Hq; a rank may run ahead of a peer by at most one call, and the inbox's two halves
- * alternate between calls so nothing still being read is overwritten. If a wait runs out, NCB_DEV_WAIT_TIMEOUT is set
- * in *status and `out` is not meaningful; the kernel still returns. Other arguments as decode_attn_fp8.
+ * Per row the second launch stores the rank state into every other rank's inbox (plain peer stores) as 8-byte words
+ * (fp32 value, call number) that validate themselves: no flags and no fences, an arrived word whose second half is
+ * the current call number holds this call's value. It then polls — bounded, about half a second — its own inbox until
+ * every word of the other ranks' states of the row carries the call number, and merges the `world` states. Every rank
+ * must make the same sequence of calls with the same B and Hq; a rank may run ahead of a peer by at most one call, and
+ * the inbox's two halves alternate between calls so nothing still being read is overwritten. If a wait runs out,
+ * NCB_DEV_WAIT_TIMEOUT is set in *status and the row's `out` is not written; the kernel still returns. Other
+ * arguments as decode_attn_fp8.
  */
 int decode_attn_fp8_sharded(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
                             void *workspace, long long workspace_bytes, void *out, int B, int Hq, int Hkv, int n_slots,
                             int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale,
-                            const void *const *inbox, void *const *flags, int world, int rank, void *epoch,
-                            void *status, void *stream);
+                            void *const *inbox, int world, int rank, void *epoch, void *status, void *stream);
 
 /* ---- library decode_step ------------------------------------------------------------------------------------
  * The rest of a decode step for at most 16 rows; replaces the reference's Hopper-only slot GEMM k_wgmma with its

@@ -14,6 +14,23 @@ from .native import check, cuda_library, pointer, stream
 PART_FLOATS = 132
 
 
+class ValueEmbed:
+    """The optional value-embedding mix of one layer for a pass of rows (reference model/kernels/decode.cu:482-494):
+    h (rows, C) bf16, the layer's normed input rows; tokens (rows,) int64; table (vocab, Hkv * 128) bf16; gate
+    (Hkv, C) fp32. C must be a multiple of 256."""
+
+    def __init__(self, h: Tensor, tokens: Tensor, table: Tensor, gate: Tensor):
+        assert h.dtype == table.dtype == torch.bfloat16 and gate.dtype == torch.float32 and tokens.dtype == torch.long
+        assert h.is_contiguous() and table.is_contiguous() and gate.is_contiguous() and tokens.is_contiguous()
+        assert h.shape[1] == gate.shape[1] and h.shape[1] % 256 == 0 and tokens.shape == (h.shape[0],)
+        assert table.shape[1] == gate.shape[0] * HEAD_DIM
+        self.h, self.tokens, self.table, self.gate = h, tokens, table, gate
+
+    def args(self) -> list:
+        return [pointer(self.h), pointer(self.tokens), pointer(self.table), pointer(self.gate), self.h.shape[1],
+                self.table.shape[0]]
+
+
 def rotary_table(positions: int, theta: float, device: "torch.device | str" = "cpu") -> tuple[Tensor, Tensor]:
     """cos, sin fp32 (positions, 64) of the angles t theta^(-2i/128), computed in fp64 and rounded once
     (reference model/modeling.py:169-176)."""
@@ -24,10 +41,11 @@ def rotary_table(positions: int, theta: float, device: "torch.device | str" = "c
 
 def kv_append(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tensor, sin: Tensor, pos: Tensor,
               cache: Fp8KVCache, Hq: int, slot_map: Tensor | None = None, q_out: Tensor | None = None,
-              status: Tensor | None = None) -> Tensor:
+              status: Tensor | None = None, ve: "ValueEmbed | None" = None) -> Tensor:
     """Norm + rotate q and k, quantise k and v to e4m3 with per-(token, head) scales and append them at `pos`.
     qkv (rows, (Hq + 2 Hkv) * 128) bf16, row stride free; gains fp32 (128,); cos/sin fp32 (T, 64); pos int32
-    (rows,); slot_map int32 (rows,) or None. Returns q_out (rows, Hq, 128) bf16."""
+    (rows,); slot_map int32 (rows,) or None; ve: the layer's value-embedding mix on v, if it has one. Rows with a
+    negative position are idle (skipped). Returns q_out (rows, Hq, 128) bf16."""
     rows, Hkv = qkv.shape[0], cache.kv_heads
     assert qkv.dtype == torch.bfloat16 and qkv.stride(-1) == 1 and qkv.shape[1] == (Hq + 2 * Hkv) * HEAD_DIM
     assert pos.dtype == torch.int32 and pos.shape == (rows,) and pos.is_contiguous()
@@ -36,10 +54,14 @@ def kv_append(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tensor, sin: Ten
     assert slot_map is None or (slot_map.dtype == torch.int32 and slot_map.shape == (rows,))
     if q_out is None:
         q_out = torch.empty((rows, Hq, HEAD_DIM), dtype=torch.bfloat16, device=qkv.device)
-    rc = cuda_library("kv_append").kv_append_fp8(
-        pointer(qkv), pointer(q_gain), pointer(k_gain), pointer(cos), pointer(sin), pointer(pos), pointer(slot_map),
-        pointer(q_out), pointer(cache.pages), rows, Hq, Hkv, qkv.stride(0), cos.shape[0], cache.n_slots,
-        cache.pages_per_slot, pointer(status), stream())
+    head = [pointer(qkv), pointer(q_gain), pointer(k_gain), pointer(cos), pointer(sin), pointer(pos), pointer(slot_map),
+            pointer(q_out), pointer(cache.pages), rows, Hq, Hkv, qkv.stride(0), cos.shape[0], cache.n_slots,
+            cache.pages_per_slot]
+    if ve is None:
+        rc = cuda_library("kv_append").kv_append_fp8(*head, pointer(status), stream())
+    else:
+        assert ve.h.shape[0] == rows and ve.gate.shape[0] == Hkv
+        rc = cuda_library("kv_append").kv_append_fp8_ve(*head, *ve.args(), pointer(status), stream())
     check(rc, "kv_append_fp8")
     return q_out
 
@@ -100,7 +122,8 @@ def decode_step_attention(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tens
                           cache: Fp8KVCache, Hq: int, max_kv_len: int, slot_map: Tensor | None = None,
                           window: int = 0, chunk_pages: int = 0, softmax_scale: float | None = None,
                           workspace: Tensor | None = None, out: Tensor | None = None,
-                          status: Tensor | None = None, slots: "list[int] | None" = None) -> Tensor:
+                          status: Tensor | None = None, slots: "list[int] | None" = None,
+                          ve: "ValueEmbed | None" = None) -> Tensor:
     """kv_append + decode_attention for one new token per sequence in two launches instead of three: the attention
     kernel norms, rotates, quantises and stores the token's q, k, v itself, then attends over positions
     [.., pos + 1). Same cache bytes and outputs as the two calls; q is not returned. Rows must address distinct
@@ -122,11 +145,14 @@ def decode_step_attention(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tens
     if out is None:
         out = torch.empty((rows, Hq, HEAD_DIM), dtype=torch.bfloat16, device=qkv.device)
     scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
-    rc = cuda_library("decode_attn").decode_step_attn_fp8(
-        pointer(qkv), pointer(q_gain), pointer(k_gain), pointer(cos), pointer(sin), pointer(pos), pointer(slot_map),
-        pointer(cache.pages), pointer(workspace), workspace.numel(), pointer(out), rows, Hq, Hkv, qkv.stride(0),
-        cos.shape[0], cache.n_slots, cache.pages_per_slot, max_kv_len, window, chunk_pages, scale, pointer(status),
-        stream())
+    head = [pointer(qkv), pointer(q_gain), pointer(k_gain), pointer(cos), pointer(sin), pointer(pos), pointer(slot_map),
+            pointer(cache.pages), pointer(workspace), workspace.numel(), pointer(out), rows, Hq, Hkv, qkv.stride(0),
+            cos.shape[0], cache.n_slots, cache.pages_per_slot, max_kv_len, window, chunk_pages, scale]
+    if ve is None:
+        rc = cuda_library("decode_attn").decode_step_attn_fp8(*head, pointer(status), stream())
+    else:
+        assert ve.h.shape[0] == rows and ve.gate.shape[0] == Hkv
+        rc = cuda_library("decode_attn").decode_step_attn_fp8_ve(*head, *ve.args(), pointer(status), stream())
     check(rc, "decode_step_attn_fp8")
     return out
 

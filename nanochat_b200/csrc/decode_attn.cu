@@ -70,6 +70,7 @@ struct AttnArgs {
     /* MULTI only: block z works on rows group_start[z] .. group_start[z + 1] - 1, which share a slot and hold
      * ascending positions; lens is per row then, and parts are indexed by row */
     const int32_t *group_start;
+    ValueEmbed ve; /* APPEND only; table == NULL: the layer has no value embedding */
 };
 
 /* ---- PTX wrappers ------------------------------------------------------------------------------------------- */
@@ -243,6 +244,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
             } else {
                 const bool is_k = item == G;
                 if (is_k) norm_rotate(x1, x2, a.k_gain, a.cs + tab, a.sn + tab, o);
+                else if (a.ve.table) ve_mix(x1, x2, a.ve, b, kvh, a.Hkv, t8, o);
                 uint8_t b1[VEC], b2[VEC];
                 const float scale = quantise(x1, x2, b1, b2);
                 const int j = p % PAGE_TOKENS;
@@ -531,17 +533,30 @@ static __device__ __forceinline__ bool merge_row_states(const MergeArgs &a, long
     const float *st = a.parts + row * a.row_stride;
     top = -INFINITY, lsum = 0.f;
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 2
-    for (int p = warp; p < n; p += MERGE_WARPS) {
-        const float *s = st + p * a.part_stride;
-        const float mp = s[0], lp = s[1];
-        const float4 o = *reinterpret_cast<const float4 *>(s + 4 + 4 * lane);
-        const float next = fmaxf(top, mp);
-        const float c0 = top == -INFINITY ? 0.f : ex2(top - next), c1 = mp == -INFINITY ? 0.f : ex2(mp - next);
-        lsum = lsum * c0 + lp * c1;
-        acc.x = acc.x * c0 + o.x * c1, acc.y = acc.y * c0 + o.y * c1;
-        acc.z = acc.z * c0 + o.z * c1, acc.w = acc.w * c0 + o.w * c1;
-        top = next;
+    constexpr int DEPTH = 4; /* states loaded before the first is folded: the loads' latencies overlap */
+    for (int p0 = warp; p0 < n; p0 += MERGE_WARPS * DEPTH) {
+        float mp[DEPTH], lp[DEPTH];
+        float4 o[DEPTH];
+#pragma unroll
+        for (int i = 0; i < DEPTH; i++) {
+            const int p = p0 + i * MERGE_WARPS;
+            if (p < n) {
+                const float *s = st + p * a.part_stride;
+                mp[i] = s[0], lp[i] = s[1];
+                o[i] = *reinterpret_cast<const float4 *>(s + 4 + 4 * lane);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < DEPTH; i++) {
+            if (p0 + i * MERGE_WARPS < n) { /* folded in index order, as a one-at-a-time loop would */
+                const float next = fmaxf(top, mp[i]);
+                const float c0 = top == -INFINITY ? 0.f : ex2(top - next), c1 = mp[i] == -INFINITY ? 0.f : ex2(mp[i] - next);
+                lsum = lsum * c0 + lp[i] * c1;
+                acc.x = acc.x * c0 + o[i].x * c1, acc.y = acc.y * c0 + o[i].y * c1;
+                acc.z = acc.z * c0 + o[i].z * c1, acc.w = acc.w * c0 + o[i].w * c1;
+                top = next;
+            }
+        }
     }
     if (lane == 0) sm[warp] = top, sl[warp] = lsum;
     so[warp][lane] = acc;
@@ -620,28 +635,40 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_rows(MergeArgs a) {
 /* ---- merge + exchange over peer memory ------------------------------------------------------------------------ */
 
 constexpr int MAX_PEERS = 8;
-constexpr uint32_t PEER_WAIT_POLLS = 1u << 22; /* x ~100 ns sleep each: roughly half a second */
+constexpr uint32_t PEER_WAIT_POLLS = 1u << 22; /* x ~100 ns each: roughly half a second */
+constexpr int PACKET_WORDS = NCB_PEER_STATE_BYTES / 8; /* one state as 8-byte (fp32 value, call number) words */
+static_assert(PACKET_WORDS >= HEAD_DIM + 2, "o[128], then m and l");
 
-/* Every rank owns an "inbox" [2][world][rows][PART] fp32 and flags [world][rows] uint32 that all peers can address,
- * and a private device word pair `epoch` = (calls completed, blocks arrived in the current call). */
+/* Every rank owns an "inbox" [2][world][rows][PACKET_WORDS] of 8-byte words that all peers can address, and a private
+ * device word pair `epoch` = (calls completed, blocks arrived in the current call). */
 struct ExchangeArgs {
-    MergeArgs local;            /* this rank's chunk states (the split kernel's workspace) */
-    float *inbox[MAX_PEERS];    /* rank q's inbox */
-    uint32_t *flags[MAX_PEERS]; /* rank q's flags: flags[q][r * rows + row] = last epoch rank r delivered `row` */
+    MergeArgs local;         /* this rank's chunk states (the split kernel's workspace) */
+    uint2 *inbox[MAX_PEERS]; /* rank q's inbox */
     int world, rank;
     uint32_t *epoch;
     int *status;
 };
 
+/* 16 bytes = two (value, call number) words, read in one piece. Volatile: each poll goes to memory. */
+static __device__ __forceinline__ uint4 load_packet_pair(const uint2 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 /* The chunk merge of k_merge and the cross-GPU exchange in one launch, one block per row: merge the row's local chunk
- * states; PUSH the rank state into every rank's inbox (plain stores over NVLink, one direction, no read round trip);
- * publish the row's flag to every rank; wait (bounded) until every rank's flag for this row has arrived here; merge
- * the `world` states from this rank's own inbox in rank order, so every rank computes bit-identical outputs. Rows are
- * independent: a block waits only for the same row's blocks on the other GPUs, never for blocks of its own grid.
- * The call's number comes from a device word the kernel itself advances (the last block to finish bumps it), so
- * the launch arguments never change and the step can be captured in a CUDA graph. Inboxes alternate between two
- * halves by the call's parity: a rank can run at most one call ahead of a peer (it needs the peer's flags of call e to
- * finish call e), so what it writes never lands in a half a slower peer still reads. */
+ * states, PUSH the rank state into every other rank's inbox with plain stores over NVLink (one direction, no read
+ * round trip), then read the other ranks' states of the same row from this rank's own inbox and merge in rank order,
+ * so every rank computes bit-identical outputs. A state travels as self-validating 8-byte words (fp32 value, call
+ * number), the scheme of low-latency collectives: an 8-byte store lands whole, so a word whose second half equals the
+ * current call number holds this call's value; no flags, no fences, nothing ordered after the data. The receiver
+ * polls its own memory (bounded) until every word of a state carries the call number. Rows are independent: a block
+ * waits only for the same row's blocks on the other GPUs, never for blocks of its own grid.
+ * The call number comes from a device word the kernel itself advances (the last block to finish bumps it), so the
+ * launch arguments never change and the step can be captured in a CUDA graph. Inboxes alternate between two halves by
+ * the call's parity: a rank can run at most one call ahead of a peer (it needs the peer's words of call e to finish
+ * call e), so what it writes never lands in a half a slower peer still reads, and a word left by call e - 2 in the
+ * same half never passes for call e. */
 __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_exchange(ExchangeArgs a) {
     const long long row = blockIdx.x, rows = a.local.rows;
     const int lane = threadIdx.x & 31;
@@ -650,48 +677,52 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_exchange(ExchangeArg
     float top, lsum;
     float4 acc;
     if (!merge_row_states(a.local, row, top, lsum, acc)) return;
-    const size_t half = (size_t)(epoch & 1u) * a.world * rows * PART;
+    const size_t half = (size_t)(epoch & 1u) * a.world * rows * PACKET_WORDS;
+    const size_t mine = half + ((size_t)a.rank * rows + row) * PACKET_WORDS;
+    const uint4 w01 = make_uint4(__float_as_uint(acc.x), epoch, __float_as_uint(acc.y), epoch);
+    const uint4 w23 = make_uint4(__float_as_uint(acc.z), epoch, __float_as_uint(acc.w), epoch);
+    const uint4 wml = make_uint4(__float_as_uint(top), epoch, __float_as_uint(lsum), epoch);
 #pragma unroll
     for (int q = 0; q < MAX_PEERS; q++) {
-        if (q < a.world) {
-            float *o = a.inbox[q] + half + ((size_t)a.rank * rows + row) * PART;
-            if (lane == 0) *reinterpret_cast<float4 *>(o) = make_float4(top, lsum, 0.f, 0.f);
-            *reinterpret_cast<float4 *>(o + 4 + 4 * lane) = acc;
+        if (q < a.world && q != a.rank) {
+            uint2 *o = a.inbox[q] + mine;
+            *reinterpret_cast<uint4 *>(o + 4 * lane) = w01;
+            *reinterpret_cast<uint4 *>(o + 4 * lane + 2) = w23;
+            if (lane == 0) *reinterpret_cast<uint4 *>(o + HEAD_DIM) = wml;
         }
     }
-    __syncwarp(); /* the warp's stores precede the flags below */
-    if (lane < a.world) { /* lane q: deliver to rank q, then wait for rank q */
-        __threadfence_system();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flags[lane] + (size_t)a.rank * rows + row), "r"(epoch)
-                     : "memory");
-        const uint32_t *mine = a.flags[a.rank] + (size_t)lane * rows + row;
-        bool ok = false;
-        for (uint32_t polls = 0; polls < PEER_WAIT_POLLS; polls++) {
-            uint32_t seen;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-            if ((int32_t)(seen - epoch) >= 0) {
-                ok = true;
-                break;
-            }
-            __nanosleep(100);
-        }
-        if (!ok) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
-    }
-    __syncwarp();
-    const float *in = a.inbox[a.rank] + half + (size_t)row * PART;
+    /* the other ranks' states of this row, from this rank's own inbox */
     float mq[MAX_PEERS], lq[MAX_PEERS];
     float4 oq[MAX_PEERS];
+    bool ok = true;
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; q++) {
+        if (q >= a.world) continue;
+        if (q == a.rank) {
+            mq[q] = top, lq[q] = lsum, oq[q] = acc;
+            continue;
+        }
+        const uint2 *in = a.inbox[a.rank] + half + ((size_t)q * rows + row) * PACKET_WORDS;
+        uint4 r01 = make_uint4(0u, 0u, 0u, 0u), r23 = r01, rml = r01;
+        bool got = false;
+        for (uint32_t polls = 0; polls < PEER_WAIT_POLLS && ok; polls++) {
+            r01 = load_packet_pair(in + 4 * lane);
+            r23 = load_packet_pair(in + 4 * lane + 2);
+            rml = load_packet_pair(in + HEAD_DIM);
+            got = r01.y == epoch && r01.w == epoch && r23.y == epoch && r23.w == epoch && rml.y == epoch && rml.w == epoch;
+            if (__all_sync(0xffffffffu, got)) break;
+            got = false;
+            __nanosleep(64);
+        }
+        if (!__all_sync(0xffffffffu, got)) ok = false; /* the remaining ranks are not waited for either */
+        mq[q] = __uint_as_float(rml.x), lq[q] = __uint_as_float(rml.z);
+        oq[q] = make_float4(__uint_as_float(r01.x), __uint_as_float(r01.z), __uint_as_float(r23.x), __uint_as_float(r23.z));
+    }
+    if (!ok && lane == 0) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
     top = -INFINITY;
 #pragma unroll
-    for (int q = 0; q < MAX_PEERS; q++) { /* written by other GPUs: bypass this SM's L1 */
-        if (q < a.world) {
-            const float *s = in + (size_t)q * rows * PART;
-            mq[q] = __ldcv(s);
-            lq[q] = __ldcv(s + 1);
-            oq[q] = __ldcv(reinterpret_cast<const float4 *>(s + 4) + lane);
-            top = fmaxf(top, mq[q]);
-        }
-    }
+    for (int q = 0; q < MAX_PEERS; q++)
+        if (q < a.world) top = fmaxf(top, mq[q]);
     lsum = 0.f;
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -702,7 +733,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_exchange(ExchangeArg
             acc.x += c * oq[q].x, acc.y += c * oq[q].y, acc.z += c * oq[q].z, acc.w += c * oq[q].w;
         }
     }
-    store_normalised(a.local.out, row, lane, lsum, acc);
+    if (ok) store_normalised(a.local.out, row, lane, lsum, acc);
     if (lane == 0) { /* the last row to finish closes the call */
         __threadfence();
         if (atomicAdd(a.epoch + 1, 1u) == (uint32_t)rows - 1u) {
@@ -738,9 +769,7 @@ struct AppendIn {
     const void *qkv, *q_gain, *k_gain, *cos, *sin;
     long long qkv_row_stride;
     int table_len;
-    /* MULTI only: block z works on rows group_start[z] .. group_start[z + 1] - 1, which share a slot and hold
-     * ascending positions; lens is per row then, and parts are indexed by row */
-    const int32_t *group_start;
+    ValueEmbed ve;
 };
 
 template <int NT, bool APPEND, bool MULTI = false> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
@@ -780,6 +809,12 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
         const uintptr_t all = (uintptr_t)app->qkv | (uintptr_t)app->q_gain | (uintptr_t)app->k_gain |
                               (uintptr_t)app->cos | (uintptr_t)app->sin;
         if (all % 16 != 0 || app->qkv_row_stride % 8 != 0) return NCB_ERR_ALIGN;
+        const ValueEmbed &ve = app->ve;
+        if (ve.table) {
+            if (!ve.h || !ve.tokens || !ve.gate || ve.C <= 0 || ve.C % 256 || ve.vocab <= 0) return NCB_ERR_ARG;
+            if (((uintptr_t)ve.h | (uintptr_t)ve.table | (uintptr_t)ve.gate) % 16 || (uintptr_t)ve.tokens % 8)
+                return NCB_ERR_ALIGN;
+        }
     }
     if (workspace_bytes < decode_attn_workspace_bytes(B, Hq, max_kv_len, Hkv, chunk_pages)) return NCB_ERR_WORKSPACE;
     const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
@@ -790,6 +825,7 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
         a.qkv = (const bf16 *)app->qkv, a.q_gain = (const float *)app->q_gain, a.k_gain = (const float *)app->k_gain;
         a.cs = (const float *)app->cos, a.sn = (const float *)app->sin;
         a.qkv_row_stride = app->qkv_row_stride, a.table_len = app->table_len;
+        a.ve = app->ve;
     }
     a.group_start = (const int32_t *)group_start;
     cudaLaunchConfig_t config = {};
@@ -841,8 +877,7 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream, bool warp_per_r
 
 /* What the merge + exchange launch needs besides the local merge (decode_attn_fp8_sharded). */
 struct ExchangeIn {
-    const void *const *inbox;
-    void *const *flags;
+    void *const *inbox;
     int world, rank;
     void *epoch;
 };
@@ -850,10 +885,7 @@ struct ExchangeIn {
 static int launch_exchange(const MergeArgs &m, const ExchangeIn &x, void *status, cudaStream_t stream) {
     ExchangeArgs a = {};
     a.local = m;
-    for (int q = 0; q < x.world; q++) {
-        a.inbox[q] = (float *)x.inbox[q];
-        a.flags[q] = (uint32_t *)x.flags[q];
-    }
+    for (int q = 0; q < x.world; q++) a.inbox[q] = (uint2 *)x.inbox[q];
     a.world = x.world, a.rank = x.rank, a.epoch = (uint32_t *)x.epoch, a.status = (int *)status;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)m.rows);
@@ -1038,6 +1070,19 @@ int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain
                   pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream, &app);
 }
 
+int decode_step_attn_fp8_ve(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                            const void *pos, const void *slot_map, void *kv_cache, void *workspace,
+                            long long workspace_bytes, void *out, int B, int Hq, int Hkv, long long qkv_row_stride,
+                            int table_len, int n_slots, int pages_per_slot, int max_kv_len, int window,
+                            int chunk_pages, float softmax_scale, const void *h, const void *tokens,
+                            const void *ve_table, const void *ve_gate, int C, int vocab, void *status, void *stream) {
+    if (!out && B > 0) return NCB_ERR_ARG;
+    AppendIn app = {qkv, q_gain, k_gain, cos, sin, qkv_row_stride, table_len};
+    app.ve = {(const bf16 *)h, (const long long *)tokens, (const bf16 *)ve_table, (const float *)ve_gate, C, vocab};
+    return attend(nullptr, kv_cache, pos, slot_map, workspace, workspace_bytes, out, nullptr, B, Hq, Hkv, n_slots,
+                  pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream, &app);
+}
+
 int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *span_lens,
                      const void *slot_map, const void *group_start, int n_groups, void *workspace,
                      long long workspace_bytes, void *out, int rows, int Hq, int Hkv, int n_slots, int pages_per_slot,
@@ -1069,17 +1114,16 @@ int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens,
 int decode_attn_fp8_sharded(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
                             void *workspace, long long workspace_bytes, void *out, int B, int Hq, int Hkv, int n_slots,
                             int pages_per_slot, int max_kv_len, int window, int chunk_pages, float softmax_scale,
-                            const void *const *inbox, void *const *flags, int world, int rank, void *epoch,
-                            void *status, void *stream) {
+                            void *const *inbox, int world, int rank, void *epoch, void *status, void *stream) {
     if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world) return NCB_ERR_ARG;
-    if (B == 0) return NCB_OK; /* every rank passes the same B: nobody publishes, nobody waits */
-    if (!out || !inbox || !flags || !epoch) return NCB_ERR_ARG;
+    if (B == 0) return NCB_OK; /* every rank passes the same B: nobody sends, nobody waits */
+    if (!out || !inbox || !epoch) return NCB_ERR_ARG;
     for (int r = 0; r < world; r++) {
-        if (!inbox[r] || !flags[r]) return NCB_ERR_ARG;
-        if (((uintptr_t)inbox[r] % 16) || ((uintptr_t)flags[r] % 4)) return NCB_ERR_ALIGN;
+        if (!inbox[r]) return NCB_ERR_ARG;
+        if ((uintptr_t)inbox[r] % 16) return NCB_ERR_ALIGN;
     }
     if ((uintptr_t)epoch % 8) return NCB_ERR_ALIGN;
-    const ExchangeIn x = {inbox, flags, world, rank, epoch};
+    const ExchangeIn x = {inbox, world, rank, epoch};
     return attend(q, kv_cache, lens, slot_map, workspace, workspace_bytes, out, nullptr, B, Hq, Hkv, n_slots,
                   pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream, nullptr, &x);
 }

@@ -26,6 +26,7 @@ struct AppendArgs {
     long long rows, qkv_row_stride;
     int Hq, Hkv, table_len, n_slots, pages_per_slot;
     int *status;
+    ValueEmbed ve; /* table == NULL: no value embedding on this layer */
 };
 
 /* Block (x, y) = rows 16 x .. 16 x + 15 of head row y (q heads, then k heads, then v heads); 8 lanes per row. */
@@ -72,6 +73,7 @@ __global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
     }
     const int head = is_k ? which - a.Hq : which - a.Hq - a.Hkv;
     if (is_k) norm_rotate(x1, x2, a.k_gain, a.cs + tab, a.sn + tab, o);
+    else if (a.ve.table) ve_mix(x1, x2, a.ve, row, head, a.Hkv, t, o);
     uint8_t b1[VEC], b2[VEC];
     const float scale = quantise(x1, x2, b1, b2);
     const int j = p % PAGE_TOKENS;
@@ -118,10 +120,12 @@ long long kv_cache_bytes(int n_slots, int kv_heads, int max_len) {
     return (long long)n_slots * kv_heads * kv_cache_pages(max_len) * PAGE_BYTES;
 }
 
-int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
-                  const void *pos, const void *slot_map, void *q_out, void *kv_cache, long long rows, int Hq,
-                  int Hkv, long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot, void *status,
-                  void *stream) {
+} /* extern "C" */
+
+static int launch_append(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                         const void *pos, const void *slot_map, void *q_out, void *kv_cache, long long rows, int Hq,
+                         int Hkv, long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot, void *status,
+                         void *stream, const ValueEmbed &ve) {
     if (rows < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || table_len <= 0 || n_slots <= 0 || pages_per_slot <= 0)
         return NCB_ERR_ARG;
     if (qkv_row_stride < (long long)(Hq + 2 * Hkv) * HEAD_DIM) return NCB_ERR_ARG;
@@ -130,12 +134,16 @@ int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const
     const uintptr_t all = (uintptr_t)qkv | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)cos | (uintptr_t)sin |
                           (uintptr_t)q_out | (uintptr_t)kv_cache;
     if (all % 16 != 0 || qkv_row_stride % 8 != 0) return NCB_ERR_ALIGN;
+    if (ve.table) {
+        if (!ve.h || !ve.tokens || !ve.gate || ve.C <= 0 || ve.C % 256 || ve.vocab <= 0) return NCB_ERR_ARG;
+        if (((uintptr_t)ve.h | (uintptr_t)ve.table | (uintptr_t)ve.gate) % 16 || (uintptr_t)ve.tokens % 8) return NCB_ERR_ALIGN;
+    }
     const long long blocks = (rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
     if (blocks > 0x7fffffffLL || Hq + 2 * Hkv > 65535) return NCB_ERR_ARG;
     AppendArgs a = {(const bf16 *)qkv, (const float *)q_gain, (const float *)k_gain, (const float *)cos,
                     (const float *)sin, (const int32_t *)pos, (const int32_t *)slot_map, (bf16 *)q_out,
                     (uint8_t *)kv_cache, rows, qkv_row_stride, Hq, Hkv, table_len, n_slots, pages_per_slot,
-                    (int *)status};
+                    (int *)status, ve};
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)blocks, (unsigned)(Hq + 2 * Hkv));
     config.blockDim = dim3(BLOCK);
@@ -146,6 +154,27 @@ int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const
     config.attrs = attribute;
     config.numAttrs = 1;
     return cudaLaunchKernelEx(&config, k_kv_append, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+}
+
+extern "C" {
+
+int kv_append_fp8(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                  const void *pos, const void *slot_map, void *q_out, void *kv_cache, long long rows, int Hq,
+                  int Hkv, long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot, void *status,
+                  void *stream) {
+    return launch_append(qkv, q_gain, k_gain, cos, sin, pos, slot_map, q_out, kv_cache, rows, Hq, Hkv, qkv_row_stride,
+                         table_len, n_slots, pages_per_slot, status, stream, ValueEmbed{});
+}
+
+int kv_append_fp8_ve(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
+                     const void *pos, const void *slot_map, void *q_out, void *kv_cache, long long rows, int Hq,
+                     int Hkv, long long qkv_row_stride, int table_len, int n_slots, int pages_per_slot, const void *h,
+                     const void *tokens, const void *ve_table, const void *ve_gate, int C, int vocab, void *status,
+                     void *stream) {
+    const ValueEmbed ve = {(const bf16 *)h, (const long long *)tokens, (const bf16 *)ve_table, (const float *)ve_gate, C,
+                           vocab};
+    return launch_append(qkv, q_gain, k_gain, cos, sin, pos, slot_map, q_out, kv_cache, rows, Hq, Hkv, qkv_row_stride,
+                         table_len, n_slots, pages_per_slot, status, stream, ve);
 }
 
 } /* extern "C" */

@@ -70,6 +70,53 @@ static __device__ __forceinline__ void norm_rotate(float *x1, float *x2, const f
     }
 }
 
+/* The optional value-embedding mix of a v head row (the reference's attn_prologue, model/kernels/decode.cu:482-494):
+ * v <- bf16(v + g ve), g = 2 sigmoid(w . h) with h the row's normed layer input (bf16 [C]) and w the kv head's gate
+ * weights (fp32 [C]), ve the token's table row for this kv head (bf16 [128]). */
+struct ValueEmbed {
+    const bf16 *h;            /* [rows][C] */
+    const long long *tokens;  /* [rows] */
+    const bf16 *table;        /* [vocab][Hkv][128] */
+    const float *gate;        /* [Hkv][C] */
+    int C, vocab;             /* C a multiple of 256 */
+};
+
+/* The reference sums the gate's dot product by FMAs per warp lane L (elements (32 k + L) 8 + j) and reduces the 32
+ * lanes with an xor butterfly over 16, 8, 4, 2, 1. Here a row has 8 lanes: lane t plays the reference's lanes t, t + 8,
+ * t + 16 and t + 24, whose first two butterfly steps (16, then 8) stay inside the thread; the steps 4, 2, 1 are the
+ * group's own butterfly. Same sums in the same order, so the gate's bits are those of oracle/kv_append_oracle.c.
+ * The sigmoid is evaluated in double precision and rounded once. */
+static __device__ __forceinline__ void ve_mix(float *x1, float *x2, const ValueEmbed &ve, long long row, int kv_head,
+                                              int Hkv, int t, int o) {
+    const bf16 *h = ve.h + (size_t)row * ve.C;
+    const float *w = ve.gate + (size_t)kv_head * ve.C;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < ve.C / 256; k++) {
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+            const int base = (k * 32 + t + 8 * m) * VEC;
+            float hv[VEC], wv[VEC];
+            load_bf16x8(h + base, hv);
+            load_f32x8(w + base, wv);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) d[m] = __fmaf_rn(hv[j], wv[j], d[m]);
+        }
+    }
+    const float s = group_sum(__fadd_rn(__fadd_rn(d[0], d[2]), __fadd_rn(d[1], d[3])));
+    const float g = (float)(2.0 / (1.0 + exp(-(double)s)));
+    long long token = ve.tokens[row];
+    if (token < 0 || token >= ve.vocab) token = 0; /* as the embedding lookup does */
+    const bf16 *e = ve.table + ((size_t)token * Hkv + kv_head) * HEAD_DIM;
+    float e1[VEC], e2[VEC];
+    load_bf16x8(e + o, e1);
+    load_bf16x8(e + HALF + o, e2);
+#pragma unroll
+    for (int i = 0; i < VEC; i++) {
+        x1[i] = __bfloat162float(__float2bfloat16_rn(__fadd_rn(x1[i], __fmul_rn(g, e1[i]))));
+        x2[i] = __bfloat162float(__float2bfloat16_rn(__fadd_rn(x2[i], __fmul_rn(g, e2[i]))));
+    }
+}
+
 static __device__ __forceinline__ uint4 pack_bf16x8(const float *v) {
     uint4 u;
     __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&u);

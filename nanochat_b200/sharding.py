@@ -76,16 +76,19 @@ def gather_states(part: Tensor, group: "dist.ProcessGroup | None" = None) -> Ten
     return out.view(world, *part.shape)
 
 
-class PeerStates:
-    """What the fused exchange + merge (decode_attn_fp8_sharded) needs on every rank: an inbox and per-row flags in
-    memory every GPU of the group can address, and this rank's private call counter.
+PEER_STATE_BYTES = 1056  # NCB_PEER_STATE_BYTES: one (m, l, o) state as 8-byte (value, call number) words
 
-    One symmetric allocation per rank: world * rows uint32 flags (padded to 256 bytes), then the inbox of
-    2 * world * rows states of 132 fp32 (two halves that calls alternate between). Each rank's merge kernel pushes
-    its row states into every rank's inbox with plain stores over NVLink, publishes per-row flags, waits (bounded)
-    for the peers' flags in its own memory and merges: no collective library on the data path. Construction is
-    collective (allocation, rendezvous, barrier); torch's symmetric memory is used for the allocation and the
-    pointer exchange only."""
+
+class PeerStates:
+    """What the fused exchange + merge (decode_attn_fp8_sharded) needs on every rank: an inbox in memory every GPU of
+    the group can address, and this rank's private call counter.
+
+    One symmetric allocation per rank: 2 * world * rows states of PEER_STATE_BYTES (two halves that calls alternate
+    between). Each rank's merge kernel pushes its row states into every other rank's inbox with plain stores over
+    NVLink, as 8-byte words that carry the call number and so validate themselves, then polls (bounded) its own inbox
+    for the peers' states and merges: no collective library, no flags and no fences on the data path. Construction is
+    collective (allocation, rendezvous, barrier); torch's symmetric memory is used for the allocation and the pointer
+    exchange only."""
 
     def __init__(self, batch: int, heads: int, group: "dist.ProcessGroup | None" = None,
                  device: "torch.device | None" = None):
@@ -96,18 +99,15 @@ class PeerStates:
         world = dist.get_world_size(group)
         assert world <= 8
         self.batch, self.heads, self.rows = batch, heads, batch * heads
-        self.flag_bytes = -(-world * self.rows * 4 // 256) * 256
-        floats = self.flag_bytes // 4 + 2 * world * self.rows * PART_FLOATS
-        self.buffer = symm_mem.empty(floats, dtype=torch.float32, device=device)
-        self.buffer.zero_()
+        self.buffer = symm_mem.empty(2 * world * self.rows * PEER_STATE_BYTES // 4, dtype=torch.int32, device=device)
+        self.buffer.zero_()  # call numbers start at 1: a zeroed word never passes for an arrived one
         self.handle = symm_mem.rendezvous(self.buffer, group)
         self.world, self.rank = self.handle.world_size, self.handle.rank
         self.epoch = torch.zeros(2, dtype=torch.int32, device=device)  # (calls completed, rows arrived)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
-        dist.barrier(group)  # every rank's flags are zero before anyone publishes
-        self._flags = (ctypes.c_void_p * self.world)(*self.handle.buffer_ptrs)
-        self._inbox = (ctypes.c_void_p * self.world)(*(p + self.flag_bytes for p in self.handle.buffer_ptrs))
+        dist.barrier(group)  # every rank's inbox is zero before anyone sends
+        self._inbox = (ctypes.c_void_p * self.world)(*self.handle.buffer_ptrs)
 
 
 def attend_kv_sharded_fused(q: Tensor, cache, local_lens: Tensor, max_local_len: int, peers: PeerStates,
@@ -131,8 +131,8 @@ def attend_kv_sharded_fused(q: Tensor, cache, local_lens: Tensor, max_local_len:
     rc = cuda_library("decode_attn").decode_attn_fp8_sharded(
         pointer(q), pointer(cache.pages), pointer(local_lens), pointer(slot_map), pointer(workspace),
         workspace.numel(), pointer(out), B, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, max_local_len,
-        window, chunk_pages, 128 ** -0.5 if softmax_scale is None else softmax_scale, peers._inbox, peers._flags,
-        peers.world, peers.rank, pointer(peers.epoch), pointer(peers.status), stream())
+        window, chunk_pages, 128 ** -0.5 if softmax_scale is None else softmax_scale, peers._inbox, peers.world,
+        peers.rank, pointer(peers.epoch), pointer(peers.status), stream())
     check(rc, "decode_attn_fp8_sharded")
     return out
 

@@ -32,7 +32,9 @@ def norm(x: torch.Tensor) -> torch.Tensor:
 class OracleDecoder:
     """cfg: dict with n_layers, hidden, n_heads, n_kv_heads, intermediate, vocab, rope_theta, max_len;
     weights: dict with embed, lm_head (bf16 [V, C]) and layers: list of dicts wqkv, wo, wup, wdown (bf16),
-    q_gain, k_gain (fp32 [128])."""
+    q_gain, k_gain (fp32 [128]) and optionally resid_lambda, x0_lambda (floats; the per-layer stream mix of
+    modeling_nanochat.py:170-171), ve_table (bf16 [V, Hkv * 128]) and ve_gate (fp32 [Hkv, C]) (the value-embedding
+    mix of modeling_nanochat.py:88-90)."""
 
     def __init__(self, cfg: dict, weights: dict, n_seqs: int):
         self.cfg, self.w = cfg, weights
@@ -46,12 +48,20 @@ class OracleDecoder:
         """One token for each sequence in `seqs` (appended at that sequence's current length): fp32 logits
         (len(seqs), V), before any logit cap."""
         cfg, Hq, Hkv = self.cfg, self.cfg["n_heads"], self.cfg["n_kv_heads"]
-        h = norm(self.w["embed"][tokens])
+        h = x0 = norm(self.w["embed"][tokens])
         for i, lw in enumerate(self.w["layers"]):
-            qkv = F.linear(norm(h), lw["wqkv"])
+            l1, l2 = lw.get("resid_lambda", 1.0), lw.get("x0_lambda", 0.0)
+            if l1 != 1.0 or l2 != 0.0:  # fp32 products and sum, rounded once
+                h = (np.float32(l1) * h.float() + np.float32(l2) * x0.float()).to(h.dtype)
+            n = norm(h)
+            qkv = F.linear(n, lw["wqkv"])
             pos = np.array([self.cache[i][s]["k_bytes"].shape[1] for s in seqs], dtype=np.int32)
+            ve = None
+            if lw.get("ve_table") is not None:
+                ve = {"h": _bits(n), "tokens": tokens.numpy(), "table": _bits(lw["ve_table"]),
+                      "gate": lw["ve_gate"].numpy()}
             new = okv.kv_append(_bits(qkv), lw["q_gain"].numpy(), lw["k_gain"].numpy(), self.cos, self.sin, pos,
-                                Hq, Hkv)
+                                Hq, Hkv, ve=ve)
             att = np.zeros((len(seqs), Hq, 128), dtype=np.uint16)
             for r, s in enumerate(seqs):
                 c = self.cache[i][s]

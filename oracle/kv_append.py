@@ -20,6 +20,8 @@ def _lib() -> ctypes.CDLL:
     lib.oracle_kv_append.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
                                                               ctypes.c_longlong] + [ctypes.c_void_p] * 6
     lib.oracle_kv_append.restype = None
+    lib.oracle_kv_append_ve.argtypes = lib.oracle_kv_append.argtypes + [ctypes.c_void_p] * 4 + [ctypes.c_int]
+    lib.oracle_kv_append_ve.restype = None
     lib.oracle_f32_to_e4m3_n.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong]
     lib.oracle_f32_to_e4m3_n.restype = None
     lib.oracle_quant_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong]
@@ -81,9 +83,11 @@ def quant_rows(x_bf16: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
 
 
 def kv_append(qkv: np.ndarray, q_gain: np.ndarray, k_gain: np.ndarray, cos: np.ndarray, sin: np.ndarray,
-              pos: np.ndarray, Hq: int, Hkv: int) -> dict[str, np.ndarray]:
+              pos: np.ndarray, Hq: int, Hkv: int, ve: "dict | None" = None) -> dict[str, np.ndarray]:
     """qkv (rows, (Hq + 2 Hkv) * 128) bf16 bit patterns; returns q (rows, Hq, 128) bf16 bits, k_bf16 (the rotated
-    k before quantisation), k_bytes, v_bytes (rows, Hkv, 128) u8 and k_scale, v_scale (rows, Hkv) fp32."""
+    k before quantisation), k_bytes, v_bytes (rows, Hkv, 128) u8 and k_scale, v_scale (rows, Hkv) fp32.
+    ve: the optional value-embedding mix on v (model/kernels/decode.cu:482-494): dict with h (rows, C) bf16 bits (the
+    layer's normed input), tokens (rows,) int64, table (vocab, Hkv * 128) bf16 bits, gate (Hkv, C) fp32."""
     qkv = np.ascontiguousarray(qkv, dtype=np.uint16)
     rows, stride = qkv.shape
     assert stride >= (Hq + 2 * Hkv) * HEAD_DIM
@@ -94,7 +98,17 @@ def kv_append(qkv: np.ndarray, q_gain: np.ndarray, k_gain: np.ndarray, cos: np.n
     out = {"q": np.empty((rows, Hq, HEAD_DIM), np.uint16), "k_bf16": np.empty((rows, Hkv, HEAD_DIM), np.uint16),
            "k_bytes": np.empty((rows, Hkv, HEAD_DIM), np.uint8), "k_scale": np.empty((rows, Hkv), np.float32),
            "v_bytes": np.empty((rows, Hkv, HEAD_DIM), np.uint8), "v_scale": np.empty((rows, Hkv), np.float32)}
-    _lib().oracle_kv_append(_p(qkv), _p(q_gain), _p(k_gain), _p(cos), _p(sin), _p(pos), rows, Hq, Hkv, stride,
-                            _p(out["q"]), _p(out["k_bf16"]), _p(out["k_bytes"]), _p(out["k_scale"]),
-                            _p(out["v_bytes"]), _p(out["v_scale"]))
+    head = [_p(qkv), _p(q_gain), _p(k_gain), _p(cos), _p(sin), _p(pos), rows, Hq, Hkv, stride, _p(out["q"]),
+            _p(out["k_bf16"]), _p(out["k_bytes"]), _p(out["k_scale"]), _p(out["v_bytes"]), _p(out["v_scale"])]
+    if ve is None:
+        _lib().oracle_kv_append(*head)
+        return out
+    h = np.ascontiguousarray(ve["h"], dtype=np.uint16)
+    tokens = np.ascontiguousarray(ve["tokens"], dtype=np.int64)
+    table = np.ascontiguousarray(ve["table"], dtype=np.uint16)
+    gate = np.ascontiguousarray(ve["gate"], dtype=np.float32)
+    C = h.shape[1]
+    assert h.shape == (rows, C) and C % 256 == 0 and gate.shape == (Hkv, C) and table.shape[1] == Hkv * HEAD_DIM
+    assert tokens.shape == (rows,) and (tokens >= 0).all() and (tokens < table.shape[0]).all()
+    _lib().oracle_kv_append_ve(*head, _p(h), _p(tokens), _p(table), _p(gate), C)
     return out

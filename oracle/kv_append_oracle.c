@@ -17,9 +17,14 @@
  *                                    64 apart
  *   model/kernels/decode.cu:494-505  q, k, v each rounded to bf16 exactly once
  *   model/kernels/decode.cu:556-564  the row's k, v go to cache position pos[b] of slot cache_slot[b]
+ *   model/kernels/decode.cu:482-494  the optional value-embedding mix v = bf16(v + 2 sigmoid(w[head] . h) ve[token]):
+ *                                    the dot product as FMAs, a warp lane owning 8 consecutive elements of every
+ *                                    256-element chunk, then an xor butterfly over offsets 16, 8, 4, 2, 1
  * Deviations, chosen so that a CPU can reproduce the GPU bit for bit: every fp32 operation is individually
  * rounded (compile with -ffp-contract=off; the reference lets nvcc contract FMAs), and rsqrtf (2 ulp, not
- * reproducible on a CPU) is replaced by a correctly rounded sqrt followed by a correctly rounded divide.
+ * reproducible on a CPU) is replaced by a correctly rounded sqrt followed by a correctly rounded divide. The
+ * gate's sigmoid is evaluated in double precision and rounded once, 2 / (1 + exp(-d)), where the reference uses
+ * fp32 expf (not reproducible across libraries); the two agree to within an ulp of fp32.
  *
  * Build: gcc -O2 -ffp-contract=off -fno-fast-math -shared -fPIC (oracle/build_oracle.py).
  */
@@ -119,6 +124,36 @@ void oracle_quant_row(const uint16_t *x, uint8_t *bytes, float *scale) {
     for (int i = 0; i < HEAD_DIM; i++) bytes[i] = oracle_f32_to_e4m3(oracle_bf16_to_f32(x[i]) / s);
 }
 
+/* The value-embedding gate of one (row, kv head): 2 sigmoid(w . h) over C elements (C a multiple of 256), h bf16 (the
+ * layer's normed input), w fp32. decode.cu:485-491's order: lane L of 32 accumulates, by FMA, elements
+ * (32 k + L) 8 + j for k = 0 .. C / 256 - 1 and j = 0 .. 7; the lanes' sums are reduced by an xor butterfly. */
+float oracle_ve_gate(const uint16_t *h, const float *w, int C) {
+    float d[32];
+    for (int lane = 0; lane < 32; lane++) {
+        float acc = 0.f;
+        for (int k = 0; k < C / 256; k++)
+            for (int j = 0; j < 8; j++) {
+                const int i = (k * 32 + lane) * 8 + j;
+                acc = fmaf(oracle_bf16_to_f32(h[i]), w[i], acc);
+            }
+        d[lane] = acc;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        float next[32];
+        for (int lane = 0; lane < 32; lane++) next[lane] = d[lane] + d[lane ^ o];
+        memcpy(d, next, sizeof d);
+    }
+    return (float)(2.0 / (1.0 + exp(-(double)d[0])));
+}
+
+/* v (128 bf16) <- bf16(v + gate * ve), each product and sum rounded (decode.cu:492-494). */
+void oracle_ve_mix(uint16_t *v, float gate, const uint16_t *ve) {
+    for (int i = 0; i < HEAD_DIM; i++) {
+        const float p = gate * oracle_bf16_to_f32(ve[i]);
+        v[i] = oracle_f32_to_bf16(oracle_bf16_to_f32(v[i]) + p);
+    }
+}
+
 /*
  * The whole step for `rows` tokens, logical (un-paged) outputs:
  *   qkv bf16 [rows][row_stride] (Hq q heads, Hkv k heads, Hkv v heads); pos int32 [rows];
@@ -126,10 +161,11 @@ void oracle_quant_row(const uint16_t *x, uint8_t *bytes, float *scale) {
  *   before quantisation, for cross-checks); k_bytes, v_bytes u8 [rows][Hkv][128]; k_scale, v_scale fp32
  *   [rows][Hkv].
  */
-void oracle_kv_append(const uint16_t *qkv, const float *q_gain, const float *k_gain, const float *cs,
-                      const float *sn, const int32_t *pos, long long rows, int Hq, int Hkv, long long row_stride,
-                      uint16_t *q_out, uint16_t *k_bf16, uint8_t *k_bytes, float *k_scale, uint8_t *v_bytes,
-                      float *v_scale) {
+static void kv_append_rows(const uint16_t *qkv, const float *q_gain, const float *k_gain, const float *cs,
+                           const float *sn, const int32_t *pos, long long rows, int Hq, int Hkv, long long row_stride,
+                           uint16_t *q_out, uint16_t *k_bf16, uint8_t *k_bytes, float *k_scale, uint8_t *v_bytes,
+                           float *v_scale, const uint16_t *hn, const long long *tokens, const uint16_t *ve_table,
+                           const float *ve_gate, int C) {
     for (long long r = 0; r < rows; r++) {
         const uint16_t *row = qkv + r * row_stride;
         const float *c = cs + (size_t)pos[r] * HALF, *s = sn + (size_t)pos[r] * HALF;
@@ -138,10 +174,33 @@ void oracle_kv_append(const uint16_t *qkv, const float *q_gain, const float *k_g
             uint16_t *kb = k_bf16 + (r * Hkv + h) * HEAD_DIM;
             oracle_qk_row(row + (Hq + h) * HEAD_DIM, k_gain, c, s, kb);
             oracle_quant_row(kb, k_bytes + (r * Hkv + h) * HEAD_DIM, k_scale + r * Hkv + h);
-            oracle_quant_row(row + (Hq + Hkv + h) * HEAD_DIM, v_bytes + (r * Hkv + h) * HEAD_DIM,
-                             v_scale + r * Hkv + h);
+            uint16_t v[HEAD_DIM];
+            memcpy(v, row + (Hq + Hkv + h) * HEAD_DIM, sizeof v);
+            if (ve_table)
+                oracle_ve_mix(v, oracle_ve_gate(hn + r * C, ve_gate + (size_t)h * C, C),
+                              ve_table + ((size_t)tokens[r] * Hkv + h) * HEAD_DIM);
+            oracle_quant_row(v, v_bytes + (r * Hkv + h) * HEAD_DIM, v_scale + r * Hkv + h);
         }
     }
+}
+
+void oracle_kv_append(const uint16_t *qkv, const float *q_gain, const float *k_gain, const float *cs,
+                      const float *sn, const int32_t *pos, long long rows, int Hq, int Hkv, long long row_stride,
+                      uint16_t *q_out, uint16_t *k_bf16, uint8_t *k_bytes, float *k_scale, uint8_t *v_bytes,
+                      float *v_scale) {
+    kv_append_rows(qkv, q_gain, k_gain, cs, sn, pos, rows, Hq, Hkv, row_stride, q_out, k_bf16, k_bytes, k_scale, v_bytes,
+                   v_scale, NULL, NULL, NULL, NULL, 0);
+}
+
+/* The same with the value-embedding mix on v: h bf16 [rows][C] (the layer's normed input), tokens int64 [rows],
+ * ve_table bf16 [vocab][Hkv][128], ve_gate fp32 [Hkv][C]. */
+void oracle_kv_append_ve(const uint16_t *qkv, const float *q_gain, const float *k_gain, const float *cs,
+                         const float *sn, const int32_t *pos, long long rows, int Hq, int Hkv, long long row_stride,
+                         uint16_t *q_out, uint16_t *k_bf16, uint8_t *k_bytes, float *k_scale, uint8_t *v_bytes,
+                         float *v_scale, const uint16_t *h, const long long *tokens, const uint16_t *ve_table,
+                         const float *ve_gate, int C) {
+    kv_append_rows(qkv, q_gain, k_gain, cs, sn, pos, rows, Hq, Hkv, row_stride, q_out, k_bf16, k_bytes, k_scale, v_bytes,
+                   v_scale, h, tokens, ve_table, ve_gate, C);
 }
 
 /* Bulk helpers for the Python side. */

@@ -57,3 +57,19 @@ def tiny_decoder_weights(seed: int = 21) -> tuple[dict, dict]:
                "q_gain": (1 + 0.1 * torch.randn(HEAD_DIM, generator=gen)).float(),
                "k_gain": (1 + 0.1 * torch.randn(HEAD_DIM, generator=gen)).float()} for _ in range(cfg["n_layers"])]
     return cfg, {"embed": w(V, C), "lm_head": w(V, C), "layers": layers}
+
+
+def tiny_decoder_weights_ve(seed: int = 23) -> tuple[dict, dict]:
+    """tiny_decoder_weights plus what the reference's own checkpoints have and the benchmark models lack: a value
+    embedding on the last layer (table bf16 [V, H * 128] ~ N(0, 0.5), gate fp32 [H, C] ~ N(0, 2 / sqrt(C)), so gates
+    spread over (0, 2)) and per-layer stream-mix lambdas away from (1, 0)."""
+    cfg, w = tiny_decoder_weights(seed)
+    gen = torch.Generator().manual_seed(seed + 1)
+    C, H, V = cfg["hidden"], cfg["n_heads"], cfg["vocab"]
+    last = w["layers"][-1]
+    last["ve_table"] = (torch.randn(V, H * HEAD_DIM, generator=gen) * 0.5).bfloat16()
+    last["ve_gate"] = (torch.randn(H, C, generator=gen) * 2 / C ** 0.5).float()
+    for lw, (l1, l2) in zip(w["layers"], [(0.9, 0.2), (1.1, -0.15)]):
+        lw["resid_lambda"], lw["x0_lambda"] = l1, l2
+    return cfg, w
+

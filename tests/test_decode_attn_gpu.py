@@ -240,12 +240,18 @@ def test_fused_append_attention_equals_the_two_kernels(Hq, Hkv):
     slot_map = torch.tensor(slots, dtype=torch.int32, device="cuda")
     pos = torch.tensor(lens, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    table = (torch.randn(40, Hkv * 128, generator=gen) * 0.7).bfloat16().cuda()
+    gate = (torch.randn(Hkv, 512, generator=gen) * 0.1).float().cuda()
     for step in range(5):
         qkv = torch.randn(B, (Hq + 2 * Hkv) * 128, generator=gen).bfloat16().cuda()
         window = 0 if step % 2 == 0 else 100
+        ve = None
+        if step >= 3:  # the last steps with the value-embedding mix on v
+            ve = ncb.attention.ValueEmbed(torch.randn(B, 512, generator=gen).bfloat16().cuda(),
+                                          torch.randint(0, 40, (B,), generator=gen).cuda(), table, gate)
         got = ncb.decode_step_attention(qkv, gain, gain, cos, sin, pos, caches[0], Hq, int(pos.max()) + 1,
-                                        slot_map=slot_map, window=window, chunk_pages=2, status=status)
-        q = ncb.kv_append(qkv, gain, gain, cos, sin, pos, caches[1], Hq, slot_map=slot_map, status=status)
+                                        slot_map=slot_map, window=window, chunk_pages=2, status=status, ve=ve)
+        q = ncb.kv_append(qkv, gain, gain, cos, sin, pos, caches[1], Hq, slot_map=slot_map, status=status, ve=ve)
         want = ncb.decode_attention(q, caches[1], pos + 1, int(pos.max()) + 1, slot_map=slot_map, window=window,
                                     chunk_pages=2, status=status)
         torch.cuda.synchronize()
@@ -289,19 +295,32 @@ def test_fused_append_attention_equals_the_two_kernels(Hq, Hkv):
         assert torch.equal(caches[0].pages[slots[b]], before[slots[b]])
 
 
+PACKET_WORDS = 132  # NCB_PEER_STATE_BYTES / 8
+
+
+def packets(states: torch.Tensor, call: int) -> torch.Tensor:
+    """(rows, 132) fp32 states (m, l, 0, 0, o[128]) -> (rows, PACKET_WORDS, 2) int32 inbox words: (value bits, call
+    number) for o[0..127], then m, then l; the rest stays zero."""
+    rows = states.shape[0]
+    out = torch.zeros((rows, PACKET_WORDS, 2), dtype=torch.int32, device=states.device)
+    bits = states.view(torch.int32)
+    out[:, :128, 0] = bits[:, 4:]
+    out[:, 128, 0], out[:, 129, 0] = bits[:, 0], bits[:, 1]
+    out[:, :130, 1] = call
+    return out
+
+
 class _OneGpuPeers:
     """The buffers of `world` 'ranks' of decode_attn_fp8_sharded, all on this GPU: per rank an inbox
-    [2][world][rows][132] fp32 and flags [world][rows] uint32, plus rank 0's call counter."""
+    [2][world][rows][PACKET_WORDS] of 8-byte words, plus rank 0's call counter."""
 
     def __init__(self, world, rows):
         import ctypes
         self.world, self.rows = world, rows
-        self.inbox = [torch.zeros((2, world, rows, 132), dtype=torch.float32, device="cuda") for _ in range(world)]
-        self.flags = [torch.zeros((world, rows), dtype=torch.int32, device="cuda") for _ in range(world)]
+        self.inbox = [torch.zeros((2, world, rows, PACKET_WORDS, 2), dtype=torch.int32, device="cuda") for _ in range(world)]
         self.epoch = torch.zeros(2, dtype=torch.int32, device="cuda")
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.p_inbox = (ctypes.c_void_p * world)(*(t.data_ptr() for t in self.inbox))
-        self.p_flags = (ctypes.c_void_p * world)(*(t.data_ptr() for t in self.flags))
 
     def call(self, q, cache, lens, max_kv_len, rank=0, chunk_pages=2):
         from nanochat_b200.native import cuda_library, pointer, stream
@@ -312,15 +331,15 @@ class _OneGpuPeers:
         rc = cuda_library("decode_attn").decode_attn_fp8_sharded(
             pointer(q), pointer(cache.pages), pointer(lens), None, pointer(workspace), workspace.numel(), pointer(out),
             B, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, max_kv_len, 0, chunk_pages, SCALE,
-            self.p_inbox, self.p_flags, self.world, rank, pointer(self.epoch), pointer(self.status), stream())
+            self.p_inbox, self.world, rank, pointer(self.epoch), pointer(self.status), stream())
         return rc, out
 
 
 def test_sharded_exchange_on_one_gpu_with_the_peer_already_delivered():
-    """decode_attn_fp8_sharded as rank 0 of two 'ranks' whose buffers both live on this GPU; the peer's states and
-    flags for the call are planted beforehand, so no kernel waits for another. The result equals decode_attn_merge
-    over the two slices' states bit for bit, the kernel delivers its own states and flags to both inboxes, advances
-    the call counter, and the next call uses the inbox's other half."""
+    """decode_attn_fp8_sharded as rank 0 of two 'ranks' whose inboxes both live on this GPU; the peer's words for the
+    call are planted beforehand, so no kernel waits for another. The result equals decode_attn_merge over the two
+    slices' states bit for bit, the kernel delivers its own state to the peer's inbox (not to its own), advances the
+    call counter, and the next call uses the inbox's other half."""
     n, cuts = 700, [0, 320, 700]
     case = helpers.attention_case(1400, 8, 2, [n, 100])
     q = helpers.bits_bf16(case["q"]).cuda()
@@ -338,29 +357,31 @@ def test_sharded_exchange_on_one_gpu_with_the_peer_already_delivered():
     rows = 2 * 8
     peers = _OneGpuPeers(2, rows)
     for call in (1, 2, 3):
-        peers.inbox[0][call % 2, 1] = parts[1].view(rows, 132)  # rank 1's states of this call, in rank 0's inbox
-        peers.flags[0][1] = call
+        peers.inbox[0][call % 2, 1] = packets(parts[1].view(rows, 132), call)  # rank 1's states, in rank 0's inbox
         rc, out = peers.call(q, caches[0], lens_of[0], 320)
         torch.cuda.synchronize()
         assert rc == 0 and peers.status.item() == 0
         assert torch.equal(out, want), call
         assert peers.epoch.tolist() == [call, 0]
-        assert peers.flags[0].tolist() == [[call] * rows] * 2 and peers.flags[1].tolist() == [[call] * rows, [0] * rows]
-        for inbox in peers.inbox:  # its own states went to both ranks, into the half of the call's parity
-            assert torch.equal(inbox[call % 2, 0], parts[0].view(rows, 132))
-    # the whole result against the float64 checker
+        # its own states went to the peer's inbox, into the half of the call's parity, and not into its own
+        assert torch.equal(peers.inbox[1][call % 2, 0], packets(parts[0].view(rows, 132), call))
+        assert not peers.inbox[0][:, 0].any()
+    # a word left by call 1 in the same half must not pass for call 3: checked above (call 3 re-planted); here a stale
+    # half alone makes the wait run out instead of merging old data
     check(case, helpers.bf16_bits(out.cpu()))
 
 
 def test_sharded_exchange_wait_runs_out_and_reports():
-    """A peer that never delivers: the bounded wait gives up after about half a second, the status word carries
-    NCB_DEV_WAIT_TIMEOUT, the call counter still advances and the context stays usable."""
+    """A peer that never delivers, and one whose words are from an older call: the bounded wait gives up after about
+    half a second, the status word carries NCB_DEV_WAIT_TIMEOUT, the call counter still advances and the context stays
+    usable."""
     import time
     case = helpers.attention_case(1401, 4, 2, [70])
     cache = load_cache(case, 128)
     q = helpers.bits_bf16(case["q"]).cuda()
     lens = torch.tensor([70], dtype=torch.int32, device="cuda")
     peers = _OneGpuPeers(2, 4)
+    peers.inbox[0][1, 1] = packets(torch.zeros((4, 132), device="cuda"), 7)  # stale: some other call's number
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     rc, _ = peers.call(q, cache, lens, 128)

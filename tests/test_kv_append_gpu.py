@@ -14,7 +14,8 @@ HEAD_DIM = 128
 
 
 def run_case(seed, rows, Hq, Hkv, max_len, n_slots, theta=1e4, pad=0, zero_rows=(), positions=None, slots=None,
-             scale=1.0):
+             scale=1.0, ve_hidden=0, vocab=50):
+    """ve_hidden > 0 adds the value-embedding mix on v with a layer input of that width."""
     gen = torch.Generator().manual_seed(seed)
     width = (Hq + 2 * Hkv) * HEAD_DIM
     qkv = (torch.randn(rows, width + pad, generator=gen) * scale).bfloat16()
@@ -31,12 +32,21 @@ def run_case(seed, rows, Hq, Hkv, max_len, n_slots, theta=1e4, pad=0, zero_rows=
     slot_map = torch.as_tensor(slots, dtype=torch.int32)
     cache = ncb.Fp8KVCache(n_slots, Hkv, max_len)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ve = ve_ref = None
+    if ve_hidden:
+        h = torch.randn(rows, ve_hidden, generator=gen).bfloat16()
+        tokens = torch.randint(0, vocab, (rows,), generator=gen)
+        table = (torch.randn(vocab, Hkv * HEAD_DIM, generator=gen) * 0.7).bfloat16()
+        gate = (torch.randn(Hkv, ve_hidden, generator=gen) * 3 / ve_hidden ** 0.5).float()  # gates all over (0, 2)
+        ve = ncb.attention.ValueEmbed(h.cuda(), tokens.cuda(), table.cuda(), gate.cuda())
+        ve_ref = {"h": helpers.bf16_bits(h), "tokens": tokens.numpy(), "table": helpers.bf16_bits(table),
+                  "gate": gate.numpy()}
     q_out = ncb.kv_append(qkv.cuda()[:, :width], q_gain.cuda(), k_gain.cuda(), cos.cuda(),
-                          sin.cuda(), pos.cuda(), cache, Hq, slot_map=slot_map.cuda(), status=status)
+                          sin.cuda(), pos.cuda(), cache, Hq, slot_map=slot_map.cuda(), status=status, ve=ve)
     torch.cuda.synchronize()
     assert status.item() == 0
     want = okv.kv_append(helpers.bf16_bits(qkv), q_gain.numpy(), k_gain.numpy(), cos.numpy(), sin.numpy(),
-                         pos.numpy(), Hq, Hkv)
+                         pos.numpy(), Hq, Hkv, ve=ve_ref)
     assert np.array_equal(helpers.bf16_bits(q_out.cpu()), want["q"]), "q bits differ"
     host = ncb.Fp8KVCache(n_slots, Hkv, max_len, device="cpu", pages=cache.pages.cpu())
     for r in range(rows):
@@ -51,6 +61,15 @@ def run_case(seed, rows, Hq, Hkv, max_len, n_slots, theta=1e4, pad=0, zero_rows=
 @pytest.mark.parametrize("Hq,Hkv", [(10, 10), (32, 8), (16, 4), (8, 1), (1, 1)])
 def test_bit_exact_random(Hq, Hkv):
     run_case(seed=Hq * 100 + Hkv, rows=97, Hq=Hq, Hkv=Hkv, max_len=1000, n_slots=5)
+
+
+@pytest.mark.parametrize("Hq,Hkv,hidden", [(10, 10, 1280), (16, 4, 2048), (2, 2, 256), (8, 1, 768)])
+def test_value_embedding_mix_is_bit_exact(Hq, Hkv, hidden):
+    """kv_append_fp8_ve: v <- bf16(v + 2 sigmoid(gate . h) ve[token]) before quantising; q, k and v bytes and scales
+    against the checker, which sums the gate in the reference's lane order."""
+    _, plain = run_case(seed=500 + Hq, rows=61, Hq=Hq, Hkv=Hkv, max_len=512, n_slots=4)
+    _, mixed = run_case(seed=500 + Hq, rows=61, Hq=Hq, Hkv=Hkv, max_len=512, n_slots=4, ve_hidden=hidden)
+    assert np.array_equal(plain["k_bytes"], mixed["k_bytes"]) and not np.array_equal(plain["v_bytes"], mixed["v_bytes"])
 
 
 def test_bit_exact_reference_rope_base_and_strided_rows():
