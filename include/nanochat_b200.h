@@ -272,6 +272,23 @@ int decode_attn_fp8_sharded(const void *q, const void *kv_cache, const void *len
  */
 int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
                 int epilogue, void *stream);
+/* 1 if skinny_gemm takes the shape, else 0 (for choosing between it and stream_gemm without a failed call). */
+int skinny_gemm_supported(int rows, int N, int K, int norm_input);
+/*
+ * The per-layer stream mix of the reference's model, h <- bf16(resid_lambda h + x0_lambda x0) with x0 the first normed
+ * embedding rows (inference/modeling_nanochat.py:170-171; k_norm RESID_NORM, decode.cu:430-432), fused where the
+ * stream is written: skinny_gemm_mix is skinny_gemm's residual epilogue followed by the NEXT layer's mix,
+ *   y = bf16(l1 * bf16(resid + bf16(x . W^T)) + l2 * x0),   x0 bf16 [rows][N];
+ * embed_norm_mix keeps x0 = rms_norm(embed[tokens]) and writes h = bf16(l1 x0 + l2 x0), the first layer's input;
+ * add_rms_norm_mix is add_rms_norm with the mix between the add and the norm. Products and the sum are individually
+ * rounded fp32 operations, then one bf16 rounding.
+ */
+int skinny_gemm_mix(const void *x, const void *w, const void *resid, const void *x0, float l1, float l2, void *y, int rows,
+                    int N, int K, int norm_input, void *stream);
+int embed_norm_mix(const void *embed, const void *tokens, void *h, void *x0, float l1, float l2, int rows, int C,
+                   int vocab, void *stream);
+int add_rms_norm_mix(void *h, const void *y, const void *x0, float l1, float l2, void *n, long long rows, int C,
+                     void *stream);
 /* h bf16 [rows][C] = rms_norm(embed[tokens]); embed bf16 [vocab][C]; tokens int64 [rows]; C a multiple of 8. */
 int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, int vocab, void *stream);
 /* h bf16 [rows][C] += y (same shape, or NULL for no add), in bf16; n bf16 [rows][C] = rms_norm(h). Any number of
@@ -322,6 +339,12 @@ int stream_gemm_split(int rows, int N, int K);
  */
 int stream_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
                 int epilogue, int split, const void *next_w, long long next_bytes, int *status, void *stream);
+
+/* stream_gemm's residual epilogue followed by the NEXT layer's stream mix (see skinny_gemm_mix):
+ * y = bf16(l1 * bf16(resid + bf16(x . W^T)) + l2 * x0), x0 bf16 [rows][N], 16-byte aligned. */
+int stream_gemm_mix(const void *x, const void *w, const void *resid, const void *x0, float l1, float l2, void *y, int rows,
+                    int N, int K, int norm_input, int split, const void *next_w, long long next_bytes, int *status,
+                    void *stream);
 
 #ifdef __cplusplus
 }

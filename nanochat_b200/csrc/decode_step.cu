@@ -32,7 +32,7 @@ constexpr int TILE_N = 8;         /* output features per block */
 constexpr int MAX_ROWS = 16;
 constexpr int MAX_K_ITERS = 20;   /* 32 k-values per iteration and warp: K <= 8 * 20 * 32 = 5120 */
 
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_RELU2 = 2, EPI_F32 = 3 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_RELU2 = 2, EPI_F32 = 3, EPI_MIX = 4 };
 
 struct GemmArgs {
     const bf16 *x;     /* [rows][K] */
@@ -40,7 +40,15 @@ struct GemmArgs {
     const bf16 *resid; /* [rows][N] for EPI_RESID (may alias y) */
     void *y;           /* [rows][N] bf16, or fp32 for EPI_F32 */
     int rows, N, K, norm_input;
+    const bf16 *x0;    /* EPI_MIX: [rows][N], the first normed embedding rows */
+    float l1, l2;      /* EPI_MIX: the next layer's (resid_lambda, x0_lambda) */
 };
+
+/* The per-layer stream mix of the reference's model (inference/modeling_nanochat.py:170-171; decode.cu:430-432):
+ * h <- bf16(l1 h + l2 x0), both products and the sum rounded in fp32, one bf16 rounding. */
+static __device__ __forceinline__ bf16 stream_mix(bf16 h, bf16 x0, float l1, float l2) {
+    return __float2bfloat16_rn(__fadd_rn(__fmul_rn(l1, __bfloat162float(h)), __fmul_rn(l2, __bfloat162float(x0))));
+}
 
 static __device__ __forceinline__ void mma_bf16(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                 uint32_t b0, uint32_t b1) {
@@ -195,8 +203,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, ITERS > 8 ? 2 : 1) k_skinny_gemm
                     reinterpret_cast<float *>(a.y)[at] = v;
                 } else {
                     bf16 out = __float2bfloat16_rn(v);
-                    if (EPI == EPI_RESID)
+                    if (EPI == EPI_RESID || EPI == EPI_MIX)
                         out = __float2bfloat16_rn(__bfloat162float(a.resid[at]) + __bfloat162float(out));
+                    if (EPI == EPI_MIX) out = stream_mix(out, a.x0[at], a.l1, a.l2);
                     if (EPI == EPI_RELU2) {
                         const float r = fmaxf(__bfloat162float(out), 0.f);
                         out = __float2bfloat16_rn(r * r);
@@ -209,9 +218,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, ITERS > 8 ? 2 : 1) k_skinny_gemm
     }
 }
 
-/* h[row] = rms_norm(embed[token[row]]), one warp per row (decode.cu:415-443 EMBED, with a bf16 table). */
-__global__ void __launch_bounds__(128) k_embed_norm(const bf16 *embed, const long long *tokens, bf16 *h, int rows, int C,
-                                                    int vocab) {
+/* x0[row] = rms_norm(embed[token[row]]), one warp per row (decode.cu:415-443 EMBED, with a bf16 table);
+ * h[row] = x0[row], or with mixing the first layer's stream mix bf16(l1 x0 + l2 x0). x0 may be NULL (not kept). */
+__global__ void __launch_bounds__(128) k_embed_norm(const bf16 *embed, const long long *tokens, bf16 *h, bf16 *x0, float l1,
+                                                    float l2, int mix, int rows, int C, int vocab) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -223,15 +233,24 @@ __global__ void __launch_bounds__(128) k_embed_norm(const bf16 *embed, const lon
     for (int i = lane * 8; i < C; i += 256) s += sumsq_bf16x8(*reinterpret_cast<const uint4 *>(e + i));
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     const float r = rsqrtf(s / (float)C + FLT_EPSILON);
-    for (int i = lane * 8; i < C; i += 256)
-        *reinterpret_cast<uint4 *>(h + (size_t)row * C + i) = scale_bf16x8(*reinterpret_cast<const uint4 *>(e + i), r);
+    for (int i = lane * 8; i < C; i += 256) {
+        uint4 v = scale_bf16x8(*reinterpret_cast<const uint4 *>(e + i), r);
+        if (x0) *reinterpret_cast<uint4 *>(x0 + (size_t)row * C + i) = v;
+        if (mix) {
+            bf16 *b = reinterpret_cast<bf16 *>(&v);
+#pragma unroll
+            for (int j = 0; j < 8; j++) b[j] = stream_mix(b[j], b[j], l1, l2);
+        }
+        *reinterpret_cast<uint4 *>(h + (size_t)row * C + i) = v;
+    }
 }
 
 /* h[row] += y[row] (bf16 add, skipped when y is NULL), n[row] = rms_norm(h[row]); one block of 256 threads per row,
  * the row held in registers between the two passes (C <= 256 * 8 * ROW_VECS). For any number of rows: the norm and
  * residual steps between library GEMMs when a pass has more than 16 rows (decode.cu:415-443 RESID_NORM / NORM). */
 constexpr int ROW_THREADS = 256, ROW_VECS = 2;
-__global__ void __launch_bounds__(ROW_THREADS) k_add_rms_norm(bf16 *h, const bf16 *y, bf16 *n, int C) {
+__global__ void __launch_bounds__(ROW_THREADS) k_add_rms_norm(bf16 *h, const bf16 *y, bf16 *n, int C, const bf16 *x0,
+                                                              float l1, float l2) {
     __shared__ float warp_sums[ROW_THREADS / 32];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -252,8 +271,15 @@ __global__ void __launch_bounds__(ROW_THREADS) k_add_rms_norm(bf16 *h, const bf1
                     const float2 fa = __bfloat1622float2(a[e]), fb = __bfloat1622float2(b[e]);
                     a[e] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
                 }
-                *reinterpret_cast<uint4 *>(h + base + i) = v[j];
             }
+            if (x0) { /* the next layer's stream mix, after the residual add */
+                const uint4 z = *reinterpret_cast<const uint4 *>(x0 + base + i);
+                bf16 *a = reinterpret_cast<bf16 *>(&v[j]);
+                const bf16 *b = reinterpret_cast<const bf16 *>(&z);
+#pragma unroll
+                for (int e = 0; e < 8; e++) a[e] = stream_mix(a[e], b[e], l1, l2);
+            }
+            if (y || x0) *reinterpret_cast<uint4 *>(h + base + i) = v[j];
             s += sumsq_bf16x8(v[j]);
         }
     }
@@ -508,6 +534,7 @@ template <int ITERS, bool HI, bool NORM> static int launch_gemm_epi(const GemmAr
     case EPI_RESID: { auto k = k_skinny_gemm<ITERS, HI, EPI_RESID, NORM>; return launch_pdl(k, dim3(grid_for(k, tiles, ITERS <= 8)), block, stream, a); }
     case EPI_RELU2: { auto k = k_skinny_gemm<ITERS, HI, EPI_RELU2, NORM>; return launch_pdl(k, dim3(grid_for(k, tiles, ITERS <= 8)), block, stream, a); }
     case EPI_F32: { auto k = k_skinny_gemm<ITERS, HI, EPI_F32, NORM>; return launch_pdl(k, dim3(grid_for(k, tiles, ITERS <= 8)), block, stream, a); }
+    case EPI_MIX: { auto k = k_skinny_gemm<ITERS, HI, EPI_MIX, NORM>; return launch_pdl(k, dim3(grid_for(k, tiles, ITERS <= 8)), block, stream, a); }
     default: return NCB_ERR_ARG;
     }
 }
@@ -523,24 +550,23 @@ template <int ITERS> static int launch_gemm_rows(const GemmArgs &a, int epilogue
                       : launch_gemm_epi<ITERS, false, false>(a, epilogue, stream);
 }
 
-extern "C" {
+/* The K / 256 values k_skinny_gemm is instantiated for. */
+static bool skinny_depth_ok(int K) {
+    switch (K / (GEMM_WARPS * 32)) {
+    case 1: case 2: case 3: case 4: case 5: case 6: case 8: case 10: case 12: case 16: case 20: return K % (GEMM_WARPS * 32) == 0;
+    default: return false;
+    }
+}
 
-/*
- * y = epilogue(norm?(x) . W^T) for rows <= 16 activation rows.
- *   x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3); resid bf16 [rows][N] for epilogue 1
- *   (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding the product), 2 relu^2, 3 fp32.
- *   norm_input != 0 applies the parameter-free RMS norm (eps FLT_EPSILON, rounded to bf16) to x first.
- * K must be a multiple of 256 and at most 5120 (at most 2048 with norm_input), N a multiple of 8.
- */
-int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
-                int epilogue, void *stream) {
+static int launch_skinny(const GemmArgs &a, int epilogue, cudaStream_t s) {
+    const int rows = a.rows, N = a.N, K = a.K;
     if (rows < 0 || rows > MAX_ROWS || N <= 0 || K <= 0 || N % TILE_N || K % (GEMM_WARPS * 32)) return NCB_ERR_ARG;
-    if (K / (GEMM_WARPS * 32) > MAX_K_ITERS) return NCB_ERR_UNSUPPORTED;
+    if (!skinny_depth_ok(K)) return NCB_ERR_UNSUPPORTED;
     if (rows == 0) return NCB_OK;
-    if (!x || !w || !y || (epilogue == EPI_RESID && !resid)) return NCB_ERR_ARG;
-    if (((uintptr_t)x | (uintptr_t)w) % 16 || (uintptr_t)y % 4) return NCB_ERR_ALIGN;
-    const GemmArgs a = {(const bf16 *)x, (const bf16 *)w, (const bf16 *)resid, y, rows, N, K, norm_input};
-    cudaStream_t s = (cudaStream_t)stream;
+    if (!a.x || !a.w || !a.y || ((epilogue == EPI_RESID || epilogue == EPI_MIX) && !a.resid) ||
+        (epilogue == EPI_MIX && !a.x0))
+        return NCB_ERR_ARG;
+    if (((uintptr_t)a.x | (uintptr_t)a.w) % 16 || (uintptr_t)a.y % 4) return NCB_ERR_ALIGN;
     switch (K / (GEMM_WARPS * 32)) {
     case 1: return launch_gemm_rows<1>(a, epilogue, s);
     case 2: return launch_gemm_rows<2>(a, epilogue, s);
@@ -557,24 +583,79 @@ int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int ro
     }
 }
 
-/* h bf16 [rows][C] = rms_norm(embed[tokens]); tokens int64 [rows]; C a multiple of 8. */
-int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, int vocab, void *stream) {
+extern "C" {
+
+/* 1 if skinny_gemm takes the shape (rows <= 16, N a multiple of 8, K / 256 one of the instantiated depths, at most
+ * 2048 with the fused norm), else 0: callers choose between this kernel and stream_gemm with it. */
+int skinny_gemm_supported(int rows, int N, int K, int norm_input) {
+    if (rows < 0 || rows > MAX_ROWS || N <= 0 || K <= 0 || N % TILE_N || !skinny_depth_ok(K)) return 0;
+    return !(norm_input && K / (GEMM_WARPS * 32) > 8);
+}
+
+/*
+ * y = epilogue(norm?(x) . W^T) for rows <= 16 activation rows.
+ *   x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3); resid bf16 [rows][N] for epilogue 1
+ *   (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding the product), 2 relu^2, 3 fp32.
+ *   norm_input != 0 applies the parameter-free RMS norm (eps FLT_EPSILON, rounded to bf16) to x first.
+ * K must be a multiple of 256 and at most 5120 (at most 2048 with norm_input), N a multiple of 8.
+ */
+int skinny_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
+                int epilogue, void *stream) {
+    if (epilogue < EPI_STORE || epilogue > EPI_F32) return NCB_ERR_ARG;
+    const GemmArgs a = {(const bf16 *)x, (const bf16 *)w, (const bf16 *)resid, y, rows, N, K, norm_input, nullptr, 1.f, 0.f};
+    return launch_skinny(a, epilogue, (cudaStream_t)stream);
+}
+
+/* skinny_gemm with the residual epilogue followed by the NEXT layer's stream mix:
+ * y = bf16(l1 * bf16(resid + bf16(x . W^T)) + l2 * x0), x0 bf16 [rows][N]. */
+int skinny_gemm_mix(const void *x, const void *w, const void *resid, const void *x0, float l1, float l2, void *y, int rows,
+                    int N, int K, int norm_input, void *stream) {
+    const GemmArgs a = {(const bf16 *)x, (const bf16 *)w, (const bf16 *)resid, y, rows, N, K, norm_input, (const bf16 *)x0, l1, l2};
+    return launch_skinny(a, EPI_MIX, (cudaStream_t)stream);
+}
+
+static int launch_embed(const void *embed, const void *tokens, void *h, void *x0, float l1, float l2, int mix, int rows,
+                        int C, int vocab, void *stream) {
     if (rows < 0 || C <= 0 || C % 8 || vocab <= 0) return NCB_ERR_ARG;
     if (rows == 0) return NCB_OK;
     if (!embed || !tokens || !h) return NCB_ERR_ARG;
-    if (((uintptr_t)embed | (uintptr_t)h) % 16) return NCB_ERR_ALIGN;
+    if (((uintptr_t)embed | (uintptr_t)h | (uintptr_t)x0) % 16) return NCB_ERR_ALIGN;
     return launch_pdl(k_embed_norm, dim3((rows + 3) / 4), dim3(128), (cudaStream_t)stream, (const bf16 *)embed,
-                      (const long long *)tokens, (bf16 *)h, rows, C, vocab);
+                      (const long long *)tokens, (bf16 *)h, (bf16 *)x0, l1, l2, mix, rows, C, vocab);
+}
+
+/* h bf16 [rows][C] = rms_norm(embed[tokens]); tokens int64 [rows]; C a multiple of 8. */
+int embed_norm(const void *embed, const void *tokens, void *h, int rows, int C, int vocab, void *stream) {
+    return launch_embed(embed, tokens, h, nullptr, 1.f, 0.f, 0, rows, C, vocab, stream);
+}
+
+/* x0 = rms_norm(embed[tokens]) kept for the later layers' mixes, h = bf16(l1 x0 + l2 x0): the first layer's input. */
+int embed_norm_mix(const void *embed, const void *tokens, void *h, void *x0, float l1, float l2, int rows, int C,
+                   int vocab, void *stream) {
+    if (!x0 && rows > 0) return NCB_ERR_ARG;
+    return launch_embed(embed, tokens, h, x0, l1, l2, 1, rows, C, vocab, stream);
+}
+
+static int launch_add_norm(void *h, const void *y, void *n, const void *x0, float l1, float l2, long long rows, int C,
+                           void *stream) {
+    if (rows < 0 || rows > 0x7fffffffLL || C <= 0 || C % 8 || C > ROW_THREADS * 8 * ROW_VECS) return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    if (!h || !n) return NCB_ERR_ARG;
+    if (((uintptr_t)h | (uintptr_t)y | (uintptr_t)n | (uintptr_t)x0) % 16) return NCB_ERR_ALIGN;
+    return launch_pdl(k_add_rms_norm, dim3((unsigned)rows), dim3(ROW_THREADS), (cudaStream_t)stream, (bf16 *)h,
+                      (const bf16 *)y, (bf16 *)n, C, (const bf16 *)x0, l1, l2);
 }
 
 /* h bf16 [rows][C] += y (same shape; NULL: no add), n = rms_norm(h). C a multiple of 8, at most 4096. */
 int add_rms_norm(void *h, const void *y, void *n, long long rows, int C, void *stream) {
-    if (rows < 0 || rows > 0x7fffffffLL || C <= 0 || C % 8 || C > ROW_THREADS * 8 * ROW_VECS) return NCB_ERR_ARG;
-    if (rows == 0) return NCB_OK;
-    if (!h || !n) return NCB_ERR_ARG;
-    if (((uintptr_t)h | (uintptr_t)y | (uintptr_t)n) % 16) return NCB_ERR_ALIGN;
-    return launch_pdl(k_add_rms_norm, dim3((unsigned)rows), dim3(ROW_THREADS), (cudaStream_t)stream, (bf16 *)h,
-                      (const bf16 *)y, (bf16 *)n, C);
+    return launch_add_norm(h, y, n, nullptr, 1.f, 0.f, rows, C, stream);
+}
+
+/* h += y, then the next layer's stream mix h = bf16(l1 h + l2 x0), then n = rms_norm(h). */
+int add_rms_norm_mix(void *h, const void *y, const void *x0, float l1, float l2, void *n, long long rows, int C,
+                     void *stream) {
+    if (!x0 && rows > 0) return NCB_ERR_ARG;
+    return launch_add_norm(h, y, n, x0, l1, l2, rows, C, stream);
 }
 
 /* u bf16 [count] = relu(u)^2 in place; count a multiple of 8. */

@@ -42,7 +42,7 @@ constexpr int THREADS = 128;
 constexpr int MAX_SPLIT = 8;                     /* portable cluster size */
 constexpr long long WAIT_CYCLES = 4000000000ll;  /* bound of every barrier wait */
 
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_RELU2 = 2, EPI_F32 = 3 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_RELU2 = 2, EPI_F32 = 3, EPI_MIX = 4 };
 
 template <int NP> struct Shape {
     /* A stage holds KSUB consecutive boxes of W and the matching boxes of x. Wider stages (2 or 4 boxes, i.e. 256
@@ -69,6 +69,8 @@ struct GemmArgs {
     const uint8_t *next_w; /* optional: bytes the NEXT kernel will stream, pulled into L2 while this one runs */
     long long next_bytes;
     int *status;
+    const bf16 *x0; /* EPI_MIX: [rows][N], the first normed embedding rows */
+    float l1, l2;   /* EPI_MIX: the next layer's (resid_lambda, x0_lambda) */
 };
 
 /* ---- PTX wrappers ------------------------------------------------------------------------------------------- */
@@ -319,39 +321,45 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
     __syncwarp(); /* the tensor-memory loads below are warp-wide */
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const size_t col = (size_t)tile * TILE_F + tid;
-    auto finish_value = [&](float v, float resid) { /* fp32 product (already normed) -> the bf16 epilogues */
+    /* fp32 product (already normed) -> the bf16 epilogues; EPI_MIX: the residual add, then the next layer's stream
+     * mix bf16(l1 h + l2 x0) with products and sum individually rounded (inference/modeling_nanochat.py:170-171) */
+    auto finish_value = [&](float v, float resid, float x0 = 0.f) {
         bf16 out = __float2bfloat16_rn(v);
-        if (EPI == EPI_RESID) out = __float2bfloat16_rn(resid + __bfloat162float(out));
+        if (EPI == EPI_RESID || EPI == EPI_MIX) out = __float2bfloat16_rn(resid + __bfloat162float(out));
+        if (EPI == EPI_MIX)
+            out = __float2bfloat16_rn(__fadd_rn(__fmul_rn(a.l1, __bfloat162float(out)), __fmul_rn(a.l2, x0)));
         if (EPI == EPI_RELU2) {
             const float p = fmaxf(__bfloat162float(out), 0.f);
             out = __float2bfloat16_rn(p * p);
         }
         return out;
     };
-    auto finish = [&](float v, float resid, size_t at) {
+    auto finish = [&](float v, float resid, float x0, size_t at) {
         if (EPI == EPI_F32)
             reinterpret_cast<float *>(a.y)[at] = v;
         else
-            reinterpret_cast<bf16 *>(a.y)[at] = finish_value(v, resid);
+            reinterpret_cast<bf16 *>(a.y)[at] = finish_value(v, resid, x0);
     };
+    constexpr bool HAS_RESID = EPI == EPI_RESID || EPI == EPI_MIX;
     const float inv_k = 1.f / (float)a.K;
 
     if (S == 1) { /* no partner: straight from tensor memory to y, 32 rows at a time, loads before stores */
 #pragma unroll 1
         for (int c = 0; c < NP / 32; c++) {
             if (c * 32 >= a.rows) break;
-            float v[32], res[32];
+            float v[32], res[32], mix[EPI == EPI_MIX ? 32 : 1];
             tmem_load32(tmem + ((uint32_t)(warp * 32) << 16) + c * 32, v);
 #pragma unroll
             for (int j = 0; j < 32; j++) {
                 const int r = c * 32 + j;
-                res[j] = EPI == EPI_RESID && r < a.rows ? __bfloat162float(a.resid[(size_t)r * a.N + col]) : 0.f;
+                res[j] = HAS_RESID && r < a.rows ? __bfloat162float(a.resid[(size_t)r * a.N + col]) : 0.f;
+                if (EPI == EPI_MIX) mix[j] = r < a.rows ? __bfloat162float(a.x0[(size_t)r * a.N + col]) : 0.f;
                 if (a.norm_input) v[j] *= rsqrtf(sumsq[r] * inv_k + FLT_EPSILON);
             }
 #pragma unroll
             for (int j = 0; j < 32; j++) {
                 const int r = c * 32 + j;
-                if (r < a.rows) finish(v[j], res[j], (size_t)r * a.N + col);
+                if (r < a.rows) finish(v[j], res[j], EPI == EPI_MIX ? mix[j] : 0.f, (size_t)r * a.N + col);
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -387,7 +395,7 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
     for (int r0 = rank + warp * S; r0 < a.rows; r0 += 4 * S * RB) {
         float4 pv[RB][MAX_SPLIT];
         float ps[RB][MAX_SPLIT];
-        uint2 res[RB];
+        uint2 res[RB], mix[RB];
 #pragma unroll
         for (int i = 0; i < RB; i++) {
             const int r = r0 + i * 4 * S;
@@ -397,7 +405,8 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
                 pv[i][s] = ok && s < S ? *reinterpret_cast<const float4 *>(peer_park[s] + r * TILE_F) : make_float4(0.f, 0.f, 0.f, 0.f);
                 ps[i][s] = ok && s < S && a.norm_input ? peer_sumsq[s][r] : 0.f;
             }
-            res[i] = EPI == EPI_RESID && ok ? *reinterpret_cast<const uint2 *>(a.resid + (size_t)r * a.N + col4) : make_uint2(0u, 0u);
+            res[i] = HAS_RESID && ok ? *reinterpret_cast<const uint2 *>(a.resid + (size_t)r * a.N + col4) : make_uint2(0u, 0u);
+            mix[i] = EPI == EPI_MIX && ok ? *reinterpret_cast<const uint2 *>(a.x0 + (size_t)r * a.N + col4) : make_uint2(0u, 0u);
         }
 #pragma unroll
         for (int i = 0; i < RB; i++) {
@@ -419,11 +428,13 @@ __global__ void __launch_bounds__(THREADS) k_stream_gemm(const __grid_constant__
                 *reinterpret_cast<float4 *>(reinterpret_cast<float *>(a.y) + at) = v;
             } else {
                 const __nv_bfloat162 *rr = reinterpret_cast<const __nv_bfloat162 *>(&res[i]);
+                const __nv_bfloat162 *mm = reinterpret_cast<const __nv_bfloat162 *>(&mix[i]);
                 const float2 r01 = __bfloat1622float2(rr[0]), r23 = __bfloat1622float2(rr[1]);
+                const float2 m01 = __bfloat1622float2(mm[0]), m23 = __bfloat1622float2(mm[1]);
                 uint2 out;
                 __nv_bfloat162 *oo = reinterpret_cast<__nv_bfloat162 *>(&out);
-                oo[0] = __halves2bfloat162(finish_value(v.x, r01.x), finish_value(v.y, r01.y));
-                oo[1] = __halves2bfloat162(finish_value(v.z, r23.x), finish_value(v.w, r23.y));
+                oo[0] = __halves2bfloat162(finish_value(v.x, r01.x, m01.x), finish_value(v.y, r01.y, m01.y));
+                oo[1] = __halves2bfloat162(finish_value(v.z, r23.x, m23.x), finish_value(v.w, r23.y, m23.y));
                 *reinterpret_cast<uint2 *>(reinterpret_cast<bf16 *>(a.y) + at) = out;
             }
         }
@@ -541,6 +552,7 @@ int launch_epi(const CUtensorMap &map_w, const CUtensorMap &map_x, const GemmArg
     case EPI_RESID: return launch<NP, EPI_RESID>(map_w, map_x, a, split, stream);
     case EPI_RELU2: return launch<NP, EPI_RELU2>(map_w, map_x, a, split, stream);
     case EPI_F32: return launch<NP, EPI_F32>(map_w, map_x, a, split, stream);
+    case EPI_MIX: return launch<NP, EPI_MIX>(map_w, map_x, a, split, stream);
     default: return NCB_ERR_ARG;
     }
 }
@@ -555,6 +567,36 @@ int stream_gemm_split(int rows, int N, int K) {
     return auto_split(rows, N / TILE_F, K / KBLK);
 }
 
+} /* extern "C" */
+
+/* The checks and the launch shared by stream_gemm and stream_gemm_mix. */
+static int run_stream_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
+                           int epilogue, int split, const void *next_w, long long next_bytes, int *status, void *stream,
+                           const void *x0, float l1, float l2) {
+    if (rows < 0 || rows > 256 || N <= 0 || K <= 0 || N % TILE_F || K % KBLK) return NCB_ERR_ARG;
+    if (epilogue < EPI_STORE || epilogue > EPI_MIX || split < 0 || split > MAX_SPLIT || split > K / KBLK) return NCB_ERR_ARG;
+    if (rows == 0) return NCB_OK;
+    const bool has_resid = epilogue == EPI_RESID || epilogue == EPI_MIX;
+    if (!x || !w || !y || (has_resid && !resid) || (epilogue == EPI_MIX && !x0)) return NCB_ERR_ARG;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)resid | (uintptr_t)x0) % 16) return NCB_ERR_ALIGN;
+    if (next_w && ((uintptr_t)next_w % 16 || next_bytes % 16 || next_bytes < 0)) return NCB_ERR_ALIGN;
+    if (split == 0) split = auto_split(rows, N / TILE_F, K / KBLK);
+    const int np = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
+    CUtensorMap map_w, map_x;
+    if (!tensor_map(w, N, K, TILE_F, &map_w) || !tensor_map(x, rows, K, np, &map_x)) return NCB_ERR_LAUNCH;
+    const GemmArgs a = {(const bf16 *)x, (const bf16 *)resid, y, rows, N, K, norm_input,
+                        next_bytes > 0 ? (const uint8_t *)next_w : nullptr, next_bytes, status, (const bf16 *)x0, l1, l2};
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (np) {
+    case 32: return launch_epi<32>(map_w, map_x, a, epilogue, split, s);
+    case 64: return launch_epi<64>(map_w, map_x, a, epilogue, split, s);
+    case 128: return launch_epi<128>(map_w, map_x, a, epilogue, split, s);
+    default: return launch_epi<256>(map_w, map_x, a, epilogue, split, s);
+    }
+}
+
+extern "C" {
+
 /*
  * y = epilogue(norm?(x) . W^T) for rows <= 256 activation rows on the tcgen05 tensor cores.
  *   x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3); resid bf16 [rows][N] for epilogue 1
@@ -568,25 +610,18 @@ int stream_gemm_split(int rows, int N, int K) {
  */
 int stream_gemm(const void *x, const void *w, const void *resid, void *y, int rows, int N, int K, int norm_input,
                 int epilogue, int split, const void *next_w, long long next_bytes, int *status, void *stream) {
-    if (rows < 0 || rows > 256 || N <= 0 || K <= 0 || N % TILE_F || K % KBLK) return NCB_ERR_ARG;
-    if (epilogue < EPI_STORE || epilogue > EPI_F32 || split < 0 || split > MAX_SPLIT || split > K / KBLK) return NCB_ERR_ARG;
-    if (rows == 0) return NCB_OK;
-    if (!x || !w || !y || (epilogue == EPI_RESID && !resid)) return NCB_ERR_ARG;
-    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)resid) % 16) return NCB_ERR_ALIGN;
-    if (next_w && ((uintptr_t)next_w % 16 || next_bytes % 16 || next_bytes < 0)) return NCB_ERR_ALIGN;
-    if (split == 0) split = auto_split(rows, N / TILE_F, K / KBLK);
-    const int np = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
-    CUtensorMap map_w, map_x;
-    if (!tensor_map(w, N, K, TILE_F, &map_w) || !tensor_map(x, rows, K, np, &map_x)) return NCB_ERR_LAUNCH;
-    const GemmArgs a = {(const bf16 *)x, (const bf16 *)resid, y, rows, N, K, norm_input,
-                        next_bytes > 0 ? (const uint8_t *)next_w : nullptr, next_bytes, status};
-    cudaStream_t s = (cudaStream_t)stream;
-    switch (np) {
-    case 32: return launch_epi<32>(map_w, map_x, a, epilogue, split, s);
-    case 64: return launch_epi<64>(map_w, map_x, a, epilogue, split, s);
-    case 128: return launch_epi<128>(map_w, map_x, a, epilogue, split, s);
-    default: return launch_epi<256>(map_w, map_x, a, epilogue, split, s);
-    }
+    if (epilogue == EPI_MIX) return NCB_ERR_ARG;
+    return run_stream_gemm(x, w, resid, y, rows, N, K, norm_input, epilogue, split, next_w, next_bytes, status, stream,
+                           nullptr, 1.f, 0.f);
+}
+
+/* stream_gemm with the residual epilogue followed by the NEXT layer's stream mix:
+ * y = bf16(l1 * bf16(resid + bf16(x . W^T)) + l2 * x0), x0 bf16 [rows][N], 16-byte aligned. */
+int stream_gemm_mix(const void *x, const void *w, const void *resid, const void *x0, float l1, float l2, void *y, int rows,
+                    int N, int K, int norm_input, int split, const void *next_w, long long next_bytes, int *status,
+                    void *stream) {
+    return run_stream_gemm(x, w, resid, y, rows, N, K, norm_input, EPI_MIX, split, next_w, next_bytes, status, stream, x0,
+                           l1, l2);
 }
 
 } /* extern "C" */

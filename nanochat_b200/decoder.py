@@ -13,8 +13,10 @@ in one CUDA graph per batch size, the reference's remedy for launch-bound decode
 Model semantics follow the reference's exported model (inference/modeling_nanochat.py:113-195): parameter-free RMS
 norm with eps FLT_EPSILON, h = x0 = norm(embed), per layer h = resid_lambda h + x0_lambda x0 (fp32, rounded once),
 QK-norm with per-dimension gains + the "-theta, split halves" rotary, relu^2 MLP, fp32 logits from the bf16 head.
-Value embeddings, sliding windows and the logit cap are not part of the benchmark configurations; windows are
-supported per layer, the cap (monotone) does not change a greedy choice (decode.cu:195).
+The reference's own checkpoints also have value embeddings on alternating layers (v + 2 sigmoid(W n) ve, fused into
+the append kernels) and learned resid / x0 lambdas (fused into the GEMM epilogue that writes the stream); both are
+optional per layer here. Sliding windows are supported per layer; the logit cap (monotone) does not change a greedy
+choice (decode.cu:195) and is applied when sampling.
 
 Prefill runs prompt tokens as rows through the same kernels, every row attending to the positions up to its own
 (decode.cu:859-863,1041-1051; inference/decoder.py:211-222); the prompt's last token is the first decode step's
@@ -78,6 +80,12 @@ class LayerWeights:
     k_gain: Tensor  # fp32 [128]
     resid_lambda: float = 1.0
     x0_lambda: float = 0.0
+    ve_table: Tensor | None = None  # bf16 [V, Hkv 128]: the layer's value embedding (model/modeling.py:35-37), or None
+    ve_gate: Tensor | None = None   # fp32 [Hkv, C]
+
+    @property
+    def mixes(self) -> bool:
+        return self.resid_lambda != 1.0 or self.x0_lambda != 0.0
 
 
 @dataclass
@@ -154,8 +162,8 @@ class Decoder:
         runs in groups of consecutive rows that read a prompt's cache once per group instead of once per row."""
         cfg, lib, s = self.cfg, cuda_library("decode_step"), stream()
         rows, C = tokens.shape[0], cfg.hidden
-        default_mix = all(l.resid_lambda == 1.0 and l.x0_lambda == 0.0 for l in self.w.layers)
-        if not default_mix or C % 8 or C > 4096 or cfg.intermediate % 8:
+        layers = self.w.layers
+        if C % 8 or C > 4096 or cfg.intermediate % 8 or any(l.ve_table is not None and C % 256 for l in layers):
             return self._hidden_rows_torch(tokens, pos, slot_map, max_kv_len, attend_last_layer)
         lens = pos + 1
         workspace = self._workspace(rows, max_kv_len)
@@ -164,18 +172,25 @@ class Decoder:
             plan = ops.PrefillPlan(host_rows[0], host_rows[1], cfg.n_heads, self.caches[0], self.device)
         h = torch.empty((rows, C), dtype=torch.bfloat16, device=self.device)
         n = torch.empty_like(h)
-        check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
+        mixing = any(l.mixes for l in layers)
+        x0 = torch.empty_like(h) if mixing else None
+        if mixing:
+            check(lib.embed_norm_mix(pointer(self.w.embed), pointer(tokens), pointer(h), pointer(x0),
+                                     layers[0].resid_lambda, layers[0].x0_lambda, rows, C, cfg.vocab, s), "embed_norm_mix")
+        else:
+            check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
         check(lib.add_rms_norm(pointer(h), None, pointer(n), rows, C, s), "add_rms_norm")
-        for i, layer in enumerate(self.w.layers):
+        for i, layer in enumerate(layers):
             qkv = n @ layer.wqkv.T
+            ve = None if layer.ve_table is None else ops.ValueEmbed(n, tokens, layer.ve_table, layer.ve_gate)
             if distinct_slots and (attend_last_layer or i < cfg.n_layers - 1):
                 att = ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos,
                                                 self.caches[i], cfg.n_heads, max_kv_len, slot_map=slot_map,
                                                 window=self.windows[i], chunk_pages=self.chunk_pages,
-                                                workspace=workspace, status=self.status)
+                                                workspace=workspace, status=self.status, ve=ve)
             else:
                 q = ops.kv_append(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
-                                  cfg.n_heads, slot_map=slot_map, status=self.status)
+                                  cfg.n_heads, slot_map=slot_map, status=self.status, ve=ve)
                 if i == cfg.n_layers - 1 and not attend_last_layer:
                     return h  # prefill: the last layer only has to fill its cache (decode.cu:862)
                 if plan is not None:
@@ -189,13 +204,18 @@ class Decoder:
             u = n @ layer.wup.T
             check(lib.relu2_inplace(pointer(u), u.numel(), s), "relu2_inplace")
             y = u @ layer.wdown.T
-            check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
+            nxt = layers[i + 1] if i + 1 < len(layers) else None
+            if nxt is not None and nxt.mixes:  # the next layer's stream mix rides on this add
+                check(lib.add_rms_norm_mix(pointer(h), pointer(y), pointer(x0), nxt.resid_lambda, nxt.x0_lambda,
+                                           pointer(n), rows, C, s), "add_rms_norm_mix")
+            else:
+                check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
         return n
 
     def _hidden_rows_torch(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int,
                            attend_last_layer: bool = True) -> Tensor:
-        """hidden_rows with torch operators around the append/attention kernels: the general form (per-layer
-        residual / x0 mixing, any hidden size)."""
+        """hidden_rows with torch operators around the append/attention kernels, for hidden sizes the norm kernels do
+        not take (not a multiple of 8, above 4096)."""
         cfg = self.cfg
         rows = tokens.shape[0]
         lens = pos + 1
@@ -204,9 +224,11 @@ class Decoder:
         for i, layer in enumerate(self.w.layers):
             if layer.resid_lambda != 1.0 or layer.x0_lambda != 0.0:
                 h = (layer.resid_lambda * h.float() + layer.x0_lambda * x0.float()).to(h.dtype)
-            qkv = rms_norm(h) @ layer.wqkv.T
+            n = rms_norm(h)
+            qkv = n @ layer.wqkv.T
+            ve = None if layer.ve_table is None else ops.ValueEmbed(n.contiguous(), tokens, layer.ve_table, layer.ve_gate)
             q = ops.kv_append(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i], cfg.n_heads,
-                              slot_map=slot_map, status=self.status)
+                              slot_map=slot_map, status=self.status, ve=ve)
             if i == cfg.n_layers - 1 and not attend_last_layer:
                 return h  # prefill: the last layer only has to fill its cache (decode.cu:862)
             att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map, window=self.windows[i],
@@ -227,20 +249,23 @@ class Decoder:
 
     def gemm_kernel(self, rows: int) -> str | None:
         """Which of this package's GEMM kernels runs a decode step of `rows` rows: "skinny" (decode_step.cu) for at
-        most 16 rows when the model fits it (hidden sizes up to 2048, since its fused norm keeps a row slice in
-        registers, intermediate sizes up to 5120, all multiples of 256), else "stream" (the tcgen05 stream_gemm) up to
-        64 rows when every GEMM width is a multiple of 128 and every depth of 64; None: cuBLAS and separate norm
-        kernels. Both need the default residual mixing."""
+        most 16 rows when it takes every GEMM of the model (skinny_gemm_supported: depths it is instantiated for, the
+        fused norm up to a depth of 2048), else "stream" (the tcgen05 stream_gemm) up to 64 rows when every GEMM
+        width is a multiple of 128 and every depth of 64; None: cuBLAS and separate norm kernels."""
         cfg = self.cfg
-        if not all(l.resid_lambda == 1.0 and l.x0_lambda == 0.0 for l in self.w.layers):
+        A = cfg.n_heads * HEAD_DIM
+        if any(l.ve_table is not None and cfg.hidden % 256 for l in self.w.layers):
             return None
-        if (rows <= 16 and cfg.hidden % 256 == 0 and cfg.hidden <= 2048 and cfg.intermediate % 256 == 0
-                and cfg.intermediate <= 5120 and (cfg.n_heads * HEAD_DIM) % 256 == 0
-                and cfg.n_heads * HEAD_DIM <= 5120 and cfg.vocab % 8 == 0):
+        ok = cuda_library("decode_step").skinny_gemm_supported
+        # a layer with a value embedding norms its input in a launch of its own (the append reads the normed rows)
+        qkv_norm = 0 if any(l.ve_table is not None for l in self.w.layers) else 1
+        if (rows <= 16 and ok(rows, cfg.qkv_width, cfg.hidden, 1) and ok(rows, cfg.qkv_width, cfg.hidden, qkv_norm)
+                and ok(rows, cfg.hidden, A, 0) and ok(rows, cfg.intermediate, cfg.hidden, 1)
+                and ok(rows, cfg.hidden, cfg.intermediate, 0) and ok(rows, cfg.vocab, cfg.hidden, 1)):
             return "skinny"
         if (rows <= 64 and self.use_stream_gemm  # the kernel takes 256 rows; cuBLAS is faster above about 64
                 and all(n % 128 == 0 for n in (cfg.hidden, cfg.intermediate, cfg.qkv_width, cfg.vocab))
-                and all(k % 64 == 0 for k in (cfg.hidden, cfg.intermediate, cfg.n_heads * HEAD_DIM))):
+                and all(k % 64 == 0 for k in (cfg.hidden, cfg.intermediate, A))):
             return "stream"
         return None
 
@@ -253,6 +278,8 @@ class Decoder:
                 "qkv": torch.empty((rows, cfg.qkv_width), dtype=bf, device=dev),
                 "att": torch.empty((rows, cfg.n_heads, HEAD_DIM), dtype=bf, device=dev),
                 "u": torch.empty((rows, cfg.intermediate), dtype=bf, device=dev),
+                "x0": torch.empty((rows, cfg.hidden), dtype=bf, device=dev),
+                "n": torch.empty((rows, cfg.hidden), dtype=bf, device=dev),
                 "trace": torch.zeros((rows, self.capacity + 1), dtype=torch.long, device=dev),
                 "logits": torch.empty((rows, cfg.vocab), dtype=torch.float32, device=dev)}
 
@@ -268,28 +295,48 @@ class Decoder:
 
         wide = cuda_library("stream_gemm") if self.gemm_kernel(rows) == "stream" else None
 
-        def gemm(x, w, resid, y, n, k, norm, epilogue, then=None):
-            """`then`: the weights of the next GEMM on the stream, prefetched into L2 meanwhile (stream_gemm only)."""
+        def gemm(x, w, resid, y, n, k, norm, epilogue, then=None, mix=None):
+            """`then`: the weights of the next GEMM on the stream, prefetched into L2 meanwhile (stream_gemm only).
+            `mix` = (l1, l2): the residual epilogue is followed by the next layer's stream mix with buf["x0"]."""
             if wide is not None:
                 then = then if self.prefetch_next else None
-                check(wide.stream_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue,
-                                       0, pointer(then), 0 if then is None else then.numel() * 2,
-                                       pointer(self.status), s), "stream_gemm")
-            else:
+                tail = [pointer(then), 0 if then is None else then.numel() * 2, pointer(self.status), s]
+                if mix is None:
+                    check(wide.stream_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue,
+                                           0, *tail), "stream_gemm")
+                else:
+                    check(wide.stream_gemm_mix(pointer(x), pointer(w), pointer(resid), pointer(buf["x0"]), mix[0], mix[1],
+                                               pointer(y), rows, n, k, norm, 0, *tail), "stream_gemm_mix")
+            elif mix is None:
                 check(lib.skinny_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, n, k, norm, epilogue,
                                       s), "skinny_gemm")
+            else:
+                check(lib.skinny_gemm_mix(pointer(x), pointer(w), pointer(resid), pointer(buf["x0"]), mix[0], mix[1],
+                                          pointer(y), rows, n, k, norm, s), "skinny_gemm_mix")
 
-        check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
         layers = self.w.layers
+        if any(l.mixes for l in layers):
+            check(lib.embed_norm_mix(pointer(self.w.embed), pointer(tokens), pointer(h), pointer(buf["x0"]),
+                                     layers[0].resid_lambda, layers[0].x0_lambda, rows, C, cfg.vocab, s), "embed_norm_mix")
+        else:
+            check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
         for i, layer in enumerate(layers):
-            gemm(h, layer.wqkv, None, qkv, cfg.qkv_width, C, 1, 0, then=layer.wo)
+            ve = None
+            if layer.ve_table is None:
+                gemm(h, layer.wqkv, None, qkv, cfg.qkv_width, C, 1, 0, then=layer.wo)
+            else:  # the value-embedding gate reads the normed rows, so they are written out once
+                check(lib.add_rms_norm(pointer(h), None, pointer(buf["n"]), rows, C, s), "add_rms_norm")
+                gemm(buf["n"], layer.wqkv, None, qkv, cfg.qkv_width, C, 0, 0, then=layer.wo)
+                ve = ops.ValueEmbed(buf["n"], tokens, layer.ve_table, layer.ve_gate)
             ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
                                       cfg.n_heads, max_kv_len, slot_map=slot_map, window=self.windows[i],
                                       chunk_pages=self.chunk_pages, workspace=workspace, out=att, status=self.status,
-                                      slots=slots)
+                                      slots=slots, ve=ve)
             gemm(att, layer.wo, h, h, C, A, 0, 1, then=layer.wup)
             gemm(h, layer.wup, None, u, Fd, C, 1, 2, then=layer.wdown)
-            gemm(u, layer.wdown, h, h, C, Fd, 0, 1, then=layers[i + 1].wqkv if i + 1 < len(layers) else None)
+            nxt = layers[i + 1] if i + 1 < len(layers) else None
+            gemm(u, layer.wdown, h, h, C, Fd, 0, 1, then=nxt.wqkv if nxt is not None else None,
+                 mix=(nxt.resid_lambda, nxt.x0_lambda) if nxt is not None and nxt.mixes else None)
         gemm(h, self.w.lm_head, None, buf["logits"], cfg.vocab, C, 1, 3)
         if choose:
             check(lib.greedy_choice(pointer(buf["logits"]), pointer(tokens), pointer(pos), rows, cfg.vocab,

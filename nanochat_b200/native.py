@@ -53,8 +53,12 @@ SIGNATURES = {
     },
     "decode_step": {
         "skinny_gemm": ([c_ptr] * 4 + [c_int] * 5 + [c_ptr], c_int),
+        "skinny_gemm_supported": ([c_int] * 4, c_int),
+        "skinny_gemm_mix": ([c_ptr] * 4 + [c_float, c_float, c_ptr] + [c_int] * 4 + [c_ptr], c_int),
         "embed_norm": ([c_ptr] * 3 + [c_int] * 3 + [c_ptr], c_int),
+        "embed_norm_mix": ([c_ptr] * 4 + [c_float, c_float] + [c_int] * 3 + [c_ptr], c_int),
         "add_rms_norm": ([c_ptr] * 3 + [c_ll, c_int, c_ptr], c_int),
+        "add_rms_norm_mix": ([c_ptr] * 3 + [c_float, c_float, c_ptr, c_ll, c_int, c_ptr], c_int),
         "relu2_inplace": ([c_ptr, c_ll, c_ptr], c_int),
         "sample_choice": ([c_ptr] * 7 + [c_float, c_ptr, c_ptr, c_int, c_int, c_ptr, c_int, c_ptr], c_int),
         "greedy_choice": ([c_ptr] * 3 + [c_int] * 2 + [c_ptr, c_int, c_ptr], c_int),
@@ -62,6 +66,7 @@ SIGNATURES = {
     "stream_gemm": {
         "stream_gemm_split": ([c_int, c_int, c_int], c_int),
         "stream_gemm": ([c_ptr] * 4 + [c_int] * 6 + [c_ptr, c_ll, c_ptr, c_ptr], c_int),
+        "stream_gemm_mix": ([c_ptr] * 4 + [c_float, c_float, c_ptr] + [c_int] * 5 + [c_ptr, c_ll, c_ptr, c_ptr], c_int),
     },
 }
 STATUS = {0: "ok", 1: "invalid argument", 2: "misaligned pointer or stride", 3: "workspace too small",

@@ -10,7 +10,7 @@ import torch
 from nanochat_b200.decoder import Decoder, DecoderConfig, DecoderWeights, LayerWeights
 from oracle.decoder import OracleDecoder
 from tests import helpers
-from tests.test_decoder_oracle import GOLDEN, teacher_forced_logits, uncapped
+from tests.test_decoder_oracle import GOLDEN, GOLDEN_VE, teacher_forced_logits, uncapped
 
 pytestmark = pytest.mark.gpu
 
@@ -22,6 +22,70 @@ def gpu_decoder(n_slots=2):
     layers = [LayerWeights(*(lw[k].cuda() for k in ("wqkv", "wo", "wup", "wdown", "q_gain", "k_gain")))
               for lw in w["layers"]]
     return Decoder(dcfg, DecoderWeights(w["embed"].cuda(), w["lm_head"].cuda(), layers), n_slots), cfg, w
+
+
+def gpu_decoder_ve(n_slots=2):
+    """The reference's own model shape: a value embedding on the last layer, stream-mix lambdas away from (1, 0)."""
+    cfg, w = helpers.tiny_decoder_weights_ve()
+    dcfg = DecoderConfig(cfg["n_layers"], cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["intermediate"],
+                         cfg["vocab"], cfg["rope_theta"], cfg["max_len"])
+    layers = [LayerWeights(*(lw[k].cuda() for k in ("wqkv", "wo", "wup", "wdown", "q_gain", "k_gain")),
+                           resid_lambda=lw["resid_lambda"], x0_lambda=lw["x0_lambda"],
+                           ve_table=lw["ve_table"].cuda() if "ve_table" in lw else None,
+                           ve_gate=lw["ve_gate"].cuda() if "ve_gate" in lw else None) for lw in w["layers"]]
+    return Decoder(dcfg, DecoderWeights(w["embed"].cuda(), w["lm_head"].cuda(), layers), n_slots), cfg, w
+
+
+@torch.no_grad()
+@pytest.mark.parametrize("path", ["rows", "fused"])
+def test_value_embedding_and_stream_mix_match_cpu_restatement_and_reference(path):
+    """A model with a value-embedding layer and non-trivial resid / x0 lambdas, teacher-forced on the golden run of
+    the reference's exported model with the same weights: the row path (cuBLAS GEMMs, add_rms_norm_mix) and the
+    fused step (skinny_gemm_mix epilogue, the mix in embed_norm, the gate inside the attention launch)."""
+    dec, cfg, w = gpu_decoder_ve()
+    assert dec.gemm_kernel(2) == "skinny"
+    slot_map = torch.arange(2, dtype=torch.int32, device="cuda")
+    pos = torch.zeros(2, dtype=torch.int32, device="cuda")
+    buf = dec.fused_buffers(2)
+
+    def step(tok):
+        if path == "fused":
+            logits = dec.fused_step(tok.cuda(), pos, slot_map, int(pos.max()) + 1, buf, choose=False).cpu()
+        else:
+            logits = dec.logits_rows(tok.cuda(), pos.clone(), slot_map, int(pos.max()) + 1).cpu()
+        pos.add_(1)
+        return logits
+
+    got = teacher_forced_logits(step, GOLDEN_VE)
+    oracle = OracleDecoder(cfg, w, n_seqs=2)
+    cpu = teacher_forced_logits(lambda tok: oracle.step(tok, [0, 1]), GOLDEN_VE)
+    err = np.abs(got - cpu)
+    assert err.max() < 1e-2 and err.mean() < 1.5e-3, (err.max(), err.mean())  # GEMM accumulation order only
+    ref = uncapped(GOLDEN_VE["logits"], float(GOLDEN_VE["softcap"]))
+    err = np.abs(got - ref)
+    assert err.max() < 2.5e-2 and err.mean() < 4e-3, (err.max(), err.mean())
+    assert int(dec.status.item()) == 0
+
+
+@torch.no_grad()
+def test_value_embedding_and_stream_mix_on_the_stream_gemm_step():
+    """The same model at 24 rows: the tcgen05 step (stream_gemm_mix epilogue) against the row path with cuBLAS."""
+    ours, cfg, _ = gpu_decoder_ve(24)
+    ref, _, _ = gpu_decoder_ve(24)
+    assert ours.gemm_kernel(24) == "stream"
+    gen = torch.Generator().manual_seed(24)
+    slot_map = torch.arange(24, dtype=torch.int32, device="cuda")
+    pos = torch.zeros(24, dtype=torch.int32, device="cuda")
+    buf = ours.fused_buffers(24)
+    for t in range(3):
+        tok = torch.randint(0, cfg["vocab"], (24,), generator=gen).cuda()
+        got = ours.fused_step(tok.clone(), pos, slot_map, t + 1, buf, choose=False).clone()
+        want = ref.logits_rows(tok, pos.clone(), slot_map, t + 1)
+        pos.add_(1)
+        err = (got - want).abs()
+        top = max(float(want.abs().max()), 1.0)
+        assert err.max() < 3e-2 * top and err.mean() < 5e-3 * top, (t, float(err.max()), float(err.mean()))
+    assert int(ours.status.item()) == 0
 
 
 @torch.no_grad()
