@@ -58,6 +58,29 @@ def test_static_scratch_matches_workspace_entry_on_two_calls_in_a_row():
         assert np.array_equal(got, want), "same kernels, same inputs: the outputs should be identical"
 
 
+def test_static_entry_point_leaves_device_memory_as_it_is():
+    """What the entry point is for: after a first call (which looks up the built-in array's address), further calls
+    change neither the driver's free-memory figure nor torch's allocator statistics."""
+    case = helpers.attention_case(1103, 8, 2, [500, 129])
+    cache = load_cache(case, 512)
+    q = helpers.bits_bf16(case["q"]).cuda()
+    lens = torch.tensor(case["lens"], dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    lib = cuda_library("decode_attn")
+    call = lambda: lib.decode_attn_fp8_static(pointer(q), pointer(cache.pages), pointer(lens), None, pointer(out), 2, 8, 2,
+                                              cache.n_slots, cache.pages_per_slot, 512, 0, 2, SCALE, None, stream())
+    assert call() == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before, allocs_before = torch.cuda.memory_reserved(), torch.cuda.memory_stats()["allocation.all.allocated"]
+    for _ in range(3):
+        assert call() == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_reserved() == reserved_before
+    assert torch.cuda.memory_stats()["allocation.all.allocated"] == allocs_before
+
+
 def test_static_scratch_refuses_what_does_not_fit():
     lib = cuda_library("decode_attn")
     p = ctypes.c_void_p(4096)
