@@ -314,6 +314,87 @@ def bench_longctx(rank: int, world: int, device, steps: int, warmup: int, timed)
             "merge, all_gather_into_tensor, merge", "parity": parity}
 
 
+def bench_kernels(device, timed, profile_range: str) -> dict:
+    """The path's other kernels on their own, each against the measured HBM bandwidth: k_kv_append on a prefill-sized
+    pass (8 prompts of 2,048 positions, the d20 head shape: 209 MB per launch, larger than L2), k_merge on the target
+    shape's states, and k_merge_exchange as a world of one (its local part: chunk merge, call counter; no peer to
+    wait for). `profile_range` brackets one of them with cudaProfilerStart/Stop for ncu."""
+    import nanochat_b200 as ncb
+    from nanochat_b200 import attention as ops
+    from nanochat_b200.native import cuda_library, pointer, stream
+
+    peak, _ = peaks()
+    out = {}
+
+    def ranged(name, fn, steps):
+        if profile_range == name:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+        ms = timed(fn, steps, 3)
+        if profile_range == name:
+            torch.cuda.profiler.stop()
+        return ms
+
+    # ---- append: a prefill pass
+    Hq, Hkv, prompts, per = 10, 10, 8, 2048
+    rows = prompts * per
+    gen = torch.Generator(device=device).manual_seed(7000)
+    qkv = torch.randn(rows, (Hq + 2 * Hkv) * D, generator=gen, device=device).bfloat16()
+    slot_map = torch.arange(prompts, dtype=torch.int32, device=device).repeat_interleave(per)
+    pos = torch.arange(per, dtype=torch.int32, device=device).repeat(prompts)
+    cache = ncb.Fp8KVCache(prompts, Hkv, per, device=device)
+    cos, sin = ncb.rotary_table(per, 1e4, device=device)
+    ones = torch.ones(D, device=device)
+    q_out = torch.empty(rows, Hq, D, dtype=torch.bfloat16, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    ms = ranged("append", lambda: ncb.kv_append(qkv, ones, ones, cos, sin, pos, cache, Hq, slot_map=slot_map, q_out=q_out,
+                                                status=status), 20)
+    nbytes = rows * ((Hq + 2 * Hkv) * 256 + Hq * 256 + 2 * Hkv * 132)
+    out["kv_append_prefill"] = {"workload": f"{rows} rows (8 prompts x 2048 positions), Hq 10, Hkv 10", "us_per_launch": ms * 1e3,
+                                "algorithmic_bytes_per_launch": nbytes, "achieved": nbytes / ms / 1e6, "unit": UNIT,
+                                "frac": nbytes / ms / 1e6 / peak}
+    assert int(status.item()) == 0
+    del qkv, cache, q_out
+
+    # ---- merge and the exchange kernel's local part, on states the split kernel left for the target shape
+    B, chunk = BATCH, 32
+    lens = [8192] * B
+    cache = synthetic_cache(lens, 8192, seed=7100, device=device)
+    q = torch.randn(B, HQ, D, generator=gen, device=device).bfloat16()
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=device)
+    workspace = torch.empty(ncb.workspace_bytes(B, HQ, HKV, 8192, chunk), dtype=torch.uint8, device=device)
+    ops.decode_attention_split(q, cache, lens_t, 8192, workspace, chunk_pages=chunk, status=status)
+    n_chunks = 8192 // 64 // chunk
+    parts = workspace.view(torch.float32).view(B * HQ, n_chunks, 132).transpose(0, 1).contiguous()  # (parts, rows, 132)
+    merged = torch.empty(B, HQ, D, dtype=torch.bfloat16, device=device)
+    ms = ranged("merge", lambda: ops.merge_partials(parts.view(n_chunks, B, HQ, 132), out=merged), 50)
+    nbytes = B * HQ * (n_chunks * 528 + 256)
+    out["merge"] = {"workload": f"{B * HQ} rows x {n_chunks} states (the target shape's split states)", "us_per_launch": ms * 1e3,
+                    "algorithmic_bytes_per_launch": nbytes, "achieved": nbytes / ms / 1e6, "unit": UNIT,
+                    "frac": nbytes / ms / 1e6 / peak, "note": "a launch-latency-sized kernel: 4.8 MB per launch"}
+    inbox = torch.zeros(2 * B * HQ * 1056 // 4, dtype=torch.int32, device=device)
+    epoch = torch.zeros(2, dtype=torch.int32, device=device)
+    import ctypes
+    p_inbox = (ctypes.c_void_p * 1)(inbox.data_ptr())
+    lib = cuda_library("decode_attn")
+
+    def sharded():
+        rc = lib.decode_attn_fp8_sharded(pointer(q), pointer(cache.pages), pointer(lens_t), None, pointer(workspace),
+                                         workspace.numel(), pointer(merged), B, HQ, HKV, cache.n_slots, cache.pages_per_slot,
+                                         8192, 0, chunk, D ** -0.5, p_inbox, 1, 0, pointer(epoch), pointer(status), stream())
+        assert rc == 0
+
+    split_only = lambda: ops.decode_attention_split(q, cache, lens_t, 8192, workspace, chunk_pages=chunk, status=status)
+    ms_both = ranged("exchange", sharded, 20)
+    ms_split = timed(split_only, 20, 3)
+    out["merge_exchange_world1"] = {"workload": "decode_attn_fp8_sharded as a world of one on the target shape: the second "
+                                                "launch merges the local chunk states, has no peer to send to or wait for, "
+                                                "and advances the call counter", "us_per_step": ms_both * 1e3,
+                                    "us_split_alone": ms_split * 1e3, "us_merge_exchange": (ms_both - ms_split) * 1e3}
+    assert int(status.item()) == 0
+    return out
+
+
 def bench_decoder(rank: int, world: int, device, new_tokens: int, profile: bool = False) -> dict:
     """End-to-end greedy decode of the random-init d20 model (20 layers, d_model 1280, 10 heads, vocab 65536, bf16
     weights ~ N(0, 0.02)): batch 8 per GPU, 512-token prompts, `new_tokens` generated tokens; every rank runs its own
@@ -496,7 +577,9 @@ def main() -> None:
     ap.add_argument("--chunk-pages", type=int, default=0)
     ap.add_argument("--decoder", type=int, default=1, help="also time end-to-end greedy decoding of d20 (0: skip)")
     ap.add_argument("--decoder-tokens", type=int, default=256, help="tokens generated per sequence in that run")
-    ap.add_argument("--profile-range", default="attention", choices=["attention", "decoder", "decoder_d32"],
+    ap.add_argument("--kernels", type=int, default=1, help="also time the append, merge and exchange kernels alone (N = 1; 0: skip)")
+    ap.add_argument("--profile-range", default="attention",
+                    choices=["attention", "decoder", "decoder_d32", "append", "merge", "exchange"],
                     help="which timed loops cudaProfilerStart/Stop bracket (for `ncu --profile-from-start off`)")
     ap.add_argument("--decoder-d32", type=int, default=1, help="also time batched decode of the d32-class model (0: skip)")
     ap.add_argument("--ragged", type=int, default=1, help="also run the ragged GQA sweep as an extra (0: skip)")
@@ -664,6 +747,7 @@ def main() -> None:
 
     head = attention_workload(args.workload, True, args.profile_range == "attention")
     ragged = attention_workload("ragged", False, False) if args.ragged and args.workload != "ragged" else None
+    kernels = bench_kernels(device, timed, args.profile_range) if args.kernels and world == 1 else None
     longctx = bench_longctx(rank, world, device, min(args.steps, 100), 5, timed) if args.longctx else None
     decoder = bench_decoder(rank, world, device, args.decoder_tokens, args.profile_range == "decoder") \
         if args.decoder else None
@@ -690,6 +774,8 @@ def main() -> None:
                               "value": rvalue, "unit": UNIT, "ms_per_step": ragged["ms_step"], "scaling": "weak",
                               "chunk_pages": ragged["chunk"], "roofline": roofline_of(ragged, None),
                               "parity": ragged["parity"]}
+        if kernels:
+            line["kernels"] = kernels
         if longctx:
             line["longctx"] = longctx
         if decoder:

@@ -17,6 +17,8 @@ constexpr int BLOCK = 128;
 constexpr int ROWS_PER_BLOCK = BLOCK / LANES; /* 16: one run of V positions that share 16-byte chunks */
 static_assert(ROWS_PER_BLOCK == 16 && BLOCK == HEAD_DIM, "a V run is 16 positions and the block has a thread per dim");
 
+namespace {
+
 struct AppendArgs {
     const bf16 *qkv;
     const float *q_gain, *k_gain, *cs, *sn;
@@ -27,16 +29,20 @@ struct AppendArgs {
     int Hq, Hkv, table_len, n_slots, pages_per_slot;
     int *status;
     ValueEmbed ve; /* table == NULL: no value embedding on this layer */
+    int heads_per_block;
 };
 
-/* Block (x, y) = rows 16 x .. 16 x + 15 of head row y (q heads, then k heads, then v heads); 8 lanes per row. */
-__global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
+/* Block (x, y) = rows 16 x .. 16 x + 15 of the head rows y hpb .. y hpb + hpb - 1 (q heads, then k heads, then v heads);
+ * 8 lanes per row. A block of a large pass walks over several head rows: positions, slots and the run test are
+ * done once, the rows' rotary entries stay in L1 between heads, and the next head's inputs are in flight while the
+ * current one is computed. */
+__global__ void __launch_bounds__(BLOCK, 6) k_kv_append(AppendArgs a) {
     /* launched with programmatic stream serialisation: wait for the kernel that produced qkv and pos, then let the
      * next kernel's launch overlap this one (it waits the same way before it reads the cache or q) */
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ __align__(16) uint8_t vt[HEAD_DIM][ROWS_PER_BLOCK]; /* a V run transposed: [dim][position] */
-    const int which = blockIdx.y, g = threadIdx.x / LANES, t = threadIdx.x % LANES, o = t * VEC;
+    const int g = threadIdx.x / LANES, t = threadIdx.x % LANES, o = t * VEC;
     const long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK, row = row0 + g;
     const bool live = row < a.rows;
     int p = 0, slot = 0;
@@ -46,57 +52,67 @@ __global__ void __launch_bounds__(BLOCK) k_kv_append(AppendArgs a) {
         slot = a.slot_map ? a.slot_map[row] : (int)row;
         valid = !(p < 0 || p >= a.table_len || p >= a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots);
         /* a negative position marks an idle row (skipped silently); anything else outside the cache is flagged */
-        if (!valid && p >= 0 && t == 0 && which == 0) flag(a.status, NCB_DEV_BAD_POSITION);
+        if (!valid && p >= 0 && t == 0 && blockIdx.y == 0) flag(a.status, NCB_DEV_BAD_POSITION);
     }
-    const bool is_k = which >= a.Hq && which < a.Hq + a.Hkv, is_v = which >= a.Hq + a.Hkv;
     /* A prefill pass appends runs of consecutive positions of one slot. When the block's 16 rows are such a run and
      * start on a 16-position boundary, their V bytes of one dim are 16 contiguous bytes of the page: they are
      * transposed through shared memory and stored as 128 16-byte chunks (2 KB contiguous) instead of 2,048 single
      * bytes. Any other block (decode steps, ragged edges) stores byte by byte. Same bytes either way. */
-    bool run = false;
-    if (is_v) {
-        const int p0 = a.pos[row0], slot0 = a.slot_map ? a.slot_map[row0] : (int)row0;
-        run = __syncthreads_and(live && valid && slot == slot0 && p == p0 + g && p0 % ROWS_PER_BLOCK == 0);
-    }
-    if (!live || !valid) return; /* never part of a run: no barrier follows for this thread */
-    const bf16 *x = a.qkv + row * a.qkv_row_stride + (size_t)which * HEAD_DIM;
-    float x1[VEC], x2[VEC];
-    load_bf16x8(x + o, x1);
-    load_bf16x8(x + HALF + o, x2);
-    const size_t tab = (size_t)p * HALF;
-    if (which < a.Hq) {
-        norm_rotate(x1, x2, a.q_gain, a.cs + tab, a.sn + tab, o);
-        bf16 *q = a.q_out + ((size_t)row * a.Hq + which) * HEAD_DIM;
-        *reinterpret_cast<uint4 *>(q + o) = pack_bf16x8(x1);
-        *reinterpret_cast<uint4 *>(q + HALF + o) = pack_bf16x8(x2);
-        return;
-    }
-    const int head = is_k ? which - a.Hq : which - a.Hq - a.Hkv;
-    if (is_k) norm_rotate(x1, x2, a.k_gain, a.cs + tab, a.sn + tab, o);
-    else if (a.ve.table) ve_mix(x1, x2, a.ve, row, head, a.Hkv, t, o);
-    uint8_t b1[VEC], b2[VEC];
-    const float scale = quantise(x1, x2, b1, b2);
+    const int p0 = a.pos[row0], slot0 = a.slot_map ? a.slot_map[row0] : (int)row0;
+    const bool run = __syncthreads_and(live && valid && slot == slot0 && p == p0 + g && p0 % ROWS_PER_BLOCK == 0);
+    const bool on = live && valid; /* the same for the 8 lanes of a row; nobody leaves before the loop's barriers */
+    const int heads = a.Hq + 2 * a.Hkv, first = blockIdx.y * a.heads_per_block;
+    const int last = min(first + a.heads_per_block, heads);
+    const bf16 *x = a.qkv + (on ? row : 0) * a.qkv_row_stride;
+    const size_t tab = (size_t)(on ? p : 0) * HALF;
     const int j = p % PAGE_TOKENS;
-    uint8_t *page = a.cache + (((size_t)slot * a.Hkv + head) * a.pages_per_slot + p / PAGE_TOKENS) * PAGE_BYTES;
-    if (is_k) {
-        store_k_row(page, j, t, b1, b2);
-        if (t == 0) reinterpret_cast<float *>(page + PAGE_KS)[j] = scale;
-        return;
+    uint4 raw1 = make_uint4(0, 0, 0, 0), raw2 = raw1;
+    if (on && first < last) {
+        raw1 = *reinterpret_cast<const uint4 *>(x + (size_t)first * HEAD_DIM + o);
+        raw2 = *reinterpret_cast<const uint4 *>(x + (size_t)first * HEAD_DIM + HALF + o);
     }
-    if (t == 0) reinterpret_cast<float *>(page + PAGE_VS)[j] = scale;
-    if (!run) {
-        store_v_row(page, j, t, b1, b2);
-        return;
-    }
+    for (int which = first; which < last; which++) {
+        float x1[VEC], x2[VEC];
+        unpack_bf16x8(raw1, x1);
+        unpack_bf16x8(raw2, x2);
+        if (on && which + 1 < last) { /* the next head row's inputs start now */
+            raw1 = *reinterpret_cast<const uint4 *>(x + (size_t)(which + 1) * HEAD_DIM + o);
+            raw2 = *reinterpret_cast<const uint4 *>(x + (size_t)(which + 1) * HEAD_DIM + HALF + o);
+        }
+        const bool is_q = which < a.Hq, is_k = !is_q && which < a.Hq + a.Hkv, is_v = !is_q && !is_k;
+        const int head = is_q ? which : is_k ? which - a.Hq : which - a.Hq - a.Hkv;
+        uint8_t *page = a.cache + (((size_t)(on ? slot : 0) * a.Hkv + (is_q ? 0 : head)) * a.pages_per_slot +
+                                   (on ? p / PAGE_TOKENS : 0)) * PAGE_BYTES;
+        uint8_t b1[VEC], b2[VEC];
+        if (on) {
+            if (!is_v) norm_rotate(x1, x2, is_q ? a.q_gain : a.k_gain, a.cs + tab, a.sn + tab, o);
+            else if (a.ve.table) ve_mix(x1, x2, a.ve, row, head, a.Hkv, t, o);
+            if (is_q) {
+                bf16 *q = a.q_out + ((size_t)row * a.Hq + head) * HEAD_DIM;
+                *reinterpret_cast<uint4 *>(q + o) = pack_bf16x8(x1);
+                *reinterpret_cast<uint4 *>(q + HALF + o) = pack_bf16x8(x2);
+            } else {
+                const float scale = quantise(x1, x2, b1, b2);
+                if (t == 0) reinterpret_cast<float *>(page + (is_k ? PAGE_KS : PAGE_VS))[j] = scale;
+                if (is_k) store_k_row16(page, j, t, b1, b2);
+                else if (!run) store_v_row(page, j, t, b1, b2);
+            }
+        }
+        if (is_v && run) { /* block-uniform: every thread of the block is in the run */
 #pragma unroll
-    for (int i = 0; i < VEC; i++) {
-        vt[o + i][g] = b1[i];
-        vt[HALF + o + i][g] = b2[i];
+            for (int i = 0; i < VEC; i++) {
+                vt[o + i][g] = b1[i];
+                vt[HALF + o + i][g] = b2[i];
+            }
+            __syncthreads();
+            const int d = threadIdx.x, j0 = j - g; /* the run's first in-page position; thread = dim */
+            *reinterpret_cast<uint4 *>(page + page_v_byte(j0, d)) = *reinterpret_cast<const uint4 *>(vt[d]);
+            __syncthreads(); /* the next v head row reuses the tile */
+        }
     }
-    __syncthreads(); /* every thread of the block is in the run */
-    const int d = threadIdx.x, j0 = j - g; /* the run's first in-page position; thread = dim */
-    *reinterpret_cast<uint4 *>(page + page_v_byte(j0, d)) = *reinterpret_cast<const uint4 *>(vt[d]);
 }
+
+} /* namespace */
 
 extern "C" {
 
@@ -140,12 +156,17 @@ static int launch_append(const void *qkv, const void *q_gain, const void *k_gain
     }
     const long long blocks = (rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
     if (blocks > 0x7fffffffLL || Hq + 2 * Hkv > 65535) return NCB_ERR_ARG;
+    /* small passes (decode steps): one head row per block, as many blocks as possible; large passes (prefill): a block
+     * walks over up to 8 head rows as long as about 2,048 blocks remain, enough to fill every SM several times */
+    const int heads = Hq + 2 * Hkv;
+    long long hpb = blocks * heads / 2048;
+    hpb = hpb < 1 ? 1 : hpb > 8 ? 8 : hpb;
     AppendArgs a = {(const bf16 *)qkv, (const float *)q_gain, (const float *)k_gain, (const float *)cos,
                     (const float *)sin, (const int32_t *)pos, (const int32_t *)slot_map, (bf16 *)q_out,
                     (uint8_t *)kv_cache, rows, qkv_row_stride, Hq, Hkv, table_len, n_slots, pages_per_slot,
-                    (int *)status, ve};
+                    (int *)status, ve, (int)hpb};
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)blocks, (unsigned)(Hq + 2 * Hkv));
+    config.gridDim = dim3((unsigned)blocks, (unsigned)((heads + hpb - 1) / hpb));
     config.blockDim = dim3(BLOCK);
     config.stream = (cudaStream_t)stream;
     cudaLaunchAttribute attribute[1];

@@ -12,6 +12,16 @@
 constexpr int LANES = 8;
 constexpr int VEC = 8;
 
+static __device__ __forceinline__ void unpack_bf16x8(const uint4 &u, float *v) {
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&u);
+#pragma unroll
+    for (int i = 0; i < VEC / 2; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
 static __device__ __forceinline__ void load_bf16x8(const bf16 *p, float *v) {
     const uint4 u = *reinterpret_cast<const uint4 *>(p);
     const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&u);
@@ -55,18 +65,20 @@ static __device__ __forceinline__ void norm_rotate(float *x1, float *x2, const f
     ss = group_sum(ss);
     const float mean = __fdiv_rn(ss, (float)HEAD_DIM);
     const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(mean, FLT_EPSILON)));
-    float g1[VEC], g2[VEC], c[VEC], s[VEC];
-    load_f32x8(gain + o, g1);
-    load_f32x8(gain + HALF + o, g2);
-    load_f32x8(cs + o, c);
-    load_f32x8(sn + o, s);
 #pragma unroll
-    for (int i = 0; i < VEC; i++) {
-        const float n1 = __fmul_rn(__fmul_rn(x1[i], r), g1[i]), n2 = __fmul_rn(__fmul_rn(x2[i], r), g2[i]);
-        const float y1 = __fadd_rn(__fmul_rn(n1, c[i]), __fmul_rn(n2, s[i]));
-        const float y2 = __fsub_rn(__fmul_rn(n2, c[i]), __fmul_rn(n1, s[i]));
-        x1[i] = __bfloat162float(__float2bfloat16_rn(y1));
-        x2[i] = __bfloat162float(__float2bfloat16_rn(y2));
+    for (int q = 0; q < VEC; q += 4) { /* four dims and their partners at a time: 16 table values live, not 32 */
+        const float4 g1 = *reinterpret_cast<const float4 *>(gain + o + q), g2 = *reinterpret_cast<const float4 *>(gain + HALF + o + q);
+        const float4 c = *reinterpret_cast<const float4 *>(cs + o + q), s = *reinterpret_cast<const float4 *>(sn + o + q);
+        const float g1v[4] = {g1.x, g1.y, g1.z, g1.w}, g2v[4] = {g2.x, g2.y, g2.z, g2.w};
+        const float cv[4] = {c.x, c.y, c.z, c.w}, sv[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float n1 = __fmul_rn(__fmul_rn(x1[q + i], r), g1v[i]), n2 = __fmul_rn(__fmul_rn(x2[q + i], r), g2v[i]);
+            const float y1 = __fadd_rn(__fmul_rn(n1, cv[i]), __fmul_rn(n2, sv[i]));
+            const float y2 = __fsub_rn(__fmul_rn(n2, cv[i]), __fmul_rn(n1, sv[i]));
+            x1[q + i] = __bfloat162float(__float2bfloat16_rn(y1));
+            x2[q + i] = __bfloat162float(__float2bfloat16_rn(y2));
+        }
     }
 }
 
@@ -145,6 +157,27 @@ static __device__ __forceinline__ float quantise(const float *x1, const float *x
     return scale;
 }
 
+
+/* The same K row as store_k_row below, as one 16-byte store per lane instead of two 8-byte ones: neighbouring lanes
+ * swap halves, so that the even lane holds chunk t/2 (its own dims 8t..8t+7 and the neighbour's) and the odd lane chunk
+ * 4 + t/2 (the partners). All 8 lanes of the row's group must call it. */
+static __device__ __forceinline__ void store_k_row16(uint8_t *page, int j, int t, const uint8_t *b1, const uint8_t *b2) {
+    unsigned long long lo, hi;
+    memcpy(&lo, b1, 8);
+    memcpy(&hi, b2, 8);
+    const unsigned mask = group_mask();
+    const bool odd = t & 1;
+    /* the even lane gives away its partners' half, the odd lane its first half */
+    const unsigned long long got = __shfl_xor_sync(mask, odd ? lo : hi, 1);
+    uint4 chunk;
+    if (odd) {
+        chunk = make_uint4((uint32_t)got, (uint32_t)(got >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
+        *reinterpret_cast<uint4 *>(page + page_k_chunk(j, 4 + (t >> 1))) = chunk;
+    } else {
+        chunk = make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)got, (uint32_t)(got >> 32));
+        *reinterpret_cast<uint4 *>(page + page_k_chunk(j, t >> 1)) = chunk;
+    }
+}
 
 /* Lane t's 8 + 8 quantised bytes of a K row into a page (global or shared) at in-page position j: dims 8t..8t+7 sit
  * in chunk t/2 at byte (t&1)*8, the partners in chunk 4 + t/2. */
