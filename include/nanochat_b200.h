@@ -346,6 +346,23 @@ int stream_gemm_mix(const void *x, const void *w, const void *resid, const void 
                     int N, int K, int norm_input, int split, const void *next_w, long long next_bytes, int *status,
                     void *stream);
 
+/* ---- library tile_gemm --------------------------------------------------------------------------------------
+ * The same GEMM for any number of rows as a tiled tcgen05 kernel (128 rows x 256 features per tile, TMA-staged operands,
+ * two accumulators in tensor memory so that the epilogue of one tile overlaps the MMAs of the next, one persistent
+ * block per SM): the GEMMs of prefill passes and of decode steps above 64 sequences, where the reference runs k_wgmma
+ * over prompt rows (model/kernels/decode.cu:232-359,1041-1051). */
+
+/*
+ * y = epilogue(x . W^T). x bf16 [rows][K]; w bf16 [N][K]; y bf16 [rows][N] (fp32 for epilogue 3); resid bf16 [rows][N]
+ * for epilogue 1 (may be y itself). epilogue: 0 store, 1 residual add (in bf16, after rounding the product), 2 relu^2,
+ * 3 fp32 store. Any rows >= 0; N a multiple of 128 (tiles are 256 wide when N is a multiple of 256); K a multiple of
+ * 64; all pointers 16-byte aligned. No fused input norm: passes of this size keep the normed rows in memory
+ * (add_rms_norm). status: optional device word for NCB_DEV_WAIT_TIMEOUT. Launched with programmatic stream
+ * serialisation.
+ */
+int tile_gemm(const void *x, const void *w, const void *resid, void *y, long long rows, int N, int K, int epilogue,
+              int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,11 +4,13 @@ Stands where the reference's NativeDecoder / decode.cu step graph stands (infere
 model/kernels/decode.cu:848-891): per layer
     norm -> qkv GEMM -> [kv_append_fp8 -> decode_attn_fp8] -> o GEMM + residual -> norm -> up GEMM, relu^2 ->
     down GEMM + residual
-then the final norm, the lm_head GEMM and an argmax. Steps of at most 16 rows run entirely on this package's
-kernels (csrc/decode_step.cu: weight-streaming GEMMs with fused norm and epilogues); larger passes (bigger batches,
-prefill) keep the GEMMs on cuBLAS and run everything between them on this package's kernels — the reference's own
-GEMM kernel is Hopper-only wgmma (decode.cu:232-359) and has to be replaced either way. The whole step is captured
-in one CUDA graph per batch size, the reference's remedy for launch-bound decode steps.
+then the final norm, the lm_head GEMM and an argmax. Every GEMM runs on this package's kernels (the reference's own
+GEMM kernel is Hopper-only wgmma, decode.cu:232-359, and has to be replaced either way): steps of at most 16 rows on
+csrc/decode_step.cu (weight-streaming mma.sync GEMMs with fused norm and epilogues), 17 to 64 rows on
+csrc/stream_gemm.cu (tcgen05 weight stream, K split over a cluster), larger passes (bigger batches, prefill) on
+csrc/tile_gemm.cu (tiled tcgen05 GEMM) with the norm / residual steps between them as kernels of their own. A library
+GEMM (torch) is only the fallback for widths that are not a multiple of 128. The whole step is captured in one CUDA
+graph per batch size, the reference's remedy for launch-bound decode steps.
 
 Model semantics follow the reference's exported model (inference/modeling_nanochat.py:113-195): parameter-free RMS
 norm with eps FLT_EPSILON, h = x0 = norm(embed), per layer h = resid_lambda h + x0_lambda x0 (fp32, rounded once),
@@ -134,7 +136,8 @@ class Decoder:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.windows = cfg.windows or [0] * cfg.n_layers
         self.use_fused = True  # decode steps of <= 64 rows run on this package's GEMM kernels when the shapes allow
-        self.use_stream_gemm = True  # ... of 17 to 64 rows on the tcgen05 stream_gemm (else cuBLAS)
+        self.use_stream_gemm = True  # ... of 17 to 64 rows on the tcgen05 stream_gemm (else the row path)
+        self.use_tile_gemm = True  # row passes (prefill, steps above 64 rows) on the tiled tcgen05 GEMM, not torch's
         self.chunk_pages = 0  # attention chunk size of decode steps; 0: the library's choice for full-length slots
         self.prefetch_next = True  # stream_gemm also pulls the next GEMM's weights into L2 (d32-class step: -1.3 %)
         self._graphs: dict[int, tuple] = {}
@@ -154,7 +157,7 @@ class Decoder:
                     attend_last_layer: bool = True, distinct_slots: bool = False,
                     host_rows: tuple[list[int], list[int]] | None = None) -> Tensor:
         """Final-normed hidden states (rows, C) bf16 of `tokens` at positions `pos` of slots `slot_map`; appends
-        every row's k, v to the caches. max_kv_len bounds pos + 1. Any number of rows: GEMMs on cuBLAS, everything
+        every row's k, v to the caches. max_kv_len bounds pos + 1. Any number of rows: GEMMs on the tiled tcgen05 kernel, everything
         between them on this package's kernels (embedding + norm, residual add + norm, relu^2, append, attention).
         distinct_slots: no two rows share a slot (a decode step), so the attention kernel may append its own
         token; prefill passes, where rows of one sequence read each other's positions, need the separate append.
@@ -181,7 +184,7 @@ class Decoder:
             check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
         check(lib.add_rms_norm(pointer(h), None, pointer(n), rows, C, s), "add_rms_norm")
         for i, layer in enumerate(layers):
-            qkv = n @ layer.wqkv.T
+            qkv = self.gemm_rows(n, layer.wqkv)
             ve = None if layer.ve_table is None else ops.ValueEmbed(n, tokens, layer.ve_table, layer.ve_gate)
             if distinct_slots and (attend_last_layer or i < cfg.n_layers - 1):
                 att = ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos,
@@ -199,11 +202,10 @@ class Decoder:
                     att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map,
                                                window=self.windows[i], chunk_pages=self.chunk_pages,
                                                workspace=workspace, status=self.status)
-            y = att.view(rows, -1) @ layer.wo.T
+            y = self.gemm_rows(att.view(rows, -1), layer.wo)
             check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
-            u = n @ layer.wup.T
-            check(lib.relu2_inplace(pointer(u), u.numel(), s), "relu2_inplace")
-            y = u @ layer.wdown.T
+            u = self.gemm_rows(n, layer.wup, epilogue=2)
+            y = self.gemm_rows(u, layer.wdown)
             nxt = layers[i + 1] if i + 1 < len(layers) else None
             if nxt is not None and nxt.mixes:  # the next layer's stream mix rides on this add
                 check(lib.add_rms_norm_mix(pointer(h), pointer(y), pointer(x0), nxt.resid_lambda, nxt.x0_lambda,
@@ -211,6 +213,23 @@ class Decoder:
             else:
                 check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
         return n
+
+    def gemm_rows(self, x: Tensor, w: Tensor, epilogue: int = 0) -> Tensor:
+        """epilogue(x . w^T) for a pass of any number of rows: x bf16 (rows, K), w bf16 (N, K); epilogue 0 store,
+        2 relu^2, 3 fp32 output. This package's tiled tcgen05 GEMM (csrc/tile_gemm.cu) when N is a multiple of 128 and
+        K of 64; other shapes (toy models) go to torch's GEMM with the same epilogue applied afterwards."""
+        rows, K, N = x.shape[0], x.shape[1], w.shape[0]
+        if self.use_tile_gemm and N % 128 == 0 and K % 64 == 0 and x.is_contiguous() and w.is_contiguous():
+            y = torch.empty((rows, N), dtype=torch.float32 if epilogue == 3 else torch.bfloat16, device=x.device)
+            check(cuda_library("tile_gemm").tile_gemm(pointer(x), pointer(w), None, pointer(y), rows, N, K, epilogue,
+                                                      pointer(self.status), stream()), "tile_gemm")
+            return y
+        if epilogue == 3:
+            return torch.mm(x, w.T, out_dtype=torch.float32)
+        y = x @ w.T
+        if epilogue == 2:
+            check(cuda_library("decode_step").relu2_inplace(pointer(y), y.numel(), stream()), "relu2_inplace")
+        return y
 
     def _hidden_rows_torch(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int,
                            attend_last_layer: bool = True) -> Tensor:
@@ -243,7 +262,7 @@ class Decoder:
 
     def head(self, hidden: Tensor) -> Tensor:
         """The bf16 head GEMM with its fp32 accumulator kept as the output (modeling_nanochat.py:190-192)."""
-        return torch.mm(hidden, self.w.lm_head.T, out_dtype=torch.float32)
+        return self.gemm_rows(hidden.contiguous(), self.w.lm_head, epilogue=3)
 
     # ---- the same pass for at most 16 rows with this package's own GEMM kernels --------------------------------
 
@@ -251,7 +270,7 @@ class Decoder:
         """Which of this package's GEMM kernels runs a decode step of `rows` rows: "skinny" (decode_step.cu) for at
         most 16 rows when it takes every GEMM of the model (skinny_gemm_supported: depths it is instantiated for, the
         fused norm up to a depth of 2048), else "stream" (the tcgen05 stream_gemm) up to 64 rows when every GEMM
-        width is a multiple of 128 and every depth of 64; None: cuBLAS and separate norm kernels."""
+        width is a multiple of 128 and every depth of 64; None: the row path (tile_gemm and separate norm kernels)."""
         cfg = self.cfg
         A = cfg.n_heads * HEAD_DIM
         if any(l.ve_table is not None and cfg.hidden % 256 for l in self.w.layers):
@@ -263,7 +282,7 @@ class Decoder:
                 and ok(rows, cfg.hidden, A, 0) and ok(rows, cfg.intermediate, cfg.hidden, 1)
                 and ok(rows, cfg.hidden, cfg.intermediate, 0) and ok(rows, cfg.vocab, cfg.hidden, 1)):
             return "skinny"
-        if (rows <= 64 and self.use_stream_gemm  # the kernel takes 256 rows; cuBLAS is faster above about 64
+        if (rows <= 64 and self.use_stream_gemm  # the kernel takes 256 rows; the tiled GEMM is faster above about 64
                 and all(n % 128 == 0 for n in (cfg.hidden, cfg.intermediate, cfg.qkv_width, cfg.vocab))
                 and all(k % 64 == 0 for k in (cfg.hidden, cfg.intermediate, A))):
             return "stream"

@@ -22,7 +22,7 @@ KERNELS = PACKAGE / "csrc"
 INCLUDE = PACKAGE.parent / "include"
 NATIVE = PACKAGE / "_native"
 HEAD_DIM = 128
-LIBRARIES = ("kv_append", "decode_attn", "decode_step", "stream_gemm")
+LIBRARIES = ("kv_append", "decode_attn", "decode_step", "stream_gemm", "tile_gemm")
 
 c_ptr, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 SIGNATURES = {
@@ -62,6 +62,9 @@ SIGNATURES = {
         "relu2_inplace": ([c_ptr, c_ll, c_ptr], c_int),
         "sample_choice": ([c_ptr] * 7 + [c_float, c_ptr, c_ptr, c_int, c_int, c_ptr, c_int, c_ptr], c_int),
         "greedy_choice": ([c_ptr] * 3 + [c_int] * 2 + [c_ptr, c_int, c_ptr], c_int),
+    },
+    "tile_gemm": {
+        "tile_gemm": ([c_ptr] * 4 + [c_ll, c_int, c_int, c_int, c_ptr, c_ptr], c_int),
     },
     "stream_gemm": {
         "stream_gemm_split": ([c_int, c_int, c_int], c_int),
