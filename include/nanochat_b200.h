@@ -178,19 +178,20 @@ int decode_step_attn_fp8_ve(const void *qkv, const void *q_gain, const void *k_g
 
 /*
  * Attention for a prefill pass (replaces k_attn over prompt rows, decode.cu:859-863,1041-1051): `rows` query rows,
- * several of which belong to one sequence. Rows are grouped on the host: group z = rows group_start[z] ..
- * group_start[z + 1] - 1 (int32 [n_groups + 1], at most 8 / (Hq / Hkv) rows each), all of one slot with ascending
- * positions. A block loads each page of the sequence once for its whole group and masks every row at its own
- * length, so a prompt's cache is read once per group instead of once per row.
- *   q bf16 [rows][Hq][128]; lens int32 [rows] (row r attends positions [0, lens[r])); span_lens int32 [rows]: the
- *   length of the LAST row of r's group (it fixes the group's chunking, which the merge must follow);
- *   slot_map int32 [rows]; out bf16 [rows][Hq][128]; workspace >= decode_attn_workspace_bytes(rows, Hq, max_kv_len,
- *   Hkv, chunk_pages); chunk_pages > 0. No window. Every row's k, v must already be in the cache (kv_append_fp8).
+ * many of which belong to one sequence. Rows are grouped on the host: block z = rows group_start[z] ..
+ * group_start[z + 1] - 1 (int32 [n_groups + 1], at most prefill_attn_rows_per_block(Hq, Hkv) rows each: 64 for
+ * Hq == Hkv, 16 for four query heads per kv head), all of one slot with ascending positions. A block streams the
+ * sequence's pages once for all its rows (a shared ring consumed by eight warps, each owning 8 / (Hq / Hkv) rows over
+ * the whole key range) and writes normalised outputs itself: no workspace, no merge launch.
+ *   q bf16 [rows][Hq][128]; lens int32 [rows] (row r attends positions [0, lens[r])); slot_map int32 [rows];
+ *   out bf16 [rows][Hq][128]. No window. Every row's k, v must already be in the cache (kv_append_fp8).
+ * A block whose longest row exceeds the cache, or whose slot is outside it, is flagged (NCB_DEV_BAD_LENGTH) and writes
+ * zeros.
  */
-int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *span_lens,
-                     const void *slot_map, const void *group_start, int n_groups, void *workspace,
-                     long long workspace_bytes, void *out, int rows, int Hq, int Hkv, int n_slots, int pages_per_slot,
-                     int max_kv_len, int chunk_pages, float softmax_scale, void *status, void *stream);
+int prefill_attn_rows_per_block(int Hq, int Hkv);
+int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
+                     const void *group_start, int n_groups, void *out, long long rows, int Hq, int Hkv, int n_slots,
+                     int pages_per_slot, float softmax_scale, void *status, void *stream);
 
 /*
  * The first of decode_attn_fp8's two launches alone: the split-KV kernel, leaving one state per (b, h, chunk) in

@@ -157,61 +157,55 @@ def decode_step_attention(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tens
     return out
 
 
-def prefill_groups(slots: list[int], positions: list[int], Hq: int, Hkv: int) -> tuple[list[int], list[int]]:
+def prefill_groups(slots: list[int], positions: list[int], limit: int) -> list[int]:
     """Group consecutive rows of a prefill pass for prefill_attention: a group is a run of rows of one slot with
-    positions ascending by one, at most 8 / (Hq / Hkv) long. Returns (group_start with the end sentinel, span_lens:
-    for every row the length pos + 1 of its group's last row)."""
+    positions ascending by one, at most `limit` long. Returns group_start with the end sentinel."""
     import numpy as np
 
-    limit, n = max(1, 8 // (Hq // Hkv)), len(slots)
+    n = len(slots)
     if n == 0:
-        return [0], []
+        return [0]
     s, p = np.asarray(slots, dtype=np.int64), np.asarray(positions, dtype=np.int64)
     run_start = np.ones(n, dtype=bool)  # a run: one slot, positions ascending by one
     run_start[1:] = (s[1:] != s[:-1]) | (p[1:] != p[:-1] + 1)
     first_of_run = np.flatnonzero(run_start)[np.cumsum(run_start) - 1]
     group_start = (np.arange(n) - first_of_run) % limit == 0  # runs are cut into groups of `limit` rows
-    starts = np.flatnonzero(group_start)
-    ends = np.append(starts[1:], n)
-    span = p[ends[np.cumsum(group_start) - 1] - 1] + 1
-    return starts.tolist() + [n], span.tolist()
+    return np.flatnonzero(group_start).tolist() + [n]
+
+
+def prefill_rows_per_block(Hq: int, Hkv: int) -> int:
+    """Rows one block of prefill_attn_fp8 takes: 64 for Hq == Hkv, 16 for four query heads per kv head."""
+    return cuda_library("decode_attn").prefill_attn_rows_per_block(Hq, Hkv)
 
 
 class PrefillPlan:
-    """What prefill_attention needs besides q for one pass of rows, built once per pass and shared by the layers:
-    the row groups, each row's group length, the rows' slots and lengths on the device, the chunk size and a
-    workspace."""
+    """What prefill_attention needs besides q for one pass of rows, built once per pass and shared by the layers: the
+    row groups (longest first, so the blocks with the most pages start first), the rows' slots and lengths on the
+    device."""
 
     def __init__(self, slots: list[int], positions: list[int], Hq: int, cache: Fp8KVCache, device):
-        Hkv = cache.kv_heads
-        starts, span = prefill_groups(slots, positions, Hq, Hkv)
+        starts = prefill_groups(slots, positions, prefill_rows_per_block(Hq, cache.kv_heads))
         self.rows, self.n_groups = len(slots), len(starts) - 1
         self.group_start = torch.tensor(starts, dtype=torch.int32, device=device)
-        self.span_lens = torch.tensor(span, dtype=torch.int32, device=device)
         self.slot_map = torch.tensor(slots, dtype=torch.int32, device=device)
         self.lens = torch.tensor(positions, dtype=torch.int32, device=device) + 1
-        self.max_kv_len = min(max(positions) + 1, cache.capacity)
-        self.chunk = chunk_pages_for(self.n_groups, Hkv, self.max_kv_len)
-        need = workspace_bytes(self.rows, Hq, Hkv, self.max_kv_len, self.chunk)
-        self.workspace = torch.empty(max(16, need), dtype=torch.uint8, device=device)
 
 
 def prefill_attention(q: Tensor, cache: Fp8KVCache, plan: PrefillPlan, softmax_scale: float | None = None,
                       out: Tensor | None = None, status: Tensor | None = None) -> Tensor:
     """Attention for a prefill pass: q (rows, Hq, 128) bf16 of the rows the plan was built for, whose k, v are
     already appended; row r attends positions [0, positions[r]] of slots[r]. Rows of one prompt should be
-    consecutive and ascending: they are processed in groups that read the prompt's cache once. Returns
-    (rows, Hq, 128) bf16."""
+    consecutive and ascending: a block takes up to prefill_rows_per_block of them and reads the prompt's cache once
+    for all. Returns (rows, Hq, 128) bf16."""
     rows, Hq = q.shape[0], q.shape[1]
     assert rows == plan.rows and q.dtype == torch.bfloat16 and q.is_contiguous()
     if out is None:
         out = torch.empty_like(q)
     scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
     rc = cuda_library("decode_attn").prefill_attn_fp8(
-        pointer(q), pointer(cache.pages), pointer(plan.lens), pointer(plan.span_lens), pointer(plan.slot_map),
-        pointer(plan.group_start), plan.n_groups, pointer(plan.workspace), plan.workspace.numel(), pointer(out), rows,
-        Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, plan.max_kv_len, plan.chunk, scale, pointer(status),
-        stream())
+        pointer(q), pointer(cache.pages), pointer(plan.lens), pointer(plan.slot_map), pointer(plan.group_start),
+        plan.n_groups, pointer(out), rows, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, scale,
+        pointer(status), stream())
     check(rc, "prefill_attn_fp8")
     return out
 

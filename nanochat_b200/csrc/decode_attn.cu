@@ -67,9 +67,6 @@ struct AttnArgs {
     const float *q_gain, *k_gain, *cs, *sn;
     long long qkv_row_stride;
     int table_len;
-    /* MULTI only: block z works on rows group_start[z] .. group_start[z + 1] - 1, which share a slot and hold
-     * ascending positions; lens is per row then, and parts are indexed by row */
-    const int32_t *group_start;
     ValueEmbed ve; /* APPEND only; table == NULL: the layer has no value embedding */
 };
 
@@ -169,15 +166,163 @@ static __device__ __forceinline__ bool row_rejected(int len, int slot, int pages
     return len > pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= n_slots || (table_len > 0 && len > table_len);
 }
 
+/* One landed page (64 positions starting at key0) for one warp: scores of the warp's query columns against the page's
+ * K rows, the online-softmax update and the accumulation of V, as described at the top of the file. [begin, len) are
+ * the attended positions (positions outside them inside the page are masked; their V bytes are zeroed in shared
+ * memory first). MULTI: column slot 4 nt + t only sees positions below slot_len[nt] (rows of a prefill pass). */
+template <int NT, bool MULTI>
+static __device__ __forceinline__ void attend_page(uint8_t *page, uint32_t page_u, int key0, int begin, int len,
+                                                   const int (&slot_len)[NT], const uint32_t (&qf)[NT][4][2],
+                                                   const float (&qfac)[NT], float (&m)[NT], float (&l)[NT],
+                                                   float (&oacc)[NT][8][4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const bool partial = key0 < begin || key0 + PAGE_TOKENS > len;
+    if (partial) { /* zero the V bytes of positions outside [begin, len) */
+#pragma unroll
+        for (int blk = 0; blk < 4; blk++) { /* 16-position blocks: (group, half) */
+            const int first = key0 + 16 * blk;
+            uint32_t keep[4];
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                keep[w] = 0;
+#pragma unroll
+                for (int bb = 0; bb < 4; bb++) {
+                    const int pos = first + 4 * w + bb;
+                    if (pos >= begin && pos < len) keep[w] |= 0xffu << (8 * bb);
+                }
+            }
+            if ((keep[0] & keep[1] & keep[2] & keep[3]) == 0xffffffffu) continue;
+            for (int d = lane; d < HEAD_DIM; d += 32) {
+                uint4 *row = reinterpret_cast<uint4 *>(page + PAGE_V + blk * 2048 + d * 16);
+                uint4 v = *row;
+                v.x &= keep[0], v.y &= keep[1], v.z &= keep[2], v.w &= keep[3];
+                *row = v;
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int gi = 0; gi < 2; gi++) { /* 32 positions at a time */
+        const int first = key0 + 32 * gi;
+        if (partial && (first >= len || first + 32 <= begin)) continue;
+        /* ---- scores: A = K rows (position 4 r + 2 mt [+ 1 for rows 8..15]), B = q ---- */
+        float sc[NT][2][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) sc[nt][mt][c] = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) {
+            const int row = 32 * gi + 4 * (lane & 7) + 2 * mt + ((lane >> 3) & 1);
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                uint32_t a0, a1, a2, a3;
+                const int c = 2 * ks + (lane >> 4);
+                ldmatrix_x4(a0, a1, a2, a3, page_u + PAGE_K + row * HEAD_DIM + ((c ^ (lane & 7)) << 4));
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) mma_e4m3(sc[nt][mt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+            }
+        }
+        /* this lane: head t of each tile, positions first + 4 g + {0, 1, 2, 3} */
+        const float4 ks4 = *reinterpret_cast<const float4 *>(page + PAGE_KS + (32 * gi + 4 * g) * 4);
+        const float4 vs4 = *reinterpret_cast<const float4 *>(page + PAGE_VS + (32 * gi + 4 * g) * 4);
+        const float ksc[4] = {ks4.x, ks4.y, ks4.z, ks4.w}, vsc[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
+        bool valid[4];
+        float lv[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int pos = first + 4 * g + j;
+            valid[j] = !partial || (pos >= begin && pos < len);
+            lv[j] = fmaxf(lg2(vsc[j]), MIN_LOG2_VSCALE);
+        }
+        uint32_t pb[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            float x[4], top = -INFINITY;
+            bool ok[4]; /* this slot may see position j: inside the span and, for MULTI, inside its own row */
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float raw = sc[nt][j >> 1][2 * (j & 1)] + sc[nt][j >> 1][2 * (j & 1) + 1] * (1.f / LO_SCALE);
+                x[j] = raw * (ksc[j] * qfac[nt]);
+                ok[j] = valid[j] && (!MULTI || first + 4 * g + j < slot_len[nt]);
+                top = fmaxf(top, ok[j] ? x[j] + lv[j] : -INFINITY);
+            }
+            top = fmaxf(head_max(top), m[nt]);
+            if (__any_sync(0xffffffffu, top > m[nt])) { /* some head's maximum moved: rescale */
+                const float c = m[nt] == -INFINITY ? 0.f : ex2(m[nt] - top);
+                l[nt] *= c;
+#pragma unroll
+                for (int dt = 0; dt < 8; dt++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) oacc[nt][dt][e] *= c;
+                m[nt] = top;
+            }
+            float p[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const bool on = ok[j] && top != -INFINITY;
+                const float e = on ? ex2(x[j] - top) : 0.f;
+                l[nt] += e;
+                p[j] = on ? e * (vsc[j] * P_SCALE) : 0.f;
+            }
+            uint32_t whi, wlo;
+            split4(p, whi, wlo);
+            /* C layout -> B layout: column g of positions 4 t .. 4 t + 3 (and + 16) lives in lane
+             * 4 t + g / 2 (and + 16), first term if g is even */
+            const int src = 4 * t + (g >> 1);
+            const uint32_t h0 = __shfl_sync(0xffffffffu, whi, src), l0 = __shfl_sync(0xffffffffu, wlo, src);
+            const uint32_t h1 = __shfl_sync(0xffffffffu, whi, src + 16), l1 = __shfl_sync(0xffffffffu, wlo, src + 16);
+            pb[nt][0] = (g & 1) ? l0 : h0;
+            pb[nt][1] = (g & 1) ? l1 : h1;
+        }
+        /* ---- values: A = V^T rows (dim 16 dt + r), B = folded probabilities ---- */
+        const uint32_t vbase = page_u + PAGE_V + gi * 4096 + (lane >> 4) * 2048 + (8 * ((lane >> 3) & 1) + (lane & 7)) * 16;
+#pragma unroll
+        for (int dt = 0; dt < 8; dt++) {
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(a0, a1, a2, a3, vbase + dt * 256);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) mma_e4m3(oacc[nt][dt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+        }
+    }
+}
+
+/* The warp's query columns as MMA B fragments: q_stage holds S slots of 128 fp32 values (bf16-valued), q_scale each
+ * slot's amax / 448. qfac[nt]: what turns lane column t's raw score into log2 units. */
+template <int NT>
+static __device__ __forceinline__ void query_fragments(const float *q_stage, const float *q_scale, int S, float scale_log2,
+                                                       uint32_t (&qf)[NT][4][2], float (&qfac)[NT], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    /* B fragments of q: column g = (head g / 2 of the tile, term g % 2); b0 = dims 32 ks + 4 t .. + 3,
+     * b1 = dims 32 ks + 16 + 4 t .. + 3 */
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int hc = 4 * nt + (g >> 1), hs = 4 * nt + t; /* the head of this lane's B column / C columns */
+        const float sc = hc < S ? q_scale[hc] : 0.f, inv = sc > 0.f ? 1.f / sc : 0.f;
+        qfac[nt] = (hs < S ? q_scale[hs] : 0.f) * scale_log2;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++)
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float x[4];
+                uint32_t hi, lo;
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    x[i] = hc < S ? q_stage[hc * HEAD_DIM + 32 * ks + 16 * half + 4 * t + i] * inv : 0.f;
+                split4(x, hi, lo);
+                qf[nt][ks][half] = (g & 1) ? lo : hi;
+            }
+    }
+
+}
+
 /* APPEND: the block first does kv_append_fp8's work for its own heads of the new token (the q rows of its group
  * into shared memory; if its chunk holds the new position, the k and v rows into the cache in global memory and
  * into the landed page in shared memory), so a decode step needs no separate append launch and no round trip of q
  * through global memory. Meant for one new token per sequence; rows that share a slot need the separate kernels. */
-/* MULTI (prefill): the N columns hold several ROWS of one sequence instead of only the heads of one row: block z
- * takes up to 4 NT / G consecutive rows of a slot (query "slots" = rows x heads of the kv group), loads each page of
- * the sequence once for all of them and masks every slot at its own row's length. Not combined with APPEND or a
- * window. */
-template <int NT, bool APPEND, bool MULTI = false>
+template <int NT, bool APPEND>
 __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];       /* WARPS stages of one page; later the merge area */
     __shared__ __align__(8) uint64_t bars[WARPS];          /* one "page landed" barrier per warp */
@@ -193,11 +338,8 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     /* launched with programmatic stream serialisation: everything this kernel reads (lens, q, the cache with the
      * token appended a moment ago) comes from kernels before it */
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    /* b: the first (or only) row of this block; S: its query slots (rows x heads of the kv group) */
-    const int b = MULTI ? a.group_start[blockIdx.z] : (int)blockIdx.z;
-    const int group_rows = MULTI ? min(a.group_start[blockIdx.z + 1] - b, 4 * NT / G) : 1;
-    const int S = group_rows * G;
-    const int given = a.lens[b + group_rows - 1]; /* the longest row's: rows ascend in position */
+    const int b = (int)blockIdx.z, S = G; /* the block's row; its query slots: the heads of the kv group */
+    const int given = a.lens[b];
     if (given < 0) return; /* an idle row: nothing appended, nothing attended, nothing flagged; the merge writes zeros */
     const int len = given + a.len_add;
     const int slot = a.slot_map ? a.slot_map[b] : b;
@@ -262,10 +404,8 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
             }
         }
     } else {
-        for (int i = tid; i < S * HEAD_DIM; i += THREADS) { /* slot = row-in-group * G + head-in-group */
-            const int sl = i / HEAD_DIM, d = i % HEAD_DIM;
-            q_stage[i] = __bfloat162float(a.q[((size_t)(b + sl / G) * a.Hq + (size_t)kvh * G + sl % G) * HEAD_DIM + d]);
-        }
+        for (int i = tid; i < S * HEAD_DIM; i += THREADS) /* the group's heads are consecutive */
+            q_stage[i] = __bfloat162float(a.q[((size_t)b * a.Hq + (size_t)kvh * G) * HEAD_DIM + i]);
     }
     __syncthreads();
     for (int h = warp; h < S; h += WARPS) {
@@ -276,33 +416,13 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     }
     __syncthreads();
 
-    /* B fragments of q: column g = (head g / 2 of the tile, term g % 2); b0 = dims 32 ks + 4 t .. + 3,
-     * b1 = dims 32 ks + 16 + 4 t .. + 3 */
     uint32_t qf[NT][4][2];
     float qfac[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        const int hc = 4 * nt + (g >> 1), hs = 4 * nt + t; /* the head of this lane's B column / C columns */
-        const float sc = hc < S ? q_scale[hc] : 0.f, inv = sc > 0.f ? 1.f / sc : 0.f;
-        qfac[nt] = (hs < S ? q_scale[hs] : 0.f) * a.scale_log2;
-#pragma unroll
-        for (int ks = 0; ks < 4; ks++)
-#pragma unroll
-            for (int half = 0; half < 2; half++) {
-                float x[4];
-                uint32_t hi, lo;
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    x[i] = hc < S ? q_stage[hc * HEAD_DIM + 32 * ks + 16 * half + 4 * t + i] * inv : 0.f;
-                split4(x, hi, lo);
-                qf[nt][ks][half] = (g & 1) ? lo : hi;
-            }
-    }
+    query_fragments<NT>(q_stage, q_scale, S, a.scale_log2, qf, qfac, lane);
 
-    int slot_len[NT]; /* MULTI: the length of the row behind this lane's slot of each tile */
+    int slot_len[NT]; /* every column belongs to the same row here */
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++)
-        slot_len[nt] = (MULTI && 4 * nt + t < S) ? a.lens[b + (4 * nt + t) / G] + a.len_add : len;
+    for (int nt = 0; nt < NT; nt++) slot_len[nt] = len;
 
     /* the warp's running state: per tile, head t's maximum (log2 units), this lane's share of the sum, and O^T
      * fragments (dims 16 dt + g, + 8; columns = head t's two terms) */
@@ -339,117 +459,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
             }
             __syncwarp();
         }
-        const bool partial = key0 < sp.begin || key0 + PAGE_TOKENS > sp.len;
-        if (partial) { /* zero the V bytes of positions outside [begin, len) */
-#pragma unroll
-            for (int blk = 0; blk < 4; blk++) { /* 16-position blocks: (group, half) */
-                const int first = key0 + 16 * blk;
-                uint32_t keep[4];
-#pragma unroll
-                for (int w = 0; w < 4; w++) {
-                    keep[w] = 0;
-#pragma unroll
-                    for (int bb = 0; bb < 4; bb++) {
-                        const int pos = first + 4 * w + bb;
-                        if (pos >= sp.begin && pos < sp.len) keep[w] |= 0xffu << (8 * bb);
-                    }
-                }
-                if ((keep[0] & keep[1] & keep[2] & keep[3]) == 0xffffffffu) continue;
-                for (int d = lane; d < HEAD_DIM; d += 32) {
-                    uint4 *row = reinterpret_cast<uint4 *>(page + PAGE_V + blk * 2048 + d * 16);
-                    uint4 v = *row;
-                    v.x &= keep[0], v.y &= keep[1], v.z &= keep[2], v.w &= keep[3];
-                    *row = v;
-                }
-            }
-            __syncwarp();
-        }
-#pragma unroll
-        for (int gi = 0; gi < 2; gi++) { /* 32 positions at a time */
-            const int first = key0 + 32 * gi;
-            if (partial && (first >= sp.len || first + 32 <= sp.begin)) continue;
-            /* ---- scores: A = K rows (position 4 r + 2 mt [+ 1 for rows 8..15]), B = q ---- */
-            float sc[NT][2][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-                    for (int c = 0; c < 4; c++) sc[nt][mt][c] = 0.f;
-#pragma unroll
-            for (int mt = 0; mt < 2; mt++) {
-                const int row = 32 * gi + 4 * (lane & 7) + 2 * mt + ((lane >> 3) & 1);
-#pragma unroll
-                for (int ks = 0; ks < 4; ks++) {
-                    uint32_t a0, a1, a2, a3;
-                    const int c = 2 * ks + (lane >> 4);
-                    ldmatrix_x4(a0, a1, a2, a3, page_u + PAGE_K + row * HEAD_DIM + ((c ^ (lane & 7)) << 4));
-#pragma unroll
-                    for (int nt = 0; nt < NT; nt++) mma_e4m3(sc[nt][mt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
-                }
-            }
-            /* this lane: head t of each tile, positions first + 4 g + {0, 1, 2, 3} */
-            const float4 ks4 = *reinterpret_cast<const float4 *>(page + PAGE_KS + (32 * gi + 4 * g) * 4);
-            const float4 vs4 = *reinterpret_cast<const float4 *>(page + PAGE_VS + (32 * gi + 4 * g) * 4);
-            const float ksc[4] = {ks4.x, ks4.y, ks4.z, ks4.w}, vsc[4] = {vs4.x, vs4.y, vs4.z, vs4.w};
-            bool valid[4];
-            float lv[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int pos = first + 4 * g + j;
-                valid[j] = !partial || (pos >= sp.begin && pos < sp.len);
-                lv[j] = fmaxf(lg2(vsc[j]), MIN_LOG2_VSCALE);
-            }
-            uint32_t pb[NT][2];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                float x[4], top = -INFINITY;
-                bool ok[4]; /* this slot may see position j: inside the span and, for MULTI, inside its own row */
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float raw = sc[nt][j >> 1][2 * (j & 1)] + sc[nt][j >> 1][2 * (j & 1) + 1] * (1.f / LO_SCALE);
-                    x[j] = raw * (ksc[j] * qfac[nt]);
-                    ok[j] = valid[j] && (!MULTI || first + 4 * g + j < slot_len[nt]);
-                    top = fmaxf(top, ok[j] ? x[j] + lv[j] : -INFINITY);
-                }
-                top = fmaxf(head_max(top), m[nt]);
-                if (__any_sync(0xffffffffu, top > m[nt])) { /* some head's maximum moved: rescale */
-                    const float c = m[nt] == -INFINITY ? 0.f : ex2(m[nt] - top);
-                    l[nt] *= c;
-#pragma unroll
-                    for (int dt = 0; dt < 8; dt++)
-#pragma unroll
-                        for (int e = 0; e < 4; e++) oacc[nt][dt][e] *= c;
-                    m[nt] = top;
-                }
-                float p[4];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const bool on = ok[j] && top != -INFINITY;
-                    const float e = on ? ex2(x[j] - top) : 0.f;
-                    l[nt] += e;
-                    p[j] = on ? e * (vsc[j] * P_SCALE) : 0.f;
-                }
-                uint32_t whi, wlo;
-                split4(p, whi, wlo);
-                /* C layout -> B layout: column g of positions 4 t .. 4 t + 3 (and + 16) lives in lane
-                 * 4 t + g / 2 (and + 16), first term if g is even */
-                const int src = 4 * t + (g >> 1);
-                const uint32_t h0 = __shfl_sync(0xffffffffu, whi, src), l0 = __shfl_sync(0xffffffffu, wlo, src);
-                const uint32_t h1 = __shfl_sync(0xffffffffu, whi, src + 16), l1 = __shfl_sync(0xffffffffu, wlo, src + 16);
-                pb[nt][0] = (g & 1) ? l0 : h0;
-                pb[nt][1] = (g & 1) ? l1 : h1;
-            }
-            /* ---- values: A = V^T rows (dim 16 dt + r), B = folded probabilities ---- */
-            const uint32_t vbase = page_u + PAGE_V + gi * 4096 + (lane >> 4) * 2048 + (8 * ((lane >> 3) & 1) + (lane & 7)) * 16;
-#pragma unroll
-            for (int dt = 0; dt < 8; dt++) {
-                uint32_t a0, a1, a2, a3;
-                ldmatrix_x4(a0, a1, a2, a3, vbase + dt * 256);
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) mma_e4m3(oacc[nt][dt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
-            }
-        }
+        attend_page<NT, false>(page, page_u, key0, sp.begin, sp.len, slot_len, qf, qfac, m, l, oacc, lane);
         __syncwarp(); /* every lane has read the stage */
         i += WARPS; /* a fixed page-to-warp map keeps the summation order, hence the output bits, reproducible */
         if (lane == 0 && i < n) {
@@ -488,10 +498,153 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
                 lsum += c * st[1];
                 o += c * st[4 + tid];
             }
-            float *out = a.parts + (((size_t)(b + h / G) * a.Hq + (size_t)kvh * G + h % G) * a.max_chunks + chunk) * PART;
+            float *out = a.parts + (((size_t)b * a.Hq + (size_t)kvh * G + h) * a.max_chunks + chunk) * PART;
             if (tid == 0) out[0] = top, out[1] = lsum;
             out[4 + tid] = o;
         }
+    }
+}
+
+/* ---- prefill attention --------------------------------------------------------------------------------------- */
+
+/* A prefill pass holds many rows of the same prompt with lengths one apart (the reference runs them through k_attn
+ * row by row, model/kernels/decode.cu:859-863,1041-1051). Here a block takes a TILE of consecutive rows of one prompt
+ * and one kv head, streams the prompt's pages ONCE through a shared ring and lets PF_WARPS warps consume every page,
+ * each for its own rows: warp w owns 8 / G rows (8 query columns = 4 per MMA tile, two tiles), i.e. 64 rows per block
+ * for G = 1 and 16 for G = 4. A prompt's cache is read once per tile instead of once per row, every warp walks all
+ * pages up to its rows' lengths with the same per-page code as the decode kernel (attend_page, rows masked at their
+ * own length), and because a warp owns its rows over the whole key range there are no partial states, no workspace
+ * and no merge launch: the warp normalises and writes bf16 outputs itself.
+ * One producer thread (an extra warp) issues the page copies; full / empty mbarriers per stage, all waits bounded. */
+constexpr int PF_WARPS = 8, PF_STAGES = 6;
+constexpr int PF_THREADS = (PF_WARPS + 1) * 32;
+constexpr int PF_SLOTS = 8; /* query columns per warp */
+constexpr size_t PF_SMEM = (size_t)PF_STAGES * PAGE_BYTES + (size_t)PF_WARPS * PF_SLOTS * HEAD_DIM * sizeof(float);
+
+struct PrefillArgs {
+    const bf16 *q;         /* [rows][Hq][128] */
+    const uint8_t *cache;
+    const int32_t *lens, *slot_map, *group_start; /* per row, per row, per block (+ end sentinel) */
+    bf16 *out;             /* [rows][Hq][128] */
+    int Hq, Hkv, n_slots, pages_per_slot;
+    float scale_log2;
+    int *status;
+};
+
+__global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_attn(PrefillArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[]; /* the page ring, then each warp's 8 x 128 fp32 staging area */
+    __shared__ __align__(8) uint64_t bars[2 * PF_STAGES];
+    __shared__ float q_scales[PF_WARPS][PF_SLOTS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int kvh = blockIdx.y, G = a.Hq / a.Hkv, rpw = max(1, PF_SLOTS / G);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int b0 = a.group_start[blockIdx.x];
+    const int n_rows = min(a.group_start[blockIdx.x + 1] - b0, PF_WARPS * rpw);
+    const int n_active = (n_rows + rpw - 1) / rpw; /* warps that have rows */
+    const int len_block = a.lens[b0 + n_rows - 1];  /* rows ascend in position: the last one is the longest */
+    const int slot = a.slot_map[b0];
+    const bool bad = len_block > a.pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= a.n_slots;
+    if (bad && tid == 0 && kvh == 0) flag(a.status, NCB_DEV_BAD_LENGTH);
+    const int n_pages = bad || len_block <= 0 ? 0 : (len_block + PAGE_TOKENS - 1) / PAGE_TOKENS;
+    const uint32_t ring = smem_u32(smem);
+    auto full = [&](int st) { return smem_u32(bars + st); };
+    auto empty = [&](int st) { return smem_u32(bars + PF_STAGES + st); };
+    if (tid == 0) {
+        for (int st = 0; st < PF_STAGES; st++) {
+            mbar_init(full(st), 1);
+            mbar_init(empty(st), n_active);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == PF_WARPS) { /* producer */
+        if (lane == 0) {
+            const uint8_t *pages = a.cache + (((size_t)(bad ? 0 : slot) * a.Hkv + kvh) * a.pages_per_slot) * PAGE_BYTES;
+            for (int i = 0; i < n_pages; i++) {
+                const int st = i % PF_STAGES;
+                if (!mbar_wait(empty(st), ((i / PF_STAGES) & 1) ^ 1)) {
+                    flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+                    break;
+                }
+                /* the consumers' reads and masking writes of the stage come before the copy engine's writes */
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                page_load(ring + st * PAGE_BYTES, pages + (size_t)i * PAGE_BYTES, full(st));
+            }
+        }
+        return;
+    }
+    if (warp >= n_active) return;
+    const int r0 = b0 + warp * rpw, rows_w = min(rpw, b0 + n_rows - r0), S = rows_w * G;
+    float *stage = reinterpret_cast<float *>(smem + (size_t)PF_STAGES * PAGE_BYTES) + (size_t)warp * PF_SLOTS * HEAD_DIM;
+    for (int i = lane; i < S * HEAD_DIM; i += 32) { /* slot = row-in-warp * G + head-in-group */
+        const int sl = i / HEAD_DIM, d = i % HEAD_DIM;
+        stage[i] = __bfloat162float(a.q[((size_t)(r0 + sl / G) * a.Hq + (size_t)kvh * G + sl % G) * HEAD_DIM + d]);
+    }
+    __syncwarp();
+    for (int h = 0; h < S; h++) {
+        float mx = 0.f;
+        for (int i = lane; i < HEAD_DIM; i += 32) mx = fmaxf(mx, fabsf(stage[h * HEAD_DIM + i]));
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) q_scales[warp][h] = mx / 448.f;
+    }
+    __syncwarp();
+    constexpr int NT = 2;
+    uint32_t qf[NT][4][2];
+    float qfac[NT];
+    query_fragments<NT>(stage, q_scales[warp], S, a.scale_log2, qf, qfac, lane);
+    int slot_len[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) slot_len[nt] = 4 * nt + t < S ? a.lens[r0 + (4 * nt + t) / G] : 0;
+    const int my_len = a.lens[r0 + rows_w - 1];
+    float m[NT], l[NT], oacc[NT][8][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        m[nt] = -INFINITY;
+        l[nt] = 0.f;
+#pragma unroll
+        for (int dt = 0; dt < 8; dt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) oacc[nt][dt][i] = 0.f;
+    }
+    bool ok = true;
+    for (int i = 0; i < n_pages; i++) {
+        const int st = i % PF_STAGES;
+        if (!mbar_wait(full(st), (i / PF_STAGES) & 1)) {
+            if (lane == 0) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+            ok = false;
+            break;
+        }
+        const int key0 = i * PAGE_TOKENS;
+        if (key0 < my_len) /* later pages only hold positions past this warp's rows */
+            attend_page<NT, true>(smem + (size_t)st * PAGE_BYTES, ring + st * PAGE_BYTES, key0, 0, len_block, slot_len, qf,
+                                  qfac, m, l, oacc, lane);
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty(st)) : "memory");
+    }
+    /* normalise: the warp's staging area takes the fp32 outputs, then each slot's 128 values go out as bf16 */
+    __syncwarp();
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int h = 4 * nt + t;
+        const float lsum = head_sum(l[nt]);
+        const bool any = ok && lsum > 0.f;
+#pragma unroll
+        for (int dt = 0; dt < 8; dt++) {
+            const float lo = (oacc[nt][dt][0] + oacc[nt][dt][1] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
+            const float hi = (oacc[nt][dt][2] + oacc[nt][dt][3] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
+            stage[h * HEAD_DIM + 16 * dt + g] = any ? __fdiv_rn(lo, lsum) : 0.f;
+            stage[h * HEAD_DIM + 16 * dt + g + 8] = any ? __fdiv_rn(hi, lsum) : 0.f;
+        }
+    }
+    __syncwarp();
+    for (int h = 0; h < S; h++) {
+        const float4 v = *reinterpret_cast<const float4 *>(stage + h * HEAD_DIM + 4 * lane);
+        uint2 u;
+        *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2 *>(a.out + ((size_t)(r0 + h / G) * a.Hq + (size_t)kvh * G + h % G) * HEAD_DIM + 4 * lane) = u;
     }
 }
 
@@ -603,33 +756,6 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
         *reinterpret_cast<float4 *>(o + 4 + 4 * lane) = acc;
     }
     if (a.out) store_normalised(a.out, row, lane, lsum, acc);
-}
-
-/* The same merge with one WARP per row, for prefill passes: tens of thousands of rows with one or two states each,
- * where a block per row spends its time starting blocks. Lane = four output dims; states are folded in index order
- * (a different summation order than k_merge: equal up to rounding, not bit for bit). */
-__global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_rows(MergeArgs a) {
-    const long long row = (long long)blockIdx.x * MERGE_WARPS + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (row >= a.rows) return;
-    const int n = states_of(a, row);
-    const float *st = a.parts + row * a.row_stride;
-    float top = -INFINITY, lsum = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 2
-    for (int p = 0; p < n; p++) {
-        const float *s = st + p * a.part_stride;
-        const float mp = s[0], lp = s[1];
-        const float4 o = *reinterpret_cast<const float4 *>(s + 4 + 4 * lane);
-        const float next = fmaxf(top, mp);
-        const float c0 = top == -INFINITY ? 0.f : ex2(top - next), c1 = mp == -INFINITY ? 0.f : ex2(mp - next);
-        lsum = lsum * c0 + lp * c1;
-        acc.x = acc.x * c0 + o.x * c1, acc.y = acc.y * c0 + o.y * c1;
-        acc.z = acc.z * c0 + o.z * c1, acc.w = acc.w * c0 + o.w * c1;
-        top = next;
-    }
-    store_normalised(a.out, row, lane, lsum, acc);
 }
 
 /* ---- merge + exchange over peer memory ------------------------------------------------------------------------ */
@@ -772,14 +898,14 @@ struct AppendIn {
     ValueEmbed ve;
 };
 
-template <int NT, bool APPEND, bool MULTI = false> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
+template <int NT, bool APPEND> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
     static bool done[MAX_DEVICES] = {};
     int device = 0;
     cudaError_t rc = cudaGetDevice(&device);
     if (rc != cudaSuccess) return rc;
     std::lock_guard<std::mutex> guard(g_device_lock);
     if (device >= 0 && device < MAX_DEVICES && done[device]) return cudaSuccess;
-    rc = cudaFuncSetAttribute(k_decode_attn<NT, APPEND, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    rc = cudaFuncSetAttribute(k_decode_attn<NT, APPEND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               (int)ATTN_SMEM);
     if (rc == cudaSuccess && device >= 0 && device < MAX_DEVICES) done[device] = true;
     return rc;
@@ -788,13 +914,12 @@ template <int NT, bool APPEND, bool MULTI = false> static cudaError_t prepare() 
 static int launch_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
                         long long workspace_bytes, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,
                         int max_kv_len, int window, int &chunk_pages, float softmax_scale, void *status,
-                        cudaStream_t stream, const AppendIn *app = nullptr, const void *group_start = nullptr,
-                        int n_groups = 0) {
+                        cudaStream_t stream, const AppendIn *app = nullptr) {
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || n_slots <= 0 || pages_per_slot <= 0 || max_kv_len < 0 ||
         window < 0 || chunk_pages < 0 || !(softmax_scale > 0.f))
         return NCB_ERR_ARG;
     if (Hq / Hkv > 8) return NCB_ERR_UNSUPPORTED;
-    if ((B > 65535 && !group_start) || Hkv > 65535) return NCB_ERR_ARG;
+    if (B > 65535 || Hkv > 65535) return NCB_ERR_ARG;
     /* the default chunk follows the caller's max_kv_len, as decode_attn_workspace_bytes() computed it, before the
      * bound is clipped to the cache: the workspace the caller sized is then never too small */
     if (chunk_pages == 0) chunk_pages = decode_attn_chunk_pages(B, Hkv, max_kv_len);
@@ -827,9 +952,8 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
         a.qkv_row_stride = app->qkv_row_stride, a.table_len = app->table_len;
         a.ve = app->ve;
     }
-    a.group_start = (const int32_t *)group_start;
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(max_chunks, Hkv, group_start ? n_groups : B);
+    config.gridDim = dim3(max_chunks, Hkv, B);
     config.blockDim = dim3(THREADS);
     config.dynamicSmemBytes = ATTN_SMEM;
     config.stream = stream;
@@ -839,11 +963,7 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     config.attrs = attribute;
     config.numAttrs = 1;
     cudaError_t rc;
-    if (group_start) { /* several rows per block: always two column tiles, 8 / G rows */
-        if (app || window || n_groups <= 0 || n_groups > 65535) return NCB_ERR_ARG;
-        if (prepare<2, false, true>() != cudaSuccess) return NCB_ERR_LAUNCH;
-        rc = cudaLaunchKernelEx(&config, k_decode_attn<2, false, true>, a);
-    } else if (Hq / Hkv <= 4 && !app) {
+    if (Hq / Hkv <= 4 && !app) {
         if (prepare<1, false>() != cudaSuccess) return NCB_ERR_LAUNCH;
         rc = cudaLaunchKernelEx(&config, k_decode_attn<1, false>, a);
     } else if (!app) {
@@ -859,9 +979,9 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     return rc == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
-static int launch_merge(const MergeArgs &a, cudaStream_t stream, bool warp_per_row = false) {
+static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
     if (a.rows == 0) return NCB_OK;
-    const long long blocks = warp_per_row ? (a.rows + MERGE_WARPS - 1) / MERGE_WARPS : a.rows; /* else a block per row */
+    const long long blocks = a.rows; /* a block per row */
     if (blocks > 0x7fffffffLL) return NCB_ERR_ARG;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)blocks);
@@ -872,7 +992,7 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream, bool warp_per_r
     attribute[0].val.programmaticStreamSerializationAllowed = 1; /* overlap its launch with the split kernel's tail */
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, warp_per_row ? k_merge_rows : k_merge, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+    return cudaLaunchKernelEx(&config, k_merge, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 /* What the merge + exchange launch needs besides the local merge (decode_attn_fp8_sharded). */
@@ -1083,24 +1203,46 @@ int decode_step_attn_fp8_ve(const void *qkv, const void *q_gain, const void *k_g
                   pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status, stream, &app);
 }
 
-int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *span_lens,
-                     const void *slot_map, const void *group_start, int n_groups, void *workspace,
-                     long long workspace_bytes, void *out, int rows, int Hq, int Hkv, int n_slots, int pages_per_slot,
-                     int max_kv_len, int chunk_pages, float softmax_scale, void *status, void *stream) {
-    if (!out || !group_start || !span_lens || !slot_map || chunk_pages <= 0 || n_groups <= 0) return NCB_ERR_ARG;
-    if ((uintptr_t)out % 16 != 0) return NCB_ERR_ALIGN;
-    int chunk = chunk_pages;
-    const int rc = launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, rows, Hq, Hkv, n_slots,
-                                pages_per_slot, max_kv_len, 0, chunk, softmax_scale, status, (cudaStream_t)stream, nullptr,
-                                group_start, n_groups);
-    if (rc != NCB_OK || rows == 0) return rc;
-    if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
-    const int max_chunks = max(1, (pages_of(max_kv_len) + chunk - 1) / chunk);
-    /* every row's states follow its group's chunking, so the merge takes each row's length from span_lens */
-    MergeArgs m = {(const float *)workspace, (long long)rows * Hq, PART, (long long)max_chunks * PART, 0,
-                   (const int32_t *)span_lens, (const int32_t *)slot_map, Hq, 0, chunk, n_slots, pages_per_slot,
-                   max_chunks, 0, (bf16 *)out, nullptr, 0};
-    return launch_merge(m, (cudaStream_t)stream, true);
+int prefill_attn_rows_per_block(int Hq, int Hkv) {
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || Hq / Hkv > PF_SLOTS) return 0;
+    return PF_WARPS * (PF_SLOTS / (Hq / Hkv));
+}
+
+int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
+                     const void *group_start, int n_groups, void *out, long long rows, int Hq, int Hkv, int n_slots,
+                     int pages_per_slot, float softmax_scale, void *status, void *stream) {
+    if (rows < 0 || n_groups < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || n_slots <= 0 || pages_per_slot <= 0 ||
+        !(softmax_scale > 0.f))
+        return NCB_ERR_ARG;
+    if (Hq / Hkv > PF_SLOTS) return NCB_ERR_UNSUPPORTED;
+    if (rows == 0 || n_groups == 0) return NCB_OK;
+    if (!q || !kv_cache || !lens || !slot_map || !group_start || !out || Hkv > 65535) return NCB_ERR_ARG;
+    if (((uintptr_t)q | (uintptr_t)kv_cache | (uintptr_t)out) % 16 != 0) return NCB_ERR_ALIGN;
+    {
+        static bool done[MAX_DEVICES] = {};
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return NCB_ERR_LAUNCH;
+        std::lock_guard<std::mutex> guard(g_device_lock);
+        if (!done[device]) {
+            if (cudaFuncSetAttribute(k_prefill_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM) != cudaSuccess)
+                return NCB_ERR_LAUNCH;
+            done[device] = true;
+        }
+    }
+    PrefillArgs a = {(const bf16 *)q, (const uint8_t *)kv_cache, (const int32_t *)lens, (const int32_t *)slot_map,
+                     (const int32_t *)group_start, (bf16 *)out, Hq, Hkv, n_slots, pages_per_slot,
+                     softmax_scale * 1.4426950408889634f, (int *)status};
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)n_groups, (unsigned)Hkv);
+    config.blockDim = dim3(PF_THREADS);
+    config.dynamicSmemBytes = PF_SMEM;
+    config.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, k_prefill_attn, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 int decode_attn_fp8_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map,

@@ -395,12 +395,16 @@ def test_sharded_exchange_wait_runs_out_and_reports():
 
 @pytest.mark.parametrize("Hq,Hkv", [(10, 10), (8, 2), (4, 1), (16, 2)])
 def test_prefill_attention_groups_rows_and_matches_the_row_wise_path(Hq, Hkv):
-    """prefill_attn_fp8 (rows of a prompt share each page load) against decode_attn_fp8 run row by row and against
-    the float64 checker: causal prefixes of three prompts of different lengths in one pass, group boundaries in the
-    middle of prompts and across page edges."""
-    lens = [150, 9, 70]
+    """prefill_attn_fp8 (a tile of a prompt's rows shares each page load; every warp owns its rows over the whole key
+    range) against decode_attn_fp8 run row by row and against the float64 checker: causal prefixes of three prompts
+    of different lengths in one pass, tile and warp boundaries in the middle of prompts and across page edges."""
+    lens = [150, 9, 200]
     case = helpers.attention_case(1500 + Hq, Hq, Hkv, lens)
-    cache = load_cache(case, 160, slots=[2, 0, 1], n_slots=3)
+    cache = load_cache(case, 256, slots=[2, 0, 1], n_slots=3)
+    for slot, n in zip([2, 0, 1], lens):  # NaN patterns past each prompt's end must never reach an output
+        tail = cache.capacity - n
+        cache.write(slot, torch.full((Hkv, tail, 128), 0x7f, dtype=torch.uint8), torch.full((Hkv, tail), float("nan")),
+                    torch.full((Hkv, tail, 128), 0x7f, dtype=torch.uint8), torch.full((Hkv, tail), float("nan")), start=n)
     gen = torch.Generator().manual_seed(1501)
     slots, positions = [], []
     for slot, n in zip([2, 0, 1], lens):
@@ -420,7 +424,8 @@ def test_prefill_attention_groups_rows_and_matches_the_row_wise_path(Hq, Hkv):
     assert float(d.max()) <= 8e-3 and float(d.mean()) <= 2e-4, (float(d.max()), float(d.mean()))
     # a few rows against the checker: the causal prefix of each prompt
     seq_of = {2: 0, 0: 1, 1: 2}
-    for r in (0, 63, 64, 149, 150, 158, 159, rows - 1):
+    assert torch.isfinite(got.float()).all()
+    for r in (0, 63, 64, 149, 150, 158, 159, 222, 223, rows - 1):
         b, n = seq_of[slots[r]], positions[r] + 1
         ref = oat.decode_attention(helpers.bf16_bits(q[r:r + 1].cpu()), [case["k_bytes"][b][:, :n]],
                                    [case["k_scale"][b][:, :n]], [case["v_bytes"][b][:, :n]], [case["v_scale"][b][:, :n]], SCALE)

@@ -115,28 +115,24 @@ def test_prefill_groups_cut_runs_into_groups_that_share_page_loads():
     from nanochat_b200.attention import prefill_groups
 
     def by_rows(slots, positions, limit):
-        starts, span = [0], [0] * len(slots)
-        for r in range(1, len(slots) + 1):
+        starts = [0]
+        for r in range(1, len(slots)):
             first = starts[-1]
-            if (r == len(slots) or r - first == limit or slots[r] != slots[first]
-                    or positions[r] != positions[r - 1] + 1):
-                for i in range(first, r):
-                    span[i] = positions[r - 1] + 1
-                if r < len(slots):
-                    starts.append(r)
-        return starts + [len(slots)], span
+            if r - first == limit or slots[r] != slots[first] or positions[r] != positions[r - 1] + 1:
+                starts.append(r)
+        return starts + [len(slots)]
 
     rng = random.Random(0)
-    for Hq, Hkv in ((8, 8), (8, 2), (8, 1), (6, 2)):
+    for limit in (64, 16, 8, 2, 1):
         for _ in range(20):
             slots, positions = [], []
             for _ in range(rng.randint(1, 6)):
-                slot, first, count = rng.randint(0, 3), rng.randint(0, 40), rng.randint(1, 30)
+                slot, first, count = rng.randint(0, 3), rng.randint(0, 40), rng.randint(1, 150)
                 slots += [slot] * count
                 positions += list(range(first, first + count))
-            assert prefill_groups(slots, positions, Hq, Hkv) == by_rows(slots, positions, max(1, 8 // (Hq // Hkv)))
-    assert prefill_groups([], [], 8, 8) == ([0], [])
-    assert prefill_groups([3], [7], 8, 2) == ([0, 1], [8])
+            assert prefill_groups(slots, positions, limit) == by_rows(slots, positions, limit)
+    assert prefill_groups([], [], 8) == [0]
+    assert prefill_groups([3], [7], 2) == [0, 1]
 
 
 def test_no_collection_restores_the_collector():

@@ -1,7 +1,7 @@
 """tile_gemm (the tiled tcgen05 GEMM for prefill passes and large decode steps) through the C ABI against a plain
 PyTorch fp32 reference of the same operation. Tolerance: the fp32 product differs from the reference only by
 summation order (about 1e-6 relative), so bf16 outputs agree to one rounding step of the largest output in the row
-block; the test allows one such step (2^-8 relative to the largest magnitude)."""
+block; the test allows one such step (at most 2^-7 relative to the largest magnitude)."""
 
 import pytest
 import torch
@@ -52,16 +52,16 @@ def test_tile_gemm_matches_torch(rows, N, K, epilogue):
     if epilogue == 3:
         assert float(err.max()) <= 2e-5 * max(top, 1.0) * (K / 64) ** 0.5
     else:
-        assert float(err.max()) <= 2 ** -8 * top + 1e-6, (float(err.max()), top)
+        assert float(err.max()) <= 2 ** -7 * top + 1e-6, (float(err.max()), top)
         assert float((err > 0).float().mean()) < 0.02  # roundings flip only where the fp32 sums straddle a boundary
 
 
 def test_tile_gemm_many_tiles_per_block_and_in_place_residual():
     """More tiles than SMs, so blocks walk over several tiles and both accumulators are in use; residual in place."""
     y, want = run(4096, 5120, 1280, 2, seed=5)  # 32 x 20 = 640 tiles
-    assert float((y.float() - want.float()).abs().max()) <= 2 ** -8 * float(want.float().abs().max()) + 1e-6
+    assert float((y.float() - want.float()).abs().max()) <= 2 ** -7 * float(want.float().abs().max()) + 1e-6
     y, want = run(700, 1280, 256, 1, seed=6, alias=True)
-    assert float((y.float() - want.float()).abs().max()) <= 2 ** -8 * float(want.float().abs().max()) + 1e-6
+    assert float((y.float() - want.float()).abs().max()) <= 2 ** -7 * float(want.float().abs().max()) + 1e-6
 
 
 def test_tile_gemm_is_deterministic_and_validates():
