@@ -510,13 +510,13 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
 /* A prefill pass holds many rows of the same prompt with lengths one apart (the reference runs them through k_attn
  * row by row, model/kernels/decode.cu:859-863,1041-1051). Here a block takes a TILE of consecutive rows of one prompt
  * and one kv head, streams the prompt's pages ONCE through a shared ring and lets PF_WARPS warps consume every page,
- * each for its own rows: warp w owns 8 / G rows (8 query columns = 4 per MMA tile, two tiles), i.e. 64 rows per block
- * for G = 1 and 16 for G = 4. A prompt's cache is read once per tile instead of once per row, every warp walks all
+ * each for its own rows: warp w owns 8 / G rows (8 query columns = 4 per MMA tile, two tiles), i.e. 88 rows per block
+ * for G = 1 and 22 for G = 4. A prompt's cache is read once per tile instead of once per row, every warp walks all
  * pages up to its rows' lengths with the same per-page code as the decode kernel (attend_page, rows masked at their
  * own length), and because a warp owns its rows over the whole key range there are no partial states, no workspace
  * and no merge launch: the warp normalises and writes bf16 outputs itself.
  * One producer thread (an extra warp) issues the page copies; full / empty mbarriers per stage, all waits bounded. */
-constexpr int PF_WARPS = 8, PF_STAGES = 6;
+constexpr int PF_WARPS = 11, PF_STAGES = 6; /* 11 consumers + the producer = 384 threads: what 168 registers allow */
 constexpr int PF_THREADS = (PF_WARPS + 1) * 32;
 constexpr int PF_SLOTS = 8; /* query columns per warp */
 constexpr size_t PF_SMEM = (size_t)PF_STAGES * PAGE_BYTES + (size_t)PF_WARPS * PF_SLOTS * HEAD_DIM * sizeof(float);

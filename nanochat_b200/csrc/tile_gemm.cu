@@ -15,6 +15,8 @@
  *     the MMAs of the next tile run while the epilogue drains the previous one;
  *   - warps 2..5: epilogue. Warp w owns the 32 tensor-memory lanes (= rows) its rank allows (w % 4), a thread reads
  *     its row 32 columns at a time (tcgen05.ld), applies the epilogue and writes 64 contiguous bytes.
+ * Tiles are dealt to the blocks round-robin; when the last round would occupy at most half of the blocks, its tiles
+ * are cut into two half-width units each (N = BN / 2 MMAs on the same stages), which shortens that round to about half.
  * Rows beyond the matrix are zero-filled by TMA on the way in and masked on the way out. The parameter-free RMS norm
  * of the inputs is not fused here: passes of this size keep the normed rows in memory anyway (add_rms_norm).
  * Every mbarrier wait is bounded; on expiry NCB_DEV_WAIT_TIMEOUT is flagged, every role abandons its remaining tiles
@@ -44,13 +46,30 @@ struct TileArgs {
     void *y;           /* [rows][N] bf16, or fp32 for EPI_F32 */
     int rows, N, K;
     int *status;
+    int split_from; /* tiles from this index on are worked on as two half-width units each (= tiles: none) */
 };
 
-/* Grid = min(tiles, SMs); block b takes tiles b, b + grid, ...; tile t = (row tile t / n_tiles, feature tile t % n_tiles),
- * so blocks that run at the same time share the x rows and cover neighbouring feature tiles. */
+/* A unit of work: a tile, or half of one. */
+struct Unit {
+    int m0, n0, width;
+};
+
+/* Grid = min(tiles, SMs); block b takes units b, b + grid, ...; tile t = (row tile t / n_tiles, feature tile t % n_tiles),
+ * so blocks that run at the same time share the x rows and cover neighbouring feature tiles. When the last round of
+ * tiles would fill at most half of the blocks (`split_from` < tiles), each of its tiles is cut into two half-width
+ * units, so that the round takes about half as long: units [0, split_from) are whole tiles, unit split_from + h is
+ * half h % 2 of tile split_from + h / 2. */
+template <int BN>
+static __device__ __forceinline__ Unit unit_of(int u, int n_tiles, int split_from) {
+    if (u < split_from) return {(u / n_tiles) * BM, (u % n_tiles) * BN, BN};
+    const int h = u - split_from, t = split_from + h / 2;
+    return {(t / n_tiles) * BM, (t % n_tiles) * BN + (h & 1) * (BN / 2), BN / 2};
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS, 1) k_tile_gemm(const __grid_constant__ CUtensorMap map_x,
-                                                          const __grid_constant__ CUtensorMap map_w, const TileArgs a) {
+                                                          const __grid_constant__ CUtensorMap map_w,
+                                                          const __grid_constant__ CUtensorMap map_w_half, const TileArgs a) {
     using T = Tile<BN>;
     constexpr int STAGES = T::STAGES;
     extern __shared__ uint8_t raw[];
@@ -67,6 +86,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_tile_gemm(const __grid_constant_
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_tiles = a.N / BN, m_tiles = (a.rows + BM - 1) / BM, tiles = n_tiles * m_tiles;
+    const int split_from = a.split_from, units = split_from + 2 * (tiles - split_from);
     const int nkb = a.K / KBLK;
 
     if (tid == 0) {
@@ -102,8 +122,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_tile_gemm(const __grid_constant_
         if (lane == 0) { /* producer */
             const uint64_t w_policy = policy_evict_last(), x_policy = policy_evict_last(); /* both are re-read by other tiles */
             uint32_t g = 0; /* k-blocks issued so far, over all of this block's tiles */
-            for (int t = blockIdx.x; t < tiles && !*failed; t += gridDim.x) {
-                const int m0 = (t / n_tiles) * BM, n0 = (t % n_tiles) * BN;
+            for (int u = blockIdx.x; u < units && !*failed; u += gridDim.x) {
+                const Unit un = unit_of<BN>(u, n_tiles, split_from);
+                const bool whole = un.width == BN;
                 for (int kb = 0; kb < nkb; kb++, g++) {
                     const int s = g % STAGES;
                     if (!mbar_wait(empty(s), ((g / STAGES) & 1) ^ 1)) {
@@ -111,19 +132,21 @@ __global__ void __launch_bounds__(THREADS, 1) k_tile_gemm(const __grid_constant_
                         *failed = 1;
                         break;
                     }
-                    mbar_expect_tx(full(s), T::STAGE_BYTES);
-                    tma_load(ring + s * T::STAGE_BYTES, &map_x, kb * KBLK, m0, full(s), x_policy);
-                    tma_load(ring + s * T::STAGE_BYTES + A_BYTES, &map_w, kb * KBLK, n0, full(s), w_policy);
+                    mbar_expect_tx(full(s), A_BYTES + (whole ? T::B_BYTES : T::B_BYTES / 2));
+                    tma_load(ring + s * T::STAGE_BYTES, &map_x, kb * KBLK, un.m0, full(s), x_policy);
+                    tma_load(ring + s * T::STAGE_BYTES + A_BYTES, whole ? &map_w : &map_w_half, kb * KBLK, un.n0, full(s),
+                             w_policy);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) { /* MMA issuer */
-            constexpr uint32_t IDESC = (1u << 4) /* fp32 accumulators */ | (1u << 7) /* A bf16 */ | (1u << 10) /* B bf16 */
-                                       | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24); /* both K-major */
+            constexpr uint32_t IDESC_BASE = (1u << 4) /* fp32 accumulators */ | (1u << 7) /* A bf16 */ | (1u << 10) /* B bf16 */
+                                            | ((uint32_t)(BM >> 4) << 24); /* both K-major; N goes to bits 17.. */
             uint32_t g = 0, it = 0;
-            for (int t = blockIdx.x; t < tiles && !*failed; t += gridDim.x, it++) {
+            for (int u = blockIdx.x; u < units && !*failed; u += gridDim.x, it++) {
                 const uint32_t buf = it & 1;
+                const uint32_t idesc = IDESC_BASE | ((uint32_t)(unit_of<BN>(u, n_tiles, split_from).width >> 3) << 17);
                 if (!mbar_wait(acc_empty(buf), ((it >> 1) & 1) ^ 1)) { /* the epilogue has drained this accumulator */
                     flag(a.status, NCB_DEV_WAIT_TIMEOUT);
                     *failed = 1;
@@ -140,7 +163,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_tile_gemm(const __grid_constant_
                     const uint32_t a_addr = ring + s * T::STAGE_BYTES, b_addr = a_addr + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < KBLK / 16; k++) /* 16 k-values = 32 bytes further along the swizzled row */
-                        umma_bf16(acc, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), IDESC, (kb | k) != 0);
+                        umma_bf16(acc, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
                     umma_commit(empty(s));
                 }
                 if (!ok) {
@@ -154,9 +177,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_tile_gemm(const __grid_constant_
     } else { /* epilogue warps 2..5: tensor-memory lanes 32 (warp % 4) .. + 31 */
         const int quarter = warp & 3;
         uint32_t it = 0;
-        for (int t = blockIdx.x; t < tiles; t += gridDim.x, it++) {
+        for (int u = blockIdx.x; u < units; u += gridDim.x, it++) {
             const uint32_t buf = it & 1;
-            const int m0 = (t / n_tiles) * BM, n0 = (t % n_tiles) * BN;
+            const Unit un = unit_of<BN>(u, n_tiles, split_from);
+            const int m0 = un.m0, n0 = un.n0;
             if (*failed || !mbar_wait(acc_full(buf), (it >> 1) & 1)) {
                 if (!*failed && lane == 0) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
                 *failed = 1;
@@ -167,7 +191,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_tile_gemm(const __grid_constant_
             const bool live = row < a.rows;
             const size_t base = (size_t)row * a.N + n0;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
+            for (int c = 0; c < un.width / 32; c++) {
                 float v[32];
                 tmem_load32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c * 32, v);
                 if (!live) continue;
@@ -221,7 +245,7 @@ int sm_count_now() {
 }
 
 template <int BN, int EPI>
-int launch(const CUtensorMap &map_x, const CUtensorMap &map_w, const TileArgs &a, cudaStream_t stream) {
+int launch(const CUtensorMap &map_x, const CUtensorMap &map_w, const CUtensorMap &map_w_half, TileArgs a, cudaStream_t stream) {
     auto kernel = k_tile_gemm<BN, EPI>;
     static std::mutex lock;
     static int prepared_device = -1; /* per instantiation: the attribute has to be set once per device */
@@ -236,6 +260,9 @@ int launch(const CUtensorMap &map_x, const CUtensorMap &map_w, const TileArgs &a
         }
     }
     const int tiles = (a.N / BN) * ((a.rows + BM - 1) / BM), sms = sm_count_now();
+    /* a last round of tiles that fills at most half of the blocks is run as half-width units */
+    const int rest = tiles % sms;
+    a.split_from = (BN == 256 && tiles > sms && rest > 0 && 2 * rest <= sms) ? tiles - rest : tiles;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(tiles < sms ? tiles : sms);
     config.blockDim = dim3(THREADS);
@@ -246,16 +273,17 @@ int launch(const CUtensorMap &map_x, const CUtensorMap &map_w, const TileArgs &a
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, kernel, map_x, map_w, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+    return cudaLaunchKernelEx(&config, kernel, map_x, map_w, map_w_half, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 template <int BN>
-int launch_epi(const CUtensorMap &map_x, const CUtensorMap &map_w, const TileArgs &a, int epilogue, cudaStream_t stream) {
+int launch_epi(const CUtensorMap &map_x, const CUtensorMap &map_w, const CUtensorMap &map_w_half, const TileArgs &a,
+               int epilogue, cudaStream_t stream) {
     switch (epilogue) {
-    case EPI_STORE: return launch<BN, EPI_STORE>(map_x, map_w, a, stream);
-    case EPI_RESID: return launch<BN, EPI_RESID>(map_x, map_w, a, stream);
-    case EPI_RELU2: return launch<BN, EPI_RELU2>(map_x, map_w, a, stream);
-    case EPI_F32: return launch<BN, EPI_F32>(map_x, map_w, a, stream);
+    case EPI_STORE: return launch<BN, EPI_STORE>(map_x, map_w, map_w_half, a, stream);
+    case EPI_RESID: return launch<BN, EPI_RESID>(map_x, map_w, map_w_half, a, stream);
+    case EPI_RELU2: return launch<BN, EPI_RELU2>(map_x, map_w, map_w_half, a, stream);
+    case EPI_F32: return launch<BN, EPI_F32>(map_x, map_w, map_w_half, a, stream);
     default: return NCB_ERR_ARG;
     }
 }
@@ -279,11 +307,13 @@ int tile_gemm(const void *x, const void *w, const void *resid, void *y, long lon
     if (!x || !w || !y || (epilogue == EPI_RESID && !resid)) return NCB_ERR_ARG;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)resid) % 16) return NCB_ERR_ALIGN;
     const int bn = N % 256 == 0 ? 256 : 128;
-    CUtensorMap map_x, map_w;
-    if (!tensor_map(x, (int)rows, K, BM, &map_x) || !tensor_map(w, N, K, bn, &map_w)) return NCB_ERR_LAUNCH;
-    const TileArgs a = {(const bf16 *)resid, y, (int)rows, N, K, status};
-    return bn == 256 ? launch_epi<256>(map_x, map_w, a, epilogue, (cudaStream_t)stream)
-                     : launch_epi<128>(map_x, map_w, a, epilogue, (cudaStream_t)stream);
+    CUtensorMap map_x, map_w, map_w_half;
+    if (!tensor_map(x, (int)rows, K, BM, &map_x) || !tensor_map(w, N, K, bn, &map_w) ||
+        !tensor_map(w, N, K, bn / 2, &map_w_half))
+        return NCB_ERR_LAUNCH;
+    const TileArgs a = {(const bf16 *)resid, y, (int)rows, N, K, status, 0};
+    return bn == 256 ? launch_epi<256>(map_x, map_w, map_w_half, a, epilogue, (cudaStream_t)stream)
+                     : launch_epi<128>(map_x, map_w, map_w_half, a, epilogue, (cudaStream_t)stream);
 }
 
 } /* extern "C" */
