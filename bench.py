@@ -356,6 +356,37 @@ def bench_kernels(device, timed, profile_range: str) -> dict:
     assert int(status.item()) == 0
     del qkv, cache, q_out
 
+    # ---- prefill attention: the rows of the same pass attend their prompts' caches (d20 heads, 8 x 511 rows)
+    per = 511
+    rows = prompts * per
+    cache = synthetic_cache([per] * prompts, per, seed=7050, device=device) if Hkv == HKV else None
+    if cache is None:
+        cache = ncb.Fp8KVCache(prompts, Hkv, per, device=device)
+        for slot in range(prompts):
+            packed = []
+            for _ in range(2):
+                packed += list(quantise_rows(torch.randn(Hkv, per, D, generator=gen, device=device)))
+            cache.write(slot, *packed)
+    slots = [s_ for s_ in range(prompts) for _ in range(per)]
+    positions = [t for _ in range(prompts) for t in range(per)]
+    plan = ops.PrefillPlan(slots, positions, Hq, cache, device)
+    q = torch.randn(rows, Hq, D, generator=gen, device=device).bfloat16()
+    att = torch.empty_like(q)
+    ms = ranged("prefill_attn", lambda: ops.prefill_attention(q, cache, plan, out=att, status=status), 20)
+    pages_read = sum(-(-(min(per, g0 + plan.rows_per_block)) // 64) for g0 in range(0, per, plan.rows_per_block)) * prompts * Hkv
+    nbytes = pages_read * 16896 + 2 * rows * Hq * 256
+    out["prefill_attention"] = {"workload": f"{rows} rows (8 prompts x 511 positions), Hq 10, Hkv 10, causal",
+                                "us_per_launch": ms * 1e3, "bytes_read_per_launch": nbytes,
+                                "note": "compute-bound: every cached position is scored against up to 88 query rows; the "
+                                        "pages (10.8 MB of cache) come from L2",
+                                "flops_per_launch": 4 * D * Hq * prompts * per * (per + 1) // 2,
+                                "achieved_tflops": 4 * D * Hq * prompts * per * (per + 1) // 2 / ms / 1e9}
+    assert int(status.item()) == 0
+    ref = torch_attention_row(cache, 3, 300, q[3 * per + 299])
+    err = error_of(att[3 * per + 299], ref)
+    assert err[0] <= PATH_MAX_ABS and err[1] <= PATH_MEAN_ABS, err
+    del cache, q, att
+
     # ---- merge and the exchange kernel's local part, on states the split kernel left for the target shape
     B, chunk = BATCH, 32
     lens = [8192] * B
@@ -579,7 +610,7 @@ def main() -> None:
     ap.add_argument("--decoder-tokens", type=int, default=256, help="tokens generated per sequence in that run")
     ap.add_argument("--kernels", type=int, default=1, help="also time the append, merge and exchange kernels alone (N = 1; 0: skip)")
     ap.add_argument("--profile-range", default="attention",
-                    choices=["attention", "decoder", "decoder_d32", "append", "merge", "exchange"],
+                    choices=["attention", "decoder", "decoder_d32", "append", "prefill_attn", "merge", "exchange"],
                     help="which timed loops cudaProfilerStart/Stop bracket (for `ncu --profile-from-start off`)")
     ap.add_argument("--decoder-d32", type=int, default=1, help="also time batched decode of the d32-class model (0: skip)")
     ap.add_argument("--ragged", type=int, default=1, help="also run the ragged GQA sweep as an extra (0: skip)")

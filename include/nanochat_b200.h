@@ -178,9 +178,10 @@ int decode_step_attn_fp8_ve(const void *qkv, const void *q_gain, const void *k_g
 
 /*
  * Attention for a prefill pass (replaces k_attn over prompt rows, decode.cu:859-863,1041-1051): `rows` query rows,
- * many of which belong to one sequence. Rows are grouped on the host: block z = rows group_start[z] ..
- * group_start[z + 1] - 1 (int32 [n_groups + 1], at most prefill_attn_rows_per_block(Hq, Hkv) rows each: 88 for
- * Hq == Hkv, 22 for four query heads per kv head), all of one slot with ascending positions. A block streams the
+ * many of which belong to one sequence. Rows are grouped on the host: block z = the group_rows[z] rows starting at
+ * row group_first[z] (int32 [n_groups] each; at most prefill_attn_rows_per_block(Hq, Hkv) rows: 88 for Hq == Hkv, 22
+ * for four query heads per kv head), all of one slot with ascending positions. Blocks start in the order of the
+ * list, so list the groups that reach furthest into their prompts first. A block streams the
  * sequence's pages once for all its rows (a shared ring consumed by eleven warps, each owning 8 / (Hq / Hkv) rows over
  * the whole key range) and writes normalised outputs itself: no workspace, no merge launch.
  *   q bf16 [rows][Hq][128]; lens int32 [rows] (row r attends positions [0, lens[r])); slot_map int32 [rows];
@@ -190,8 +191,8 @@ int decode_step_attn_fp8_ve(const void *qkv, const void *q_gain, const void *k_g
  */
 int prefill_attn_rows_per_block(int Hq, int Hkv);
 int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
-                     const void *group_start, int n_groups, void *out, long long rows, int Hq, int Hkv, int n_slots,
-                     int pages_per_slot, float softmax_scale, void *status, void *stream);
+                     const void *group_first, const void *group_rows, int n_groups, void *out, long long rows, int Hq,
+                     int Hkv, int n_slots, int pages_per_slot, float softmax_scale, void *status, void *stream);
 
 /*
  * The first of decode_attn_fp8's two launches alone: the split-KV kernel, leaving one state per (b, h, chunk) in

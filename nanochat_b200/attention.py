@@ -184,9 +184,14 @@ class PrefillPlan:
     device."""
 
     def __init__(self, slots: list[int], positions: list[int], Hq: int, cache: Fp8KVCache, device):
-        starts = prefill_groups(slots, positions, prefill_rows_per_block(Hq, cache.kv_heads))
+        self.rows_per_block = prefill_rows_per_block(Hq, cache.kv_heads)
+        starts = prefill_groups(slots, positions, self.rows_per_block)
         self.rows, self.n_groups = len(slots), len(starts) - 1
-        self.group_start = torch.tensor(starts, dtype=torch.int32, device=device)
+        # blocks start in list order: the groups that reach furthest into their prompts (most pages) go first, so
+        # the short ones fill the gaps at the end
+        order = sorted(range(self.n_groups), key=lambda z: (-positions[starts[z + 1] - 1], z))
+        self.group_first = torch.tensor([starts[z] for z in order], dtype=torch.int32, device=device)
+        self.group_rows = torch.tensor([starts[z + 1] - starts[z] for z in order], dtype=torch.int32, device=device)
         self.slot_map = torch.tensor(slots, dtype=torch.int32, device=device)
         self.lens = torch.tensor(positions, dtype=torch.int32, device=device) + 1
 
@@ -203,8 +208,8 @@ def prefill_attention(q: Tensor, cache: Fp8KVCache, plan: PrefillPlan, softmax_s
         out = torch.empty_like(q)
     scale = HEAD_DIM ** -0.5 if softmax_scale is None else softmax_scale
     rc = cuda_library("decode_attn").prefill_attn_fp8(
-        pointer(q), pointer(cache.pages), pointer(plan.lens), pointer(plan.slot_map), pointer(plan.group_start),
-        plan.n_groups, pointer(out), rows, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, scale,
+        pointer(q), pointer(cache.pages), pointer(plan.lens), pointer(plan.slot_map), pointer(plan.group_first),
+        pointer(plan.group_rows), plan.n_groups, pointer(out), rows, Hq, cache.kv_heads, cache.n_slots, cache.pages_per_slot, scale,
         pointer(status), stream())
     check(rc, "prefill_attn_fp8")
     return out

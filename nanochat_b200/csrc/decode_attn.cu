@@ -524,7 +524,7 @@ constexpr size_t PF_SMEM = (size_t)PF_STAGES * PAGE_BYTES + (size_t)PF_WARPS * P
 struct PrefillArgs {
     const bf16 *q;         /* [rows][Hq][128] */
     const uint8_t *cache;
-    const int32_t *lens, *slot_map, *group_start; /* per row, per row, per block (+ end sentinel) */
+    const int32_t *lens, *slot_map, *group_first, *group_rows; /* per row, per row, per block, per block */
     bf16 *out;             /* [rows][Hq][128] */
     int Hq, Hkv, n_slots, pages_per_slot;
     float scale_log2;
@@ -539,8 +539,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_attn(PrefillArgs a) {
     const int kvh = blockIdx.y, G = a.Hq / a.Hkv, rpw = max(1, PF_SLOTS / G);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int b0 = a.group_start[blockIdx.x];
-    const int n_rows = min(a.group_start[blockIdx.x + 1] - b0, PF_WARPS * rpw);
+    const int b0 = a.group_first[blockIdx.x];
+    const int n_rows = min(a.group_rows[blockIdx.x], PF_WARPS * rpw);
     const int n_active = (n_rows + rpw - 1) / rpw; /* warps that have rows */
     const int len_block = a.lens[b0 + n_rows - 1];  /* rows ascend in position: the last one is the longest */
     const int slot = a.slot_map[b0];
@@ -1209,14 +1209,14 @@ int prefill_attn_rows_per_block(int Hq, int Hkv) {
 }
 
 int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
-                     const void *group_start, int n_groups, void *out, long long rows, int Hq, int Hkv, int n_slots,
-                     int pages_per_slot, float softmax_scale, void *status, void *stream) {
+                     const void *group_first, const void *group_rows, int n_groups, void *out, long long rows, int Hq,
+                     int Hkv, int n_slots, int pages_per_slot, float softmax_scale, void *status, void *stream) {
     if (rows < 0 || n_groups < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || n_slots <= 0 || pages_per_slot <= 0 ||
         !(softmax_scale > 0.f))
         return NCB_ERR_ARG;
     if (Hq / Hkv > PF_SLOTS) return NCB_ERR_UNSUPPORTED;
     if (rows == 0 || n_groups == 0) return NCB_OK;
-    if (!q || !kv_cache || !lens || !slot_map || !group_start || !out || Hkv > 65535) return NCB_ERR_ARG;
+    if (!q || !kv_cache || !lens || !slot_map || !group_first || !group_rows || !out || Hkv > 65535) return NCB_ERR_ARG;
     if (((uintptr_t)q | (uintptr_t)kv_cache | (uintptr_t)out) % 16 != 0) return NCB_ERR_ALIGN;
     {
         static bool done[MAX_DEVICES] = {};
@@ -1230,7 +1230,7 @@ int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, cons
         }
     }
     PrefillArgs a = {(const bf16 *)q, (const uint8_t *)kv_cache, (const int32_t *)lens, (const int32_t *)slot_map,
-                     (const int32_t *)group_start, (bf16 *)out, Hq, Hkv, n_slots, pages_per_slot,
+                     (const int32_t *)group_first, (const int32_t *)group_rows, (bf16 *)out, Hq, Hkv, n_slots, pages_per_slot,
                      softmax_scale * 1.4426950408889634f, (int *)status};
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)n_groups, (unsigned)Hkv);

@@ -46,7 +46,7 @@ SIGNATURES = {
         "decode_step_attn_fp8_ve": ([c_ptr] * 9 + [c_ll, c_ptr, c_int, c_int, c_int, c_ll] + [c_int] * 6
                                     + [c_float] + [c_ptr] * 4 + [c_int, c_int, c_ptr, c_ptr], c_int),
         "prefill_attn_rows_per_block": ([c_int, c_int], c_int),
-        "prefill_attn_fp8": ([c_ptr] * 5 + [c_int, c_ptr, c_ll] + [c_int] * 4 + [c_float, c_ptr, c_ptr], c_int),
+        "prefill_attn_fp8": ([c_ptr] * 6 + [c_int, c_ptr, c_ll] + [c_int] * 4 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_fp8_split": ([c_ptr] * 5 + [c_ll] + [c_int] * 8 + [c_float, c_ptr, c_ptr], c_int),
         "decode_attn_merge": ([c_ptr, c_int, c_ll, c_ptr, c_ptr], c_int),
         "decode_attn_fp8_sharded": ([c_ptr] * 5 + [c_ll, c_ptr] + [c_int] * 8 + [c_float, c_ptr, c_int, c_int, c_ptr,
