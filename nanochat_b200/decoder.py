@@ -464,17 +464,26 @@ class Decoder:
         B = len(first_tokens)
         assert B <= self.n_slots and max(positions) + steps <= self.capacity
         sampled = temperature > 0.0
-        graph, side, tokens, pos, logits, trace, ctl = self._step_graph(B, sampled, self.planned_chunk(positions, steps))
+        key = (B, sampled, self.planned_chunk(positions, steps), False)
+        graph, side, tokens, pos, logits, trace, ctl = self._step_graph(*key)
+        # The step's rows are the slots in descending order of length: the attention kernel's blocks start in row
+        # order, and a ragged batch that starts with its longest sequences leaves the shortest tail of idle SMs.
+        # (A row is computed from its own slot alone, so the order changes no result.)
+        order = sorted(range(B), key=lambda b: (-positions[b], b))
+        row_of = {b: r for r, b in enumerate(order)}
+        slot_map = self._graph_tensors[key][0]
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
-            tokens.copy_(torch.tensor(first_tokens, dtype=torch.long))
-            pos.copy_(torch.tensor(positions, dtype=torch.int32))
+            slot_map.copy_(torch.tensor(order, dtype=torch.int32))
+            tokens.copy_(torch.tensor([first_tokens[b] for b in order], dtype=torch.long))
+            pos.copy_(torch.tensor([positions[b] for b in order], dtype=torch.int32))
             first = pos.clone()
             if sampled:
+                seeds = seeds if seeds is not None else list(range(B))
                 ctl["temperature"].fill_(temperature)
                 ctl["top_p"].fill_(top_p)
-                ctl["seed"].copy_(torch.tensor(seeds if seeds is not None else list(range(B)), dtype=torch.long))
+                ctl["seed"].copy_(torch.tensor([seeds[b] for b in order], dtype=torch.long))
                 ctl["first"].copy_(first)
             begin.record()
             for _ in range(steps):
@@ -486,7 +495,8 @@ class Decoder:
         code = int(self.status.item())
         if code:
             raise RuntimeError(f"device status {code:#x} (NCB_DEV_* bits)")
-        return out.tolist(), begin.elapsed_time(end) * 1e-3
+        rows = out.tolist()
+        return [rows[row_of[b]] for b in range(B)], begin.elapsed_time(end) * 1e-3
 
     @torch.no_grad()
     def generate(self, prompts: list[list[int]], max_new_tokens: int, temperature: float = 0.0, top_p: float = 1.0,

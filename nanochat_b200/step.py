@@ -4,8 +4,9 @@ The reference runs its whole step as captured graphs launched from Python throug
 (model/kernels/decode.cu:848-902,1000-1016,1107-1110; inference/decoder.py:285) because at decode sizes the step is
 bound by launch latency, not by kernels. This is the same idea for the part of the step this package owns:
 
-    pinned host qkv rows + positions --copy--> device --decode_step_attn_fp8 (append + attend)--> cache, out
-    --copy--> pinned host
+    pinned host qkv rows + positions --copy--> device --decode_step_attn_fp8 (append + attend)--> cache;
+    the merge kernel writes the bf16 output rows straight into the pinned host buffer (it is written once and never
+    re-read by the GPU, so no device copy and no copy node are needed: the stores cross PCIe as they are produced)
 
 The caller writes `qkv_host` and `pos_host`, calls run(), and reads `out_host`. Sequence lengths are pos + 1 (the
 new token is attended through the cache). The graph is sized for the cache's capacity, so it stays valid as the
@@ -37,7 +38,6 @@ class DecodeStep:
         self.out_host = torch.zeros((batch, Hq, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
         self.qkv = torch.empty((batch, width), dtype=torch.bfloat16, device=dev)
         self.pos = torch.empty(batch, dtype=torch.int32, device=dev)
-        self.out = torch.empty((batch, Hq, HEAD_DIM), dtype=torch.bfloat16, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         need = ops.workspace_bytes(batch, Hq, Hkv, self.max_kv_len, self.chunk_pages)
         self.workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
@@ -58,8 +58,7 @@ class DecodeStep:
         ops.decode_step_attention(self.qkv, self.q_gain, self.k_gain, self.cos, self.sin, self.pos, self.cache,
                                   self.Hq, self.max_kv_len, slot_map=self.slot_map, window=self.window,
                                   chunk_pages=self.chunk_pages, softmax_scale=self.softmax_scale,
-                                  workspace=self.workspace, out=self.out, status=self.status, slots=self.slots)
-        self.out_host.copy_(self.out, non_blocking=True)
+                                  workspace=self.workspace, out=self.out_host, status=self.status, slots=self.slots)
 
     def capture(self) -> None:
         """Run the step once eagerly (first-use set-up must happen outside capture; the token it appends is
