@@ -387,6 +387,34 @@ def bench_kernels(device, timed, profile_range: str) -> dict:
     assert err[0] <= PATH_MAX_ABS and err[1] <= PATH_MEAN_ABS, err
     del cache, q, att
 
+    # ---- the tiled tcgen05 GEMM on a prefill pass's largest projection (4,088 rows x d20's MLP up-projection)
+    from nanochat_b200.native import cuda_library as _lib
+    rows, N, K = 4088, 5120, 1280
+    x = torch.randn(rows, K, generator=gen, device=device).bfloat16()
+    w = (torch.randn(N, K, generator=gen, device=device) * 0.02).bfloat16()
+    y = torch.empty(rows, N, dtype=torch.bfloat16, device=device)
+
+    def gemm():
+        rc = _lib("tile_gemm").tile_gemm(pointer(x), pointer(w), None, pointer(y), rows, N, K, 2, pointer(status), stream())
+        assert rc == 0
+
+    ms = ranged("tile_gemm", gemm, 20)
+    want = (x[:64].float() @ w.float().T).bfloat16().float().clamp_min(0).square().bfloat16()
+    assert float((y[:64].float() - want.float()).abs().max()) <= 2 ** -7 * float(want.float().abs().max()) + 1e-6
+    flops = 2 * rows * N * K
+    tensor_peak = 1610.8
+    try:
+        tensor_peak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"])
+    except Exception:
+        pass
+    out["tile_gemm_prefill"] = {"workload": f"{rows} x {K} bf16 rows times a {N} x {K} weight matrix, relu^2 epilogue",
+                                "us_per_launch": ms * 1e3, "flops_per_launch": flops, "bound": "tensor",
+                                "achieved": flops / ms / 1e9, "unit": "TFLOP/s", "peak": tensor_peak,
+                                "frac": flops / ms / 1e9 / tensor_peak,
+                                "peak_kind": "measured cuBLAS bf16 burst (MEASURED_PEAKS.json bf16_tflops), else 1610.8"}
+    assert int(status.item()) == 0
+    del x, w, y
+
     # ---- merge and the exchange kernel's local part, on states the split kernel left for the target shape
     B, chunk = BATCH, 32
     lens = [8192] * B
@@ -610,7 +638,7 @@ def main() -> None:
     ap.add_argument("--decoder-tokens", type=int, default=256, help="tokens generated per sequence in that run")
     ap.add_argument("--kernels", type=int, default=1, help="also time the append, merge and exchange kernels alone (N = 1; 0: skip)")
     ap.add_argument("--profile-range", default="attention",
-                    choices=["attention", "decoder", "decoder_d32", "append", "prefill_attn", "merge", "exchange"],
+                    choices=["attention", "decoder", "decoder_d32", "append", "prefill_attn", "tile_gemm", "merge", "exchange"],
                     help="which timed loops cudaProfilerStart/Stop bracket (for `ncu --profile-from-start off`)")
     ap.add_argument("--decoder-d32", type=int, default=1, help="also time batched decode of the d32-class model (0: skip)")
     ap.add_argument("--ragged", type=int, default=1, help="also run the ragged GQA sweep as an extra (0: skip)")
