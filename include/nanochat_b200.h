@@ -160,6 +160,10 @@ int decode_attn_fp8_partial(const void *q, const void *kv_cache, const void *len
  * max_kv_len bounds pos[b] + 1. Rows must address distinct slots (rows sharing a slot, as in prefill, need the
  * separate entry points, where every row's append lands before any row attends). pos[b] < 0 marks an idle row: no
  * append, no attention, a zero output row, no status bit (the reference's inactive slots, decode.cu:555,573).
+ * Stream contract: the split kernel starts its first page copies before it waits for the launch before it (programmatic
+ * dependent launch), so a kernel launched IMMEDIATELY before this call on the stream that releases its dependents
+ * early (every kernel of these libraries does) must not write pos, slot_map or this cache (in a decode step it is the
+ * qkv projection; copies, ordinary kernels and anything earlier are always complete).
  */
 int decode_step_attn_fp8(const void *qkv, const void *q_gain, const void *k_gain, const void *cos, const void *sin,
                          const void *pos, const void *slot_map, void *kv_cache, void *workspace,
@@ -253,7 +257,9 @@ int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out,
  * must make the same sequence of calls with the same B and Hq; a rank may run ahead of a peer by at most one call, and
  * the inbox's two halves alternate between calls so nothing still being read is overwritten. If a wait runs out,
  * NCB_DEV_WAIT_TIMEOUT is set in *status and the row's `out` is not written; the kernel still returns. Other
- * arguments as decode_attn_fp8.
+ * arguments as decode_attn_fp8. Stream contract: as for decode_step_attn_fp8, the kernel launched immediately before
+ * this call must not write lens, slot_map or cached positions below lens[b] - 1 (appending the newest token there is
+ * fine: the page that holds it is only read after the wait).
  */
 int decode_attn_fp8_sharded(const void *q, const void *kv_cache, const void *lens, const void *slot_map,
                             void *workspace, long long workspace_bytes, void *out, int B, int Hq, int Hkv, int n_slots,

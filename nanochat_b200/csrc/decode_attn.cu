@@ -62,6 +62,7 @@ struct AttnArgs {
     float scale_log2; /* softmax scale * log2(e) */
     int *status;
     int len_add; /* a sequence's length is lens[b] + len_add (1 when lens holds the new token's position) */
+    int early;   /* the predecessor launch leaves lens, slot_map and all but the newest cached position alone */
     /* APPEND only: the new token's fused projection row and what its q/k row math needs (kv_append_fp8's inputs) */
     const bf16 *qkv;
     const float *q_gain, *k_gain, *cs, *sn;
@@ -335,9 +336,11 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     const int chunk = blockIdx.x, kvh = blockIdx.y;
     const int G = a.Hq / a.Hkv;
 
-    /* launched with programmatic stream serialisation: everything this kernel reads (lens, q, the cache with the
-     * token appended a moment ago) comes from kernels before it */
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    /* Launched with programmatic stream serialisation: what this kernel reads comes from kernels before it, and it
+     * waits for them here — unless the entry point's contract says that the launch immediately before this one leaves
+     * the lengths, the slot map and all but the newest cached position alone (a.early): then the block works out its
+     * pages and starts its first page copies BEFORE waiting, under the predecessor's tail. */
+    if (!a.early) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = (int)blockIdx.z, S = G; /* the block's row; its query slots: the heads of the kv group */
     const int given = a.lens[b];
     if (given < 0) return; /* an idle row: nothing appended, nothing attended, nothing flagged; the merge writes zeros */
@@ -357,11 +360,18 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     uint8_t *page = smem + (size_t)warp * PAGE_BYTES; /* this warp's stage */
     const uint32_t page_u = smem_u32(page), bar = smem_u32(bars + warp);
 
+    /* Pages below the one that holds the newest position were written at least one step ago. The appending variant
+     * may take that page early too: it patches the new token's row into the landed page anyway. */
+    const bool first_now = !a.early || APPEND || pg0 + warp < (len - 1) / PAGE_TOKENS;
     if (lane == 0) { /* arm this warp's barrier and start its first page before anything else happens */
         mbar_init(bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (warp < n) page_load(page_u, pages + (size_t)warp * PAGE_BYTES, bar);
+        if (warp < n && first_now) page_load(page_u, pages + (size_t)warp * PAGE_BYTES, bar);
+    }
+    if (a.early) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (lane == 0 && warp < n && !first_now) page_load(page_u, pages + (size_t)warp * PAGE_BYTES, bar);
     }
     /* the group's queries as fp32 (bf16 values) and each head's scale amax / 448 */
     const int new_page = (len - 1) / PAGE_TOKENS - pg0; /* APPEND: the chunk page that receives the new token */
@@ -914,7 +924,7 @@ template <int NT, bool APPEND> static cudaError_t prepare() { /* opt in to the l
 static int launch_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
                         long long workspace_bytes, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,
                         int max_kv_len, int window, int &chunk_pages, float softmax_scale, void *status,
-                        cudaStream_t stream, const AppendIn *app = nullptr) {
+                        cudaStream_t stream, const AppendIn *app = nullptr, bool early = false) {
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || n_slots <= 0 || pages_per_slot <= 0 || max_kv_len < 0 ||
         window < 0 || chunk_pages < 0 || !(softmax_scale > 0.f))
         return NCB_ERR_ARG;
@@ -945,7 +955,7 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
     AttnArgs a = {(const bf16 *)q, (const uint8_t *)kv_cache, (const int32_t *)lens, (const int32_t *)slot_map,
                   (float *)workspace, B, Hq, Hkv, n_slots, pages_per_slot, window, chunk_pages, max_chunks,
-                  softmax_scale * 1.4426950408889634f, (int *)status, app ? 1 : 0};
+                  softmax_scale * 1.4426950408889634f, (int *)status, app ? 1 : 0, (app || early) ? 1 : 0};
     if (app) {
         a.qkv = (const bf16 *)app->qkv, a.q_gain = (const float *)app->q_gain, a.k_gain = (const float *)app->k_gain;
         a.cs = (const float *)app->cos, a.sn = (const float *)app->sin;
@@ -1027,7 +1037,7 @@ static int attend(const void *q, const void *kv_cache, const void *lens, const v
     if (((uintptr_t)out | (uintptr_t)part_out) % 16 != 0) return NCB_ERR_ALIGN;
     const int rc = launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots,
                                 pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status,
-                                (cudaStream_t)stream, app);
+                                (cudaStream_t)stream, app, exchange != nullptr);
     if (rc != NCB_OK || B == 0) return rc;
     if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
     const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
