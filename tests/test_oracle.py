@@ -142,35 +142,3 @@ def test_attention_oracle_window():
                                window=40)
     assert np.array_equal(full, win)
 
-
-def test_shared_reciprocal_rule_of_the_append_kernel_matches_ieee_division():
-    """The append kernel divides a row's values by the row scale through one correctly rounded reciprocal and falls back
-    to the IEEE division near e4m3 rounding midpoints, below 2^-6 and for extreme scales (csrc/kv_row.cuh,
-    quotient_for_e4m3). The rule restated in numpy (float32 products and quotients are IEEE there too) must give the
-    checker's bytes for every input: random rows and quotients planted on and next to every midpoint."""
-    rng = np.random.default_rng(7)
-
-    def bytes_both_ways(x, s):
-        x, s = x.astype(np.float32), s.astype(np.float32)
-        exact = (x / s).astype(np.float32)
-        q0 = (x * (np.float32(1.0) / s).astype(np.float32)).astype(np.float32)
-        bits = q0.view(np.uint32) & np.uint32(0x7fffffff)
-        off = (bits & np.uint32(0xFFFFF)).astype(np.int64) - 0x80000
-        shared = (s > np.float32(1e-30)) & (s < np.float32(1e30))
-        safe = shared & ((bits == 0) | ((bits >= np.uint32(0x3C800000)) & (np.abs(off) > 4)))
-        return okv.f32_to_e4m3(np.where(safe, q0, exact)), okv.f32_to_e4m3(exact), float(safe.mean())
-
-    n = 3_000_000
-    amax = np.abs(rng.standard_normal(n).astype(np.float32) * 3) + np.float32(1e-3)
-    amax = (amax.view(np.uint32) & np.uint32(0xffff0000)).view(np.float32)  # bf16-valued, as in the kernel
-    x = ((amax * rng.random(n).astype(np.float32)).view(np.uint32) & np.uint32(0xffff0000)).view(np.float32)
-    x *= rng.choice([-1, 1], n).astype(np.float32)
-    got, want, fast = bytes_both_ways(x, (amax / np.float32(448.0)).astype(np.float32))
-    assert np.array_equal(got, want) and fast > 0.99
-    e4 = np.array([okv.E4M3_TABLE[b] for b in range(0x01, 0x7f)], dtype=np.float64)
-    mids = np.concatenate([(e4[:-1] + e4[1:]) / 2, e4])
-    for scale_range in ((-20, 20), (-80, -60), (60, 80)):
-        s = np.exp(rng.uniform(*scale_range, n)).astype(np.float32)
-        x = (rng.choice(mids, n) * s.astype(np.float64) * (1 + rng.integers(-6, 7, n) * 2.0 ** -24)).astype(np.float32)
-        got, want, _ = bytes_both_ways(x, s)
-        assert np.array_equal(got, want), scale_range
