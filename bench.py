@@ -568,6 +568,47 @@ def bench_decoder_d32(rank: int, world: int, device, new_tokens: int, profile: b
             "scaling": "weak (batch-sharded replicas)"}
 
 
+def pin_to_local_cores(local: int, world: int) -> str:
+    """With several ranks on one host, give each rank its own slice of the cores this process may use, taken from the
+    NUMA node its GPU hangs off when sysfs tells (else an even slice): the end-to-end loop is driven by the host (one
+    graph launch and one synchronisation per step), and ranks that wander over each other's cores cost it more than
+    the GPUs do. Returns what was done, for the JSON line."""
+    try:
+        allowed = sorted(os.sched_getaffinity(0))
+        if world <= 1 or len(allowed) < 2 * world:
+            return "not pinned"
+        node_cpus = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = int(visible.split(",")[local]) if visible and visible.split(",")[local].isdigit() else local
+            bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(physical)).busId
+            bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+            if len(bus.split(":")[0]) == 8:
+                bus = bus[4:]
+            node = int(Path(f"/sys/bus/pci/devices/{bus}/numa_node").read_text())
+            if node >= 0:
+                cpus = set()
+                for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+                node_cpus = [c for c in allowed if c in cpus]
+        except Exception:
+            node_cpus = None
+        per = len(allowed) // world
+        mine = allowed[local * per:(local + 1) * per]
+        how = "even slice of the allowed cores"
+        if node_cpus and len(node_cpus) >= per:
+            # ranks of one node share its cores in local-rank order
+            offset = (local * per) % max(1, len(node_cpus) - per + 1)
+            mine, how = node_cpus[offset:offset + per], "slice of the GPU's NUMA node"
+        os.sched_setaffinity(0, mine)
+        return f"{len(mine)} cores, {how}"
+    except Exception as e:  # an unusual host: run unpinned
+        return f"not pinned ({type(e).__name__})"
+
+
 def cpu_model() -> str:
     try:
         for line in Path("/proc/cpuinfo").read_text().splitlines():
@@ -660,6 +701,7 @@ def main() -> None:
     from nanochat_b200.sharding import shard_batch
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    pinned = pin_to_local_cores(local, world)
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
@@ -822,6 +864,7 @@ def main() -> None:
             "warmup": args.warmup, "ms_per_step": head["ms_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "e4m3 operands, fp32 accumulate and softmax", "data": "synthetic",
             "config": config_of(args, world, extra={"chunk_pages": head["chunk"], "timed_loops": REPEATS,
+                                                    "host_cores_per_rank": pinned,
                                                     "pct_of_8TBs_per_gpu": value / world / 80.0}),
             "clocks": head["clocks"], "e2e": head["e2e"], "gpu_launches": 2 * args.steps * REPEATS,
             "roofline": roofline_of(head, traffic), "parity": head["parity"],
