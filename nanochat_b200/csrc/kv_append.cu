@@ -99,14 +99,19 @@ __global__ void __launch_bounds__(BLOCK, 6) k_kv_append(AppendArgs a) {
             }
         }
         if (is_v && run) { /* block-uniform: every thread of the block is in the run */
+            /* a dim's 16 positions are four words; word k of dim d sits at word k ^ ((d >> 3) & 3), which spreads the
+             * eight lanes of a row (dims 8 apart, else all on one bank) over four banks */
+            const int col = g ^ ((t & 3) << 2);
 #pragma unroll
             for (int i = 0; i < VEC; i++) {
-                vt[o + i][g] = b1[i];
-                vt[HALF + o + i][g] = b2[i];
+                vt[o + i][col] = b1[i];
+                vt[HALF + o + i][col] = b2[i];
             }
             __syncthreads();
             const int d = threadIdx.x, j0 = j - g; /* the run's first in-page position; thread = dim */
-            *reinterpret_cast<uint4 *>(page + page_v_byte(j0, d)) = *reinterpret_cast<const uint4 *>(vt[d]);
+            const uint32_t *w = reinterpret_cast<const uint32_t *>(vt[d]);
+            const int sw = (d >> 3) & 3;
+            *reinterpret_cast<uint4 *>(page + page_v_byte(j0, d)) = make_uint4(w[sw], w[1 ^ sw], w[2 ^ sw], w[3 ^ sw]);
             __syncthreads(); /* the next v head row reuses the tile */
         }
     }
