@@ -90,3 +90,18 @@ def test_invalid_requests_are_refused_before_anything_runs():
         list(nd.generate([Request(input_ids=prompt(70, 4), max_new_tokens=0)]))
     with pytest.raises(ValueError):
         list(make(2).generate([Request(input_ids=prompt(71, 100), max_new_tokens=100)]))  # 99 + 100 > 192 positions
+
+
+def test_prompts_seen_before_come_from_the_prompt_store():
+    """The same prompt in several requests is prefilled once; later requests copy its pages from pinned host memory
+    into whatever slot they land in and produce the same stream (inference/decoder.py:193-232)."""
+    nd = make(2, store=512)
+    p = prompt(80, 70)
+    calls = []
+    original = nd.decoder.prefill
+    nd.decoder.prefill = lambda prompts, slots, **kw: (calls.append(len(prompts)), original(prompts, slots, **kw))
+    reqs = [Request(input_ids=p, max_new_tokens=5), Request(input_ids=prompt(81, 3), max_new_tokens=2),
+            Request(input_ids=p, max_new_tokens=5), Request(input_ids=p, max_new_tokens=5)]
+    out = dict(nd.generate(reqs))
+    assert out[0] == out[2] == out[3] and len(out[0]) >= 1
+    assert sum(calls) == 2  # the long prompt once, the short one once
