@@ -681,28 +681,30 @@ static __device__ __forceinline__ int states_of(const MergeArgs &a, long long ro
     return min(span_of(len, a.window, a.chunk_pages).n_chunks, a.max_chunks);
 }
 
-constexpr int MERGE_WARPS = 4;
+constexpr int MERGE_WARPS = 4;      /* rows with at most 16 states */
+constexpr int MERGE_WARPS_WIDE = 8; /* rows with more: every warp still gets its states in one batch of loads */
 
-/* The states of one row folded by a block of MERGE_WARPS warps: warp w folds states w, w + 4, ... into a running
- * state (its loads are independent of the fold, so they overlap), then warp 0 merges the four running states through
+/* The states of one row folded by a block of W warps: warp w folds states w, w + W, ... into a running
+ * state (its loads are independent of the fold, so they overlap), then warp 0 merges the W running states through
  * shared memory. Lane = four output dims. Returns true in warp 0, whose lanes then hold the row's un-normalised state
  * (top in log2 units, lsum, acc); the other warps are done. */
+template <int W>
 static __device__ __forceinline__ bool merge_row_states(const MergeArgs &a, long long row, float &top, float &lsum,
                                                         float4 &acc) {
-    __shared__ float sm[MERGE_WARPS], sl[MERGE_WARPS];
-    __shared__ float4 so[MERGE_WARPS][32];
+    __shared__ float sm[W], sl[W];
+    __shared__ float4 so[W][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = states_of(a, row);
     const float *st = a.parts + row * a.row_stride;
     top = -INFINITY, lsum = 0.f;
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
     constexpr int DEPTH = 4; /* states loaded before the first is folded: the loads' latencies overlap */
-    for (int p0 = warp; p0 < n; p0 += MERGE_WARPS * DEPTH) {
+    for (int p0 = warp; p0 < n; p0 += W * DEPTH) {
         float mp[DEPTH], lp[DEPTH];
         float4 o[DEPTH];
 #pragma unroll
         for (int i = 0; i < DEPTH; i++) {
-            const int p = p0 + i * MERGE_WARPS;
+            const int p = p0 + i * W;
             if (p < n) {
                 const float *s = st + p * a.part_stride;
                 mp[i] = s[0], lp[i] = s[1];
@@ -711,7 +713,7 @@ static __device__ __forceinline__ bool merge_row_states(const MergeArgs &a, long
         }
 #pragma unroll
         for (int i = 0; i < DEPTH; i++) {
-            if (p0 + i * MERGE_WARPS < n) { /* folded in index order, as a one-at-a-time loop would */
+            if (p0 + i * W < n) { /* folded in index order, as a one-at-a-time loop would */
                 const float next = fmaxf(top, mp[i]);
                 const float c0 = top == -INFINITY ? 0.f : ex2(top - next), c1 = mp[i] == -INFINITY ? 0.f : ex2(mp[i] - next);
                 lsum = lsum * c0 + lp[i] * c1;
@@ -725,11 +727,13 @@ static __device__ __forceinline__ bool merge_row_states(const MergeArgs &a, long
     so[warp][lane] = acc;
     __syncthreads();
     if (warp != 0) return false;
-    top = fmaxf(fmaxf(sm[0], sm[1]), fmaxf(sm[2], sm[3]));
+    top = sm[0];
+#pragma unroll
+    for (int w = 1; w < W; w++) top = fmaxf(top, sm[w]);
     lsum = 0.f;
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int w = 0; w < MERGE_WARPS; w++) {
+    for (int w = 0; w < W; w++) {
         const float c = sm[w] == -INFINITY ? 0.f : ex2(sm[w] - top);
         const float4 o = so[w][lane];
         lsum += c * sl[w];
@@ -750,8 +754,9 @@ static __device__ __forceinline__ void store_normalised(bf16 *out, long long row
     *reinterpret_cast<uint2 *>(out + row * HEAD_DIM + 4 * lane) = u;
 }
 
-/* One block per row. */
-__global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
+/* One block of W warps per row. */
+template <int W>
+__global__ void __launch_bounds__(W * 32) k_merge(MergeArgs a) {
     const long long row = blockIdx.x;
     const int lane = threadIdx.x & 31;
     /* launched with programmatic stream serialisation: wait here until the grid before it (the split kernel, whose
@@ -759,7 +764,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge(MergeArgs a) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     float top, lsum;
     float4 acc;
-    if (!merge_row_states(a, row, top, lsum, acc)) return;
+    if (!merge_row_states<W>(a, row, top, lsum, acc)) return;
     if (a.part_out) {
         float *o = a.part_out + row * PART;
         if (lane == 0) *reinterpret_cast<float4 *>(o) = make_float4(top, lsum, 0.f, 0.f);
@@ -805,14 +810,15 @@ static __device__ __forceinline__ uint4 load_packet_pair(const uint2 *p) {
  * the call's parity: a rank can run at most one call ahead of a peer (it needs the peer's words of call e to finish
  * call e), so what it writes never lands in a half a slower peer still reads, and a word left by call e - 2 in the
  * same half never passes for call e. */
-__global__ void __launch_bounds__(MERGE_WARPS * 32) k_merge_exchange(ExchangeArgs a) {
+template <int W>
+__global__ void __launch_bounds__(W * 32) k_merge_exchange(ExchangeArgs a) {
     const long long row = blockIdx.x, rows = a.local.rows;
     const int lane = threadIdx.x & 31;
     asm volatile("griddepcontrol.wait;" ::: "memory"); /* this rank's chunk states are complete and visible */
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(a.epoch) + 1u;
     float top, lsum;
     float4 acc;
-    if (!merge_row_states(a.local, row, top, lsum, acc)) return;
+    if (!merge_row_states<W>(a.local, row, top, lsum, acc)) return;
     const size_t half = (size_t)(epoch & 1u) * a.world * rows * PACKET_WORDS;
     const size_t mine = half + ((size_t)a.rank * rows + row) * PACKET_WORDS;
     const uint4 w01 = make_uint4(__float_as_uint(acc.x), epoch, __float_as_uint(acc.y), epoch);
@@ -995,14 +1001,17 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
     if (blocks > 0x7fffffffLL) return NCB_ERR_ARG;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)blocks);
-    config.blockDim = dim3(MERGE_WARPS * 32);
+    const bool wide = a.n_parts == 0 ? a.max_chunks > 4 * MERGE_WARPS : a.n_parts > 4 * MERGE_WARPS;
+    config.blockDim = dim3((wide ? MERGE_WARPS_WIDE : MERGE_WARPS) * 32);
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1; /* overlap its launch with the split kernel's tail */
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, k_merge, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+    const cudaError_t rc = wide ? cudaLaunchKernelEx(&config, k_merge<MERGE_WARPS_WIDE>, a)
+                                : cudaLaunchKernelEx(&config, k_merge<MERGE_WARPS>, a);
+    return rc == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 /* What the merge + exchange launch needs besides the local merge (decode_attn_fp8_sharded). */
@@ -1019,14 +1028,17 @@ static int launch_exchange(const MergeArgs &m, const ExchangeIn &x, void *status
     a.world = x.world, a.rank = x.rank, a.epoch = (uint32_t *)x.epoch, a.status = (int *)status;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)m.rows);
-    config.blockDim = dim3(MERGE_WARPS * 32);
+    const bool wide = m.n_parts == 0 ? m.max_chunks > 4 * MERGE_WARPS : m.n_parts > 4 * MERGE_WARPS;
+    config.blockDim = dim3((wide ? MERGE_WARPS_WIDE : MERGE_WARPS) * 32);
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, k_merge_exchange, a) == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
+    const cudaError_t rc = wide ? cudaLaunchKernelEx(&config, k_merge_exchange<MERGE_WARPS_WIDE>, a)
+                                : cudaLaunchKernelEx(&config, k_merge_exchange<MERGE_WARPS>, a);
+    return rc == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
 static int attend(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
