@@ -157,9 +157,10 @@ def decode_step_attention(qkv: Tensor, q_gain: Tensor, k_gain: Tensor, cos: Tens
     return out
 
 
-def prefill_groups(slots: list[int], positions: list[int], limit: int) -> list[int]:
+def prefill_groups(slots, positions, limit: int) -> list[int]:
     """Group consecutive rows of a prefill pass for prefill_attention: a group is a run of rows of one slot with
-    positions ascending by one, at most `limit` long. Returns group_start with the end sentinel."""
+    positions ascending by one, at most `limit` long. slots, positions: sequences or numpy arrays. Returns
+    group_start with the end sentinel."""
     import numpy as np
 
     n = len(slots)
@@ -183,17 +184,21 @@ class PrefillPlan:
     row groups (longest first, so the blocks with the most pages start first), the rows' slots and lengths on the
     device."""
 
-    def __init__(self, slots: list[int], positions: list[int], Hq: int, cache: Fp8KVCache, device):
+    def __init__(self, slots, positions, Hq: int, cache: Fp8KVCache, device):
+        import numpy as np
+
+        slots, positions = np.asarray(slots, dtype=np.int32), np.asarray(positions, dtype=np.int32)
         self.rows_per_block = prefill_rows_per_block(Hq, cache.kv_heads)
-        starts = prefill_groups(slots, positions, self.rows_per_block)
+        starts = np.asarray(prefill_groups(slots, positions, self.rows_per_block), dtype=np.int32)
         self.rows, self.n_groups = len(slots), len(starts) - 1
         # blocks start in list order: the groups that reach furthest into their prompts (most pages) go first, so
         # the short ones fill the gaps at the end
-        order = sorted(range(self.n_groups), key=lambda z: (-positions[starts[z + 1] - 1], z))
-        self.group_first = torch.tensor([starts[z] for z in order], dtype=torch.int32, device=device)
-        self.group_rows = torch.tensor([starts[z + 1] - starts[z] for z in order], dtype=torch.int32, device=device)
-        self.slot_map = torch.tensor(slots, dtype=torch.int32, device=device)
-        self.lens = torch.tensor(positions, dtype=torch.int32, device=device) + 1
+        reach = positions[starts[1:] - 1] if self.n_groups else positions[:0]
+        order = np.argsort(-reach.astype(np.int64), kind="stable")
+        self.group_first = torch.from_numpy(starts[:-1][order].copy()).to(device)
+        self.group_rows = torch.from_numpy((starts[1:] - starts[:-1])[order].copy()).to(device)
+        self.slot_map = torch.from_numpy(slots).to(device)
+        self.lens = torch.from_numpy(positions + 1).to(device)
 
 
 def prefill_attention(q: Tensor, cache: Fp8KVCache, plan: PrefillPlan, softmax_scale: float | None = None,

@@ -155,7 +155,7 @@ class Decoder:
 
     def hidden_rows(self, tokens: Tensor, pos: Tensor, slot_map: Tensor, max_kv_len: int,
                     attend_last_layer: bool = True, distinct_slots: bool = False,
-                    host_rows: tuple[list[int], list[int]] | None = None) -> Tensor:
+                    host_rows: "tuple | None" = None) -> Tensor:
         """Final-normed hidden states (rows, C) bf16 of `tokens` at positions `pos` of slots `slot_map`; appends
         every row's k, v to the caches. max_kv_len bounds pos + 1. Any number of rows: GEMMs on the tiled tcgen05 kernel, everything
         between them on this package's kernels (embedding + norm, residual add + norm, relu^2, append, attention).
@@ -369,14 +369,23 @@ class Decoder:
         """Cache positions 0 .. len - 2 of every prompt (its last token is the first decode input). Sequences are
         processed in passes of at most rows_per_pass rows; a pass holds whole position ranges in order, so every row
         finds the earlier positions of its sequence either in the cache or earlier in its own pass."""
-        todo = [(slot, t, tok) for slot, p in zip(slots, prompts) for t, tok in enumerate(p[:-1])]
-        for at in range(0, len(todo), rows_per_pass):
-            part = todo[at:at + rows_per_pass]
-            slot_map = torch.tensor([s for s, _, _ in part], dtype=torch.int32, device=self.device)
-            pos = torch.tensor([t for _, t, _ in part], dtype=torch.int32, device=self.device)
-            tokens = torch.tensor([k for _, _, k in part], dtype=torch.long, device=self.device)
-            self.hidden_rows(tokens, pos, slot_map, max(t for _, t, _ in part) + 1, attend_last_layer=False,
-                             host_rows=([s for s, _, _ in part], [t for _, t, _ in part]))
+        import numpy as np
+
+        counts = [len(p) - 1 for p in prompts]
+        total = sum(counts)
+        if total == 0:
+            return
+        # the rows of all passes as arrays (a prompt of thousands of tokens must not cost a Python loop per row)
+        slot_rows = np.repeat(np.asarray(slots, dtype=np.int32), counts)
+        pos_rows = np.concatenate([np.arange(n, dtype=np.int32) for n in counts])
+        token_rows = np.concatenate([np.asarray(p[:-1], dtype=np.int64) for p in prompts])
+        for at in range(0, total, rows_per_pass):
+            part = slice(at, min(at + rows_per_pass, total))
+            slot_map = torch.from_numpy(slot_rows[part]).to(self.device, non_blocking=True)
+            pos = torch.from_numpy(pos_rows[part]).to(self.device, non_blocking=True)
+            tokens = torch.from_numpy(token_rows[part]).to(self.device, non_blocking=True)
+            self.hidden_rows(tokens, pos, slot_map, int(pos_rows[part].max()) + 1, attend_last_layer=False,
+                             host_rows=(slot_rows[part], pos_rows[part]))
 
     # ---- decode -----------------------------------------------------------------------------------------------
 
