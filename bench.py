@@ -432,7 +432,7 @@ def bench_kernels(device, timed, profile_range: str) -> dict:
                     "algorithmic_bytes_per_launch": nbytes, "achieved": nbytes / ms / 1e6, "unit": UNIT,
                     "frac": nbytes / ms / 1e6 / peak, "note": "a launch-latency-sized kernel: 4.8 MB per launch"}
     inbox = torch.zeros(2 * B * HQ * 1056 // 4, dtype=torch.int32, device=device)
-    epoch = torch.zeros(2 + B * HKV, dtype=torch.int32, device=device)
+    epoch = torch.zeros(2, dtype=torch.int32, device=device)
     import ctypes
     p_inbox = (ctypes.c_void_p * 1)(inbox.data_ptr())
     lib = cuda_library("decode_attn")

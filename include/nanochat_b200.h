@@ -239,21 +239,18 @@ int decode_attn_merge(const void *parts, int n_parts, long long rows, void *out,
 
 /*
  * decode_attn_fp8 for sequences whose positions are sharded by length over the GPUs of one box (each rank's cache
- * holds a contiguous slice of every sequence; lens are the LOCAL lengths): the split-KV kernel whose last block per
- * (sequence, kv head) merges this rank's chunk states for the head group, exchanges the (m, l, o) state of every row
- * with the other ranks over peer memory (NVLink) and merges across ranks — one launch; with more (sequence, kv head)
- * pairs than SMs the merge + exchange is a second launch (a block waiting for peers holds a block slot, and the pairs
- * must not be able to hold them all). Every rank ends with the full out bf16 [B][Hq][128], bit-identical on all
+ * holds a contiguous slice of every sequence; lens are the LOCAL lengths): the split-KV launch, then ONE launch that
+ * merges this rank's chunk states, exchanges the (m, l, o) state of every row with the other ranks over peer memory
+ * (NVLink) and merges across ranks, so that every rank ends with the full out bf16 [B][Hq][128], bit-identical on all
  * ranks (states are merged in rank order). No collective library on the data path. The merge rule of
  * decode.cu:548,661-670 is associative, which is what makes the sharding exact. No counterpart in the reference,
  * which runs on one GPU.
  *   inbox   host array of `world` (<= 8) device pointers, the same on every rank: inbox[r] is rank r's buffer of
  *           2 * world * B * Hq * NCB_PEER_STATE_BYTES bytes, addressable from every GPU (peer-mapped / symmetric
  *           memory), 16-byte aligned, zeroed once before the first call (and the ranks synchronised)
- *   epoch   this rank's own 2 + B * Hkv device uint32 words, zeroed once: the call number (the kernel advances it by
- *           one per call, so the launch arguments never change and a step can be captured in a CUDA graph and
- *           replayed), a count of finished rows, and one ticket per (sequence, kv head)
- * Per row, the rank state goes into every other rank's inbox (plain peer stores) as 8-byte words
+ *   epoch   this rank's own two device uint32 words, zeroed once; the kernel advances the first by one per call, so
+ *           the launch arguments never change and a step can be captured in a CUDA graph and replayed
+ * Per row the second launch stores the rank state into every other rank's inbox (plain peer stores) as 8-byte words
  * (fp32 value, call number) that validate themselves: no flags and no fences, an arrived word whose second half is
  * the current call number holds this call's value. It then polls — bounded, about half a second — its own inbox until
  * every word of the other ranks' states of the row carries the call number, and merges the `world` states. Every rank

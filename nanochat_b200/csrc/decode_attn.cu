@@ -53,22 +53,6 @@ constexpr size_t ATTN_SMEM = (size_t)WARPS * PAGE_BYTES;
 static_assert(WARPS * 4 * 2 * PART * sizeof(float) <= ATTN_SMEM, "the merge area reuses the ring");
 static_assert(THREADS >= HEAD_DIM && 12 % WARPS == 0, "the final merge maps one thread to one output dim");
 
-constexpr int MAX_PEERS = 8;
-constexpr uint32_t PEER_WAIT_POLLS = 1u << 22; /* x ~100 ns each: roughly half a second */
-constexpr int PACKET_WORDS = NCB_PEER_STATE_BYTES / 8; /* one state as 8-byte (fp32 value, call number) words */
-static_assert(PACKET_WORDS >= HEAD_DIM + 2, "o[128], then m and l");
-
-/* Every rank owns an "inbox" [2][world][rows][PACKET_WORDS] of 8-byte words that all peers can address, and a private
- * device word pair `epoch` = (calls completed, rows finished in the current call). */
-struct Exchange {
-    uint2 *inbox[MAX_PEERS]; /* rank q's inbox */
-    int world, rank;
-    uint32_t *epoch;
-    int *status;
-    bf16 *out;      /* [rows][128] */
-    long long rows;
-};
-
 struct AttnArgs {
     const bf16 *q;
     const uint8_t *cache;
@@ -85,10 +69,6 @@ struct AttnArgs {
     long long qkv_row_stride;
     int table_len;
     ValueEmbed ve; /* APPEND only; table == NULL: the layer has no value embedding */
-    /* XCHG only (positions sharded by length over GPUs): the block that finishes last for a (row, kv head) merges that
-     * head group's chunk states and exchanges them with the other ranks itself; tickets[B][Hkv] count finished blocks */
-    Exchange xchg;
-    uint32_t *tickets;
 };
 
 /* ---- PTX wrappers ------------------------------------------------------------------------------------------- */
@@ -339,114 +319,11 @@ static __device__ __forceinline__ void query_fragments(const float *q_stage, con
 
 }
 
-/* ---- exchange of row states over peer memory ------------------------------------------------------------------ */
-
-/* 16 bytes = two (value, call number) words, read in one piece. Volatile: each poll goes to memory. */
-static __device__ __forceinline__ uint4 load_packet_pair(const uint2 *p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
-
-/* out[row][4 lane .. 4 lane + 3] = acc / lsum as bf16 (the reference's __fdiv_rn then round, decode.cu:674); a row
- * without any position gives zeros. */
-static __device__ __forceinline__ void store_normalised(bf16 *out, long long row, int lane, float lsum, const float4 &acc) {
-    const bool any = lsum > 0.f;
-    const float x = any ? __fdiv_rn(acc.x, lsum) : 0.f, y = any ? __fdiv_rn(acc.y, lsum) : 0.f;
-    const float z = any ? __fdiv_rn(acc.z, lsum) : 0.f, w = any ? __fdiv_rn(acc.w, lsum) : 0.f;
-    uint2 u;
-    *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(x, y);
-    *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(z, w);
-    *reinterpret_cast<uint2 *>(out + row * HEAD_DIM + 4 * lane) = u;
-}
-
-/* One warp, one row: PUSH the rank's state (top, lsum, acc; lane = four output dims) into every other rank's inbox with
- * plain stores over NVLink (one direction, no read round trip), then read the other ranks' states of the same row from
- * this rank's own inbox and merge in rank order, so every rank computes bit-identical outputs. A state travels as
- * self-validating 8-byte words (fp32 value, call number), the scheme of low-latency collectives: an 8-byte store lands
- * whole, so a word whose second half equals the current call number holds this call's value; no flags, no fences,
- * nothing ordered after the data. The receiver polls its own memory (bounded) until every word of a state carries the
- * call number. The warp waits only for the same row's warps on the other GPUs, never for work of its own grid.
- * The call number comes from a device word that the last row to finish advances, so launch arguments never change and
- * the step can be captured in a CUDA graph. Inboxes alternate between two halves by the call's parity: a rank can run
- * at most one call ahead of a peer (it needs the peer's words of call e to finish call e), so what it writes never
- * lands in a half a slower peer still reads, and a word left by call e - 2 in the same half never passes for call e. */
-static __device__ __forceinline__ void exchange_row(const Exchange &x, long long row, float top, float lsum, float4 acc,
-                                                    int lane) {
-    const long long rows = x.rows;
-    const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(x.epoch) + 1u;
-    const size_t half = (size_t)(epoch & 1u) * x.world * rows * PACKET_WORDS;
-    const size_t mine = half + ((size_t)x.rank * rows + row) * PACKET_WORDS;
-    const uint4 w01 = make_uint4(__float_as_uint(acc.x), epoch, __float_as_uint(acc.y), epoch);
-    const uint4 w23 = make_uint4(__float_as_uint(acc.z), epoch, __float_as_uint(acc.w), epoch);
-    const uint4 wml = make_uint4(__float_as_uint(top), epoch, __float_as_uint(lsum), epoch);
-#pragma unroll
-    for (int q = 0; q < MAX_PEERS; q++) {
-        if (q < x.world && q != x.rank) {
-            uint2 *o = x.inbox[q] + mine;
-            *reinterpret_cast<uint4 *>(o + 4 * lane) = w01;
-            *reinterpret_cast<uint4 *>(o + 4 * lane + 2) = w23;
-            if (lane == 0) *reinterpret_cast<uint4 *>(o + HEAD_DIM) = wml;
-        }
-    }
-    /* the other ranks' states of this row, from this rank's own inbox */
-    float mq[MAX_PEERS], lq[MAX_PEERS];
-    float4 oq[MAX_PEERS];
-    bool ok = true;
-#pragma unroll
-    for (int q = 0; q < MAX_PEERS; q++) {
-        if (q >= x.world) continue;
-        if (q == x.rank) {
-            mq[q] = top, lq[q] = lsum, oq[q] = acc;
-            continue;
-        }
-        const uint2 *in = x.inbox[x.rank] + half + ((size_t)q * rows + row) * PACKET_WORDS;
-        uint4 r01 = make_uint4(0u, 0u, 0u, 0u), r23 = r01, rml = r01;
-        bool got = false;
-        for (uint32_t polls = 0; polls < PEER_WAIT_POLLS && ok; polls++) {
-            r01 = load_packet_pair(in + 4 * lane);
-            r23 = load_packet_pair(in + 4 * lane + 2);
-            rml = load_packet_pair(in + HEAD_DIM);
-            got = r01.y == epoch && r01.w == epoch && r23.y == epoch && r23.w == epoch && rml.y == epoch && rml.w == epoch;
-            if (__all_sync(0xffffffffu, got)) break;
-            got = false;
-            __nanosleep(64);
-        }
-        if (!__all_sync(0xffffffffu, got)) ok = false; /* the remaining ranks are not waited for either */
-        mq[q] = __uint_as_float(rml.x), lq[q] = __uint_as_float(rml.z);
-        oq[q] = make_float4(__uint_as_float(r01.x), __uint_as_float(r01.z), __uint_as_float(r23.x), __uint_as_float(r23.z));
-    }
-    if (!ok && lane == 0) flag(x.status, NCB_DEV_WAIT_TIMEOUT);
-    top = -INFINITY;
-#pragma unroll
-    for (int q = 0; q < MAX_PEERS; q++)
-        if (q < x.world) top = fmaxf(top, mq[q]);
-    lsum = 0.f;
-    acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int q = 0; q < MAX_PEERS; q++) {
-        if (q < x.world) {
-            const float c = mq[q] == -INFINITY ? 0.f : ex2(mq[q] - top);
-            lsum += c * lq[q];
-            acc.x += c * oq[q].x, acc.y += c * oq[q].y, acc.z += c * oq[q].z, acc.w += c * oq[q].w;
-        }
-    }
-    if (ok) store_normalised(x.out, row, lane, lsum, acc);
-    if (lane == 0) { /* the last row to finish closes the call */
-        __threadfence();
-        if (atomicAdd(x.epoch + 1, 1u) == (uint32_t)rows - 1u) {
-            x.epoch[1] = 0u;
-            __threadfence();
-            *reinterpret_cast<volatile uint32_t *>(x.epoch) = epoch;
-        }
-    }
-}
-
 /* APPEND: the block first does kv_append_fp8's work for its own heads of the new token (the q rows of its group
  * into shared memory; if its chunk holds the new position, the k and v rows into the cache in global memory and
  * into the landed page in shared memory), so a decode step needs no separate append launch and no round trip of q
  * through global memory. Meant for one new token per sequence; rows that share a slot need the separate kernels. */
-template <int NT, bool APPEND, bool XCHG = false>
+template <int NT, bool APPEND>
 __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];       /* WARPS stages of one page; later the merge area */
     __shared__ __align__(8) uint64_t bars[WARPS];          /* one "page landed" barrier per warp */
@@ -466,25 +343,14 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     if (!a.early) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = (int)blockIdx.z, S = G; /* the block's row; its query slots: the heads of the kv group */
     const int given = a.lens[b];
-    /* XCHG: a row this rank has nothing for (idle, refused, no positions in its slice) still owes the other ranks an
-     * empty state; the row's first block sends it */
-    auto nothing = [&]() {
-        if (XCHG && chunk == 0) {
-            if (a.early) asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (int h = warp; h < G; h += WARPS)
-                exchange_row(a.xchg, (long long)b * a.Hq + (long long)kvh * G + h, -INFINITY, 0.f,
-                             make_float4(0.f, 0.f, 0.f, 0.f), lane);
-        }
-    };
-    if (given < 0) return nothing(); /* an idle row: nothing appended, nothing attended, nothing flagged; a zero row */
+    if (given < 0) return; /* an idle row: nothing appended, nothing attended, nothing flagged; the merge writes zeros */
     const int len = given + a.len_add;
     const int slot = a.slot_map ? a.slot_map[b] : b;
     if (row_rejected(len, slot, a.pages_per_slot, a.n_slots, APPEND ? a.table_len : 0)) {
         if (tid == 0 && chunk == 0 && kvh == 0) flag(a.status, APPEND ? NCB_DEV_BAD_POSITION : NCB_DEV_BAD_LENGTH);
-        return nothing(); /* the merge kernel makes the same test and writes zeros */
+        return; /* the merge kernel makes the same test and writes zeros */
     }
     const Span sp = span_of(len, a.window, a.chunk_pages);
-    if (sp.n_chunks == 0) return nothing();
     if (chunk >= sp.n_chunks) return;
     const int pg0 = sp.first_page + chunk * sp.chunk;
     const int n = min(sp.chunk, sp.last_page - pg0);
@@ -646,49 +512,6 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
             if (tid == 0) out[0] = top, out[1] = lsum;
             out[4 + tid] = o;
         }
-    }
-    if (!XCHG) return;
-    /* The block that finishes last for this (row, kv head) merges the head group's chunk states and exchanges them:
-     * no second launch, and rows that finish early exchange while other rows are still streaming. */
-    __shared__ int last;
-    __threadfence(); /* this block's states before its ticket */
-    __syncthreads();
-    if (tid == 0) {
-        uint32_t *ticket = a.tickets + (size_t)b * a.Hkv + kvh;
-        last = atomicAdd(ticket, 1u) == (uint32_t)sp.n_chunks - 1u;
-        if (last) *ticket = 0u; /* ready for the next call */
-        __threadfence();
-    }
-    __syncthreads();
-    if (!last) return;
-    for (int h = warp; h < G; h += WARPS) { /* a warp per head; lane = four output dims */
-        const long long row = (long long)b * a.Hq + (long long)kvh * G + h;
-        const float *st = a.parts + row * a.max_chunks * PART;
-        float top = -INFINITY, lsum = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        constexpr int DEPTH = 8; /* states loaded before the first is folded */
-        for (int p0 = 0; p0 < sp.n_chunks; p0 += DEPTH) {
-            float mp[DEPTH], lp[DEPTH];
-            float4 o[DEPTH];
-#pragma unroll
-            for (int i = 0; i < DEPTH; i++)
-                if (p0 + i < sp.n_chunks) { /* written by other blocks a moment ago: read past L1 */
-                    const float *s_ = st + (size_t)(p0 + i) * PART;
-                    mp[i] = __ldcg(s_), lp[i] = __ldcg(s_ + 1);
-                    o[i] = __ldcg(reinterpret_cast<const float4 *>(s_ + 4) + lane);
-                }
-#pragma unroll
-            for (int i = 0; i < DEPTH; i++)
-                if (p0 + i < sp.n_chunks) {
-                    const float next = fmaxf(top, mp[i]);
-                    const float c0 = top == -INFINITY ? 0.f : ex2(top - next), c1 = mp[i] == -INFINITY ? 0.f : ex2(mp[i] - next);
-                    lsum = lsum * c0 + lp[i] * c1;
-                    acc.x = acc.x * c0 + o[i].x * c1, acc.y = acc.y * c0 + o[i].y * c1;
-                    acc.z = acc.z * c0 + o[i].z * c1, acc.w = acc.w * c0 + o[i].w * c1;
-                    top = next;
-                }
-        }
-        exchange_row(a.xchg, row, top, lsum, acc, lane);
     }
 }
 
@@ -919,6 +742,18 @@ static __device__ __forceinline__ bool merge_row_states(const MergeArgs &a, long
     return true;
 }
 
+/* out[row][4 lane .. 4 lane + 3] = acc / lsum as bf16 (the reference's __fdiv_rn then round, decode.cu:674); a row
+ * without any position gives zeros. */
+static __device__ __forceinline__ void store_normalised(bf16 *out, long long row, int lane, float lsum, const float4 &acc) {
+    const bool any = lsum > 0.f;
+    const float x = any ? __fdiv_rn(acc.x, lsum) : 0.f, y = any ? __fdiv_rn(acc.y, lsum) : 0.f;
+    const float z = any ? __fdiv_rn(acc.z, lsum) : 0.f, w = any ? __fdiv_rn(acc.w, lsum) : 0.f;
+    uint2 u;
+    *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(x, y);
+    *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(z, w);
+    *reinterpret_cast<uint2 *>(out + row * HEAD_DIM + 4 * lane) = u;
+}
+
 /* One block of W warps per row. */
 template <int W>
 __global__ void __launch_bounds__(W * 32) k_merge(MergeArgs a) {
@@ -938,22 +773,117 @@ __global__ void __launch_bounds__(W * 32) k_merge(MergeArgs a) {
     if (a.out) store_normalised(a.out, row, lane, lsum, acc);
 }
 
-/* ---- merge + exchange in one launch ------------------------------------------------------------------------------ */
+/* ---- merge + exchange over peer memory ------------------------------------------------------------------------ */
 
+constexpr int MAX_PEERS = 8;
+constexpr uint32_t PEER_WAIT_POLLS = 1u << 22; /* x ~100 ns each: roughly half a second */
+constexpr int PACKET_WORDS = NCB_PEER_STATE_BYTES / 8; /* one state as 8-byte (fp32 value, call number) words */
+static_assert(PACKET_WORDS >= HEAD_DIM + 2, "o[128], then m and l");
+
+/* Every rank owns an "inbox" [2][world][rows][PACKET_WORDS] of 8-byte words that all peers can address, and a private
+ * device word pair `epoch` = (calls completed, blocks arrived in the current call). */
 struct ExchangeArgs {
-    MergeArgs local; /* this rank's chunk states (the split kernel's workspace) */
-    Exchange x;
+    MergeArgs local;         /* this rank's chunk states (the split kernel's workspace) */
+    uint2 *inbox[MAX_PEERS]; /* rank q's inbox */
+    int world, rank;
+    uint32_t *epoch;
+    int *status;
 };
 
-/* The chunk merge of k_merge and the cross-GPU exchange (exchange_row) in one launch, one block per row. */
+/* 16 bytes = two (value, call number) words, read in one piece. Volatile: each poll goes to memory. */
+static __device__ __forceinline__ uint4 load_packet_pair(const uint2 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+/* The chunk merge of k_merge and the cross-GPU exchange in one launch, one block per row: merge the row's local chunk
+ * states, PUSH the rank state into every other rank's inbox with plain stores over NVLink (one direction, no read
+ * round trip), then read the other ranks' states of the same row from this rank's own inbox and merge in rank order,
+ * so every rank computes bit-identical outputs. A state travels as self-validating 8-byte words (fp32 value, call
+ * number), the scheme of low-latency collectives: an 8-byte store lands whole, so a word whose second half equals the
+ * current call number holds this call's value; no flags, no fences, nothing ordered after the data. The receiver
+ * polls its own memory (bounded) until every word of a state carries the call number. Rows are independent: a block
+ * waits only for the same row's blocks on the other GPUs, never for blocks of its own grid.
+ * The call number comes from a device word the kernel itself advances (the last block to finish bumps it), so the
+ * launch arguments never change and the step can be captured in a CUDA graph. Inboxes alternate between two halves by
+ * the call's parity: a rank can run at most one call ahead of a peer (it needs the peer's words of call e to finish
+ * call e), so what it writes never lands in a half a slower peer still reads, and a word left by call e - 2 in the
+ * same half never passes for call e. */
 template <int W>
 __global__ void __launch_bounds__(W * 32) k_merge_exchange(ExchangeArgs a) {
-    const long long row = blockIdx.x;
+    const long long row = blockIdx.x, rows = a.local.rows;
+    const int lane = threadIdx.x & 31;
     asm volatile("griddepcontrol.wait;" ::: "memory"); /* this rank's chunk states are complete and visible */
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(a.epoch) + 1u;
     float top, lsum;
     float4 acc;
     if (!merge_row_states<W>(a.local, row, top, lsum, acc)) return;
-    exchange_row(a.x, row, top, lsum, acc, threadIdx.x & 31);
+    const size_t half = (size_t)(epoch & 1u) * a.world * rows * PACKET_WORDS;
+    const size_t mine = half + ((size_t)a.rank * rows + row) * PACKET_WORDS;
+    const uint4 w01 = make_uint4(__float_as_uint(acc.x), epoch, __float_as_uint(acc.y), epoch);
+    const uint4 w23 = make_uint4(__float_as_uint(acc.z), epoch, __float_as_uint(acc.w), epoch);
+    const uint4 wml = make_uint4(__float_as_uint(top), epoch, __float_as_uint(lsum), epoch);
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; q++) {
+        if (q < a.world && q != a.rank) {
+            uint2 *o = a.inbox[q] + mine;
+            *reinterpret_cast<uint4 *>(o + 4 * lane) = w01;
+            *reinterpret_cast<uint4 *>(o + 4 * lane + 2) = w23;
+            if (lane == 0) *reinterpret_cast<uint4 *>(o + HEAD_DIM) = wml;
+        }
+    }
+    /* the other ranks' states of this row, from this rank's own inbox */
+    float mq[MAX_PEERS], lq[MAX_PEERS];
+    float4 oq[MAX_PEERS];
+    bool ok = true;
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; q++) {
+        if (q >= a.world) continue;
+        if (q == a.rank) {
+            mq[q] = top, lq[q] = lsum, oq[q] = acc;
+            continue;
+        }
+        const uint2 *in = a.inbox[a.rank] + half + ((size_t)q * rows + row) * PACKET_WORDS;
+        uint4 r01 = make_uint4(0u, 0u, 0u, 0u), r23 = r01, rml = r01;
+        bool got = false;
+        for (uint32_t polls = 0; polls < PEER_WAIT_POLLS && ok; polls++) {
+            r01 = load_packet_pair(in + 4 * lane);
+            r23 = load_packet_pair(in + 4 * lane + 2);
+            rml = load_packet_pair(in + HEAD_DIM);
+            got = r01.y == epoch && r01.w == epoch && r23.y == epoch && r23.w == epoch && rml.y == epoch && rml.w == epoch;
+            if (__all_sync(0xffffffffu, got)) break;
+            got = false;
+            __nanosleep(64);
+        }
+        if (!__all_sync(0xffffffffu, got)) ok = false; /* the remaining ranks are not waited for either */
+        mq[q] = __uint_as_float(rml.x), lq[q] = __uint_as_float(rml.z);
+        oq[q] = make_float4(__uint_as_float(r01.x), __uint_as_float(r01.z), __uint_as_float(r23.x), __uint_as_float(r23.z));
+    }
+    if (!ok && lane == 0) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+    top = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; q++)
+        if (q < a.world) top = fmaxf(top, mq[q]);
+    lsum = 0.f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; q++) {
+        if (q < a.world) {
+            const float c = mq[q] == -INFINITY ? 0.f : ex2(mq[q] - top);
+            lsum += c * lq[q];
+            acc.x += c * oq[q].x, acc.y += c * oq[q].y, acc.z += c * oq[q].z, acc.w += c * oq[q].w;
+        }
+    }
+    if (ok) store_normalised(a.local.out, row, lane, lsum, acc);
+    if (lane == 0) { /* the last row to finish closes the call */
+        __threadfence();
+        if (atomicAdd(a.epoch + 1, 1u) == (uint32_t)rows - 1u) {
+            a.epoch[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(a.epoch) = epoch;
+        }
+    }
 }
 
 /* ---- host side ---------------------------------------------------------------------------------------------- */
@@ -984,29 +914,14 @@ struct AppendIn {
     ValueEmbed ve;
 };
 
-/* What the merge + exchange launch needs besides the local merge (decode_attn_fp8_sharded). */
-struct ExchangeIn {
-    void *const *inbox;
-    int world, rank;
-    void *epoch;
-};
-
-static Exchange exchange_of(const ExchangeIn &x, void *out, long long rows, void *status) {
-    Exchange e = {};
-    for (int q = 0; q < x.world; q++) e.inbox[q] = (uint2 *)x.inbox[q];
-    e.world = x.world, e.rank = x.rank, e.epoch = (uint32_t *)x.epoch, e.status = (int *)status;
-    e.out = (bf16 *)out, e.rows = rows;
-    return e;
-}
-
-template <int NT, bool APPEND, bool XCHG = false> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
+template <int NT, bool APPEND> static cudaError_t prepare() { /* opt in to the large dynamic shared memory, once per device */
     static bool done[MAX_DEVICES] = {};
     int device = 0;
     cudaError_t rc = cudaGetDevice(&device);
     if (rc != cudaSuccess) return rc;
     std::lock_guard<std::mutex> guard(g_device_lock);
     if (device >= 0 && device < MAX_DEVICES && done[device]) return cudaSuccess;
-    rc = cudaFuncSetAttribute(k_decode_attn<NT, APPEND, XCHG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    rc = cudaFuncSetAttribute(k_decode_attn<NT, APPEND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               (int)ATTN_SMEM);
     if (rc == cudaSuccess && device >= 0 && device < MAX_DEVICES) done[device] = true;
     return rc;
@@ -1015,8 +930,7 @@ template <int NT, bool APPEND, bool XCHG = false> static cudaError_t prepare() {
 static int launch_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
                         long long workspace_bytes, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,
                         int max_kv_len, int window, int &chunk_pages, float softmax_scale, void *status,
-                        cudaStream_t stream, const AppendIn *app = nullptr, bool early = false,
-                        const ExchangeIn *fused = nullptr, void *out = nullptr) {
+                        cudaStream_t stream, const AppendIn *app = nullptr, bool early = false) {
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || n_slots <= 0 || pages_per_slot <= 0 || max_kv_len < 0 ||
         window < 0 || chunk_pages < 0 || !(softmax_scale > 0.f))
         return NCB_ERR_ARG;
@@ -1065,17 +979,7 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
     config.attrs = attribute;
     config.numAttrs = 1;
     cudaError_t rc;
-    if (fused) { /* the last block of every (row, kv head) merges and exchanges: no second launch */
-        a.xchg = exchange_of(*fused, out, (long long)B * Hq, status);
-        a.tickets = (uint32_t *)fused->epoch + 2;
-        if (Hq / Hkv <= 4) {
-            if (prepare<1, false, true>() != cudaSuccess) return NCB_ERR_LAUNCH;
-            rc = cudaLaunchKernelEx(&config, k_decode_attn<1, false, true>, a);
-        } else {
-            if (prepare<2, false, true>() != cudaSuccess) return NCB_ERR_LAUNCH;
-            rc = cudaLaunchKernelEx(&config, k_decode_attn<2, false, true>, a);
-        }
-    } else if (Hq / Hkv <= 4 && !app) {
+    if (Hq / Hkv <= 4 && !app) {
         if (prepare<1, false>() != cudaSuccess) return NCB_ERR_LAUNCH;
         rc = cudaLaunchKernelEx(&config, k_decode_attn<1, false>, a);
     } else if (!app) {
@@ -1110,10 +1014,18 @@ static int launch_merge(const MergeArgs &a, cudaStream_t stream) {
     return rc == cudaSuccess ? NCB_OK : NCB_ERR_LAUNCH;
 }
 
+/* What the merge + exchange launch needs besides the local merge (decode_attn_fp8_sharded). */
+struct ExchangeIn {
+    void *const *inbox;
+    int world, rank;
+    void *epoch;
+};
+
 static int launch_exchange(const MergeArgs &m, const ExchangeIn &x, void *status, cudaStream_t stream) {
     ExchangeArgs a = {};
     a.local = m;
-    a.x = exchange_of(x, m.out, m.rows, status);
+    for (int q = 0; q < x.world; q++) a.inbox[q] = (uint2 *)x.inbox[q];
+    a.world = x.world, a.rank = x.rank, a.epoch = (uint32_t *)x.epoch, a.status = (int *)status;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)m.rows);
     const bool wide = m.n_parts == 0 ? m.max_chunks > 4 * MERGE_WARPS : m.n_parts > 4 * MERGE_WARPS;
@@ -1135,14 +1047,10 @@ static int attend(const void *q, const void *kv_cache, const void *lens, const v
                   void *stream, const AppendIn *app = nullptr, const ExchangeIn *exchange = nullptr) {
     if (!out && !part_out) return NCB_ERR_ARG;
     if (((uintptr_t)out | (uintptr_t)part_out) % 16 != 0) return NCB_ERR_ALIGN;
-    /* Sharded by length: when the (row, kv head) pairs are few against the GPU's block slots, the split kernel's last
-     * block per pair merges and exchanges itself (a block that waits for peers holds a slot, so the pairs must never
-     * be able to hold them all); else a second launch does it. */
-    const bool in_kernel = exchange && (long long)B * Hkv <= sm_count();
     const int rc = launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots,
                                 pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status,
-                                (cudaStream_t)stream, app, exchange != nullptr, in_kernel ? exchange : nullptr, out);
-    if (rc != NCB_OK || B == 0 || in_kernel) return rc;
+                                (cudaStream_t)stream, app, exchange != nullptr);
+    if (rc != NCB_OK || B == 0) return rc;
     if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
     const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
     MergeArgs m = {(const float *)workspace, (long long)B * Hq, PART, (long long)max_chunks * PART, 0,

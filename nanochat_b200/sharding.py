@@ -103,8 +103,7 @@ class PeerStates:
         self.buffer.zero_()  # call numbers start at 1: a zeroed word never passes for an arrived one
         self.handle = symm_mem.rendezvous(self.buffer, group)
         self.world, self.rank = self.handle.world_size, self.handle.rank
-        # (calls completed, rows finished), then one ticket per (sequence, kv head): batch * heads words are enough
-        self.epoch = torch.zeros(2 + self.rows, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)  # (calls completed, rows arrived)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's inbox is zero before anyone sends
