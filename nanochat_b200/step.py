@@ -33,11 +33,16 @@ class DecodeStep:
         self.max_kv_len = min(max_kv_len or cache.capacity, cache.capacity)
         self.chunk_pages = chunk_pages or ops.chunk_pages_for(batch, Hkv, self.max_kv_len)
         width = (Hq + 2 * Hkv) * HEAD_DIM
-        self.qkv_host = torch.zeros((batch, width), dtype=torch.bfloat16).pin_memory()
-        self.pos_host = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        # qkv rows and positions share ONE pinned buffer and one device buffer, so a step's inputs cross PCIe in a
+        # single copy (a second copy node costs about as much as the 0.8 MB themselves)
+        qkv_bytes = batch * width * 2
+        self.in_host = torch.zeros(qkv_bytes + batch * 4, dtype=torch.uint8).pin_memory()
+        self.in_dev = torch.empty(qkv_bytes + batch * 4, dtype=torch.uint8, device=dev)
+        self.qkv_host = self.in_host[:qkv_bytes].view(torch.bfloat16).view(batch, width)
+        self.pos_host = self.in_host[qkv_bytes:].view(torch.int32)
         self.out_host = torch.zeros((batch, Hq, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
-        self.qkv = torch.empty((batch, width), dtype=torch.bfloat16, device=dev)
-        self.pos = torch.empty(batch, dtype=torch.int32, device=dev)
+        self.qkv = self.in_dev[:qkv_bytes].view(torch.bfloat16).view(batch, width)
+        self.pos = self.in_dev[qkv_bytes:].view(torch.int32)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         need = ops.workspace_bytes(batch, Hq, Hkv, self.max_kv_len, self.chunk_pages)
         self.workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
@@ -53,8 +58,7 @@ class DecodeStep:
         return self.out_host.numel() * 2
 
     def _enqueue(self) -> None:
-        self.qkv.copy_(self.qkv_host, non_blocking=True)
-        self.pos.copy_(self.pos_host, non_blocking=True)
+        self.in_dev.copy_(self.in_host, non_blocking=True)
         ops.decode_step_attention(self.qkv, self.q_gain, self.k_gain, self.cos, self.sin, self.pos, self.cache,
                                   self.Hq, self.max_kv_len, slot_map=self.slot_map, window=self.window,
                                   chunk_pages=self.chunk_pages, softmax_scale=self.softmax_scale,
