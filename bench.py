@@ -377,7 +377,7 @@ def bench_kernels(device, timed, profile_range: str) -> dict:
     nbytes = pages_read * 16896 + 2 * rows * Hq * 256
     out["prefill_attention"] = {"workload": f"{rows} rows (8 prompts x 511 positions), Hq 10, Hkv 10, causal",
                                 "us_per_launch": ms * 1e3, "bytes_read_per_launch": nbytes,
-                                "note": "compute-bound: every cached position is scored against up to 88 query rows; the "
+                                "note": "compute-bound: every cached position is scored against up to 64 query rows per block; the "
                                         "pages (10.8 MB of cache) come from L2",
                                 "flops_per_launch": 4 * D * Hq * prompts * per * (per + 1) // 2,
                                 "achieved_tflops": 4 * D * Hq * prompts * per * (per + 1) // 2 / ms / 1e9}

@@ -183,11 +183,12 @@ int decode_step_attn_fp8_ve(const void *qkv, const void *q_gain, const void *k_g
 /*
  * Attention for a prefill pass (replaces k_attn over prompt rows, decode.cu:859-863,1041-1051): `rows` query rows,
  * many of which belong to one sequence. Rows are grouped on the host: block z = the group_rows[z] rows starting at
- * row group_first[z] (int32 [n_groups] each; at most prefill_attn_rows_per_block(Hq, Hkv) rows: 88 for Hq == Hkv, 22
- * for four query heads per kv head), all of one slot with ascending positions. Blocks start in the order of the
- * list, so list the groups that reach furthest into their prompts first. A block streams the
- * sequence's pages once for all its rows (a shared ring consumed by eleven warps, each owning 8 / (Hq / Hkv) rows over
- * the whole key range) and writes normalised outputs itself: no workspace, no merge launch.
+ * row group_first[z] (int32 [n_groups] each; at most prefill_attn_rows_per_block(Hq, Hkv) rows: 64 for Hq == Hkv, 16
+ * for four query heads per kv head; at most 16 query heads per kv head), all of one slot with ascending positions.
+ * Blocks start in the order of the list, so list the groups that reach furthest into their prompts first. A block
+ * streams the sequence's pages once for all its rows (a shared ring consumed by four warps, each owning
+ * 16 / (Hq / Hkv) rows over the whole key range; the cache bytes are widened to f16 in registers and both
+ * contractions run as f16 tensor-core MMAs) and writes normalised outputs itself: no workspace, no merge launch.
  *   q bf16 [rows][Hq][128]; lens int32 [rows] (row r attends positions [0, lens[r])); slot_map int32 [rows];
  *   out bf16 [rows][Hq][128]. No window. Every row's k, v must already be in the cache (kv_append_fp8).
  * A block whose longest row exceeds the cache, or whose slot is outside it, is flagged (NCB_DEV_BAD_LENGTH) and writes

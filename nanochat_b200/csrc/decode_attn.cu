@@ -167,39 +167,45 @@ static __device__ __forceinline__ bool row_rejected(int len, int slot, int pages
     return len > pages_per_slot * PAGE_TOKENS || slot < 0 || slot >= n_slots || (table_len > 0 && len > table_len);
 }
 
+/* Zero the V bytes of the page's positions outside [begin, len): an e4m3 NaN byte times a zero probability would
+ * still be NaN. One warp; the caller synchronises it afterwards. */
+static __device__ __forceinline__ void zero_v_outside(uint8_t *page, int key0, int begin, int len, int lane) {
+#pragma unroll
+    for (int blk = 0; blk < 4; blk++) { /* 16-position blocks: (group, half) */
+        const int first = key0 + 16 * blk;
+        uint32_t keep[4];
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            keep[w] = 0;
+#pragma unroll
+            for (int bb = 0; bb < 4; bb++) {
+                const int pos = first + 4 * w + bb;
+                if (pos >= begin && pos < len) keep[w] |= 0xffu << (8 * bb);
+            }
+        }
+        if ((keep[0] & keep[1] & keep[2] & keep[3]) == 0xffffffffu) continue;
+        for (int d = lane; d < HEAD_DIM; d += 32) {
+            uint4 *row = reinterpret_cast<uint4 *>(page + PAGE_V + blk * 2048 + d * 16);
+            uint4 v = *row;
+            v.x &= keep[0], v.y &= keep[1], v.z &= keep[2], v.w &= keep[3];
+            *row = v;
+        }
+    }
+}
+
 /* One landed page (64 positions starting at key0) for one warp: scores of the warp's query columns against the page's
  * K rows, the online-softmax update and the accumulation of V, as described at the top of the file. [begin, len) are
  * the attended positions (positions outside them inside the page are masked; their V bytes are zeroed in shared
- * memory first). MULTI: column slot 4 nt + t only sees positions below slot_len[nt] (rows of a prefill pass). */
-template <int NT, bool MULTI>
+ * memory first). */
+template <int NT>
 static __device__ __forceinline__ void attend_page(uint8_t *page, uint32_t page_u, int key0, int begin, int len,
-                                                   const int (&slot_len)[NT], const uint32_t (&qf)[NT][4][2],
+                                                   const uint32_t (&qf)[NT][4][2],
                                                    const float (&qfac)[NT], float (&m)[NT], float (&l)[NT],
                                                    float (&oacc)[NT][8][4], int lane) {
     const int g = lane >> 2, t = lane & 3;
     const bool partial = key0 < begin || key0 + PAGE_TOKENS > len;
-    if (partial) { /* zero the V bytes of positions outside [begin, len) */
-#pragma unroll
-        for (int blk = 0; blk < 4; blk++) { /* 16-position blocks: (group, half) */
-            const int first = key0 + 16 * blk;
-            uint32_t keep[4];
-#pragma unroll
-            for (int w = 0; w < 4; w++) {
-                keep[w] = 0;
-#pragma unroll
-                for (int bb = 0; bb < 4; bb++) {
-                    const int pos = first + 4 * w + bb;
-                    if (pos >= begin && pos < len) keep[w] |= 0xffu << (8 * bb);
-                }
-            }
-            if ((keep[0] & keep[1] & keep[2] & keep[3]) == 0xffffffffu) continue;
-            for (int d = lane; d < HEAD_DIM; d += 32) {
-                uint4 *row = reinterpret_cast<uint4 *>(page + PAGE_V + blk * 2048 + d * 16);
-                uint4 v = *row;
-                v.x &= keep[0], v.y &= keep[1], v.z &= keep[2], v.w &= keep[3];
-                *row = v;
-            }
-        }
+    if (partial) {
+        zero_v_outside(page, key0, begin, len, lane);
         __syncwarp();
     }
 #pragma unroll
@@ -242,12 +248,12 @@ static __device__ __forceinline__ void attend_page(uint8_t *page, uint32_t page_
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             float x[4], top = -INFINITY;
-            bool ok[4]; /* this slot may see position j: inside the span and, for MULTI, inside its own row */
+            bool ok[4]; /* this slot may see position j: inside the span */
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const float raw = sc[nt][j >> 1][2 * (j & 1)] + sc[nt][j >> 1][2 * (j & 1) + 1] * (1.f / LO_SCALE);
                 x[j] = raw * (ksc[j] * qfac[nt]);
-                ok[j] = valid[j] && (!MULTI || first + 4 * g + j < slot_len[nt]);
+                ok[j] = valid[j];
                 top = fmaxf(top, ok[j] ? x[j] + lv[j] : -INFINITY);
             }
             top = fmaxf(head_max(top), m[nt]);
@@ -430,10 +436,6 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     float qfac[NT];
     query_fragments<NT>(q_stage, q_scale, S, a.scale_log2, qf, qfac, lane);
 
-    int slot_len[NT]; /* every column belongs to the same row here */
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++) slot_len[nt] = len;
-
     /* the warp's running state: per tile, head t's maximum (log2 units), this lane's share of the sum, and O^T
      * fragments (dims 16 dt + g, + 8; columns = head t's two terms) */
     float m[NT], l[NT], oacc[NT][8][4];
@@ -469,7 +471,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
             }
             __syncwarp();
         }
-        attend_page<NT, false>(page, page_u, key0, sp.begin, sp.len, slot_len, qf, qfac, m, l, oacc, lane);
+        attend_page<NT>(page, page_u, key0, sp.begin, sp.len, qf, qfac, m, l, oacc, lane);
         __syncwarp(); /* every lane has read the stage */
         i += WARPS; /* a fixed page-to-warp map keeps the summation order, hence the output bits, reproducible */
         if (lane == 0 && i < n) {
@@ -519,17 +521,30 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
 
 /* A prefill pass holds many rows of the same prompt with lengths one apart (the reference runs them through k_attn
  * row by row, model/kernels/decode.cu:859-863,1041-1051). Here a block takes a TILE of consecutive rows of one prompt
- * and one kv head, streams the prompt's pages ONCE through a shared ring and lets PF_WARPS warps consume every page,
- * each for its own rows: warp w owns 8 / G rows (8 query columns = 4 per MMA tile, two tiles), i.e. 88 rows per block
- * for G = 1 and 22 for G = 4. A prompt's cache is read once per tile instead of once per row, every warp walks all
- * pages up to its rows' lengths with the same per-page code as the decode kernel (attend_page, rows masked at their
- * own length), and because a warp owns its rows over the whole key range there are no partial states, no workspace
- * and no merge launch: the warp normalises and writes bf16 outputs itself.
- * One producer thread (an extra warp) issues the page copies; full / empty mbarriers per stage, all waits bounded. */
-constexpr int PF_WARPS = 11, PF_STAGES = 6; /* 11 consumers + the producer = 384 threads: what 168 registers allow */
-constexpr int PF_THREADS = (PF_WARPS + 1) * 32;
-constexpr int PF_SLOTS = 8; /* query columns per warp */
-constexpr size_t PF_SMEM = (size_t)PF_STAGES * PAGE_BYTES + (size_t)PF_WARPS * PF_SLOTS * HEAD_DIM * sizeof(float);
+ * and one kv head and streams the prompt's pages ONCE through a ring shared by its PF_WARPS warps; a warp owns 16
+ * query slots (16 / G rows x the G heads of the kv group) over the whole key range, so there are no partial states,
+ * no workspace and no merge launch: the warp normalises and writes its bf16 outputs itself.
+ *
+ * The arithmetic differs from the decode kernel's, because here the tensor pipe, not HBM, is the limit, and on this
+ * architecture every mma.sync with e4m3 operands costs four extra fp32 adds and operand shuffling around the MMA
+ * itself (measured: 546 instructions per page for 32 of them). So the page's bytes are widened to f16 in registers
+ * (exact: e4m3 is a subset of f16) and both contractions run as m16n8k16 f16 MMAs with the QUERY SLOTS as the M
+ * dimension: scores S = Q K^T come out as (slot, key) tiles whose accumulator layout is already the A operand layout
+ * of P V, so probabilities need no shuffles, and queries (bf16, exact in f16 after a power-of-two scale) and
+ * probabilities (f16, 11 bits) need no two-term split. Key columns are permuted so that one lane's four
+ * probabilities of a 16-key step are four consecutive positions: exactly the four V bytes an ldmatrix row hands that
+ * lane. K rows are fetched as B operands by ldmatrix straight from the swizzled page (two rows of a matrix share a
+ * bank group: a two-way conflict, the price of the permutation), V^T rows likewise, conflict-free.
+ * The K scale multiplies the fp32 score, the V scale is folded into the probability, and the running maximum tracks
+ * score + log2(v scale), as in the decode kernel.
+ *
+ * Page ring: PF_STAGES stages, one "landed" mbarrier each. Warps consume pages 0 .. their last page in order; the
+ * LAST warp to finish with a stage (a shared counter against the number of warps that need that page) issues the
+ * copy of the page PF_STAGES further on into it, so no warp is set aside as a producer. All waits are bounded. */
+constexpr int PF_WARPS = 4, PF_STAGES = 4; /* 3 blocks per SM: 12 warps at 168 registers, 12 stages of 16.9 KB */
+constexpr int PF_THREADS = PF_WARPS * 32;
+constexpr int PF_SLOTS = 16; /* query slots per warp: the M of the MMA */
+constexpr size_t PF_SMEM = (size_t)PF_STAGES * PAGE_BYTES;
 
 struct PrefillArgs {
     const bf16 *q;         /* [rows][Hq][128] */
@@ -541,16 +556,48 @@ struct PrefillArgs {
     int *status;
 };
 
-__global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_attn(PrefillArgs a) {
-    extern __shared__ __align__(128) uint8_t smem[]; /* the page ring, then each warp's 8 x 128 fp32 staging area */
-    __shared__ __align__(8) uint64_t bars[2 * PF_STAGES];
-    __shared__ float q_scales[PF_WARPS][PF_SLOTS];
+/* d += A B, A 16x16 f16 (row), B 16x8 f16 (col), fp32 accumulators. */
+static __device__ __forceinline__ void mma_f16(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+/* The four e4m3 bytes of x as two f16x2 words (exact): lo from bytes 0, 1, hi from bytes 2, 3. */
+static __device__ __forceinline__ void widen_e4m3x4(uint32_t x, uint32_t &lo, uint32_t &hi) {
+    uint16_t l, h;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(l), "=h"(h) : "r"(x));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"(l));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"(h));
+}
+static __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+/* max / sum over the 4 lanes that share lane / 4 (one query slot's key columns) */
+static __device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+static __device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+__global__ void __launch_bounds__(PF_THREADS, 3) k_prefill_attn(PrefillArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[]; /* the page ring */
+    __shared__ __align__(8) uint64_t bars[PF_STAGES];
+    __shared__ int finished[PF_STAGES]; /* warps done with the stage's current page */
+    __shared__ int warp_len[PF_WARPS];  /* each warp's longest row */
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int kvh = blockIdx.y, G = a.Hq / a.Hkv, rpw = max(1, PF_SLOTS / G);
+    /* blocks are dispatched in index order and the groups are listed longest-first: with the kv head as the fastest
+     * index the whole launch starts its longest blocks first, not each head's in turn */
+    const int group = blockIdx.x / a.Hkv, kvh = blockIdx.x % a.Hkv, G = a.Hq / a.Hkv, rpw = PF_SLOTS / G;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int b0 = a.group_first[blockIdx.x];
-    const int n_rows = min(a.group_rows[blockIdx.x], PF_WARPS * rpw);
+    const int b0 = a.group_first[group];
+    const int n_rows = min(a.group_rows[group], PF_WARPS * rpw);
     const int n_active = (n_rows + rpw - 1) / rpw; /* warps that have rows */
     const int len_block = a.lens[b0 + n_rows - 1];  /* rows ascend in position: the last one is the longest */
     const int slot = a.slot_map[b0];
@@ -558,103 +605,210 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_attn(PrefillArgs a) {
     if (bad && tid == 0 && kvh == 0) flag(a.status, NCB_DEV_BAD_LENGTH);
     const int n_pages = bad || len_block <= 0 ? 0 : (len_block + PAGE_TOKENS - 1) / PAGE_TOKENS;
     const uint32_t ring = smem_u32(smem);
+    const uint8_t *pages = a.cache + (((size_t)(bad ? 0 : slot) * a.Hkv + kvh) * a.pages_per_slot) * PAGE_BYTES;
     auto full = [&](int st) { return smem_u32(bars + st); };
-    auto empty = [&](int st) { return smem_u32(bars + PF_STAGES + st); };
+    const int r0 = b0 + warp * rpw, rows_w = max(0, min(rpw, b0 + n_rows - r0)), S = rows_w * G;
+    const int my_len = rows_w > 0 && !bad ? a.lens[r0 + rows_w - 1] : 0;
+    if (lane == 0) warp_len[warp] = my_len;
     if (tid == 0) {
         for (int st = 0; st < PF_STAGES; st++) {
             mbar_init(full(st), 1);
-            mbar_init(empty(st), n_active);
+            finished[st] = 0;
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int i = 0; i < min(n_pages, PF_STAGES); i++)
+            page_load(ring + i * PAGE_BYTES, pages + (size_t)i * PAGE_BYTES, full(i));
     }
     __syncthreads();
-    if (warp == PF_WARPS) { /* producer */
-        if (lane == 0) {
-            const uint8_t *pages = a.cache + (((size_t)(bad ? 0 : slot) * a.Hkv + kvh) * a.pages_per_slot) * PAGE_BYTES;
-            for (int i = 0; i < n_pages; i++) {
-                const int st = i % PF_STAGES;
-                if (!mbar_wait(empty(st), ((i / PF_STAGES) & 1) ^ 1)) {
-                    flag(a.status, NCB_DEV_WAIT_TIMEOUT);
-                    break;
-                }
-                /* the consumers' reads and masking writes of the stage come before the copy engine's writes */
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                page_load(ring + st * PAGE_BYTES, pages + (size_t)i * PAGE_BYTES, full(st));
-            }
-        }
-        return;
-    }
     if (warp >= n_active) return;
-    const int r0 = b0 + warp * rpw, rows_w = min(rpw, b0 + n_rows - r0), S = rows_w * G;
-    float *stage = reinterpret_cast<float *>(smem + (size_t)PF_STAGES * PAGE_BYTES) + (size_t)warp * PF_SLOTS * HEAD_DIM;
-    for (int i = lane; i < S * HEAD_DIM; i += 32) { /* slot = row-in-warp * G + head-in-group */
-        const int sl = i / HEAD_DIM, d = i % HEAD_DIM;
-        stage[i] = __bfloat162float(a.q[((size_t)(r0 + sl / G) * a.Hq + (size_t)kvh * G + sl % G) * HEAD_DIM + d]);
+
+    /* ---- the warp's queries as A fragments: slot g (and g + 8) = row (slot / G), head (slot % G) of the group;
+     * k slots (2t, 2t+1) and (2t+8, 2t+9) of step s take dims 16 s + 4 t .. + 3, the order the cache bytes arrive in */
+    uint32_t qa[8][4];
+    float qfac[2];
+    int row_len[2];
+#pragma unroll
+    for (int rr = 0; rr < 2; rr++) {
+        const int sl = g + 8 * rr;
+        const bool on = sl < S;
+        const int row = r0 + (on ? sl / G : 0);
+        const bf16 *src = a.q + ((size_t)row * a.Hq + (size_t)kvh * G + (on ? sl % G : 0)) * HEAD_DIM + 4 * t;
+        float x[8][4], amax = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; s++) {
+            const uint2 u = on ? *reinterpret_cast<const uint2 *>(src + 16 * s) : make_uint2(0u, 0u);
+            x[s][0] = __uint_as_float(u.x << 16), x[s][1] = __uint_as_float(u.x & 0xffff0000u);
+            x[s][2] = __uint_as_float(u.y << 16), x[s][3] = __uint_as_float(u.y & 0xffff0000u);
+#pragma unroll
+            for (int e = 0; e < 4; e++) amax = fmaxf(amax, fabsf(x[s][e]));
+        }
+        amax = quad_max(amax);
+        /* bf16 values are exact in f16 once the row's largest magnitude is below 2^15: a power-of-two scale */
+        const int expo = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;
+        const int down = max(0, min(expo - 14, 126));
+        const float mul = __uint_as_float((uint32_t)(127 - down) << 23), back = __uint_as_float((uint32_t)(127 + down) << 23);
+        qfac[rr] = a.scale_log2 * back;
+        row_len[rr] = on ? a.lens[row] : 0;
+#pragma unroll
+        for (int s = 0; s < 8; s++) {
+            qa[s][rr] = pack_f16x2(x[s][0] * mul, x[s][1] * mul);
+            qa[s][2 + rr] = pack_f16x2(x[s][2] * mul, x[s][3] * mul);
+        }
     }
-    __syncwarp();
-    for (int h = 0; h < S; h++) {
-        float mx = 0.f;
-        for (int i = lane; i < HEAD_DIM; i += 32) mx = fmaxf(mx, fabsf(stage[h * HEAD_DIM + i]));
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) q_scales[warp][h] = mx / 448.f;
-    }
-    __syncwarp();
-    constexpr int NT = 2;
-    uint32_t qf[NT][4][2];
-    float qfac[NT];
-    query_fragments<NT>(stage, q_scales[warp], S, a.scale_log2, qf, qfac, lane);
-    int slot_len[NT];
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, oacc[16][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) slot_len[nt] = 4 * nt + t < S ? a.lens[r0 + (4 * nt + t) / G] : 0;
-    const int my_len = a.lens[r0 + rows_w - 1];
-    float m[NT], l[NT], oacc[NT][8][4];
+    for (int nd = 0; nd < 16; nd++)
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        m[nt] = -INFINITY;
-        l[nt] = 0.f;
-#pragma unroll
-        for (int dt = 0; dt < 8; dt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) oacc[nt][dt][i] = 0.f;
-    }
+        for (int e = 0; e < 4; e++) oacc[nd][e] = 0.f;
+
+    /* ldmatrix rows of this lane. K: matrix c = lane / 8 is score tile c, whose column n = lane % 8 is the key
+     * 16 (c / 2) + 4 (n / 2) + 2 (c % 2) + n % 2 of a 32-key half page; V^T: matrix = 8 dims, row = dim lane. */
+    const int kc = lane >> 3, kn = lane & 7;
+    const int krow = 16 * (kc >> 1) + 4 * (kn >> 1) + 2 * (kc & 1) + (kn & 1);
+    const uint32_t kswz = (uint32_t)((krow >> 2) & 7) << 4;
+    const int my_pages = (my_len + PAGE_TOKENS - 1) / PAGE_TOKENS;
     bool ok = true;
-    for (int i = 0; i < n_pages; i++) {
+    for (int i = 0; i < my_pages; i++) {
         const int st = i % PF_STAGES;
         if (!mbar_wait(full(st), (i / PF_STAGES) & 1)) {
             if (lane == 0) flag(a.status, NCB_DEV_WAIT_TIMEOUT);
+            mbar_wait(full(st), (i / PF_STAGES) & 1); /* the block must not exit under a copy still in flight */
             ok = false;
             break;
         }
+        uint8_t *page = smem + (size_t)st * PAGE_BYTES;
+        const uint32_t page_u = ring + st * PAGE_BYTES;
         const int key0 = i * PAGE_TOKENS;
-        if (key0 < my_len) /* later pages only hold positions past this warp's rows */
-            attend_page<NT, true>(smem + (size_t)st * PAGE_BYTES, ring + st * PAGE_BYTES, key0, 0, len_block, slot_len, qf,
-                                  qfac, m, l, oacc, lane);
+        if (key0 + PAGE_TOKENS > len_block) { /* bytes past the block's last position may be anything: zero their V */
+            zero_v_outside(page, key0, 0, len_block, lane);
+            __syncwarp();
+        }
+#pragma unroll
+        for (int gi = 0; gi < 2; gi++) {
+            const int first = key0 + 32 * gi;
+            if (first >= my_len) continue;
+            /* ---- scores: A = q, B = K rows ---- */
+            float sc[4][4];
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) sc[c][e] = 0.f;
+            const uint32_t kbase = page_u + PAGE_K + (32 * gi + krow) * HEAD_DIM;
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+                uint32_t kr[4];
+                ldmatrix_x4(kr[0], kr[1], kr[2], kr[3], kbase + (((uint32_t)s << 4) ^ kswz));
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t b0, b1;
+                    widen_e4m3x4(kr[c], b0, b1);
+                    mma_f16(sc[c], qa[s][0], qa[s][1], qa[s][2], qa[s][3], b0, b1);
+                }
+            }
+            /* this lane: slots g and g + 8, positions first + 16 h + 4 t + e: tile 2 h + e / 2, column pair e % 2 */
+            float ksc[2][4], vsc[2][4], lv[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const float4 k4 = *reinterpret_cast<const float4 *>(page + PAGE_KS + (32 * gi + 16 * h + 4 * t) * 4);
+                const float4 v4 = *reinterpret_cast<const float4 *>(page + PAGE_VS + (32 * gi + 16 * h + 4 * t) * 4);
+                ksc[h][0] = k4.x, ksc[h][1] = k4.y, ksc[h][2] = k4.z, ksc[h][3] = k4.w;
+                vsc[h][0] = v4.x, vsc[h][1] = v4.y, vsc[h][2] = v4.z, vsc[h][3] = v4.w;
+#pragma unroll
+                for (int e = 0; e < 4; e++) lv[h][e] = fmaxf(lg2(vsc[h][e]), MIN_LOG2_VSCALE);
+            }
+            const bool diagonal = first + 32 > min(row_len[0], row_len[1]); /* some position is masked for this lane */
+            float top[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) {
+                float best = -INFINITY;
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        float &x = sc[2 * h + (e >> 1)][2 * rr + (e & 1)];
+                        x *= ksc[h][e] * qfac[rr];
+                        const bool seen = !diagonal || first + 16 * h + 4 * t + e < row_len[rr];
+                        best = fmaxf(best, seen ? x + lv[h][e] : -INFINITY);
+                    }
+                top[rr] = fmaxf(quad_max(best), m[rr]);
+            }
+            if (__any_sync(0xffffffffu, top[0] > m[0] || top[1] > m[1])) { /* some slot's maximum moved: rescale */
+                const float c0 = m[0] == -INFINITY ? 0.f : ex2(m[0] - top[0]);
+                const float c1 = m[1] == -INFINITY ? 0.f : ex2(m[1] - top[1]);
+                l[0] *= c0, l[1] *= c1;
+#pragma unroll
+                for (int nd = 0; nd < 16; nd++) {
+                    oacc[nd][0] *= c0, oacc[nd][1] *= c0;
+                    oacc[nd][2] *= c1, oacc[nd][3] *= c1;
+                }
+                m[0] = top[0], m[1] = top[1];
+            }
+            uint32_t pa[2][4]; /* per 16-key step h: A fragments of the folded probabilities */
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++)
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    float p[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float x = sc[2 * h + (e >> 1)][2 * rr + (e & 1)];
+                        const bool seen = (!diagonal || first + 16 * h + 4 * t + e < row_len[rr]) && top[rr] != -INFINITY;
+                        const float w = seen ? ex2(x - top[rr]) : 0.f;
+                        l[rr] += w;
+                        p[e] = seen ? w * (vsc[h][e] * P_SCALE) : 0.f;
+                    }
+                    pa[h][rr] = pack_f16x2(p[0], p[1]);
+                    pa[h][2 + rr] = pack_f16x2(p[2], p[3]);
+                }
+            /* ---- values: A = probabilities, B = V^T rows (dim 8 nd + n), the lane's four positions per row ---- */
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint32_t vbase = page_u + PAGE_V + gi * 4096 + h * 2048 + lane * 16;
+#pragma unroll
+                for (int qd = 0; qd < 4; qd++) {
+                    uint32_t vr[4];
+                    ldmatrix_x4(vr[0], vr[1], vr[2], vr[3], vbase + qd * 512);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        uint32_t b0, b1;
+                        widen_e4m3x4(vr[j], b0, b1);
+                        mma_f16(oacc[4 * qd + j], pa[h][0], pa[h][1], pa[h][2], pa[h][3], b0, b1);
+                    }
+                }
+            }
+        }
+        /* done with the stage: the last of the warps that needed this page refills it */
         __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty(st)) : "memory");
-    }
-    /* normalise: the warp's staging area takes the fp32 outputs, then each slot's 128 values go out as bf16 */
-    __syncwarp();
+        if (lane == 0) {
+            int need = 0;
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        const int h = 4 * nt + t;
-        const float lsum = head_sum(l[nt]);
-        const bool any = ok && lsum > 0.f;
-#pragma unroll
-        for (int dt = 0; dt < 8; dt++) {
-            const float lo = (oacc[nt][dt][0] + oacc[nt][dt][1] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
-            const float hi = (oacc[nt][dt][2] + oacc[nt][dt][3] * (1.f / LO_SCALE)) * (1.f / P_SCALE);
-            stage[h * HEAD_DIM + 16 * dt + g] = any ? __fdiv_rn(lo, lsum) : 0.f;
-            stage[h * HEAD_DIM + 16 * dt + g + 8] = any ? __fdiv_rn(hi, lsum) : 0.f;
+            for (int w = 0; w < PF_WARPS; w++) need += (w < n_active && warp_len[w] > key0) ? 1 : 0;
+            __threadfence_block(); /* this warp's reads of the stage come before the count */
+            if (atomicAdd(&finished[st], 1) == need - 1) {
+                atomicExch(&finished[st], 0);
+                if (i + PF_STAGES < n_pages) {
+                    __threadfence_block();
+                    /* the warps' reads and masking writes of the stage come before the copy engine's writes */
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    page_load(page_u, pages + (size_t)(i + PF_STAGES) * PAGE_BYTES, full(st));
+                }
+            }
         }
     }
-    __syncwarp();
-    for (int h = 0; h < S; h++) {
-        const float4 v = *reinterpret_cast<const float4 *>(stage + h * HEAD_DIM + 4 * lane);
-        uint2 u;
-        *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(v.x, v.y);
-        *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(v.z, v.w);
-        *reinterpret_cast<uint2 *>(a.out + ((size_t)(r0 + h / G) * a.Hq + (size_t)kvh * G + h % G) * HEAD_DIM + 4 * lane) = u;
+    /* ---- normalise and store: slot g's (and g + 8's) dims 8 nd + 2 t, + 1 ---- */
+#pragma unroll
+    for (int rr = 0; rr < 2; rr++) {
+        const int sl = g + 8 * rr;
+        const float lsum = quad_sum(l[rr]);
+        if (sl >= S) continue;
+        const float inv = ok && lsum > 0.f ? __fdiv_rn(1.f, lsum * P_SCALE) : 0.f;
+        bf16 *dst = a.out + ((size_t)(r0 + sl / G) * a.Hq + (size_t)kvh * G + sl % G) * HEAD_DIM + 2 * t;
+#pragma unroll
+        for (int nd = 0; nd < 16; nd++)
+            *reinterpret_cast<__nv_bfloat162 *>(dst + 8 * nd) =
+                __floats2bfloat162_rn(oacc[nd][2 * rr] * inv, oacc[nd][2 * rr + 1] * inv);
     }
 }
 
@@ -1238,7 +1392,9 @@ int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, cons
         return NCB_ERR_ARG;
     if (Hq / Hkv > PF_SLOTS) return NCB_ERR_UNSUPPORTED;
     if (rows == 0 || n_groups == 0) return NCB_OK;
-    if (!q || !kv_cache || !lens || !slot_map || !group_first || !group_rows || !out || Hkv > 65535) return NCB_ERR_ARG;
+    if (!q || !kv_cache || !lens || !slot_map || !group_first || !group_rows || !out ||
+        (long long)n_groups * Hkv > 0x7fffffffLL)
+        return NCB_ERR_ARG;
     if (((uintptr_t)q | (uintptr_t)kv_cache | (uintptr_t)out) % 16 != 0) return NCB_ERR_ALIGN;
     {
         static bool done[MAX_DEVICES] = {};
@@ -1255,7 +1411,7 @@ int prefill_attn_fp8(const void *q, const void *kv_cache, const void *lens, cons
                      (const int32_t *)group_first, (const int32_t *)group_rows, (bf16 *)out, Hq, Hkv, n_slots, pages_per_slot,
                      softmax_scale * 1.4426950408889634f, (int *)status};
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)n_groups, (unsigned)Hkv);
+    config.gridDim = dim3((unsigned)((long long)n_groups * Hkv));
     config.blockDim = dim3(PF_THREADS);
     config.dynamicSmemBytes = PF_SMEM;
     config.stream = (cudaStream_t)stream;

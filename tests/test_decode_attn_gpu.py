@@ -393,7 +393,7 @@ def test_sharded_exchange_wait_runs_out_and_reports():
     assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0  # the device still answers
 
 
-@pytest.mark.parametrize("Hq,Hkv", [(10, 10), (8, 2), (4, 1), (16, 2)])
+@pytest.mark.parametrize("Hq,Hkv", [(10, 10), (8, 2), (4, 1), (16, 2), (10, 2), (16, 1)])
 def test_prefill_attention_groups_rows_and_matches_the_row_wise_path(Hq, Hkv):
     """prefill_attn_fp8 (a tile of a prompt's rows shares each page load; every warp owns its rows over the whole key
     range) against decode_attn_fp8 run row by row and against the float64 checker: causal prefixes of three prompts
@@ -417,15 +417,20 @@ def test_prefill_attention_groups_rows_and_matches_the_row_wise_path(Hq, Hkv):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     plan = ncb.attention.PrefillPlan(slots, positions, Hq, cache, "cuda")
     got = ncb.attention.prefill_attention(q, cache, plan, status=status)
-    want = ncb.decode_attention(q, cache, lens_t, max(lens), slot_map=slot_map, status=status)
     torch.cuda.synchronize()
     assert status.item() == 0
-    d = (got.float() - want.float()).abs()
-    assert float(d.max()) <= 8e-3 and float(d.mean()) <= 2e-4, (float(d.max()), float(d.mean()))
+    if Hq // Hkv <= 8:  # the decode kernel's limit; the two kernels round differently (f16 operands here, two-term
+        # e4m3 there), so outputs may differ by one bf16 step (2^-7 relative) on top of the small absolute term
+        want = ncb.decode_attention(q, cache, lens_t, max(lens), slot_map=slot_map, status=status)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        d = (got.float() - want.float()).abs()
+        assert bool((d <= 8e-3 + 2.0 ** -7 * want.float().abs()).all()) and float(d.mean()) <= 2e-4, \
+            (float(d.max()), float(d.mean()))
     # a few rows against the checker: the causal prefix of each prompt
     seq_of = {2: 0, 0: 1, 1: 2}
     assert torch.isfinite(got.float()).all()
-    for r in (0, 63, 64, 149, 150, 158, 159, 222, 223, rows - 1):
+    for r in (0, 15, 16, 63, 64, 127, 128, 149, 150, 158, 159, 222, 223, 300, rows - 1):
         b, n = seq_of[slots[r]], positions[r] + 1
         ref = oat.decode_attention(helpers.bf16_bits(q[r:r + 1].cpu()), [case["k_bytes"][b][:, :n]],
                                    [case["k_scale"][b][:, :n]], [case["v_bytes"][b][:, :n]], [case["v_scale"][b][:, :n]], SCALE)
