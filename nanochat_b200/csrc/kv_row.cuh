@@ -138,7 +138,7 @@ static __device__ __forceinline__ uint4 pack_bf16x8(const float *v) {
 }
 
 /* scale = amax / 448 over the group's 128 values; bytes = e4m3(x / scale); a zero row gives scale 0, bytes 0.
- * The row's 16 quotients share one correctly rounded reciprocal r = RN(1 / scale): q0 = RN(x r), the exact remainder
+ * The row's 16 quotients share one correctly rounded reciprocal r = RN(1 / scale): q0 = RN(x r), the remainder
  * e = fma(-scale, q0, x), q = fma(e, r, q0) is the correctly rounded x / scale (Markstein's division step; checked
  * exhaustively for every pair of bf16 mantissas and every exponent difference that does not round to zero, which is
  * the whole input domain here: x and amax are bf16-valued). Three instructions per value instead of an IEEE division;

@@ -170,9 +170,7 @@ class Decoder:
             return self._hidden_rows_torch(tokens, pos, slot_map, max_kv_len, attend_last_layer)
         lens = pos + 1
         workspace = self._workspace(rows, max_kv_len)
-        plan = None
-        if host_rows is not None and not any(self.windows):
-            plan = ops.PrefillPlan(host_rows[0], host_rows[1], cfg.n_heads, self.caches[0], self.device)
+        plan, grouped = None, host_rows is not None and not any(self.windows)
         h = torch.empty((rows, C), dtype=torch.bfloat16, device=self.device)
         n = torch.empty_like(h)
         mixing = any(l.mixes for l in layers)
@@ -196,37 +194,48 @@ class Decoder:
                                   cfg.n_heads, slot_map=slot_map, status=self.status, ve=ve)
                 if i == cfg.n_layers - 1 and not attend_last_layer:
                     return h  # prefill: the last layer only has to fill its cache (decode.cu:862)
+                if grouped and plan is None:  # built while the GPU already runs the launches above
+                    plan = ops.PrefillPlan(host_rows[0], host_rows[1], cfg.n_heads, self.caches[0], self.device)
                 if plan is not None:
                     att = ops.prefill_attention(q, self.caches[i], plan, status=self.status)
                 else:
                     att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map,
                                                window=self.windows[i], chunk_pages=self.chunk_pages,
                                                workspace=workspace, status=self.status)
-            y = self.gemm_rows(att.view(rows, -1), layer.wo)
-            check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
+            self.gemm_rows(att.view(rows, -1), layer.wo, resid=h)  # h += att . wo^T in the GEMM's epilogue
+            check(lib.add_rms_norm(pointer(h), None, pointer(n), rows, C, s), "add_rms_norm")
             u = self.gemm_rows(n, layer.wup, epilogue=2)
-            y = self.gemm_rows(u, layer.wdown)
             nxt = layers[i + 1] if i + 1 < len(layers) else None
             if nxt is not None and nxt.mixes:  # the next layer's stream mix rides on this add
+                y = self.gemm_rows(u, layer.wdown)
                 check(lib.add_rms_norm_mix(pointer(h), pointer(y), pointer(x0), nxt.resid_lambda, nxt.x0_lambda,
                                            pointer(n), rows, C, s), "add_rms_norm_mix")
             else:
-                check(lib.add_rms_norm(pointer(h), pointer(y), pointer(n), rows, C, s), "add_rms_norm")
+                self.gemm_rows(u, layer.wdown, resid=h)
+                check(lib.add_rms_norm(pointer(h), None, pointer(n), rows, C, s), "add_rms_norm")
         return n
 
-    def gemm_rows(self, x: Tensor, w: Tensor, epilogue: int = 0) -> Tensor:
+    def gemm_rows(self, x: Tensor, w: Tensor, epilogue: int = 0, resid: "Tensor | None" = None) -> Tensor:
         """epilogue(x . w^T) for a pass of any number of rows: x bf16 (rows, K), w bf16 (N, K); epilogue 0 store,
-        2 relu^2, 3 fp32 output. This package's tiled tcgen05 GEMM (csrc/tile_gemm.cu) when N is a multiple of 128 and
-        K of 64; other shapes (toy models) go to torch's GEMM with the same epilogue applied afterwards."""
+        2 relu^2, 3 fp32 output; resid (rows, N) bf16: resid += bf16(x . w^T) in place (epilogue 1), returned.
+        This package's tiled tcgen05 GEMM (csrc/tile_gemm.cu) when N is a multiple of 128 and K of 64; other shapes
+        (toy models) go to torch's GEMM with the same epilogue applied afterwards."""
         rows, K, N = x.shape[0], x.shape[1], w.shape[0]
+        if resid is not None:
+            assert epilogue == 0 and resid.is_contiguous() and resid.shape == (rows, N)
+            epilogue = 1
         if self.use_tile_gemm and N % 128 == 0 and K % 64 == 0 and x.is_contiguous() and w.is_contiguous():
-            y = torch.empty((rows, N), dtype=torch.float32 if epilogue == 3 else torch.bfloat16, device=x.device)
-            check(cuda_library("tile_gemm").tile_gemm(pointer(x), pointer(w), None, pointer(y), rows, N, K, epilogue,
-                                                      pointer(self.status), stream()), "tile_gemm")
+            y = resid if resid is not None else torch.empty(
+                (rows, N), dtype=torch.float32 if epilogue == 3 else torch.bfloat16, device=x.device)
+            check(cuda_library("tile_gemm").tile_gemm(pointer(x), pointer(w), None if resid is None else pointer(resid),
+                                                      pointer(y), rows, N, K, epilogue, pointer(self.status), stream()),
+                  "tile_gemm")
             return y
         if epilogue == 3:
             return torch.mm(x, w.T, out_dtype=torch.float32)
         y = x @ w.T
+        if epilogue == 1:
+            return resid.add_(y)
         if epilogue == 2:
             check(cuda_library("decode_step").relu2_inplace(pointer(y), y.numel(), stream()), "relu2_inplace")
         return y
