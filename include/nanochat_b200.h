@@ -372,6 +372,17 @@ int stream_gemm_mix(const void *x, const void *w, const void *resid, const void 
 int tile_gemm(const void *x, const void *w, const void *resid, void *y, long long rows, int N, int K, int epilogue,
               int *status, void *stream);
 
+/*
+ * tile_gemm with the kernel form chosen by the caller. form 1: one block per 128 x 256 (or 128 x 128) tile. form 2: a
+ * pair of blocks on neighbouring SMs per 256 x 256 or 256 x 320 tile (tcgen05 cta_group::2: each block stages its own
+ * 128 rows of x and half of the W tile, so a block loads a third less per product; the 320-wide tile is taken where it
+ * makes fewer, fuller rounds, e.g. N = 1280); N must be a multiple of 256 or 640, else NCB_ERR_UNSUPPORTED. form 0:
+ * tile_gemm's own choice (pairs where they apply and rows > 128). All forms give the same bits. No counterpart in the
+ * reference (its GEMM is one kernel form).
+ */
+int tile_gemm_form(const void *x, const void *w, const void *resid, void *y, long long rows, int N, int K, int epilogue,
+                   int form, int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -66,6 +66,7 @@ SIGNATURES = {
     },
     "tile_gemm": {
         "tile_gemm": ([c_ptr] * 4 + [c_ll, c_int, c_int, c_int, c_ptr, c_ptr], c_int),
+        "tile_gemm_form": ([c_ptr] * 4 + [c_ll, c_int, c_int, c_int, c_int, c_ptr, c_ptr], c_int),
     },
     "stream_gemm": {
         "stream_gemm_split": ([c_int, c_int, c_int], c_int),

@@ -23,7 +23,7 @@ def reference(x, w, resid, epilogue):
     return y
 
 
-def run(rows, N, K, epilogue, seed=0, alias=False):
+def run(rows, N, K, epilogue, seed=0, alias=False, form=0):
     gen = torch.Generator(device="cuda").manual_seed(seed)
     x = torch.randn(rows, K, generator=gen, device="cuda").bfloat16()
     w = (torch.randn(N, K, generator=gen, device="cuda") * K ** -0.5).bfloat16()
@@ -34,8 +34,12 @@ def run(rows, N, K, epilogue, seed=0, alias=False):
         y.copy_(resid)
         resid = y
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    rc = cuda_library("tile_gemm").tile_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, N, K, epilogue,
-                                             pointer(status), stream())
+    lib = cuda_library("tile_gemm")
+    if form == 0:
+        rc = lib.tile_gemm(pointer(x), pointer(w), pointer(resid), pointer(y), rows, N, K, epilogue, pointer(status), stream())
+    else:
+        rc = lib.tile_gemm_form(pointer(x), pointer(w), pointer(resid), pointer(y), rows, N, K, epilogue, form,
+                                pointer(status), stream())
     torch.cuda.synchronize()
     assert rc == 0 and status.item() == 0
     return y, want
@@ -54,6 +58,29 @@ def test_tile_gemm_matches_torch(rows, N, K, epilogue):
     else:
         assert float(err.max()) <= 2 ** -7 * top + 1e-6, (float(err.max()), top)
         assert float((err > 0).float().mean()) < 0.02  # roundings flip only where the fp32 sums straddle a boundary
+
+
+@pytest.mark.parametrize("rows,N,K", [(129, 256, 64), (256, 640, 64), (300, 640, 256), (700, 1280, 256), (511, 3840, 1280),
+                                      (4088, 1280, 5120), (4088, 5120, 1280), (5000, 2560, 128), (9500, 2048, 192)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+def test_block_pair_form_gives_the_single_block_form_bits(rows, N, K, epilogue):
+    """tile_gemm_form: a pair of blocks per 256 x 256 or 256 x 320 tile (form 2) against one block per tile (form 1):
+    the same bits (a product's k-blocks are accumulated in the same order), several tiles per pair, half-width last
+    rounds, row tiles that end inside a pair's second block, and both against torch."""
+    one, want = run(rows, N, K, epilogue, seed=rows + N + K + epilogue, form=1)
+    two, _ = run(rows, N, K, epilogue, seed=rows + N + K + epilogue, form=2)
+    auto, _ = run(rows, N, K, epilogue, seed=rows + N + K + epilogue, form=0)
+    assert torch.equal(one, two) and torch.equal(one, auto)
+    err = (two.float() - want.float()).abs()
+    top = float(want.float().abs().max())
+    assert float(err.max()) <= (2e-5 * max(top, 1.0) * (K / 64) ** 0.5 if epilogue == 3 else 2 ** -7 * top + 1e-6)
+
+
+def test_block_pair_form_refuses_other_widths():
+    import ctypes
+    lib, p = cuda_library("tile_gemm"), ctypes.c_void_p(4096)
+    assert lib.tile_gemm_form(p, p, None, p, 300, 384, 64, 0, 2, None, None) == 5   # neither a multiple of 256 nor of 640
+    assert lib.tile_gemm_form(p, p, None, p, 300, 256, 64, 0, 3, None, None) == 1   # no such form
 
 
 def test_tile_gemm_many_tiles_per_block_and_in_place_residual():
