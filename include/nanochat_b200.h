@@ -44,7 +44,7 @@ enum {
     NCB_ERR_ALIGN = 2,       /* a pointer or stride misses its required alignment */
     NCB_ERR_WORKSPACE = 3,   /* the workspace is smaller than decode_attn_workspace_bytes() */
     NCB_ERR_LAUNCH = 4,      /* the CUDA runtime refused the launch; see cudaGetLastError */
-    NCB_ERR_UNSUPPORTED = 5, /* Hq / Hkv above 8 */
+    NCB_ERR_UNSUPPORTED = 5, /* a shape this kernel does not take: Hq / Hkv above its limit, a GEMM width its form cannot tile */
     NCB_ERR_STATIC_LIMIT = 6 /* decode_attn_fp8_static: the call needs more than NCB_STATIC_SCRATCH_BYTES */
 };
 

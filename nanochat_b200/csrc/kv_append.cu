@@ -128,7 +128,7 @@ const char *ncb_status_string(int status) {
     case NCB_ERR_ALIGN: return "misaligned pointer or stride";
     case NCB_ERR_WORKSPACE: return "workspace too small";
     case NCB_ERR_LAUNCH: return "kernel launch failed";
-    case NCB_ERR_UNSUPPORTED: return "unsupported head ratio";
+    case NCB_ERR_UNSUPPORTED: return "unsupported shape (head ratio, tile width)";
     case NCB_ERR_STATIC_LIMIT: return "needs more than the built-in scratch";
     default: return "unknown status";
     }

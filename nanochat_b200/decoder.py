@@ -390,10 +390,15 @@ class Decoder:
         token_rows = np.concatenate([np.asarray(p[:-1], dtype=np.int64) for p in prompts])
         for at in range(0, total, rows_per_pass):
             part = slice(at, min(at + rows_per_pass, total))
-            slot_map = torch.from_numpy(slot_rows[part]).to(self.device, non_blocking=True)
-            pos = torch.from_numpy(pos_rows[part]).to(self.device, non_blocking=True)
-            tokens = torch.from_numpy(token_rows[part]).to(self.device, non_blocking=True)
-            self.hidden_rows(tokens, pos, slot_map, int(pos_rows[part].max()) + 1, attend_last_layer=False,
+            n = part.stop - part.start
+            # tokens, positions and slots of the pass cross to the device in ONE copy
+            packed = np.empty(2 * n, dtype=np.int64)
+            packed[:n] = token_rows[part]
+            packed[n:].view(np.int32)[:n] = pos_rows[part]
+            packed[n:].view(np.int32)[n:] = slot_rows[part]
+            dev = torch.from_numpy(packed).to(self.device, non_blocking=True)
+            tokens, small = dev[:n], dev[n:].view(torch.int32)
+            self.hidden_rows(tokens, small[:n], small[n:], int(pos_rows[part].max()) + 1, attend_last_layer=False,
                              host_rows=(slot_rows[part], pos_rows[part]))
 
     # ---- decode -----------------------------------------------------------------------------------------------

@@ -75,7 +75,7 @@ SIGNATURES = {
     },
 }
 STATUS = {0: "ok", 1: "invalid argument", 2: "misaligned pointer or stride", 3: "workspace too small",
-          4: "kernel launch failed", 5: "unsupported head ratio", 6: "needs more than the built-in scratch"}
+          4: "kernel launch failed", 5: "unsupported shape (head ratio, tile width)", 6: "needs more than the built-in scratch"}
 
 
 class NativeError(RuntimeError):
