@@ -685,6 +685,7 @@ def main() -> None:
     ap.add_argument("--ragged", type=int, default=1, help="also run the ragged GQA sweep as an extra (0: skip)")
     ap.add_argument("--longctx", type=int, default=1, help="also time the KV-length-sharded long-context case (0: skip)")
     ap.add_argument("--e2e-steps", type=int, default=200, help="steps of the end-to-end loop (profiling runs shrink it)")
+    ap.add_argument("--e2e-parts", type=int, default=0, help="row groups of the end-to-end step that run as parallel graph branches (0: DecodeStep's choice)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -782,7 +783,7 @@ def main() -> None:
             cos, sin = ncb.rotary_table(max_len, 1e4, device=device)
             ones = torch.ones(D, device=device)
             host_gen = torch.Generator().manual_seed(3000 + rank)
-            decode = ncb.DecodeStep(cache, HQ, cos, sin, ones, ones, B, chunk_pages=chunk)
+            decode = ncb.DecodeStep(cache, HQ, cos, sin, ones, ones, B, chunk_pages=chunk, parts=args.e2e_parts)
             decode.qkv_host.copy_(torch.randn(decode.qkv_host.shape, generator=host_gen).bfloat16())
             decode.pos_host.copy_(torch.tensor(lens, dtype=torch.int32))
 
@@ -815,9 +816,12 @@ def main() -> None:
             res["e2e"] = {"value": nbytes / seconds / 1e9, "unit": UNIT, "h2d_bytes_per_step": decode.h2d_bytes,
                           "d2h_bytes_per_step": decode.d2h_bytes, "steps": e2e_steps,
                           "ms_per_step": seconds / e2e_steps * 1e3,
+                          "parts": decode.parts,
                           "what": "DecodeStep.run(): pinned-host qkv rows + positions in, decode_step_attn_fp8 (append "
-                                  "+ attention; one CUDA graph with the copies), output to pinned host, synchronised "
-                                  "every step; the KV cache is resident decoder state"}
+                                  "+ attention; one CUDA graph with the copies, the rows in `parts` groups that run "
+                                  "as parallel branches so that later groups' copies cross PCIe under earlier "
+                                  "groups' attention), output to pinned host, synchronised every step; the KV cache "
+                                  "is resident decoder state"}
             del decode
         if profiled:
             torch.cuda.profiler.stop()

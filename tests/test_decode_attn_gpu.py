@@ -199,17 +199,20 @@ def test_append_then_attend():
     check(case, helpers.bf16_bits(out.cpu()))
 
 
-def test_decode_step_graph_matches_eager_operators():
-    """DecodeStep (copies + append + attention as one CUDA graph, pinned host buffers) against the same operators
-    called one by one, over several steps of a growing ragged batch."""
+@pytest.mark.parametrize("lens,parts", [([130, 5, 64], 0), ([130, 5, 64, 200], 2), ([130, 5, 64, 200, 1, 77, 63, 128], 4)])
+def test_decode_step_graph_matches_eager_operators(lens, parts):
+    """DecodeStep (copies + append + attention as one CUDA graph, pinned host buffers; the rows in 1, 2 or 4 groups
+    that run as parallel branches of the graph) against the same operators called one by one, over several steps of
+    a growing ragged batch."""
     gen = torch.Generator().manual_seed(1200)
-    Hq, Hkv, lens = 8, 2, [130, 5, 64]
+    Hq, Hkv = 8, 2
     B = len(lens)
     case = helpers.attention_case(1201, Hq, Hkv, lens)
     cos, sin = ncb.rotary_table(256, 1e4, device="cuda")
     gain = (1 + 0.1 * torch.randn(128, generator=gen)).cuda()
     caches = [load_cache(case, 256) for _ in range(2)]
-    step = ncb.DecodeStep(caches[0], Hq, cos, sin, gain, gain, B)
+    step = ncb.DecodeStep(caches[0], Hq, cos, sin, gain, gain, B, parts=parts)
+    assert step.parts == (parts or 1)
     pos = torch.tensor(lens, dtype=torch.int32)
     for _ in range(4):
         qkv = torch.randn(B, (Hq + 2 * Hkv) * 128, generator=gen).bfloat16()
