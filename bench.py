@@ -523,7 +523,7 @@ def bench_decoder_d32(rank: int, world: int, device, new_tokens: int, profile: b
     """Batched decode of a random-init d32-class model (32 layers, d_model 2048, 16 query / 4 KV heads, relu^2 MLP of
     8192, vocab 65536): batch 32 per GPU (256 over 8 GPUs), ragged contexts uniform in [256, 8192] already in the fp8
     caches (synthetic quantised K/V, the same pages in every layer), `new_tokens` greedy tokens. Every step appends
-    and attends in every layer. Rows above 16 run the GEMMs on cuBLAS."""
+    and attends in every layer; at 32 rows the GEMMs run on the tcgen05 weight-stream kernel (stream_gemm)."""
     import torch.distributed as dist
 
     import nanochat_b200 as ncb
