@@ -119,8 +119,51 @@ def rms_norm(x: Tensor) -> Tensor:
     return F.rms_norm(x, (x.size(-1),), eps=EPS)
 
 
+MAX_SLOTS = 1024            # the reference's MAX_BATCH (model/kernels/decode.cu:29)
+ALLOC_GRANULE = 2 << 20     # cudaMalloc rounds a large block up to the next 2 MiB (decode.cu:955-957)
+
+
+def slot_bytes(cfg: DecoderConfig) -> int:
+    """Device bytes one more slot costs a decoder of this shape: its pages in every layer's cache plus its rows of the
+    step's buffers (hidden, qkv, attention output, MLP, x0, normed rows in bf16; fp32 logits and sampling
+    probabilities; the int64 token trace), each rounded up to 256 bytes as the allocator rounds them. The reference
+    sums its per-slot buffers the same way (slot_buffers / padded, decode.cu:977-979)."""
+    from .kv_cache import PAGE_BYTES, cache_pages
+
+    def padded(n: int) -> int:
+        return (n + 255) // 256 * 256
+
+    pages = cache_pages(cfg.max_len)
+    cache = cfg.n_layers * cfg.n_kv_heads * pages * PAGE_BYTES
+    rows = sum(padded(2 * n) for n in (cfg.hidden, cfg.qkv_width, cfg.n_heads * HEAD_DIM, cfg.intermediate,
+                                       cfg.hidden, cfg.hidden))
+    rows += 2 * padded(4 * cfg.vocab) + padded(8 * (pages * 64 + 1))
+    return cache + rows
+
+
+def slots_that_fit(cfg: DecoderConfig, free_bytes: int, max_slots: int = MAX_SLOTS) -> int:
+    """How many slots a decoder of this shape gets out of `free_bytes` of device memory: the most (at most max_slots)
+    whose block fits the free memory rounded down to the allocation granule, the reference's rule for its batch size
+    (dec_create, decode.cu:983-987: `B = min(free / slot, MAX_BATCH)`, and it refuses to start with none). Measure
+    `free_bytes` after the weights are on the device (torch.cuda.mem_get_info()[0]); keep what else the process
+    needs (workspaces, the prefill pass's rows, CUDA graphs) out of it."""
+    usable = free_bytes // ALLOC_GRANULE * ALLOC_GRANULE
+    n = min(usable // slot_bytes(cfg), max_slots)
+    if n < 1:
+        raise MemoryError(f"not one slot of {slot_bytes(cfg)} bytes fits {free_bytes} free bytes")
+    return int(n)
+
+
 class Decoder:
     """Greedy decoding of up to n_slots sequences with an fp8 KV cache per layer."""
+
+    @classmethod
+    def sized_for_free_memory(cls, cfg: DecoderConfig, weights: DecoderWeights, device: "torch.device | str" = "cuda",
+                              reserve_bytes: int = 2 << 30, max_slots: int = MAX_SLOTS, **kwargs) -> "Decoder":
+        """A decoder with as many slots as the device's free memory holds (slots_that_fit) after `reserve_bytes` are
+        set aside for workspaces, prefill rows and graphs: how the reference sizes its batch (decode.cu:983-987)."""
+        free, _ = torch.cuda.mem_get_info(torch.device(device))
+        return cls(cfg, weights, slots_that_fit(cfg, max(free - reserve_bytes, 0), max_slots), device, **kwargs)
 
     def __init__(self, cfg: DecoderConfig, weights: DecoderWeights, n_slots: int, device: "torch.device | str" = "cuda",
                  prompt_store: int = 0, softcap: float = 0.0):

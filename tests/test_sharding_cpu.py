@@ -168,3 +168,22 @@ def test_decode_step_attention_refuses_rows_that_share_a_slot():
     with pytest.raises(ValueError, match="share a slot"):
         ops.decode_step_attention(x, None, None, None, None, None, None, 2, 64, slots=[0, 1, 0])
 
+
+
+def test_slots_that_fit_follows_the_reference_rule():
+    """The number of slots from free device memory: whole slots of the free bytes rounded down to 2 MiB, capped."""
+    from nanochat_b200.decoder import ALLOC_GRANULE, MAX_SLOTS, DecoderConfig, slot_bytes, slots_that_fit
+    from nanochat_b200.kv_cache import PAGE_BYTES
+
+    cfg = DecoderConfig(n_layers=20, hidden=1280, n_heads=10, n_kv_heads=10, intermediate=5120, vocab=65536,
+                        rope_theta=10000.0, max_len=2048)
+    per = slot_bytes(cfg)
+    assert per > 20 * 10 * 32 * PAGE_BYTES  # the cache pages of all layers, and the step's rows on top
+    assert per - 20 * 10 * 32 * PAGE_BYTES < 2 << 20
+    assert slots_that_fit(cfg, 10 * per + ALLOC_GRANULE) == 10
+    assert slots_that_fit(cfg, 10 * per + ALLOC_GRANULE - 1) in (9, 10)
+    assert slots_that_fit(cfg, per // ALLOC_GRANULE * ALLOC_GRANULE + ALLOC_GRANULE) == 1
+    assert slots_that_fit(cfg, 10 ** 15) == MAX_SLOTS
+    assert slots_that_fit(cfg, 10 ** 15, max_slots=64) == 64
+    with pytest.raises(MemoryError):
+        slots_that_fit(cfg, per - 1)
