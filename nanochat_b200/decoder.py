@@ -71,6 +71,25 @@ class DecoderConfig:
     def qkv_width(self) -> int:
         return (self.n_heads + 2 * self.n_kv_heads) * HEAD_DIM
 
+    @staticmethod
+    def from_exported(config, max_len: int | None = None) -> "DecoderConfig":
+        """From the exported model's configuration (inference/modeling_nanochat.py NanochatConfig: any object or dict
+        with its field names). A layer's window is the config's sliding_window where layer_types says
+        "sliding_attention", else 0 (full attention)."""
+        get = config.get if isinstance(config, dict) else lambda k, d=None: getattr(config, k, d)
+        if get("head_dim", HEAD_DIM) != HEAD_DIM:
+            raise ValueError(f"head_dim {get('head_dim')}: the kernels take {HEAD_DIM}")
+        L = get("num_hidden_layers")
+        types = get("layer_types") or ["full_attention"] * L
+        windows = [int(get("sliding_window") or 0) if t == "sliding_attention" else 0 for t in types]
+        rope = get("rope_parameters") or {}
+        return DecoderConfig(n_layers=L, hidden=get("hidden_size"), n_heads=get("num_attention_heads"),
+                             n_kv_heads=get("num_key_value_heads") or get("num_attention_heads"),
+                             intermediate=get("intermediate_size"), vocab=get("vocab_size"),
+                             rope_theta=float(rope.get("rope_theta", get("rope_theta", 10000.0))),
+                             max_len=max_len or get("max_position_embeddings"),
+                             windows=windows if any(windows) else [])
+
 
 @dataclass
 class LayerWeights:
@@ -95,6 +114,34 @@ class DecoderWeights:
     embed: Tensor    # bf16 [V, C]
     lm_head: Tensor  # bf16 [V, C]
     layers: list[LayerWeights]
+
+    @staticmethod
+    def from_state_dict(state: dict, cfg: DecoderConfig, device: "torch.device | str" = "cuda") -> "DecoderWeights":
+        """From a checkpoint of the exported model (the names of inference/modeling_nanochat.py: model.embed_tokens,
+        lm_head, model.layers.i.self_attn.{q,k,v,o}_proj, .q_norm_weight / .k_norm_weight, .ve_gate,
+        model.layers.i.mlp.{up,down}_proj, model.value_embeds.i, model.resid_lambdas / x0_lambdas). GEMM weights,
+        the embedding and value-embedding tables become bf16 (the forward's rounding at use, as the reference's
+        decoder takes them, inference/decoder.py:155-165); gains, gates and lambdas stay fp32."""
+        def t(name: str, dtype) -> Tensor:
+            return state[name].detach().to(device=device, dtype=dtype).contiguous()
+
+        bf, f32 = torch.bfloat16, torch.float32
+        resid = state["model.resid_lambdas"].float().tolist() if "model.resid_lambdas" in state else [1.0] * cfg.n_layers
+        x0 = state["model.x0_lambdas"].float().tolist() if "model.x0_lambdas" in state else [0.0] * cfg.n_layers
+        layers = []
+        for i in range(cfg.n_layers):
+            p = f"model.layers.{i}."
+            wqkv = torch.cat([t(p + f"self_attn.{n}_proj.weight", bf) for n in "qkv"], 0)
+            if wqkv.shape != (cfg.qkv_width, cfg.hidden):
+                raise ValueError(f"layer {i}: q, k, v projections of {tuple(wqkv.shape)}, expected {(cfg.qkv_width, cfg.hidden)}")
+            ve = f"model.value_embeds.{i}.weight" in state
+            layers.append(LayerWeights(
+                wqkv, t(p + "self_attn.o_proj.weight", bf), t(p + "mlp.up_proj.weight", bf),
+                t(p + "mlp.down_proj.weight", bf), t(p + "self_attn.q_norm_weight", f32),
+                t(p + "self_attn.k_norm_weight", f32), resid_lambda=float(resid[i]), x0_lambda=float(x0[i]),
+                ve_table=t(f"model.value_embeds.{i}.weight", bf) if ve else None,
+                ve_gate=t(p + "self_attn.ve_gate.weight", f32) if ve else None))
+        return DecoderWeights(t("model.embed_tokens.weight", bf), t("lm_head.weight", bf), layers)
 
     @staticmethod
     def random_init(cfg: DecoderConfig, seed: int, device: "torch.device | str", std: float = 0.02,

@@ -187,3 +187,42 @@ def test_slots_that_fit_follows_the_reference_rule():
     assert slots_that_fit(cfg, 10 ** 15, max_slots=64) == 64
     with pytest.raises(MemoryError):
         slots_that_fit(cfg, per - 1)
+
+
+def test_weights_and_config_load_from_the_exported_model_s_names():
+    """DecoderWeights.from_state_dict / DecoderConfig.from_exported against the layout the golden generator feeds the
+    reference's exported model (tests/golden/make_golden_decoder.py): same tensors back, fused qkv in q, k, v order."""
+    from nanochat_b200.decoder import DecoderConfig, DecoderWeights
+
+    cfg, w = helpers.tiny_decoder_weights_ve()
+    H, L = cfg["n_heads"], cfg["n_layers"]
+    state = {"model.embed_tokens.weight": w["embed"], "lm_head.weight": w["lm_head"],
+             "model.resid_lambdas": torch.tensor([lw["resid_lambda"] for lw in w["layers"]]),
+             "model.x0_lambdas": torch.tensor([lw["x0_lambda"] for lw in w["layers"]])}
+    for i, lw in enumerate(w["layers"]):
+        p = f"model.layers.{i}."
+        q, k, v = lw["wqkv"].split(H * 128, dim=0)
+        state.update({p + "self_attn.q_proj.weight": q, p + "self_attn.k_proj.weight": k,
+                      p + "self_attn.v_proj.weight": v, p + "self_attn.o_proj.weight": lw["wo"],
+                      p + "mlp.up_proj.weight": lw["wup"], p + "mlp.down_proj.weight": lw["wdown"],
+                      p + "self_attn.q_norm_weight": lw["q_gain"], p + "self_attn.k_norm_weight": lw["k_gain"]})
+        if "ve_table" in lw:
+            state.update({f"model.value_embeds.{i}.weight": lw["ve_table"], p + "self_attn.ve_gate.weight": lw["ve_gate"]})
+    exported = {"vocab_size": cfg["vocab"], "hidden_size": cfg["hidden"], "intermediate_size": cfg["intermediate"],
+                "num_hidden_layers": L, "num_attention_heads": H, "num_key_value_heads": H, "head_dim": 128,
+                "max_position_embeddings": 256, "rope_parameters": {"rope_type": "default", "rope_theta": 10000.0},
+                "sliding_window": 64, "layer_types": ["sliding_attention", "full_attention"]}
+    c = DecoderConfig.from_exported(exported)
+    assert (c.n_layers, c.hidden, c.n_heads, c.n_kv_heads, c.intermediate, c.vocab, c.max_len) == (L, 256, H, H, 1024, 512, 256)
+    assert c.windows == [64, 0] and c.rope_theta == 10000.0
+    got = DecoderWeights.from_state_dict(state, c, device="cpu")
+    assert torch.equal(got.embed, w["embed"]) and torch.equal(got.lm_head, w["lm_head"])
+    for lw, g in zip(w["layers"], got.layers):
+        for name in ("wqkv", "wo", "wup", "wdown", "q_gain", "k_gain"):
+            assert torch.equal(getattr(g, name), lw[name]), name
+        assert (g.resid_lambda, g.x0_lambda) == (pytest.approx(lw["resid_lambda"]), pytest.approx(lw["x0_lambda"]))
+        assert (g.ve_table is None) == ("ve_table" not in lw)
+        if g.ve_table is not None:
+            assert torch.equal(g.ve_table, lw["ve_table"]) and torch.equal(g.ve_gate, lw["ve_gate"])
+    with pytest.raises(ValueError):
+        DecoderConfig.from_exported({**exported, "head_dim": 64})
