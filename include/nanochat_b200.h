@@ -134,7 +134,9 @@ long long decode_attn_workspace_bytes(int B, int Hq, int max_kv_len, int Hkv, in
  *   window    0 for none, else the number of most recent positions attended (decode.cu:575)
  *   chunk_pages  0 for the built-in choice
  * Two launches: the split-KV kernel (one block per sequence, kv head and chunk of pages; all Hq/Hkv query heads
- * of the kv head share each K/V byte) and the merge kernel.
+ * of the kv head share each K/V byte) and the merge kernel. When max_kv_len and chunk_pages leave every sequence one
+ * chunk (at most four pages of cache, or a chunk size of at least the cache's pages) the split kernel's blocks
+ * normalise and write `out` themselves and there is no second launch; the output bits are the same either way.
  */
 int decode_attn_fp8(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
                     long long workspace_bytes, void *out, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,

@@ -69,6 +69,7 @@ struct AttnArgs {
     long long qkv_row_stride;
     int table_len;
     ValueEmbed ve; /* APPEND only; table == NULL: the layer has no value embedding */
+    bf16 *direct;  /* one chunk per sequence (max_chunks == 1): the block normalises and writes out[B][Hq][128] itself */
 };
 
 /* ---- PTX wrappers ------------------------------------------------------------------------------------------- */
@@ -349,18 +350,33 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
     if (!a.early) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = (int)blockIdx.z, S = G; /* the block's row; its query slots: the heads of the kv group */
     const int given = a.lens[b];
-    if (given < 0) return; /* an idle row: nothing appended, nothing attended, nothing flagged; the merge writes zeros */
+    /* direct mode has no merge launch behind it to write the zero rows of idle, refused and empty sequences */
+    auto zero_row = [&]() {
+        if (a.direct && tid < HEAD_DIM)
+            for (int h = 0; h < G; h++) a.direct[((size_t)b * a.Hq + (size_t)kvh * G + h) * HEAD_DIM + tid] = __float2bfloat16_rn(0.f);
+    };
+    if (given < 0) { /* an idle row: nothing appended, nothing attended, nothing flagged; its output is a zero row */
+        zero_row();
+        return;
+    }
     const int len = given + a.len_add;
     const int slot = a.slot_map ? a.slot_map[b] : b;
     if (row_rejected(len, slot, a.pages_per_slot, a.n_slots, APPEND ? a.table_len : 0)) {
         if (tid == 0 && chunk == 0 && kvh == 0) flag(a.status, APPEND ? NCB_DEV_BAD_POSITION : NCB_DEV_BAD_LENGTH);
+        zero_row();
         return; /* the merge kernel makes the same test and writes zeros */
     }
     const Span sp = span_of(len, a.window, a.chunk_pages);
-    if (chunk >= sp.n_chunks) return;
+    if (chunk >= sp.n_chunks) {
+        if (chunk == 0) zero_row(); /* an empty sequence */
+        return;
+    }
     const int pg0 = sp.first_page + chunk * sp.chunk;
     const int n = min(sp.chunk, sp.last_page - pg0);
-    if (n <= 0) return;
+    if (n <= 0) {
+        if (chunk == 0) zero_row();
+        return;
+    }
 
     const uint8_t *pages = a.cache + (((size_t)slot * a.Hkv + kvh) * a.pages_per_slot + pg0) * PAGE_BYTES;
     uint8_t *page = smem + (size_t)warp * PAGE_BYTES; /* this warp's stage */
@@ -509,6 +525,11 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM) k_decode_attn(AttnArgs
                 const float c = st[0] == -INFINITY ? 0.f : ex2(st[0] - top);
                 lsum += c * st[1];
                 o += c * st[4 + tid];
+            }
+            if (a.direct) { /* the sequence's only chunk: bf16(o / l), the merge kernel's arithmetic on a single state */
+                a.direct[((size_t)b * a.Hq + (size_t)kvh * G + h) * HEAD_DIM + tid] =
+                    __float2bfloat16_rn(lsum > 0.f ? __fdiv_rn(o, lsum) : 0.f);
+                continue;
             }
             float *out = a.parts + (((size_t)b * a.Hq + (size_t)kvh * G + h) * a.max_chunks + chunk) * PART;
             if (tid == 0) out[0] = top, out[1] = lsum;
@@ -1084,7 +1105,7 @@ template <int NT, bool APPEND> static cudaError_t prepare() { /* opt in to the l
 static int launch_split(const void *q, const void *kv_cache, const void *lens, const void *slot_map, void *workspace,
                         long long workspace_bytes, int B, int Hq, int Hkv, int n_slots, int pages_per_slot,
                         int max_kv_len, int window, int &chunk_pages, float softmax_scale, void *status,
-                        cudaStream_t stream, const AppendIn *app = nullptr, bool early = false) {
+                        cudaStream_t stream, const AppendIn *app = nullptr, bool early = false, void *direct_out = nullptr) {
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || n_slots <= 0 || pages_per_slot <= 0 || max_kv_len < 0 ||
         window < 0 || chunk_pages < 0 || !(softmax_scale > 0.f))
         return NCB_ERR_ARG;
@@ -1122,6 +1143,7 @@ static int launch_split(const void *q, const void *kv_cache, const void *lens, c
         a.qkv_row_stride = app->qkv_row_stride, a.table_len = app->table_len;
         a.ve = app->ve;
     }
+    a.direct = max_chunks == 1 ? (bf16 *)direct_out : nullptr; /* only a sequence's sole chunk may write the output */
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(max_chunks, Hkv, B);
     config.blockDim = dim3(THREADS);
@@ -1201,12 +1223,16 @@ static int attend(const void *q, const void *kv_cache, const void *lens, const v
                   void *stream, const AppendIn *app = nullptr, const ExchangeIn *exchange = nullptr) {
     if (!out && !part_out) return NCB_ERR_ARG;
     if (((uintptr_t)out | (uintptr_t)part_out) % 16 != 0) return NCB_ERR_ALIGN;
+    /* One chunk per sequence (short caches, or a chunk size at least the cache's pages): the split kernel's blocks
+     * normalise and write the output themselves and there is no merge launch (launch_split takes `out` only then). */
+    void *direct = (out && !part_out && !exchange) ? out : nullptr;
     const int rc = launch_split(q, kv_cache, lens, slot_map, workspace, workspace_bytes, B, Hq, Hkv, n_slots,
                                 pages_per_slot, max_kv_len, window, chunk_pages, softmax_scale, status,
-                                (cudaStream_t)stream, app, exchange != nullptr);
+                                (cudaStream_t)stream, app, exchange != nullptr, direct);
     if (rc != NCB_OK || B == 0) return rc;
     if (max_kv_len > pages_per_slot * PAGE_TOKENS) max_kv_len = pages_per_slot * PAGE_TOKENS;
     const int max_chunks = max(1, (pages_of(max_kv_len) + chunk_pages - 1) / chunk_pages);
+    if (direct && max_chunks == 1) return NCB_OK;
     MergeArgs m = {(const float *)workspace, (long long)B * Hq, PART, (long long)max_chunks * PART, 0,
                    (const int32_t *)lens, (const int32_t *)slot_map, Hq, window, chunk_pages, n_slots, pages_per_slot,
                    max_chunks, app ? 1 : 0, (bf16 *)out, (float *)part_out, app ? app->table_len : 0};
@@ -1241,7 +1267,10 @@ static int static_scratch(void **ptr) {
  * ceil(p / WARPS) (its warps walk their pages one after the other), a block beyond its sequence's chunks IDLE_US.
  * The modelled makespan tracks the measured kernel time up to a constant (the bytes' own streaming time) across
  * chunk sizes, batch shapes and ragged lengths, including the steps where one more wave of blocks appears; the
- * chunk size with the smallest makespan wins, the larger one on ties (fewer states to merge). lens == NULL takes
+ * chunk size with the smallest makespan wins, the larger one on ties (fewer states to merge). A chunk size that leaves
+ * every sequence ONE chunk is spared the merge launch (the blocks write the output themselves), but the model gives
+ * that no credit: on a 12-page cache three pages per warp in one launch measured slower (604 us per d20 step) than one
+ * page per warp and a merge launch (552 - 572 us). lens == NULL takes
  * every sequence as max_kv_len long. Chunks stay between one page per warp and 32 pages (longer ones gain nothing
  * and unbalance ragged batches).
  */
