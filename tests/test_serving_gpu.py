@@ -40,20 +40,16 @@ def test_a_requests_tokens_do_not_depend_on_the_batch_or_the_slot():
 
 def test_more_requests_than_slots_match_one_request_at_a_time():
     """Eight requests of different prompt lengths through two slots against each request run alone in a one-request
-    batch of the same decoder shape: the same streams up to the first near-tie (prefill passes hold different rows in
-    the two runs, and their cuBLAS GEMMs may sum in a different order)."""
+    batch of the same decoder shape: the same streams, token for token. Prefill passes hold different rows in the two
+    runs, but every kernel of a pass computes a row from that row alone in an order fixed by the shapes (the tiled
+    GEMM accumulates a row's k-blocks in the same order wherever the row lands, the prefill attention's warps never
+    mix their query slots), so a prompt's cache bytes do not depend on what else is in the pass."""
     reqs = [Request(input_ids=prompt(40 + i, n), max_new_tokens=6 + i) for i, n in enumerate((3, 65, 17, 1, 130, 64, 9, 33))]
     nd = make(2)
     together = dict(nd.generate(reqs))
-    agreed = 0
     for i, r in enumerate(reqs):
         alone = dict(make(2).generate([r]))[0]
-        k = 0
-        while k < min(len(alone), len(together[i])) and alone[k] == together[i][k]:
-            k += 1
-        agreed += k == len(alone) == len(together[i])
-        assert k >= 1 or not alone, (i, alone, together[i])
-    assert agreed >= 6  # most streams never meet a near-tie
+        assert alone == together[i], (i, alone, together[i])
 
 
 def test_stopping_criteria_token_limits_and_masks():
