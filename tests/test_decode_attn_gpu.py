@@ -374,6 +374,42 @@ def test_sharded_exchange_on_one_gpu_with_the_peer_already_delivered():
     check(case, helpers.bf16_bits(out.cpu()))
 
 
+@pytest.mark.parametrize("world,rank", [(4, 1), (8, 0), (8, 5), (8, 7)])
+def test_sharded_exchange_as_any_rank_of_a_larger_world(world, rank):
+    """The same stand-in for worlds of four and eight: this GPU plays `rank`, the other ranks' words are planted in
+    its inbox. The output equals decode_attn_merge over all slices' states in rank order (what every rank computes, so
+    all ranks agree bit for bit), and its own state lands in every peer's inbox at its own rank's place."""
+    n = 64 * 3 * world + 37
+    cuts = [0] + [64 * 3 * (r + 1) for r in range(world - 1)] + [n]
+    case = helpers.attention_case(1410 + world + rank, 8, 2, [n, 250])
+    q = helpers.bits_bf16(case["q"]).cuda()
+    parts, caches, lens_of = [], [], []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        sl = {**case, "lens": [max(0, min(b, L) - min(a, L)) for L in case["lens"]]}
+        for key in ("k_bytes", "k_scale", "v_bytes", "v_scale"):
+            sl[key] = [x[:, a:b] for x in case[key]]
+        cache = load_cache(sl, max(max(sl["lens"]), 1))
+        lens = torch.tensor(sl["lens"], dtype=torch.int32, device="cuda")
+        parts.append(ncb.decode_attention_partial(q, cache, lens, max_kv_len=max(max(sl["lens"]), 1), chunk_pages=2))
+        caches.append(cache)
+        lens_of.append(lens)
+    want = ncb.merge_partials(torch.stack(parts))
+    rows = 2 * 8
+    peers = _OneGpuPeers(world, rows)
+    for call in (1, 2):
+        for r in range(world):
+            if r != rank:
+                peers.inbox[rank][call % 2, r] = packets(parts[r].view(rows, 132), call)
+        rc, out = peers.call(q, caches[rank], lens_of[rank], cuts[rank + 1] - cuts[rank], rank=rank)
+        torch.cuda.synchronize()
+        assert rc == 0 and peers.status.item() == 0
+        assert torch.equal(out, want), call
+        for r in range(world):
+            if r != rank:
+                assert torch.equal(peers.inbox[r][call % 2, rank], packets(parts[rank].view(rows, 132), call))
+    check(case, helpers.bf16_bits(out.cpu()))
+
+
 def test_sharded_exchange_wait_runs_out_and_reports():
     """A peer that never delivers, and one whose words are from an older call: the bounded wait gives up after about
     half a second, the status word carries NCB_DEV_WAIT_TIMEOUT, the call counter still advances and the context stays
