@@ -483,6 +483,56 @@ def bench_decoder(rank: int, world: int, device, new_tokens: int, profile: bool 
             "prefill_s": prefill_s, "scaling": "weak (replicas)"}
 
 
+def bench_serving(rank: int, world: int, device) -> dict:
+    """Continuous batching through the public host loop (nanochat_b200.serving.NativeDecoder.generate, the shape of
+    the reference's NativeDecoder.generate): the random-init d20 model with 8 slots per GPU serves 32 greedy requests
+    per GPU with prompts of 32 to 512 tokens and 32 to 96 new tokens each; slots are refilled from the queue as
+    requests finish, prompts of newly started requests are prefilled between steps, one host synchronisation per step.
+    tokens/s counts generated tokens over the wall time of the whole call (prefill included), max over ranks."""
+    import torch.distributed as dist
+
+    from nanochat_b200.decoder import Decoder, DecoderConfig, DecoderWeights
+    from nanochat_b200.serving import NativeDecoder, Request
+
+    cfg = DecoderConfig(n_layers=20, hidden=1280, n_heads=10, n_kv_heads=10, intermediate=5120, vocab=65536,
+                        rope_theta=10000.0, max_len=640)
+    server = NativeDecoder(Decoder(cfg, DecoderWeights.random_init(cfg, 0, device, on_device=True), 8, device),
+                           end_token=65535)
+    gen = torch.Generator().manual_seed(400 + rank)
+
+    def requests():
+        lengths = torch.randint(32, 513, (32,), generator=gen).tolist()
+        budgets = torch.randint(32, 97, (32,), generator=gen).tolist()
+        return [Request(input_ids=torch.randint(0, 65535, (n,), generator=gen).tolist(), max_new_tokens=m)
+                for n, m in zip(lengths, budgets)]
+
+    list(server.generate(requests()))  # warm-up: every kernel form's first use, the allocator's pools
+    runs = []
+    for _ in range(3):  # three different request sets; the median run is reported
+        batch = requests()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        done = list(server.generate(batch))
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        first = sorted(t[1] - t[0] for t in server.timings.values())
+        runs.append((seconds / max(1, sum(len(ids) for _, ids in done)), seconds, sum(len(ids) for _, ids in done),
+                     first[len(first) // 2]))
+    runs.sort()
+    _, seconds, tokens, ttft = runs[1]
+    stats = torch.tensor([seconds, float(tokens)], device=device)
+    if world > 1:
+        worst = stats[:1].clone()
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        dist.all_reduce(stats)
+        stats[0] = worst[0]
+    seconds, tokens = stats.tolist()
+    return {"workload": "random-init d20, 8 slots per GPU, 32 greedy requests per GPU (prompts 32-512 tokens, 32-96 new "
+                        "tokens), continuous batching through NativeDecoder.generate",
+            "tokens_per_s": tokens / seconds, "generated_tokens": int(tokens), "seconds": seconds,
+            "median_time_to_first_token_ms": ttft * 1e3, "scaling": "weak (replicas)"}
+
+
 def bench_decoder_cpu(steps: int) -> dict:
     """The CPU port of the reference's decoder (oracle/decoder.py: the exported model's operators on torch CPU
     bf16, op for op) on the d20 workload, all host threads: batch 8, 512 positions already in the caches (synthetic
@@ -856,6 +906,7 @@ def main() -> None:
     longctx = bench_longctx(rank, world, device, min(args.steps, 100), 5, timed) if args.longctx else None
     decoder = bench_decoder(rank, world, device, args.decoder_tokens, args.profile_range == "decoder") \
         if args.decoder else None
+    serving = bench_serving(rank, world, device) if args.decoder else None
     d32_profiled = args.profile_range == "decoder_d32"  # two steps are enough for a launch list
     decoder_d32 = bench_decoder_d32(rank, world, device, 2 if d32_profiled else 128, d32_profiled) \
         if args.decoder_d32 else None
@@ -886,6 +937,8 @@ def main() -> None:
             line["longctx"] = longctx
         if decoder:
             line["decoder"] = decoder
+        if serving:
+            line["serving"] = serving
         if decoder_d32:
             line["decoder_d32"] = decoder_d32
         if world == 1 and args.cpu_seconds > 0:

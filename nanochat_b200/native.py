@@ -126,10 +126,12 @@ def pointer(t: "torch.Tensor | None") -> ctypes.c_void_p:
 
 
 def stream() -> ctypes.c_void_p:
-    """The current CUDA stream, which the kernels launch on."""
+    """The current CUDA stream of the current device, which the kernels launch on. (The raw handle straight from
+    torch's C layer: a row pass makes a hundred launches, and building a torch.cuda.Stream object for each cost
+    more host time than small passes spend on the device.)"""
     import torch
 
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def check(status: int, what: str) -> None:

@@ -155,6 +155,7 @@ class NativeDecoder:
         graph, side, tokens, pos, logits, trace, ctl = decoder._step_graph(self.batch, True, 0, masked=True)
         self.graph, self.side, self.dev_tokens, self.dev_pos, self.ctl = graph, side, tokens, pos, ctl
         self.host_tokens = torch.zeros(self.batch, dtype=torch.long).pin_memory()
+        self.host_status = torch.zeros(1, dtype=torch.int32).pin_memory()  # travels with the tokens: no second sync
         self.masked = [False] * self.batch
         with torch.cuda.stream(side):
             pos.fill_(-1)
@@ -210,10 +211,11 @@ class NativeDecoder:
         with torch.cuda.stream(self.side):
             self.graph.replay()
             self.host_tokens.copy_(self.dev_tokens, non_blocking=True)
+            self.host_status.copy_(self.decoder.status, non_blocking=True)
 
     def tokens(self) -> list[int]:
         self.side.synchronize()
-        code = int(self.decoder.status.item())
+        code = int(self.host_status[0])
         if code:
             raise RuntimeError(f"device status {code:#x} (NCB_DEV_* bits)")
         return self.host_tokens.tolist()
