@@ -263,6 +263,12 @@ class Decoder:
         plan, grouped = None, host_rows is not None and not any(self.windows)
         h = torch.empty((rows, C), dtype=torch.bfloat16, device=self.device)
         n = torch.empty_like(h)
+        # the layers run one after the other on one stream, so they share their intermediate buffers (a pass of a
+        # few hundred rows is bound by the host's launches: every allocation saved is host time saved)
+        qkv_buf = torch.empty((rows, cfg.qkv_width), dtype=torch.bfloat16, device=self.device)
+        q_buf = torch.empty((rows, cfg.n_heads, HEAD_DIM), dtype=torch.bfloat16, device=self.device)
+        att_buf = torch.empty_like(q_buf)
+        u_buf = torch.empty((rows, cfg.intermediate), dtype=torch.bfloat16, device=self.device)
         mixing = any(l.mixes for l in layers)
         x0 = torch.empty_like(h) if mixing else None
         if mixing:
@@ -272,29 +278,29 @@ class Decoder:
             check(lib.embed_norm(pointer(self.w.embed), pointer(tokens), pointer(h), rows, C, cfg.vocab, s), "embed_norm")
         check(lib.add_rms_norm(pointer(h), None, pointer(n), rows, C, s), "add_rms_norm")
         for i, layer in enumerate(layers):
-            qkv = self.gemm_rows(n, layer.wqkv)
+            qkv = self.gemm_rows(n, layer.wqkv, out=qkv_buf)
             ve = None if layer.ve_table is None else ops.ValueEmbed(n, tokens, layer.ve_table, layer.ve_gate)
             if distinct_slots and (attend_last_layer or i < cfg.n_layers - 1):
                 att = ops.decode_step_attention(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos,
                                                 self.caches[i], cfg.n_heads, max_kv_len, slot_map=slot_map,
                                                 window=self.windows[i], chunk_pages=self.chunk_pages,
-                                                workspace=workspace, status=self.status, ve=ve)
+                                                workspace=workspace, out=att_buf, status=self.status, ve=ve)
             else:
                 q = ops.kv_append(qkv, layer.q_gain, layer.k_gain, self.cos, self.sin, pos, self.caches[i],
-                                  cfg.n_heads, slot_map=slot_map, status=self.status, ve=ve)
+                                  cfg.n_heads, slot_map=slot_map, q_out=q_buf, status=self.status, ve=ve)
                 if i == cfg.n_layers - 1 and not attend_last_layer:
                     return h  # prefill: the last layer only has to fill its cache (decode.cu:862)
                 if grouped and plan is None:  # built while the GPU already runs the launches above
                     plan = ops.PrefillPlan(host_rows[0], host_rows[1], cfg.n_heads, self.caches[0], self.device)
                 if plan is not None:
-                    att = ops.prefill_attention(q, self.caches[i], plan, status=self.status)
+                    att = ops.prefill_attention(q, self.caches[i], plan, out=att_buf, status=self.status)
                 else:
                     att = ops.decode_attention(q, self.caches[i], lens, max_kv_len, slot_map=slot_map,
                                                window=self.windows[i], chunk_pages=self.chunk_pages,
-                                               workspace=workspace, status=self.status)
+                                               workspace=workspace, out=att_buf, status=self.status)
             self.gemm_rows(att.view(rows, -1), layer.wo, resid=h)  # h += att . wo^T in the GEMM's epilogue
             check(lib.add_rms_norm(pointer(h), None, pointer(n), rows, C, s), "add_rms_norm")
-            u = self.gemm_rows(n, layer.wup, epilogue=2)
+            u = self.gemm_rows(n, layer.wup, epilogue=2, out=u_buf)
             nxt = layers[i + 1] if i + 1 < len(layers) else None
             if nxt is not None and nxt.mixes:  # the next layer's stream mix rides on this add
                 y = self.gemm_rows(u, layer.wdown)
@@ -305,9 +311,11 @@ class Decoder:
                 check(lib.add_rms_norm(pointer(h), None, pointer(n), rows, C, s), "add_rms_norm")
         return n
 
-    def gemm_rows(self, x: Tensor, w: Tensor, epilogue: int = 0, resid: "Tensor | None" = None) -> Tensor:
+    def gemm_rows(self, x: Tensor, w: Tensor, epilogue: int = 0, resid: "Tensor | None" = None,
+                  out: "Tensor | None" = None) -> Tensor:
         """epilogue(x . w^T) for a pass of any number of rows: x bf16 (rows, K), w bf16 (N, K); epilogue 0 store,
-        2 relu^2, 3 fp32 output; resid (rows, N) bf16: resid += bf16(x . w^T) in place (epilogue 1), returned.
+        2 relu^2, 3 fp32 output; resid (rows, N) bf16: resid += bf16(x . w^T) in place (epilogue 1), returned; out: a
+        bf16 (rows, N) buffer to write into instead of a new tensor (the result is whatever is returned).
         This package's tiled tcgen05 GEMM (csrc/tile_gemm.cu) when N is a multiple of 128 and K of 64; other shapes
         (toy models) go to torch's GEMM with the same epilogue applied afterwards."""
         rows, K, N = x.shape[0], x.shape[1], w.shape[0]
@@ -315,7 +323,7 @@ class Decoder:
             assert epilogue == 0 and resid.is_contiguous() and resid.shape == (rows, N)
             epilogue = 1
         if self.use_tile_gemm and N % 128 == 0 and K % 64 == 0 and x.is_contiguous() and w.is_contiguous():
-            y = resid if resid is not None else torch.empty(
+            y = resid if resid is not None else out if out is not None and epilogue != 3 else torch.empty(
                 (rows, N), dtype=torch.float32 if epilogue == 3 else torch.bfloat16, device=x.device)
             check(cuda_library("tile_gemm").tile_gemm(pointer(x), pointer(w), None if resid is None else pointer(resid),
                                                       pointer(y), rows, N, K, epilogue, pointer(self.status), stream()),
