@@ -4,7 +4,7 @@
  * CPU-baseline legs may load it.
  *
  * Parity status: the reference has no fp8 cache and no test or golden vector for this path, so the quantise rule
- * is pinned by this file's own definition (BASELINE.json: per-(token, head) scale = amax / 448, e4m3 round to
+ * is pinned by this file's own definition (the rule this path is specified with: per-(token, head) scale = amax / 448, e4m3 round to
  * nearest even) and the e4m3 conversion is pinned exhaustively against torch.float8_e4m3fn
  * (tests/test_oracle.py). The q/k row math restates the reference and is pinned, within one bf16 ulp, against
  * outputs of the reference's own inference/modeling_nanochat.py:qk_norm_rope (tests/golden/).
